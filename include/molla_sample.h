@@ -1,0 +1,150 @@
+/*
+ * molla_sample.h - C ABI of the B200 token-sampling library.
+ *
+ * The library replaces one stage of the tamnd/molla inference server: the step
+ * that turns a [batch x vocab] block of fp32 logits into next-token ids. In the
+ * reference that stage is the host-side `Sampler` of
+ * src/molla/engine/sample.mojo, called once per answered row from the decode
+ * loop (src/molla/engine/batch.mojo:503-519) after the whole logit block has
+ * been copied device -> host. Here the logits are consumed where the forward
+ * pass left them, on the device, and only the token ids (and, when asked for,
+ * logprobs) come back.
+ *
+ * Conventions (they follow how molla calls C, src/molla/tls/openssl.mojo:53-139
+ * and src/molla/sys/clock.mojo:37-58): plain `extern "C"` functions, scalars and
+ * raw pointers only, per-row parameters as parallel arrays (no struct layout to
+ * agree on), no callbacks, no C++ types, nothing thrown across the boundary.
+ * Every function that can fail returns an int32 status: 0 is success, negative
+ * is an argument error found before anything was launched, positive is an error
+ * the CUDA runtime or the device reported. `molla_sample_last_error()` gives
+ * the text. Nothing here creates a CUDA context or a stream: work is enqueued
+ * on the stream the caller passes (0 = the default stream) in the caller's
+ * current context, and is asynchronous unless stated otherwise.
+ *
+ * There is no CPU fallback. Built for sm_100a only.
+ */
+#ifndef MOLLA_SAMPLE_H
+#define MOLLA_SAMPLE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOLLA_SAMPLE_ABI_VERSION 1
+
+/* status codes */
+#define MOLLA_OK 0
+#define MOLLA_ERR_ARGUMENT (-1)   /* null pointer, negative size, bad alignment */
+#define MOLLA_ERR_VOCAB (-2)      /* vocabulary too wide for the on-chip row buffer */
+#define MOLLA_ERR_WORKSPACE (-3)  /* workspace missing or too small */
+#define MOLLA_ERR_CONFIG (-4)     /* a sampler setting outside SamplerConfig.check's rules */
+#define MOLLA_ERR_CUDA 1          /* a CUDA runtime call failed */
+#define MOLLA_ERR_DEVICE 2        /* the kernel reported an error (see row status) */
+
+/* Per-row status bits written to `d_row_status` (0 = clean row). The TIE bits
+ * are not errors: they mark rows whose answer in the reference depends on the
+ * unstable order its heapsort leaves equal probabilities in
+ * (src/molla/engine/sample.mojo:440-483); the library then orders equal
+ * probabilities by token id and says so. */
+#define MOLLA_ROW_INVALID_CONFIG 0x001u /* row skipped, token = -1 (rules of sample.mojo:140-154) */
+#define MOLLA_ROW_UNSUPPORTED 0x002u    /* min_p / typical_p requested: not implemented, token = -1 */
+#define MOLLA_ROW_TOPK_TIE 0x004u       /* the top-k boundary splits a run of equal probabilities */
+#define MOLLA_ROW_TOPP_TIE 0x008u       /* the top-p cut splits a run of equal probabilities */
+#define MOLLA_ROW_CHOSEN_TIE 0x010u     /* the chosen token shares its probability with another kept one */
+#define MOLLA_ROW_LOAD_TIMEOUT 0x020u   /* a bounded wait on the row load ran out; result invalid */
+#define MOLLA_ROW_SLOW_PATH 0x040u      /* informational: a sequential fallback ran for this row */
+#define MOLLA_ROW_DEGENERATE 0x080u     /* more equal values than the candidate buffer holds; token = -1 */
+
+/* Replaces nothing in the reference; lets a binding check what it loaded. */
+int32_t molla_sample_abi_version(void);
+
+/* Text of the last error on this host thread ("" if none). */
+const char *molla_sample_last_error(void);
+
+/* draw(seed, counter): the reference's counter-based uniform in [0,1), bit for
+ * bit. Replaces `draw` at src/molla/engine/sample.mojo:62-71 (and `_mix`,
+ * :49-59). Host function, no device work. */
+float molla_sample_draw(uint64_t seed, uint64_t counter);
+
+/* Bytes of device workspace `molla_sample_batch` needs for a block of this
+ * shape (never zero; 256-byte aligned sizes). Negative status on bad
+ * arguments. The reference keeps the equivalent scratch inside each Sampler
+ * (`ids`/`vals`, src/molla/engine/sample.mojo:173-177). */
+int64_t molla_sample_workspace_bytes(int32_t B, int32_t V, int32_t top_n);
+
+/*
+ * Sample one token for every row of a device-resident logit block.
+ *
+ * Replaces, for all B answered rows at once, the loop
+ *     for r in range(len(answered)): streams[i].sampler.pick(self.logits, r)
+ * at src/molla/engine/batch.mojo:509-511 together with the device->host copy
+ * before it (:504-508), i.e. `Sampler.pick` (src/molla/engine/sample.mojo:
+ * 295-359) with every stage it calls (:365-594) and `argmax`
+ * (src/molla/nn/kernel.mojo:571-585).
+ *
+ * d_logits      [B x V] fp32, row r at d_logits + r*row_stride (floats); read only.
+ * Per-row arrays, all device pointers of length B (the fields of SamplerConfig,
+ * src/molla/engine/sample.mojo:74-126, plus the sampler's counter):
+ *   d_temperature (<= 0 is greedy), d_top_k (0 = off), d_top_p (1 = off),
+ *   d_min_p (0 = off), d_typical_p (1 = off), d_repeat_penalty (1 = off),
+ *   d_frequency_penalty, d_presence_penalty (0 = off),
+ *   d_window_on (uint8: repeat_last_n > 0), d_seed, d_drawn (draw number).
+ *   Any of d_min_p, d_typical_p, d_window_on may be NULL (= off / off / on).
+ * d_hist, d_hist_off   the filled part of each row's penalty window
+ *   (Sampler.recent[0..filled), sample.mojo:167-171,260-266): row r's ids are
+ *   d_hist[d_hist_off[r] .. d_hist_off[r+1]), int64 like Mojo's Int. NULL = none.
+ * d_bias_ids, d_bias_vals, d_bias_off   each row's logit-bias list in the order
+ *   `bias()` appended it (sample.mojo:217-234,381-396). NULL = none.
+ * top_n         number of top logprobs per row (0..20); logprobs are of the raw
+ *   logits as in `Sampler.logprobs` (sample.mojo:268-293).
+ * d_workspace   device scratch of at least molla_sample_workspace_bytes().
+ * stream        cudaStream_t as a pointer (NULL = default stream).
+ * Outputs (device): d_tokens [B] int32 (required); d_chosen_logprob [B] or
+ *   NULL; d_top_ids / d_top_logprobs [B x top_n] or NULL when top_n == 0;
+ *   d_row_status [B] uint32 (required); d_diag [B x 4] floats or NULL
+ *   (softmax denominator, kept-mass sum, draw target, chosen probability:
+ *   testing aid).
+ */
+int32_t molla_sample_batch(
+    const float *d_logits, int64_t row_stride, int32_t B, int32_t V,
+    const float *d_temperature, const int32_t *d_top_k, const float *d_top_p,
+    const float *d_min_p, const float *d_typical_p, const float *d_repeat_penalty,
+    const float *d_frequency_penalty, const float *d_presence_penalty,
+    const uint8_t *d_window_on, const uint64_t *d_seed, const uint64_t *d_drawn,
+    const int64_t *d_hist, const int32_t *d_hist_off, const int64_t *d_bias_ids,
+    const float *d_bias_vals, const int32_t *d_bias_off, int32_t top_n, void *d_workspace,
+    int64_t workspace_bytes, void *stream, int32_t *d_tokens, float *d_chosen_logprob,
+    int32_t *d_top_ids, float *d_top_logprobs, uint32_t *d_row_status, float *d_diag);
+
+/* The rows after logit bias and penalties, before temperature: what
+ * `_bias` and `_penalise` (sample.mojo:381-417) leave in `vals`. Same arguments
+ * as above where they share a name; d_out is [B x V] fp32, dense. For parity
+ * checks of the penalty arithmetic. */
+int32_t molla_sample_penalised(
+    const float *d_logits, int64_t row_stride, int32_t B, int32_t V,
+    const float *d_repeat_penalty, const float *d_frequency_penalty,
+    const float *d_presence_penalty, const uint8_t *d_window_on, const int64_t *d_hist,
+    const int32_t *d_hist_off, const int64_t *d_bias_ids, const float *d_bias_vals,
+    const int32_t *d_bias_off, void *d_workspace, int64_t workspace_bytes, void *stream,
+    float *d_out);
+
+/* Full-row logprobs of the raw logits: `Sampler.logprobs`
+ * (src/molla/engine/sample.mojo:268-293) for every row. d_out is [B x V]. */
+int32_t molla_sample_logprobs(const float *d_logits, int64_t row_stride, int32_t B, int32_t V,
+                              void *stream, float *d_out);
+
+/* exp(x) exactly as the kernels evaluate it, element-wise on the device:
+ * the one arithmetic dependency the reference takes from outside its tree
+ * (`exp` of the Mojo standard library, imported at sample.mojo:40). For tests. */
+int32_t molla_sample_expf(const float *d_x, int64_t n, void *stream, float *d_out);
+
+/* cudaStreamSynchronize on `stream`, returning a status; then, if
+ * `d_row_status` is given, nothing else is implied: rows report for themselves. */
+int32_t molla_sample_sync(void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOLLA_SAMPLE_H */

@@ -1,0 +1,90 @@
+"""ctypes binding of libmolla_sample.so, the C ABI declared in include/molla_sample.h.
+
+There is no fallback: if the shared library is missing or does not load, importing
+callers get an error that says so. The library is built in-tree by
+`molla_b200.build.build_library()`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("MOLLA_SAMPLE_LIB", os.path.join(_HERE, "lib", "libmolla_sample.so"))
+
+# status codes and row-status bits (mirrors of the header's #defines)
+OK = 0
+ERR_ARGUMENT, ERR_VOCAB, ERR_WORKSPACE, ERR_CONFIG = -1, -2, -3, -4
+ERR_CUDA, ERR_DEVICE = 1, 2
+ROW_INVALID_CONFIG = 0x001
+ROW_UNSUPPORTED = 0x002
+ROW_TOPK_TIE = 0x004
+ROW_TOPP_TIE = 0x008
+ROW_CHOSEN_TIE = 0x010
+ROW_LOAD_TIMEOUT = 0x020
+ROW_SLOW_PATH = 0x040
+ROW_DEGENERATE = 0x080
+ROW_TIE_BITS = ROW_TOPK_TIE | ROW_TOPP_TIE | ROW_CHOSEN_TIE
+ROW_ERROR_BITS = ROW_INVALID_CONFIG | ROW_UNSUPPORTED | ROW_LOAD_TIMEOUT | ROW_DEGENERATE
+
+EXPORTS = (
+    "molla_sample_abi_version", "molla_sample_last_error", "molla_sample_draw",
+    "molla_sample_workspace_bytes", "molla_sample_batch", "molla_sample_penalised",
+    "molla_sample_logprobs", "molla_sample_expf", "molla_sample_sync",
+)
+
+
+class MollaSampleError(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__(f"molla_sample status {status}: {text}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib():
+    """The loaded library. Raises if it is not there: nothing else can do its work."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m molla_b200.build` "
+            "(there is no CPU or PyTorch fallback for the sampling kernels)")
+    L = C.CDLL(LIB_PATH)
+    vp, i32, i64, u64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_float
+    L.molla_sample_abi_version.restype = i32
+    L.molla_sample_abi_version.argtypes = []
+    L.molla_sample_last_error.restype = C.c_char_p
+    L.molla_sample_last_error.argtypes = []
+    L.molla_sample_draw.restype = f32
+    L.molla_sample_draw.argtypes = [u64, u64]
+    L.molla_sample_workspace_bytes.restype = i64
+    L.molla_sample_workspace_bytes.argtypes = [i32, i32, i32]
+    L.molla_sample_batch.restype = i32
+    L.molla_sample_batch.argtypes = [vp, i64, i32, i32] + [vp] * 16 + [i32, vp, i64, vp] + [vp] * 6
+    L.molla_sample_penalised.restype = i32
+    L.molla_sample_penalised.argtypes = [vp, i64, i32, i32] + [vp] * 9 + [vp, i64, vp, vp]
+    L.molla_sample_logprobs.restype = i32
+    L.molla_sample_logprobs.argtypes = [vp, i64, i32, i32, vp, vp]
+    L.molla_sample_expf.restype = i32
+    L.molla_sample_expf.argtypes = [vp, i64, vp, vp]
+    L.molla_sample_sync.restype = i32
+    L.molla_sample_sync.argtypes = [vp]
+    _lib = L
+    return L
+
+
+def last_error() -> str:
+    return (lib().molla_sample_last_error() or b"").decode("utf-8", "replace")
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise MollaSampleError(status, last_error())
+
+
+def draw(seed: int, counter: int) -> float:
+    m = (1 << 64) - 1
+    return float(lib().molla_sample_draw(seed & m, counter & m))

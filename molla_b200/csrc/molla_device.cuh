@@ -1,0 +1,147 @@
+// Device-side building blocks shared by the sampling kernels: the pinned fp32
+// exponential, the counter-based PRNG, warp/block reductions and scans, and the
+// mbarrier / bulk-copy wrappers. sm_100a only.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace molla {
+
+constexpr int NT = 1024;     // threads per CTA
+constexpr int NWARP = NT / 32;
+
+// ---- PRNG: the reference's splitmix64 finaliser and counter-based draw
+// (src/molla/engine/sample.mojo:49-71), bit for bit. --------------------------
+__host__ __device__ inline uint64_t mix64(uint64_t z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__host__ __device__ inline float draw01(uint64_t seed, uint64_t counter) {
+    uint64_t h = mix64(seed ^ mix64(counter + 0x9E3779B97F4A7C15ull));
+    return (float)(int64_t)(h >> 40) * (1.0f / 16777216.0f);  // exact: a 24-bit integer times 2^-24
+}
+
+// ---- exp(x) in fp32 from fused multiply-adds only: 2^n * exp(r) with
+// n = rint(x*log2 e), r = x - n*ln2 (two-piece ln2) and a degree-7 Taylor
+// polynomial in Horner form. The CPU checker evaluates the same sequence, so the
+// two agree bit for bit; the result is within 1 ulp of the exact exponential.
+// It stands in for `exp` of the Mojo standard library (sample.mojo:40,290,433).
+__device__ __forceinline__ float scale2(float v, int n) {
+    if (n >= -126) return __fmul_rn(v, __int_as_float((n + 127) << 23));
+    float a = __int_as_float((n + 64 + 127) << 23);
+    float b = __int_as_float((-64 + 127) << 23);
+    return __fmul_rn(__fmul_rn(v, a), b);
+}
+__device__ __forceinline__ float expf_pinned(float x) {
+    if (x != x) return x;
+    if (x > 88.72284f) return __int_as_float(0x7f800000);
+    if (x < -104.0f) return 0.0f;
+    const float LOG2E = 1.442695040888963f;
+    const float LN2_HI = 0.693145751953125f;
+    const float LN2_LO = 1.428606765330187e-06f;
+    const float MAGIC = 12582912.0f;
+    float t = __fmaf_rn(x, LOG2E, MAGIC);
+    float nf = __fsub_rn(t, MAGIC);
+    float r = __fmaf_rn(nf, -LN2_HI, x);
+    r = __fmaf_rn(nf, -LN2_LO, r);
+    float p = 1.0f / 5040.0f;
+    p = __fmaf_rn(p, r, 1.0f / 720.0f);
+    p = __fmaf_rn(p, r, 1.0f / 120.0f);
+    p = __fmaf_rn(p, r, 1.0f / 24.0f);
+    p = __fmaf_rn(p, r, 1.0f / 6.0f);
+    p = __fmaf_rn(p, r, 0.5f);
+    p = __fmaf_rn(p, r, 1.0f);
+    p = __fmaf_rn(p, r, 1.0f);
+    int n = (int)nf;
+    if (n > 127) return __fmul_rn(scale2(p, n - 64), 18446744073709551616.0f);
+    return scale2(p, n);
+}
+
+__device__ __forceinline__ int fexpo(float x) {  // floor(log2 x) of a positive normal float
+    return (int)((__float_as_uint(x) >> 23) & 0xFF) - 127;
+}
+__device__ __forceinline__ float fpow2(int j) {  // 2^j, -126 <= j <= 127
+    return __int_as_float((j + 127) << 23);
+}
+
+// ---- warp / block collectives -------------------------------------------------
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// (value, index) argmax, ties to the lower index (src/molla/nn/kernel.mojo:571-585)
+__device__ __forceinline__ void warp_argmax(float &v, int &i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+    }
+}
+template <class T>
+__device__ __forceinline__ T warp_incl_scan(T v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        T y = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += y;
+    }
+    return v;
+}
+// Exclusive scan over the NT threads of a CTA; `ws` is NWARP elements of shared
+// scratch. Every thread gets its exclusive prefix and the block total.
+template <class T>
+__device__ __forceinline__ T block_excl_scan(T v, T *ws, T *total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    T inc = warp_incl_scan(v, lane);
+    __syncthreads();  // ws may still be read by an earlier call
+    if (lane == 31) ws[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        T w = ws[lane];
+        T wi = warp_incl_scan(w, lane);
+        ws[lane] = wi - w;
+        if (lane == 31) ws[NWARP] = wi;
+    }
+    __syncthreads();
+    T out = ws[warp] + (inc - v);
+    *total = ws[NWARP];
+    return out;
+}
+
+// ---- mbarrier + bulk copy (TMA without a tensor map, never multicast) ---------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+            "r"(smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+}  // namespace molla
