@@ -118,6 +118,30 @@ int32_t molla_sample_batch(
     int64_t workspace_bytes, void *stream, int32_t *d_tokens, float *d_chosen_logprob,
     int32_t *d_top_ids, float *d_top_logprobs, uint32_t *d_row_status, float *d_diag);
 
+/*
+ * The same call for a caller whose logits are in host memory, which is where the
+ * reference's decode loop has them after `copy_out` (src/molla/engine/batch.mojo:
+ * 504-508, `Buffer` of src/molla/nn/tensor.mojo:270-296): every argument that is a
+ * device pointer above is a host pointer here (pinned memory makes the copies
+ * asynchronous), the block and the parameters are copied into `d_workspace`, the
+ * rows are sampled, the results are copied back and the stream is synchronised
+ * before returning. Settings are validated on the host first with the rules and
+ * messages of `SamplerConfig.check` (sample.mojo:140-154) and `Sampler.bias`
+ * (:225-232): MOLLA_ERR_CONFIG, nothing launched. `temperature` is required;
+ * the other per-row arrays may be NULL as above.
+ */
+int64_t molla_sample_host_workspace_bytes(int32_t B, int32_t V, int64_t n_hist, int64_t n_bias,
+                                          int32_t top_n);
+int32_t molla_sample_batch_host(
+    const float *h_logits, int64_t row_stride, int32_t B, int32_t V, const float *temperature,
+    const int32_t *top_k, const float *top_p, const float *min_p, const float *typical_p,
+    const float *repeat_penalty, const float *frequency_penalty, const float *presence_penalty,
+    const uint8_t *window_on, const uint64_t *seed, const uint64_t *drawn, const int64_t *hist,
+    const int32_t *hist_off, const int64_t *bias_ids, const float *bias_vals,
+    const int32_t *bias_off, int32_t top_n, void *d_workspace, int64_t workspace_bytes,
+    void *stream, int32_t *h_tokens, float *h_chosen_logprob, int32_t *h_top_ids,
+    float *h_top_logprobs, uint32_t *h_row_status);
+
 /* The rows after logit bias and penalties, before temperature: what
  * `_bias` and `_penalise` (sample.mojo:381-417) leave in `vals`. Same arguments
  * as above where they share a name; d_out is [B x V] fp32, dense. For parity
@@ -139,6 +163,11 @@ int32_t molla_sample_logprobs(const float *d_logits, int64_t row_stride, int32_t
  * the one arithmetic dependency the reference takes from outside its tree
  * (`exp` of the Mojo standard library, imported at sample.mojo:40). For tests. */
 int32_t molla_sample_expf(const float *d_x, int64_t n, void *stream, float *d_out);
+
+/* Testing aid with no counterpart in the reference: when given a device buffer of
+ * B x 16 int64, later molla_sample_batch calls from any thread record clock64() stamps
+ * at the phase boundaries of each row (NULL switches it off again). */
+void molla_sample_debug_profile(void *d_stamps);
 
 /* cudaStreamSynchronize on `stream`, returning a status; then, if
  * `d_row_status` is given, nothing else is implied: rows report for themselves. */

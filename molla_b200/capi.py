@@ -29,8 +29,9 @@ ROW_ERROR_BITS = ROW_INVALID_CONFIG | ROW_UNSUPPORTED | ROW_LOAD_TIMEOUT | ROW_D
 
 EXPORTS = (
     "molla_sample_abi_version", "molla_sample_last_error", "molla_sample_draw",
-    "molla_sample_workspace_bytes", "molla_sample_batch", "molla_sample_penalised",
-    "molla_sample_logprobs", "molla_sample_expf", "molla_sample_sync",
+    "molla_sample_workspace_bytes", "molla_sample_batch", "molla_sample_host_workspace_bytes",
+    "molla_sample_batch_host", "molla_sample_penalised",
+    "molla_sample_logprobs", "molla_sample_expf", "molla_sample_sync", "molla_sample_debug_profile",
 )
 
 
@@ -64,12 +65,18 @@ def lib():
     L.molla_sample_workspace_bytes.argtypes = [i32, i32, i32]
     L.molla_sample_batch.restype = i32
     L.molla_sample_batch.argtypes = [vp, i64, i32, i32] + [vp] * 16 + [i32, vp, i64, vp] + [vp] * 6
+    L.molla_sample_host_workspace_bytes.restype = i64
+    L.molla_sample_host_workspace_bytes.argtypes = [i32, i32, i64, i64, i32]
+    L.molla_sample_batch_host.restype = i32
+    L.molla_sample_batch_host.argtypes = [vp, i64, i32, i32] + [vp] * 16 + [i32, vp, i64, vp] + [vp] * 5
     L.molla_sample_penalised.restype = i32
     L.molla_sample_penalised.argtypes = [vp, i64, i32, i32] + [vp] * 9 + [vp, i64, vp, vp]
     L.molla_sample_logprobs.restype = i32
     L.molla_sample_logprobs.argtypes = [vp, i64, i32, i32, vp, vp]
     L.molla_sample_expf.restype = i32
     L.molla_sample_expf.argtypes = [vp, i64, vp, vp]
+    L.molla_sample_debug_profile.restype = None
+    L.molla_sample_debug_profile.argtypes = [vp]
     L.molla_sample_sync.restype = i32
     L.molla_sample_sync.argtypes = [vp]
     _lib = L

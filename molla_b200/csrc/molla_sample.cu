@@ -60,6 +60,7 @@ struct BatchArgs {
     int S;             // slice capacity in floats (multiple of 4)
     int L;             // chunk length per thread (odd), L*NT >= S
     int *row_counter;  // workspace: next row to hand out
+    long long *prof;   // optional [B x 16] clock64 stamps per row (testing aid)
 };
 
 struct Bcast {       // decisions published by CTA 0 to every CTA of the cluster
@@ -102,6 +103,8 @@ struct __align__(16) Aux {
     unsigned long long tot_q; unsigned long long tot_c;
     Bcast bc;
 };
+
+#define STAMP(i) do { if (a.prof && c.rank == 0 && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
 
 enum { EV_NONE = 0, EV_CUT = 1, EV_DRAW = 2, EV_LIMIT = 3, EV_EXHAUSTED = 4, EV_DEGENERATE = 5 };
 
@@ -669,6 +672,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         }
         const bool penalizing = won && H > 0 && (rp != 1.0f || fp != 0.0f || pp != 0.0f);
 
+        STAMP(0);
         // ---- 1. fetch this CTA's slice of the row, once, from HBM
         const float *src = a.logits + (long long)r * a.row_stride + c.base;
         {
@@ -697,6 +701,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             __syncthreads();
         }
 
+        STAMP(1);
         // ---- 2. logit bias, then penalties, scattered over the window's tokens
         // (sample.mojo:381-417: bias first, each in the reference's operation order)
         if (nb > 0) {
@@ -754,6 +759,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         }
         if (a.penalised_only) { c.cluster.sync(); continue; }
 
+        STAMP(2);
         // ---- 3. maximum and its first index (kernel.mojo:571-585, sample.mojo:342-346)
         float mx = -INFINITY;
         int mi = 0x7fffffff;
@@ -772,6 +778,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 if (ov > xmax || (ov == xmax && oi < imax)) { xmax = ov; imax = oi; }
             }
         }
+        STAMP(3);
         const long long n_lim = (k > 0 && k < a.V) ? (long long)k : (long long)a.V;
 
         int token = -1;
@@ -794,6 +801,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 nties += (e == 1.0f) ? 1 : 0;
             }
             A->cmax[c.tid] = cmx;
+            STAMP(4);
             if (n_lim == 1) {
                 // top-k of one: the sort's first element is a maximum (sample.mojo:485-490)
                 int tot;
@@ -806,6 +814,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             } else {
                 // ---- 5. the softmax denominator, exactly as the sequential loop rounds it
                 p1_build(c, csum);
+                STAMP(5);
                 if (c.rank == 0 && c.tid == 0) {
                     P1Walk w;
                     p1_walk(c, false, 0.0f, w);
@@ -814,6 +823,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 }
                 c.cluster.sync();
                 const float Z = A->bc.s;
+                STAMP(6);
                 if (A->bc.aux) status |= MOLLA_ROW_SLOW_PATH;
                 dZ = Z;
                 const float u01 = draw01(a.seed ? a.seed[r] : 0ull, a.drawn ? a.drawn[r] : 0ull);
@@ -885,6 +895,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         c.cluster.sync();
                         status |= MOLLA_ROW_SLOW_PATH;
                     }
+                    STAMP(7);
                     const unsigned int tau_head = (hb >= NBINS) ? 0x7F800000u : ((unsigned int)hb << BIN_SHIFT);
                     // ---- head walk on CTA 0 (sample.mojo:497-506 then :580-590)
                     if (c.rank == 0) {
@@ -934,6 +945,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     }
                     c.cluster.sync();
                     const Bcast hbq = A->bc;
+                    STAMP(8);
                     status |= (unsigned int)hbq.aux;
                     if (hbq.event == EV_DRAW) {
                         token = hbq.idx; dp = hbq.p;
@@ -1009,6 +1021,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 }
             }
         }
+        STAMP(9);
         if (c.rank == 0 && c.tid == 0) {
             a.tokens[r] = token;
             a.row_status[r] = status;
@@ -1122,6 +1135,7 @@ __global__ void expf_kernel(const float *x, long long n, float *out) {
 // Host side of the C ABI
 // =============================================================================
 thread_local char g_err[512] = "";
+long long *g_prof = nullptr;
 
 int fail(int code, const char *fmt, const char *detail = "") {
     snprintf(g_err, sizeof(g_err), fmt, detail);
@@ -1242,6 +1256,7 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
     a.tokens = d_tokens; a.row_status = d_row_status; a.diag = d_diag;
     a.penalised = nullptr; a.penalised_only = 0;
     a.row_counter = (int *)d_workspace;
+    a.prof = g_prof;
     int rc = launch_rows(a, st);
     if (rc != MOLLA_OK) return rc;
     if (d_chosen_logprob || top_n > 0) {
@@ -1254,6 +1269,115 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
     }
+    return MOLLA_OK;
+}
+
+// ---- host-buffer form ---------------------------------------------------------
+namespace {
+inline size_t al256(size_t n) { return (n + 255) & ~(size_t)255; }
+struct HostLayout {
+    size_t logits, f[8], win, seed, drawn, k, hist, hist_off, bias_ids, bias_vals, bias_off;
+    size_t tokens, status, chosen, top_ids, top_lps, total;
+};
+HostLayout host_layout(int B, int V, long long n_hist, long long n_bias, int top_n) {
+    HostLayout L;
+    size_t o = 256;  // the batched call's own workspace comes first
+    L.logits = o; o += al256((size_t)B * V * 4);
+    for (int i = 0; i < 8; i++) { L.f[i] = o; o += al256((size_t)B * 4); }
+    L.k = o; o += al256((size_t)B * 4);
+    L.win = o; o += al256((size_t)B);
+    L.seed = o; o += al256((size_t)B * 8);
+    L.drawn = o; o += al256((size_t)B * 8);
+    L.hist = o; o += al256((size_t)(n_hist > 0 ? n_hist : 1) * 8);
+    L.hist_off = o; o += al256((size_t)(B + 1) * 4);
+    L.bias_ids = o; o += al256((size_t)(n_bias > 0 ? n_bias : 1) * 8);
+    L.bias_vals = o; o += al256((size_t)(n_bias > 0 ? n_bias : 1) * 4);
+    L.bias_off = o; o += al256((size_t)(B + 1) * 4);
+    L.tokens = o; o += al256((size_t)B * 4);
+    L.status = o; o += al256((size_t)B * 4);
+    L.chosen = o; o += al256((size_t)B * 4);
+    L.top_ids = o; o += al256((size_t)B * (top_n > 0 ? top_n : 1) * 4);
+    L.top_lps = o; o += al256((size_t)B * (top_n > 0 ? top_n : 1) * 4);
+    L.total = o;
+    return L;
+}
+}  // namespace
+
+int64_t molla_sample_host_workspace_bytes(int32_t B, int32_t V, int64_t n_hist, int64_t n_bias, int32_t top_n) {
+    if (B < 0 || V <= 0 || n_hist < 0 || n_bias < 0 || top_n < 0 || top_n > TOPN_MAX)
+        return fail(MOLLA_ERR_ARGUMENT, "bad shape for the workspace query%s");
+    return (int64_t)host_layout(B, V, n_hist, n_bias, top_n).total;
+}
+
+int32_t molla_sample_batch_host(const float *h_logits, int64_t row_stride, int32_t B, int32_t V,
+                                const float *temperature, const int32_t *top_k, const float *top_p,
+                                const float *min_p, const float *typical_p, const float *repeat_penalty,
+                                const float *frequency_penalty, const float *presence_penalty,
+                                const uint8_t *window_on, const uint64_t *seed, const uint64_t *drawn,
+                                const int64_t *hist, const int32_t *hist_off, const int64_t *bias_ids,
+                                const float *bias_vals, const int32_t *bias_off, int32_t top_n,
+                                void *d_workspace, int64_t workspace_bytes, void *stream, int32_t *h_tokens,
+                                float *h_chosen_logprob, int32_t *h_top_ids, float *h_top_logprobs,
+                                uint32_t *h_row_status) {
+    g_err[0] = 0;
+    if (!h_logits || !h_tokens || !h_row_status || !temperature) return fail(MOLLA_ERR_ARGUMENT, "logits, temperature, tokens and row status are required%s");
+    if (B < 0 || V <= 0 || row_stride < V) return fail(MOLLA_ERR_ARGUMENT, "bad block shape%s");
+    if (top_n < 0 || top_n > TOPN_MAX || (top_n > 0 && (!h_top_ids || !h_top_logprobs))) return fail(MOLLA_ERR_ARGUMENT, "bad top_n arguments%s");
+    if ((hist == nullptr) != (hist_off == nullptr)) return fail(MOLLA_ERR_ARGUMENT, "history ids and offsets go together%s");
+    if ((bias_ids == nullptr) != (bias_off == nullptr) || (bias_ids && !bias_vals)) return fail(MOLLA_ERR_ARGUMENT, "bias ids, values and offsets go together%s");
+    if (B == 0) return MOLLA_OK;
+    // SamplerConfig.check (sample.mojo:140-154) and Sampler.bias (:225-232), before anything is launched
+    for (int r = 0; r < B; r++) {
+        if (!(temperature[r] >= 0)) return fail(MOLLA_ERR_CONFIG, "a temperature cannot be negative%s");
+        if (top_k && top_k[r] < 0) return fail(MOLLA_ERR_CONFIG, "a top-k cannot be negative%s");
+        if (top_p && !(top_p[r] > 0 && top_p[r] <= 1)) return fail(MOLLA_ERR_CONFIG, "a top-p has to be above zero and at most one%s");
+        if (min_p && !(min_p[r] >= 0 && min_p[r] <= 1)) return fail(MOLLA_ERR_CONFIG, "a min-p has to be between zero and one%s");
+        if (typical_p && !(typical_p[r] > 0 && typical_p[r] <= 1)) return fail(MOLLA_ERR_CONFIG, "a typical-p has to be above zero and at most one%s");
+        if (repeat_penalty && !(repeat_penalty[r] > 0)) return fail(MOLLA_ERR_CONFIG, "a repetition penalty of zero or less erases a logit%s");
+    }
+    const long long n_hist = hist_off ? hist_off[B] : 0, n_bias = bias_off ? bias_off[B] : 0;
+    for (long long j = 0; j < n_bias; j++)
+        if (bias_ids[j] < 0 || bias_ids[j] >= V) return fail(MOLLA_ERR_CONFIG, "a logit bias names a token outside the vocabulary%s");
+    const HostLayout L = host_layout(B, V, n_hist, n_bias, top_n);
+    if (!d_workspace || workspace_bytes < (int64_t)L.total) return fail(MOLLA_ERR_WORKSPACE, "workspace missing or too small%s");
+    char *w = (char *)d_workspace;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaMemsetAsync(w, 0, 256, st);
+    if (e == cudaSuccess)
+        e = cudaMemcpy2DAsync(w + L.logits, (size_t)V * 4, h_logits, (size_t)row_stride * 4, (size_t)V * 4, (size_t)B, cudaMemcpyHostToDevice, st);
+    const float *fsrc[8] = {temperature, top_p, min_p, typical_p, repeat_penalty, frequency_penalty, presence_penalty, nullptr};
+    for (int i = 0; i < 7 && e == cudaSuccess; i++)
+        if (fsrc[i]) e = cudaMemcpyAsync(w + L.f[i], fsrc[i], (size_t)B * 4, cudaMemcpyHostToDevice, st);
+    auto up = [&](size_t off, const void *src, size_t bytes) { if (src && bytes && e == cudaSuccess) e = cudaMemcpyAsync(w + off, src, bytes, cudaMemcpyHostToDevice, st); };
+    up(L.k, top_k, (size_t)B * 4); up(L.win, window_on, (size_t)B); up(L.seed, seed, (size_t)B * 8); up(L.drawn, drawn, (size_t)B * 8);
+    up(L.hist, hist, (size_t)n_hist * 8); up(L.hist_off, hist_off, (size_t)(B + 1) * 4);
+    up(L.bias_ids, bias_ids, (size_t)n_bias * 8); up(L.bias_vals, bias_vals, (size_t)n_bias * 4); up(L.bias_off, bias_off, (size_t)(B + 1) * 4);
+    if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "host to device copy failed: %s", cudaGetErrorString(e));
+    auto dp = [&](size_t off, const void *src) -> void * { return src ? (void *)(w + off) : nullptr; };
+    int rc = molla_sample_batch(
+        (const float *)(w + L.logits), V, B, V, (const float *)dp(L.f[0], temperature), (const int32_t *)dp(L.k, top_k),
+        (const float *)dp(L.f[1], top_p), (const float *)dp(L.f[2], min_p), (const float *)dp(L.f[3], typical_p),
+        (const float *)dp(L.f[4], repeat_penalty), (const float *)dp(L.f[5], frequency_penalty),
+        (const float *)dp(L.f[6], presence_penalty), (const uint8_t *)dp(L.win, window_on),
+        (const uint64_t *)dp(L.seed, seed), (const uint64_t *)dp(L.drawn, drawn), (const int64_t *)dp(L.hist, hist),
+        (const int32_t *)dp(L.hist_off, hist_off), (const int64_t *)dp(L.bias_ids, bias_ids),
+        (const float *)dp(L.bias_vals, bias_vals), (const int32_t *)dp(L.bias_off, bias_off), top_n, w, 256, stream,
+        (int32_t *)(w + L.tokens), h_chosen_logprob ? (float *)(w + L.chosen) : nullptr,
+        top_n > 0 ? (int32_t *)(w + L.top_ids) : nullptr, top_n > 0 ? (float *)(w + L.top_lps) : nullptr,
+        (uint32_t *)(w + L.status), nullptr);
+    if (rc != MOLLA_OK) return rc;
+    e = cudaMemcpyAsync(h_tokens, w + L.tokens, (size_t)B * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_row_status, w + L.status, (size_t)B * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess && h_chosen_logprob) e = cudaMemcpyAsync(h_chosen_logprob, w + L.chosen, (size_t)B * 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess && top_n > 0) {
+        e = cudaMemcpyAsync(h_top_ids, w + L.top_ids, (size_t)B * top_n * 4, cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(h_top_logprobs, w + L.top_lps, (size_t)B * top_n * 4, cudaMemcpyDeviceToHost, st);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "device to host copy failed: %s", cudaGetErrorString(e));
+    for (int r = 0; r < B; r++)
+        if (h_row_status[r] & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG))
+            return fail(MOLLA_ERR_DEVICE, "a row reported an error in its status word%s");
     return MOLLA_OK;
 }
 
@@ -1306,6 +1430,8 @@ int32_t molla_sample_expf(const float *d_x, int64_t n, void *stream, float *d_ou
     if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "expf launch failed: %s", cudaGetErrorString(e));
     return MOLLA_OK;
 }
+
+void molla_sample_debug_profile(void *d_stamps) { g_prof = (long long *)d_stamps; }
 
 int32_t molla_sample_sync(void *stream) {
     cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);

@@ -144,6 +144,56 @@ def sample_batch(logits: torch.Tensor, p: dict, top_n: int = 0, want_logprob: bo
                 top_logprobs=top_lps, diag=diag)
 
 
+class HostBlock:
+    """Host-resident inputs and outputs for `sample_batch_host`: the logit block and the
+    per-row parameters in pinned memory (what the reference's decode loop holds after
+    `copy_out`), plus the device workspace the call stages them in."""
+
+    def __init__(self, w: dict, device, top_n: int = 0, want_logprob: bool = False):
+        self.B, self.V = w["logits"].shape
+        self.device = torch.device(device)
+        self.top_n = top_n
+        self.logits = torch.from_numpy(np.ascontiguousarray(w["logits"], np.float32)).pin_memory()
+        self.p = {}
+        for k, dt in _PARAM_DTYPES.items():
+            if k in w and w[k] is not None:
+                a = np.ascontiguousarray(w[k], dtype=dt)
+                if dt == np.uint64:
+                    a = a.view(np.int64)
+                if a.size == 0:
+                    a = np.zeros(1, a.dtype)
+                self.p[k] = torch.from_numpy(a.copy()).pin_memory()
+        n_hist = int(w["hist_off"][-1]) if "hist_off" in w else 0
+        n_bias = int(w["bias_off"][-1]) if "bias_off" in w else 0
+        n = capi.lib().molla_sample_host_workspace_bytes(self.B, self.V, n_hist, n_bias, top_n)
+        if n < 0:
+            raise capi.MollaSampleError(int(n), capi.last_error())
+        self.ws_bytes = int(n)
+        self.ws = torch.zeros(self.ws_bytes, dtype=torch.uint8, device=self.device)
+        self.tokens = torch.empty(self.B, dtype=torch.int32).pin_memory()
+        self.status = torch.empty(self.B, dtype=torch.int32).pin_memory()
+        self.chosen = torch.empty(self.B, dtype=torch.float32).pin_memory() if want_logprob else None
+        self.top_ids = torch.empty((self.B, max(top_n, 1)), dtype=torch.int32).pin_memory() if top_n else None
+        self.top_lps = torch.empty((self.B, max(top_n, 1)), dtype=torch.float32).pin_memory() if top_n else None
+        self.h2d_bytes = self.logits.numel() * 4 + sum(t.numel() * t.element_size() for t in self.p.values())
+        self.d2h_bytes = self.B * 8 + (self.B * 4 if want_logprob else 0) + self.B * top_n * 8
+
+
+def sample_batch_host(hb: HostBlock) -> None:
+    """Host block in, host tokens out: copies, launch and copies back in one synchronous
+    C call (`molla_sample_batch_host`). Results land in hb.tokens / hb.status / ..."""
+    g = hb.p.get
+    rc = capi.lib().molla_sample_batch_host(
+        _ptr(hb.logits), hb.V, hb.B, hb.V,
+        _ptr(g("temperature")), _ptr(g("top_k")), _ptr(g("top_p")), _ptr(g("min_p")),
+        _ptr(g("typical_p")), _ptr(g("repeat_penalty")), _ptr(g("frequency_penalty")),
+        _ptr(g("presence_penalty")), _ptr(g("window_on")), _ptr(g("seed")), _ptr(g("drawn")),
+        _ptr(g("hist")), _ptr(g("hist_off")), _ptr(g("bias_ids")), _ptr(g("bias_vals")),
+        _ptr(g("bias_off")), hb.top_n, _ptr(hb.ws), hb.ws_bytes, _stream_ptr(hb.device),
+        _ptr(hb.tokens), _ptr(hb.chosen), _ptr(hb.top_ids), _ptr(hb.top_lps), _ptr(hb.status))
+    capi.check(rc)
+
+
 def penalised(logits: torch.Tensor, p: dict, workspace: Workspace | None = None) -> torch.Tensor:
     """The block after logit bias and penalties, before temperature (sample.mojo:381-417)."""
     B, V = logits.shape
