@@ -1,10 +1,10 @@
 // The token-sampling kernel and its C ABI (declared in include/molla_sample.h).
 //
-// One thread-block cluster owns one logit row at a time: the row is fetched from
-// HBM exactly once (bulk asynchronous copies into shared memory, one slice per
-// CTA of the cluster) and every later pass - penalties, maximum, exponentials,
-// the softmax denominator, candidate selection, the top-p cut and the draw -
-// reads it from shared / distributed shared memory.
+// One CTA owns one logit row at a time. The row is streamed through shared memory
+// in tiles staged by bulk asynchronous copies (TMA without a tensor map), twice:
+// pass A reads it from HBM and finds the maximum; pass B, a moment later, finds
+// the same bytes in L2 and does everything else. With one CTA per SM about 150
+// rows are in flight, which is less than the L2 holds, so HBM sees each logit once.
 //
 // The reference (src/molla/engine/sample.mojo) defines its result through
 // *sequential* fp32 sums: the softmax denominator is accumulated in vocabulary
@@ -15,17 +15,21 @@
 //   * a running fp32 sum of non-negative terms stays inside one binade
 //     [2^j, 2^(j+1)) for long stretches; there `s + a` rounds to a multiple of
 //     ulp = 2^(j-23), so every term contributes the integer rne(a/ulp) and the
-//     contributions add exactly, in any order (`p1_*` below);
+//     contributions add exactly, in any order;
 //   * the few places where that fails - the running sum crossing into the next
 //     binade, a term that is large against the sum, a rounding tie whose
 //     direction depends on the parity of the sum - are found in parallel and
-//     replayed sequentially by one thread.
+//     replayed sequentially by one thread;
+//   * a term smaller than half an ulp of the running sum adds nothing at all.
+//     The running sum is never below the largest term before it, so a logit more
+//     than ~17.5 (in temperature-scaled units) below the running maximum cannot
+//     change any sum and can never be drawn: its exponential is not evaluated.
 // What cannot be reproduced is the order the reference's unstable heapsort
 // (:440-483) leaves equal probabilities in; rows where that order could matter
 // are marked in the row status (MOLLA_ROW_*_TIE) and equal probabilities are
 // ordered by token id.
-#include <cooperative_groups.h>
 #include <cuda_runtime.h>
+#include <math.h>
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
@@ -33,18 +37,23 @@
 #include "../../include/molla_sample.h"
 #include "molla_device.cuh"
 
-namespace cg = cooperative_groups;
 using namespace molla;
 
 namespace {
 
-constexpr int NBINS = 2048;      // histogram bins over the top bits of exp(v - max) in [0, 1]
-constexpr int BIN_SHIFT = 19;    // sign + 8 exponent + 4 mantissa bits
-constexpr int NC = 2048;         // candidate-list capacity (head list, gathered bins)
-constexpr int HEAD_MAX = 1025;   // the sorted head covers top-k + 1 up to this many
-constexpr int HIST_STAGE = 4096; // history ids staged in shared memory
-constexpr short SUS = -32768;    // chunk that must be replayed sequentially
+constexpr int LT = 11;              // elements per thread per tile (odd: conflict-free strides)
+constexpr int TILE = NT * LT;       // 11264 floats = 45056 bytes per tile
+constexpr int MAX_TILES = 64;       // V <= 720896
+constexpr int NBINS = 2048;         // histogram bins over the top bits of exp(v - max) in [0, 1]
+constexpr int BIN_SHIFT = 19;       // sign + 8 exponent + 4 mantissa bits
+constexpr int NC = 2048;            // candidate-list capacity (head list, gathered bins)
+constexpr int HEAD_NEED = 128;      // the sorted head covers top-k + 1 up to this many
+constexpr int HSLOTS = 2048;        // hash slots for penalised / biased tokens
+constexpr int PATCH_MAX = 1024;     // window + bias entries per row
+constexpr short SUS = -32768;       // chunk that must be replayed sequentially
 constexpr int TOPN_MAX = 20;
+constexpr float REL_MARGIN = 18.0f; // > 25.25*ln2 = 17.5: below this nothing can matter
+constexpr unsigned int W_BITS = 0x32800000u;  // 2^-26: what the descending walks can ever need
 
 struct BatchArgs {
     const float *logits; long long row_stride; int B, V;
@@ -57,14 +66,9 @@ struct BatchArgs {
     int *tokens; unsigned int *row_status; float *diag;
     float *penalised;  // optional dump [B x V]
     int penalised_only;
-    int S;             // slice capacity in floats (multiple of 4)
-    int L;             // chunk length per thread (odd), L*NT >= S
-    int *row_counter;  // workspace: next row to hand out
-    long long *prof;   // optional [B x 16] clock64 stamps per row (testing aid)
-};
-
-struct Bcast {       // decisions published by CTA 0 to every CTA of the cluster
-    float s; unsigned int tau; int event; int idx; float p; long long pos; int aux;
+    int *row_counter;            // scratch: next row to hand out (zeroed before the launch)
+    unsigned long long *wlist;   // scratch: per-CTA list of (exp bits, token id), V entries each
+    long long *prof;             // optional [B x 16] clock64 stamps per row (testing aid)
 };
 
 struct __align__(16) Aux {
@@ -81,63 +85,53 @@ struct __align__(16) Aux {
             unsigned long long hq[NBINS];
             unsigned int hc[NBINS];
         } h;
-        int hist_tok[HIST_STAGE];
     } u;
-    float cmax[NT];
     unsigned long long cand[NC];
     float pc[NC];
     float pre[NC];
-    unsigned int hidx[NC];          // head: token id, bit 31 = equal to a neighbour
-    unsigned long long xs[2][16];   // cluster exchange slots, two banks used alternately
-    unsigned long long stage;
+    unsigned int hidx[NC];  // head: token id, bit 31 = equal to a neighbour
+    int hkey[HSLOTS];
+    int hcnt[HSLOTS];
+    float hval[HSLOTS];
+    float tilemax[MAX_TILES];
     double wsd[NWARP + 1];
     unsigned long long wsu[NWARP + 1];
     float wsf[NWARP + 1];
     int wsi[NWARP + 1];
-    uint64_t mbar;
+    uint64_t mbar[2];
     int nseg;
     int ncand;
+    int nw;
+    int cur_row;
     int evt_thread;
     int specbin;
     int hit_bin; unsigned long long hit_qbefore; unsigned long long hit_cbefore;
     unsigned long long tot_q; unsigned long long tot_c;
-    Bcast bc;
+    // the sequential walker's state and results
+    float walk_s; int walk_found; int walk_idx; int walk_slow;
+    // decisions published by thread 0
+    float b_s; unsigned int b_tau; int b_event; int b_idx; float b_p; long long b_pos; int b_aux;
+    float b_sum; float b_target;
 };
-
-#define STAMP(i) do { if (a.prof && c.rank == 0 && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
 
 enum { EV_NONE = 0, EV_CUT = 1, EV_DRAW = 2, EV_LIMIT = 3, EV_EXHAUSTED = 4, EV_DEGENERATE = 5 };
 
 struct Ctx {
-    cg::cluster_group cluster;
-    int cs, rank, tid, lane, warp;
-    float *row;
+    int tid, lane, warp;
+    float *tb;            // two tile buffers
+    unsigned int *bm;     // bitmap of patched tokens
     Aux *A;
-    int S, L, V, base, nloc;
-    int c0, c1;  // this thread's chunk of local indices
-    int xph;     // exchange counter (selects the slot bank)
+    int V, ntiles;
+    bool patching;
+    const float *src;     // this row in global memory
+    bool aligned;
+    unsigned int par[2];  // mbarrier phase parity per buffer
+    unsigned int status;
 };
 
-// ---- cluster-wide exchange: every CTA publishes one 64-bit value (valid in its
-// thread 0), all CTAs read all. Two slot banks alternate so that a fast CTA's
-// next exchange cannot overwrite a value a slow CTA has not read yet.
-__device__ __forceinline__ const unsigned long long *xchg(Ctx &c, unsigned long long v) {
-    Aux *A = c.A;
-    const int bank = c.xph & 1;
-    c.xph++;
-    if (c.tid == 0) A->stage = v;
-    __syncthreads();
-    if (c.tid < c.cs) {
-        Aux *RA = c.cluster.map_shared_rank(A, c.tid);
-        RA->xs[bank][c.rank] = A->stage;
-    }
-    c.cluster.sync();
-    return A->xs[bank];
-}
-__device__ __forceinline__ unsigned long long pack_fi(float f, int i) {
-    return ((unsigned long long)__float_as_uint(f) << 32) | (unsigned long long)(unsigned int)i;
-}
+#define STAMP(i) do { if (a.prof && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
 
+// ---- block collectives (NT threads) ----------------------------------------------
 __device__ __forceinline__ float block_max(Ctx &c, float v) {
     v = warp_max(v);
     __syncthreads();
@@ -164,7 +158,7 @@ __device__ __forceinline__ void block_argmax(Ctx &c, float &v, int &i) {
     v = bv; i = bi;
 }
 
-// ---- bitonic sort, descending, of n2 (power of two) keys in shared memory -----
+// bitonic sort, descending, of n2 (power of two) keys in shared memory
 __device__ void bitonic_desc(unsigned long long *k, int n2, int tid) {
     for (int size = 2; size <= n2; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
@@ -173,238 +167,297 @@ __device__ void bitonic_desc(unsigned long long *k, int n2, int tid) {
                 int pos = ((i / stride) * stride * 2) + (i % stride);
                 int par = pos + stride;
                 bool desc = ((pos & size) == 0);
-                unsigned long long a = k[pos], b = k[par];
-                if ((a < b) == desc) { k[pos] = b; k[par] = a; }
+                unsigned long long x = k[pos], y = k[par];
+                if ((x < y) == desc) { k[pos] = y; k[par] = x; }
             }
         }
     }
     __syncthreads();
 }
 
+__device__ __forceinline__ unsigned int fkey(float f) {  // order-preserving key of a float
+    unsigned int b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float fkey_inv(unsigned int k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__device__ __forceinline__ int key_idx(unsigned long long k) {
+    return (int)(0xFFFFFFFFu - (unsigned int)(k & 0xFFFFFFFFull));
+}
+__device__ __forceinline__ float key_val(unsigned long long k) {
+    return __uint_as_float((unsigned int)(k >> 32));
+}
+__device__ __forceinline__ unsigned long long make_key(unsigned int ebits, int idx) {
+    return ((unsigned long long)ebits << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)idx);
+}
+
+// ---- tile pipeline: tile t of the row lands in buffer t & 1 ------------------------
+__device__ __forceinline__ void tile_issue(Ctx &c, int t) {
+    // one thread; the buffer is free (a __syncthreads separates its last reader from here)
+    const int b = t & 1;
+    long long left = (long long)c.V - (long long)t * TILE;
+    const int n = (int)(left > TILE ? TILE : left);
+    const int nbulk = n & ~3;
+    if (nbulk <= 0) return;
+    fence_proxy_async();
+    mbar_expect_tx(&c.A->mbar[b], (uint32_t)nbulk * 4u);
+    const float *s = c.src + (long long)t * TILE;
+    float *d = c.tb + b * TILE;
+    const int PIECE = 4096;  // floats per bulk copy (16 KB)
+    for (int o = 0; o < nbulk; o += PIECE) {
+        int m = nbulk - o < PIECE ? nbulk - o : PIECE;
+        bulk_g2s(d + o, s + o, (uint32_t)m * 4u, &c.A->mbar[b]);
+    }
+}
+
+// Start a pass over the row: tile 0 is requested.
+__device__ __forceinline__ void tiles_begin(Ctx &c) {
+    __syncthreads();  // both buffers are free
+    if (c.aligned && c.tid == 0) tile_issue(c, 0);
+}
+
+// Make tile t available in shared memory (returns its buffer) and request tile t + 1.
+__device__ __forceinline__ float *tile_acquire(Ctx &c, int t, int &n_tile) {
+    const int b = t & 1;
+    long long left = (long long)c.V - (long long)t * TILE;
+    n_tile = (int)(left > TILE ? TILE : left);
+    float *buf = c.tb + b * TILE;
+    __syncthreads();  // everyone is done with the other buffer (tile t - 1)
+    if (c.aligned) {
+        if (c.tid == 0 && t + 1 < c.ntiles) tile_issue(c, t + 1);
+        const int nbulk = n_tile & ~3;
+        for (int i = nbulk + c.tid; i < n_tile; i += NT) buf[i] = __ldg(c.src + (long long)t * TILE + i);
+        if (nbulk > 0) {
+            bool done = false;
+            for (int spin = 0; spin < (1 << 22); spin++) {
+                if (mbar_try_wait(&c.A->mbar[b], c.par[b])) { done = true; break; }
+            }
+            if (!done) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
+            c.par[b] ^= 1u;
+        }
+        if (n_tile & 3) __syncthreads();
+    } else {
+        const float *s = c.src + (long long)t * TILE;
+        for (int i = c.tid; i < n_tile; i += NT) buf[i] = __ldg(s + i);
+        __syncthreads();
+    }
+    return buf;
+}
+
+// ---- patched tokens: bitmap over the vocabulary + a small hash of their values -----
+__device__ __forceinline__ int hslot(int tok) { return (int)(((unsigned int)tok * 2654435761u) >> 21); }
+
+__device__ __forceinline__ float patch_lookup(const Ctx &c, int tok, float x) {
+    int s = hslot(tok);
+    for (int probe = 0; probe < HSLOTS; probe++) {
+        int k = c.A->hkey[s];
+        if (k == tok) return c.A->hval[s];
+        if (k < 0) return x;
+        s = (s + 1) & (HSLOTS - 1);
+    }
+    return x;
+}
+// bits j = 1 where element g0 + j (j < 32) is patched
+__device__ __forceinline__ unsigned int patch_mask(const Ctx &c, int g0) {
+    if (!c.patching) return 0u;
+    const int w = g0 >> 5, sh = g0 & 31;
+    const int nwords = (c.V + 31) >> 5;
+    unsigned int lo = c.bm[w];
+    unsigned int hi = (w + 1 < nwords) ? c.bm[w + 1] : 0u;
+    return __funnelshift_r(lo, hi, sh);
+}
+
 // =============================================================================
-// P1: the exact sequential fp32 sum of row[0..V) in vocabulary order.
+// The exact sequential fp32 sum, one tile at a time (vocabulary order).
 // =============================================================================
-// Build: every thread owns a contiguous chunk. From approximate prefix sums each
-// chunk guesses the binade(s) the true running sum can be in when it reaches the
-// chunk (a margin of 2^-12 covers the rounding drift of the true sum) and adds up
-// its terms' integer contributions for that binade (`pa`) and, when the guess
-// straddles a power of two, for the next one (`pb`). Chunks holding a rounding
-// tie, a term >= sum/4, or a span of more than two binades are left to the
-// sequential replay. `csum` (per-thread fp32 chunk sum) is an input.
-__device__ void p1_build(Ctx &c, float csum) {
+// Every thread owns LT consecutive terms of the tile. From approximate prefix sums
+// each chunk guesses the binade(s) the true running sum can be in when it reaches
+// the chunk (a margin of 2^-12 covers the rounding drift of the true sum) and adds
+// up its terms' integer contributions for that binade (`pa`) and, when the guess
+// straddles a power of two, for the next one (`pb`). Chunks holding a rounding tie,
+// a term >= sum/4, or a span of more than two binades are replayed term by term.
+// Thread 0 then carries the exact sum across the tile from those tables.
+struct Walker {
+    float s; int found; long long idx; int slow;
+};
+
+__device__ __forceinline__ void p1_sim(const float *buf, int i0, int i1, long long gbase, bool locate,
+                                       float target, Walker &w) {
+    float s = w.s;
+    for (int i = i0; i < i1; i++) {
+        s = __fadd_rn(s, buf[i]);
+        if (locate && target < s) { w.found = 1; w.idx = gbase + i; break; }
+    }
+    w.s = s;
+}
+
+__device__ void p1_walk_tile(Ctx &c, const float *buf, int n_tile, long long gbase, bool locate, float target,
+                             Walker &w) {
+    Aux *A = c.A;
+    const int nseg = A->nseg;
+    const double *PA = A->u.p1.pa, *PB = A->u.p1.pb;
+    for (int si = 0; si < nseg && !(locate && w.found); si++) {
+        const int t0 = A->u.p1.seg[si];
+        const int t1 = (si + 1 < nseg) ? (int)A->u.p1.seg[si + 1] : NT;
+        const int j = A->u.p1.ja[t0];
+        const int e0 = min(n_tile, t0 * LT), e1 = min(n_tile, t1 * LT);
+        if (e1 <= e0) continue;
+        if (j == SUS) {
+            if (A->u.p1.csum[t0] != 0.0f) p1_sim(buf, e0, e1, gbase, locate, target, w);
+            continue;
+        }
+        const bool dual = A->u.p1.dual[t0] != 0;
+        const double pa0 = PA[t0], pa1 = PA[t1], pb0 = PB[t0], pb1 = PB[t1];
+        if (pa1 == pa0 && pb1 == pb0) continue;  // every term rounds to nothing in either binade
+        bool ok = false;
+        if (w.s > 0.0f) {
+            const int js = fexpo(w.s);
+            const double sd = (double)w.s;
+            // step over chunks [ta, tb) with table P, valid while the sum stays below lim
+            auto bulk = [&](const double *P, int ta, int tb, double lim) -> bool {
+                double sn = (double)w.s + (P[tb] - P[ta]);
+                if (!(sn < lim)) return false;
+                if (locate && target < (float)sn) {
+                    int lo_ = ta, hi_ = tb - 1;  // first chunk whose end value exceeds the target
+                    while (lo_ < hi_) {
+                        int mid = (lo_ + hi_) >> 1;
+                        if (target < (float)((double)w.s + (P[mid + 1] - P[ta]))) hi_ = mid;
+                        else lo_ = mid + 1;
+                    }
+                    w.s = (float)((double)w.s + (P[lo_] - P[ta]));
+                    p1_sim(buf, min(n_tile, lo_ * LT), min(n_tile, (lo_ + 1) * LT), gbase, true, target, w);
+                    return true;
+                }
+                w.s = (float)sn;
+                return true;
+            };
+            if (!dual) {
+                if (js == j) ok = bulk(PA, t0, t1, ldexp(1.0, j + 1));
+            } else if (js == j + 1) {
+                ok = bulk(PB, t0, t1, ldexp(1.0, j + 2));
+            } else if (js == j) {
+                const double lim = ldexp(1.0, j + 1);
+                if (sd + (pa1 - pa0) < lim) {
+                    ok = bulk(PA, t0, t1, lim);
+                } else {
+                    // the running sum leaves binade j inside this segment: find the chunk
+                    int lo_ = t0, hi_ = t1 - 1;
+                    while (lo_ < hi_) {
+                        int mid = (lo_ + hi_) >> 1;
+                        if (sd + (PA[mid + 1] - pa0) >= lim) hi_ = mid;
+                        else lo_ = mid + 1;
+                    }
+                    const int ts = lo_;
+                    bool fine = true;
+                    if (ts > t0) fine = bulk(PA, t0, ts, lim);
+                    if (fine) {
+                        ok = true;
+                        if (!(locate && w.found)) {
+                            p1_sim(buf, min(n_tile, ts * LT), min(n_tile, (ts + 1) * LT), gbase, locate, target, w);
+                            if (!(locate && w.found) && ts + 1 < t1) {
+                                if (!(fexpo(w.s) == j + 1 && bulk(PB, ts + 1, t1, ldexp(1.0, j + 2)))) {
+                                    w.slow = 1;
+                                    p1_sim(buf, min(n_tile, (ts + 1) * LT), e1, gbase, locate, target, w);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        if (!ok) {
+            w.slow = 1;
+            p1_sim(buf, e0, e1, gbase, locate, target, w);
+        }
+    }
+}
+
+// One tile of the sum. `e` are this thread's terms (zero past `nchunk`), already written
+// to `buf`; `sbase` is the approximate sum of everything before the tile.
+__device__ void p1_tile(Ctx &c, const float (&e)[LT], int nchunk, float csum, const float *buf, int n_tile,
+                        long long gbase, double &sbase, bool locate, float target) {
     Aux *A = c.A;
     const float EPS = 1.0f / 4096.0f;
     double tot;
-    double ex = block_excl_scan<double>((double)csum, A->wsd, &tot);
-    const unsigned long long *xs = xchg(c, (unsigned long long)__double_as_longlong(tot));
-    double basesum = 0.0;
-    for (int r = 0; r < c.rank; r++) basesum += __longlong_as_double((long long)xs[r]);
-    double sst = basesum + ex;
+    const double ex = block_excl_scan<double>((double)csum, A->wsd, &tot);
+    if (tot == 0.0) return;  // nothing in this tile can change the sum
+    const double sst = sbase + ex;
     short ja = SUS;
     unsigned char dual = 0;
     float da = 0.0f, db = 0.0f;
-    float lo = (float)(sst * (1.0 - (double)EPS));
-    float hi = (float)((sst + (double)csum) * (1.0 + (double)EPS));
-    if (lo > 0.0f && c.c1 > c.c0) {
-        int jl = fexpo(lo), j2 = fexpo(hi);
+    const float lo = (float)(sst * (1.0 - (double)EPS));
+    const float hi = (float)((sst + (double)csum) * (1.0 + (double)EPS));
+    if (lo > 0.0f && nchunk > 0) {
+        const int jl = fexpo(lo), j2 = fexpo(hi);
         if (j2 <= jl + 1 && jl >= -100 && j2 <= 100) {
             bool bad = false;
             const bool two = (j2 == jl + 1);
             const float C1 = __fmul_rn(1.5f, fpow2(jl)), h1 = fpow2(jl - 24), b1 = fpow2(jl - 1);
             const float C2 = __fmul_rn(1.5f, fpow2(jl + 1)), h2 = fpow2(jl - 23);
-            for (int i = c.c0; i < c.c1; i++) {
-                float e = c.row[i];
-                float q = __fsub_rn(__fadd_rn(e, C1), C1);
-                float r = __fsub_rn(e, q);
-                bad |= (fabsf(r) == h1) | (e >= b1);
+#pragma unroll
+            for (int i = 0; i < LT; i++) {
+                const float v = e[i];
+                const float q = __fsub_rn(__fadd_rn(v, C1), C1);
+                const float r = __fsub_rn(v, q);
+                bad |= (fabsf(r) == h1) | (v >= b1);
                 da = __fadd_rn(da, q);
-                if (two) {
-                    float q2 = __fsub_rn(__fadd_rn(e, C2), C2);
-                    float r2 = __fsub_rn(e, q2);
-                    bad |= (fabsf(r2) == h2);
-                    db = __fadd_rn(db, q2);
-                }
+                const float q2 = __fsub_rn(__fadd_rn(v, C2), C2);
+                const float r2 = __fsub_rn(v, q2);
+                bad |= two & (fabsf(r2) == h2);
+                db = __fadd_rn(db, q2);
             }
             if (!bad) { ja = (short)jl; dual = two ? 1 : 0; }
         }
     }
-    if (c.c1 <= c.c0) { ja = SUS; }  // empty chunk: replay does nothing
     if (ja == SUS) { da = 0.0f; db = 0.0f; dual = 0; }
-    A->u.p1.csum[c.tid] = (c.c1 > c.c0) ? csum : 0.0f;
+    A->u.p1.csum[c.tid] = (nchunk > 0) ? csum : 0.0f;
     A->u.p1.ja[c.tid] = ja;
     A->u.p1.dual[c.tid] = dual;
     double t2;
-    double pa = block_excl_scan<double>((double)da, A->wsd, &t2);
+    const double pa = block_excl_scan<double>((double)da, A->wsd, &t2);
     A->u.p1.pa[c.tid] = pa;
     if (c.tid == NT - 1) A->u.p1.pa[NT] = t2;
-    double pb = block_excl_scan<double>((double)(dual ? db : da), A->wsd, &t2);
+    const double pb = block_excl_scan<double>((double)(dual ? db : da), A->wsd, &t2);
     A->u.p1.pb[c.tid] = pb;
     if (c.tid == NT - 1) A->u.p1.pb[NT] = t2;
     __syncthreads();
     // segment list: chunks where (binade guess, dual, replay) changes
-    bool start = (c.tid == 0) || ja == SUS || A->u.p1.ja[c.tid - 1] != ja ||
-                 A->u.p1.dual[c.tid - 1] != dual;
-    unsigned int bal = __ballot_sync(0xffffffffu, start);
-    int wcount = __popc(bal);
+    const bool start = (c.tid == 0) || ja == SUS || A->u.p1.ja[c.tid - 1] != ja || A->u.p1.dual[c.tid - 1] != dual;
+    const unsigned int bal = __ballot_sync(0xffffffffu, start);
     int wtot;
-    int wex = block_excl_scan<int>(c.lane == 0 ? wcount : 0, A->wsi, &wtot);
+    int wex = block_excl_scan<int>(c.lane == 0 ? __popc(bal) : 0, A->wsi, &wtot);
     wex = __shfl_sync(0xffffffffu, wex, 0);
-    if (start) {
-        int pos = wex + __popc(bal & ((1u << c.lane) - 1u));
-        A->u.p1.seg[pos] = (unsigned short)c.tid;
-    }
+    if (start) A->u.p1.seg[wex + __popc(bal & ((1u << c.lane) - 1u))] = (unsigned short)c.tid;
     if (c.tid == 0) A->nseg = wtot;
-    c.cluster.sync();
-}
-
-// Walk (one thread): replays the sum across the whole cluster from the tables
-// p1_build left in every CTA's shared memory. With `locate`, stops at the first
-// index i whose running sum exceeds `target` (strictly) and returns it.
-struct P1Walk {
-    float s;
-    int found;      // locate mode: index found
-    long long idx;  // global vocabulary index
-    int slow;       // a fallback replay ran
-};
-
-__device__ __forceinline__ void p1_sim(const float *rrow, int i0, int i1, long long gbase,
-                                       bool locate, float target, P1Walk &w) {
-    float s = w.s;
-    int i = i0;
-    while (i < i1) {
-        float buf[8];
-        int n = min(8, i1 - i);
-#pragma unroll
-        for (int k = 0; k < 8; k++) buf[k] = (k < n) ? rrow[i + k] : 0.0f;
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            if (k < n) {
-                s = __fadd_rn(s, buf[k]);
-                if (locate && !w.found && target < s) { w.found = 1; w.idx = gbase + i + k; }
-            }
-        }
-        if (locate && w.found) break;
-        i += n;
+    __syncthreads();
+    if (c.tid == 0) {
+        Walker w; w.s = A->walk_s; w.found = A->walk_found; w.idx = A->walk_idx; w.slow = A->walk_slow;
+        p1_walk_tile(c, buf, n_tile, gbase, locate, target, w);
+        A->walk_s = w.s; A->walk_found = w.found; A->walk_idx = (int)w.idx; A->walk_slow = w.slow;
     }
-    w.s = s;
-}
-
-__device__ void p1_walk(Ctx &c, bool locate, float target, P1Walk &w) {
-    w.s = 0.0f; w.found = 0; w.idx = -1; w.slow = 0;
-    const int L = c.L;
-    for (int r = 0; r < c.cs && !(locate && w.found); r++) {
-        Aux *RA = c.cluster.map_shared_rank(c.A, r);
-        const float *rrow = c.cluster.map_shared_rank(c.row, r);
-        const long long gbase = (long long)r * c.S;
-        long long nl = (long long)c.V - gbase;
-        const int nloc = (int)(nl < 0 ? 0 : (nl > c.S ? c.S : nl));
-        const int nseg = RA->nseg;
-        const double *PA = RA->u.p1.pa, *PB = RA->u.p1.pb;
-        for (int si = 0; si < nseg && !(locate && w.found); si++) {
-            const int t0 = RA->u.p1.seg[si];
-            const int t1 = (si + 1 < nseg) ? (int)RA->u.p1.seg[si + 1] : NT;
-            const int j = RA->u.p1.ja[t0];
-            const int e0 = min(nloc, t0 * L), e1 = min(nloc, t1 * L);
-            if (e1 <= e0) continue;
-            if (j == SUS) {
-                if (RA->u.p1.csum[t0] != 0.0f) p1_sim(rrow, e0, e1, gbase, locate, target, w);
-                continue;
-            }
-            const bool dual = RA->u.p1.dual[t0] != 0;
-            const double pa0 = PA[t0], pa1 = PA[t1], pb0 = PB[t0], pb1 = PB[t1];
-            if (pa1 == pa0 && pb1 == pb0) continue;  // all terms round to nothing in either binade
-            bool ok = false;
-            if (w.s > 0.0f) {
-                const int js = fexpo(w.s);
-                const double sd = (double)w.s;
-                // bulk step over chunks [ta, tb) using table P, valid while the sum stays below lim
-                auto bulk = [&](const double *P, int ta, int tb, double lim) -> bool {
-                    double sn = (double)w.s + (P[tb] - P[ta]);
-                    if (!(sn < lim)) return false;
-                    if (locate && target < (float)sn) {
-                        // first chunk t in [ta, tb) whose end value exceeds the target
-                        int lo_ = ta, hi_ = tb - 1;
-                        while (lo_ < hi_) {
-                            int mid = (lo_ + hi_) >> 1;
-                            if (target < (float)((double)w.s + (P[mid + 1] - P[ta]))) hi_ = mid;
-                            else lo_ = mid + 1;
-                        }
-                        w.s = (float)((double)w.s + (P[lo_] - P[ta]));
-                        p1_sim(rrow, min(nloc, lo_ * L), min(nloc, (lo_ + 1) * L), gbase, true, target, w);
-                        return true;
-                    }
-                    w.s = (float)sn;
-                    return true;
-                };
-                if (!dual) {
-                    if (js == j) ok = bulk(PA, t0, t1, ldexp(1.0, j + 1));
-                } else if (js == j + 1) {
-                    ok = bulk(PB, t0, t1, ldexp(1.0, j + 2));
-                } else if (js == j) {
-                    const double lim = ldexp(1.0, j + 1);
-                    if (sd + (pa1 - pa0) < lim) {
-                        ok = bulk(PA, t0, t1, lim);
-                    } else {
-                        // the running sum leaves binade j inside this segment: find the chunk
-                        int lo_ = t0, hi_ = t1 - 1;
-                        while (lo_ < hi_) {
-                            int mid = (lo_ + hi_) >> 1;
-                            if (sd + (PA[mid + 1] - pa0) >= lim) hi_ = mid;
-                            else lo_ = mid + 1;
-                        }
-                        const int ts = lo_;
-                        bool fine = true;
-                        if (ts > t0) fine = bulk(PA, t0, ts, lim);
-                        if (fine && !(locate && w.found)) {
-                            p1_sim(rrow, min(nloc, ts * L), min(nloc, (ts + 1) * L), gbase, locate, target, w);
-                            if (!(locate && w.found) && ts + 1 < t1) {
-                                if (fexpo(w.s) == j + 1 && bulk(PB, ts + 1, t1, ldexp(1.0, j + 2))) {
-                                } else {
-                                    w.slow = 1;
-                                    p1_sim(rrow, min(nloc, (ts + 1) * L), e1, gbase, locate, target, w);
-                                }
-                            }
-                            ok = true;
-                        } else if (fine) {
-                            ok = true;
-                        } else {
-                            ok = false;  // cannot happen (ts chosen so the prefix stays below lim)
-                        }
-                    }
-                }
-            }
-            if (!ok) {
-                w.slow = 1;
-                p1_sim(rrow, e0, e1, gbase, locate, target, w);
-            }
-        }
-    }
+    __syncthreads();
+    sbase += tot;
 }
 
 // =============================================================================
-// Histogram search shared by head selection and the descending walk.
-// Thread t owns bins NBINS-1-2t and NBINS-2-2t, so a scan over threads runs
-// through the bins in descending order. Totals are summed over the cluster's
-// CTAs; every CTA computes the same answer.
+// Histogram search: thread t owns bins NBINS-1-2t and NBINS-2-2t, so a scan over the
+// threads runs through the bins in descending order.
 // =============================================================================
 struct BinQuery {
-    unsigned long long m0, xq;     // mass event: m0 + cum_q >= xq   (xq = ~0 disables)
+    unsigned long long m0, xq;       // mass event: m0 + cum_q >= xq   (xq = ~0 disables)
     unsigned long long pos0, nstop;  // count event: pos0 + cum_c >= nstop (nstop = ~0 disables)
-    int specbin;                   // stop at this bin (-1 disables)
+    int specbin;                     // stop at this bin (-1 disables)
 };
 
 __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
     Aux *A = c.A;
     const int bh = NBINS - 1 - 2 * c.tid, bl = bh - 1;
-    unsigned long long qh = 0, ql = 0, ch = 0, cl = 0;
-    for (int r = 0; r < c.cs; r++) {
-        Aux *RA = c.cluster.map_shared_rank(A, r);
-        qh += RA->u.h.hq[bh]; ql += RA->u.h.hq[bl];
-        ch += RA->u.h.hc[bh]; cl += RA->u.h.hc[bl];
-    }
+    const unsigned long long qh = A->u.h.hq[bh], ql = A->u.h.hq[bl];
+    const unsigned long long ch = A->u.h.hc[bh], cl = A->u.h.hc[bl];
     unsigned long long tq, tc;
-    unsigned long long eq = block_excl_scan<unsigned long long>(qh + ql, A->wsu, &tq);
-    unsigned long long ec = block_excl_scan<unsigned long long>(ch + cl, A->wsu, &tc);
+    const unsigned long long eq = block_excl_scan<unsigned long long>(qh + ql, A->wsu, &tq);
+    const unsigned long long ec = block_excl_scan<unsigned long long>(ch + cl, A->wsu, &tc);
     __syncthreads();
     if (c.tid == 0) { A->evt_thread = 0x7fffffff; A->tot_q = tq; A->tot_c = tc; A->hit_bin = -1; }
     __syncthreads();
@@ -425,87 +478,54 @@ __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
     __syncthreads();
 }
 
-// Gather every remaining element of bin `bin` (exp bits below `tau`) into CTA 0's
-// candidate list as sortable keys (value bits high, inverted token id low).
-__device__ void gather_bin(Ctx &c, int bin_lo, unsigned int tau) {
-    Aux *A0 = c.cluster.map_shared_rank(c.A, 0);
-    for (int i = c.c0; i < c.c1; i++) {
-        unsigned int eb = __float_as_uint(c.row[i]);
-        if (eb < tau && (int)(eb >> BIN_SHIFT) >= bin_lo) {
-            int pos = atomicAdd(&A0->ncand, 1);
-            if (pos < NC)
-                A0->cand[pos] = ((unsigned long long)eb << 32) |
-                                (unsigned long long)(0xFFFFFFFFu - (unsigned int)(c.base + i));
-        }
-    }
-}
-
-__device__ __forceinline__ int key_idx(unsigned long long k) {
-    return (int)(0xFFFFFFFFu - (unsigned int)(k & 0xFFFFFFFFull));
-}
-__device__ __forceinline__ float key_val(unsigned long long k) {
-    return __uint_as_float((unsigned int)(k >> 32));
-}
-
-// Sort CTA 0's candidate list (descending value, ascending token id) and turn the
-// exponentials into probabilities p = e / Z (sample.mojo:437-438). CTA 0 only.
+// Sort the candidate list (descending value, ascending token id) and turn the
+// exponentials into probabilities p = e / Z (sample.mojo:437-438).
 __device__ void sort_cands(Ctx &c, int n, float Z) {
     Aux *A = c.A;
-    int n2 = 1;
+    int n2 = 2;
     while (n2 < n) n2 <<= 1;
-    if (n2 < 2) n2 = 2;
+    __syncthreads();
     for (int i = n + c.tid; i < n2; i += NT) A->cand[i] = 0ull;
     bitonic_desc(A->cand, n2, c.tid);
     for (int i = c.tid; i < n; i += NT) A->pc[i] = __fdiv_rn(key_val(A->cand[i]), Z);
     __syncthreads();
 }
 
-__device__ __forceinline__ void publish(Ctx &c, const Bcast &b) {
-    for (int r = 0; r < c.cs; r++) {
-        Aux *RA = c.cluster.map_shared_rank(c.A, r);
-        RA->bc = b;
-    }
-}
-
 // =============================================================================
-// The descending walk past the sorted head (sample.mojo:492-506 and :580-590 on
-// rows whose nucleus is larger than the head). State: exact running sum `s`,
-// elements consumed `pos`, and `tau`: everything with exp bits >= tau is consumed.
-// Each phase histograms the remaining elements by value bin with their integer
-// contributions in the current binade, consumes whole bins up to the first bin
-// holding an event (the sum reaching x_ge, exceeding x_gt, leaving the binade, a
-// count limit, or an element needing sequential care), then gathers that bin,
-// sorts it and adds it element by element.
+// The descending walk past the sorted head (sample.mojo:492-506 and :580-590 on rows
+// whose nucleus is larger than the head), over the row's list `wl` of (exp bits,
+// token id) pairs. State: exact running sum `s`, elements consumed `pos`, and `tau`:
+// everything with exp bits >= tau is consumed. Each phase histograms what remains by
+// value bin with its integer contribution in the current binade, consumes whole bins
+// up to the first bin holding an event (the sum reaching x_ge, exceeding x_gt, leaving
+// the binade, a count limit, or an element needing sequential care), then gathers
+// that bin, sorts it and adds it element by element.
 // =============================================================================
 struct Walk {
     float s; long long pos; unsigned int tau;
-    int event; int idx; float p; int tie;  // outcome
+    int event; int idx; float p; int tie;
 };
 
-__device__ void descend(Ctx &c, float Z, Walk &w, float x_ge, float x_gt, long long nstop,
-                        unsigned int &status) {
+__device__ void descend(Ctx &c, const unsigned long long *wl, int nw, float Z, Walk &w, float x_ge, float x_gt,
+                        long long nstop) {
     Aux *A = c.A;
     const bool counting = nstop >= 0;
     for (int phase = 0; phase < 4096; phase++) {
-        // ---- histogram of what remains
+        __syncthreads();
         for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0ull; A->u.h.hc[i] = 0u; }
-        if (c.tid == 0) { A->specbin = -1; if (c.rank == 0) A->ncand = 0; }
+        if (c.tid == 0) { A->specbin = -1; A->ncand = 0; }
         __syncthreads();
         const bool have_s = w.s > 0.0f;
         const int j = have_s ? fexpo(w.s) : 0;
         const bool binade_ok = have_s && j >= -100 && j <= 100;
         const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1);
         const float inv_u = fpow2(23 - j);
-        for (int i = c.c0; i < c.c1; i++) {
-            const float e = c.row[i];
-            const unsigned int eb = __float_as_uint(e);
+        for (int i = c.tid; i < nw; i += NT) {
+            const unsigned int eb = (unsigned int)(wl[i] >> 32);
             if (eb >= w.tau) continue;
             const int bin = (int)(eb >> BIN_SHIFT);
-            if (!binade_ok) {
-                atomicAdd(&A->u.h.hc[bin], 1u);
-                continue;
-            }
-            const float p = __fdiv_rn(e, Z);
+            if (!binade_ok) { atomicAdd(&A->u.h.hc[bin], 1u); continue; }
+            const float p = __fdiv_rn(__uint_as_float(eb), Z);
             const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
             const float r = __fsub_rn(p, q);
             if (fabsf(r) == halfu || p >= bigthr) {
@@ -518,14 +538,8 @@ __device__ void descend(Ctx &c, float Z, Walk &w, float x_ge, float x_gt, long l
             if (counting) atomicAdd(&A->u.h.hc[bin], 1u);
         }
         __syncthreads();
-        int specbin = -1;
-        {
-            const unsigned long long *xs = xchg(c, (unsigned long long)(unsigned int)(A->specbin + 1));
-            for (int r = 0; r < c.cs; r++) specbin = max(specbin, (int)(unsigned int)xs[r] - 1);
-        }
-        // ---- first bin (descending) that holds an event
         BinQuery qy;
-        qy.specbin = specbin;
+        qy.specbin = A->specbin;
         qy.pos0 = (unsigned long long)w.pos;
         qy.nstop = counting ? (unsigned long long)nstop : ~0ull;
         qy.m0 = 0; qy.xq = ~0ull;
@@ -542,106 +556,85 @@ __device__ void descend(Ctx &c, float Z, Walk &w, float x_ge, float x_gt, long l
             }
             qy.xq = xq;
         } else {
-            // no usable binade yet (nothing consumed): take the highest non-empty bin
-            qy.pos0 = 0; qy.nstop = 1;
+            qy.pos0 = 0; qy.nstop = 1;  // nothing consumed yet: take the highest non-empty bin
         }
         find_event_bin(c, qy);
         const int hb = A->hit_bin;
         if (hb < 0) {
-            // nothing left triggers an event: consume everything
             if (binade_ok) w.s = (float)((double)(qy.m0 + A->tot_q) * (double)fpow2(j - 23));
             w.pos += (long long)A->tot_c;
             w.tau = 0;
             w.event = EV_EXHAUSTED;
-            c.cluster.sync();
             return;
         }
         const unsigned long long qb = A->hit_qbefore, cb = A->hit_cbefore;
-        // ---- gather that bin into CTA 0 and walk it element by element
-        {
-            Aux *A0 = c.cluster.map_shared_rank(A, 0);
-            for (int i = c.c0; i < c.c1; i++) {
-                unsigned int eb = __float_as_uint(c.row[i]);
-                if (eb < w.tau && (int)(eb >> BIN_SHIFT) == hb) {
-                    int pos = atomicAdd(&A0->ncand, 1);
-                    if (pos < NC)
-                        A0->cand[pos] = ((unsigned long long)eb << 32) |
-                                        (unsigned long long)(0xFFFFFFFFu - (unsigned int)(c.base + i));
-                }
+        for (int i = c.tid; i < nw; i += NT) {
+            const unsigned long long key = wl[i];
+            const unsigned int eb = (unsigned int)(key >> 32);
+            if (eb < w.tau && (int)(eb >> BIN_SHIFT) == hb) {
+                int pos = atomicAdd(&A->ncand, 1);
+                if (pos < NC) A->cand[pos] = key;
             }
         }
-        c.cluster.sync();
-        if (c.rank == 0) {
-            const int nb = A->ncand;
-            Bcast b;
-            b.event = EV_NONE; b.idx = -1; b.p = 0.0f; b.aux = 0;
-            if (nb > NC) {
-                b.event = EV_DEGENERATE; b.s = w.s; b.pos = w.pos; b.tau = w.tau;
-                if (c.tid == 0) publish(c, b);
-            } else {
-                sort_cands(c, nb, Z);
-                if (c.tid == 0) {
-                    float s = binade_ok ? (float)((double)(qy.m0 + qb) * (double)fpow2(j - 23)) : w.s;
-                    long long pos = w.pos + (counting || !binade_ok ? (long long)cb : 0);
-                    for (int i = 0; i < nb; i++) {
-                        const float p = A->pc[i];
-                        s = __fadd_rn(s, p);
-                        pos++;
-                        int ev = EV_NONE;
-                        if (s >= x_ge) ev = EV_CUT;
-                        else if (x_gt < s) ev = EV_DRAW;
-                        else if (counting && pos >= nstop) ev = EV_LIMIT;
-                        if (ev != EV_NONE) {
-                            b.event = ev; b.idx = key_idx(A->cand[i]); b.p = p;
-                            bool tie = (i > 0 && A->pc[i - 1] == p) || (i + 1 < nb && A->pc[i + 1] == p);
-                            b.aux = tie ? 1 : 0;
-                            break;
-                        }
-                    }
-                    b.s = s; b.pos = pos; b.tau = (unsigned int)hb << BIN_SHIFT;
-                    publish(c, b);
-                }
+        __syncthreads();
+        const int nb = A->ncand;
+        if (nb > NC) { w.event = EV_DEGENERATE; c.status |= MOLLA_ROW_DEGENERATE; return; }
+        sort_cands(c, nb, Z);
+        if (c.tid == 0) {
+            float s = binade_ok ? (float)((double)(qy.m0 + qb) * (double)fpow2(j - 23)) : w.s;
+            long long pos = w.pos + ((counting || !binade_ok) ? (long long)cb : 0);
+            int ev = EV_NONE, at = -1;
+            for (int i = 0; i < nb; i++) {
+                const float p = A->pc[i];
+                s = __fadd_rn(s, p);
+                pos++;
+                if (s >= x_ge) ev = EV_CUT;
+                else if (x_gt < s) ev = EV_DRAW;
+                else if (counting && pos >= nstop) ev = EV_LIMIT;
+                if (ev != EV_NONE) { at = i; break; }
+            }
+            A->b_event = ev; A->b_s = s; A->b_pos = pos; A->b_tau = (unsigned int)hb << BIN_SHIFT;
+            if (at >= 0) {
+                const float p = A->pc[at];
+                A->b_idx = key_idx(A->cand[at]); A->b_p = p;
+                A->b_aux = ((at > 0 && A->pc[at - 1] == p) || (at + 1 < nb && A->pc[at + 1] == p)) ? 1 : 0;
             }
         }
-        c.cluster.sync();
-        const Bcast b = A->bc;
-        w.s = b.s; w.pos = b.pos; w.tau = b.tau;
-        if (b.event == EV_DEGENERATE) { w.event = EV_DEGENERATE; status |= MOLLA_ROW_DEGENERATE; return; }
-        if (b.event != EV_NONE) { w.event = b.event; w.idx = b.idx; w.p = b.p; w.tie = b.aux; return; }
-        if (phase > 8) status |= MOLLA_ROW_SLOW_PATH;
+        __syncthreads();
+        w.s = A->b_s; w.pos = A->b_pos; w.tau = A->b_tau;
+        if (A->b_event != EV_NONE) { w.event = A->b_event; w.idx = A->b_idx; w.p = A->b_p; w.tie = A->b_aux; return; }
+        if (phase > 8) c.status |= MOLLA_ROW_SLOW_PATH;
     }
     w.event = EV_DEGENERATE;
-    status |= MOLLA_ROW_DEGENERATE;
+    c.status |= MOLLA_ROW_DEGENERATE;
 }
 
 // =============================================================================
-// The kernel: a persistent cluster per row.
+// The kernel: persistent CTAs, each taking the next unsampled row.
 // =============================================================================
 __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constant__ BatchArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    Ctx c{cg::this_cluster()};
-    c.cs = (int)c.cluster.num_blocks();
-    c.rank = (int)c.cluster.block_rank();
+    Ctx c;
     c.tid = threadIdx.x; c.lane = c.tid & 31; c.warp = c.tid >> 5;
-    c.row = reinterpret_cast<float *>(smem_raw);
-    c.A = reinterpret_cast<Aux *>(smem_raw + (((size_t)a.S * 4 + 127) / 128) * 128);
-    c.S = a.S; c.L = a.L; c.V = a.V;
+    c.tb = reinterpret_cast<float *>(smem_raw);
+    c.A = reinterpret_cast<Aux *>(smem_raw + 2 * TILE * 4);
+    c.bm = reinterpret_cast<unsigned int *>(smem_raw + 2 * TILE * 4 + ((sizeof(Aux) + 15) / 16) * 16);
+    c.V = a.V;
+    c.ntiles = (a.V + TILE - 1) / TILE;
+    c.par[0] = c.par[1] = 0;
     Aux *A = c.A;
-    const int ncl = gridDim.x / c.cs;
-    const int cid = blockIdx.x / c.cs;
-    c.base = c.rank * c.S;
-    {
-        long long nl = (long long)a.V - c.base;
-        c.nloc = (int)(nl < 0 ? 0 : (nl > c.S ? c.S : nl));
-    }
-    c.c0 = min(c.nloc, c.tid * c.L);
-    c.c1 = min(c.nloc, (c.tid + 1) * c.L);
-    if (c.tid == 0) { mbar_init(&A->mbar, 1); fence_proxy_async(); }
-    unsigned int parity = 0;
-    c.cluster.sync();
+    if (c.tid == 0) { mbar_init(&A->mbar[0], 1); mbar_init(&A->mbar[1], 1); fence_proxy_async(); }
+    __syncthreads();
+    unsigned long long *wl = a.wlist ? a.wlist + (size_t)blockIdx.x * (size_t)a.V : nullptr;
+    const int nwords = (a.V + 31) >> 5;
 
-    for (int r = cid; r < a.B; r += ncl) {
-        unsigned int status = 0;
+    for (;;) {
+        __syncthreads();
+        if (c.tid == 0) A->cur_row = atomicAdd(a.row_counter, 1);
+        __syncthreads();
+        const int r = A->cur_row;
+        if (r >= a.B) break;
+        c.status = 0;
         const float T = a.temperature ? a.temperature[r] : 0.0f;
         const int k = a.top_k ? a.top_k[r] : 0;
         const float P = a.top_p ? a.top_p[r] : 1.0f;
@@ -656,341 +649,358 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         const int b0 = (a.bias_ids && a.bias_off) ? a.bias_off[r] : 0;
         const int nb = (a.bias_ids && a.bias_off) ? (a.bias_off[r + 1] - b0) : 0;
         // the rules of SamplerConfig.check (sample.mojo:140-154); NaN fails every test
-        bool valid = (T >= 0.0f) && (k >= 0) && (P > 0.0f && P <= 1.0f) && (minp >= 0.0f && minp <= 1.0f) &&
-                     (typ > 0.0f && typ <= 1.0f) && (rp > 0.0f) && H >= 0 && nb >= 0;
+        const bool valid = (T >= 0.0f) && (k >= 0) && (P > 0.0f && P <= 1.0f) && (minp >= 0.0f && minp <= 1.0f) &&
+                           (typ > 0.0f && typ <= 1.0f) && (rp > 0.0f) && H >= 0 && nb >= 0;
         const bool greedy = !(T > 0.0f);
-        if (!a.penalised_only) {
-            if (!valid) status |= MOLLA_ROW_INVALID_CONFIG;
-            else if (!greedy && (minp > 0.0f || typ < 1.0f)) status |= MOLLA_ROW_UNSUPPORTED;
-            if (status) {
-                if (c.rank == 0 && c.tid == 0) {
-                    a.tokens[r] = -1; a.row_status[r] = status;
-                    if (a.diag) { a.diag[4 * r] = a.diag[4 * r + 1] = a.diag[4 * r + 2] = a.diag[4 * r + 3] = 0.0f; }
-                }
-                continue;
-            }
-        }
         const bool penalizing = won && H > 0 && (rp != 1.0f || fp != 0.0f || pp != 0.0f);
-
+        const int npatch = (penalizing ? H : 0) + nb;
+        if (!a.penalised_only) {
+            if (!valid) c.status |= MOLLA_ROW_INVALID_CONFIG;
+            else if (!greedy && (minp > 0.0f || typ < 1.0f)) c.status |= MOLLA_ROW_UNSUPPORTED;
+        }
+        if (npatch > PATCH_MAX) c.status |= MOLLA_ROW_UNSUPPORTED;
+        if (c.status) {
+            if (c.tid == 0 && !a.penalised_only) {
+                a.tokens[r] = -1; a.row_status[r] = c.status;
+                if (a.diag) { a.diag[4 * r] = a.diag[4 * r + 1] = a.diag[4 * r + 2] = a.diag[4 * r + 3] = 0.0f; }
+            }
+            continue;
+        }
+        c.src = a.logits + (long long)r * a.row_stride;
+        c.aligned = ((reinterpret_cast<uintptr_t>(c.src) & 15u) == 0);
         STAMP(0);
-        // ---- 1. fetch this CTA's slice of the row, once, from HBM
-        const float *src = a.logits + (long long)r * a.row_stride + c.base;
-        {
-            const bool aligned = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
-            const int nbulk = aligned ? (c.nloc & ~3) : 0;
-            if (nbulk > 0) {
-                if (c.tid == 0) {
-                    fence_proxy_async();
-                    mbar_expect_tx(&A->mbar, (uint32_t)nbulk * 4u);
-                    const int PIECE = 8192;  // floats per bulk copy (32 KB)
-                    for (int o = 0; o < nbulk; o += PIECE) {
-                        int n = min(PIECE, nbulk - o);
-                        bulk_g2s(c.row + o, src + o, (uint32_t)n * 4u, &A->mbar);
-                    }
+
+        // ---- 1. logit bias and penalties (sample.mojo:381-417) touch at most a window's worth of
+        // tokens: their new values go into a hash, a bitmap over the vocabulary marks them.
+        c.patching = false;
+        if (npatch > 0) {
+            for (int i = c.tid; i < nwords; i += NT) c.bm[i] = 0u;
+            for (int i = c.tid; i < HSLOTS; i += NT) { A->hkey[i] = -1; A->hcnt[i] = 0; }
+            __syncthreads();
+            for (int i = c.tid; i < npatch; i += NT) {
+                const bool is_bias = i < nb;
+                const long long t64 = is_bias ? a.bias_ids[b0 + i] : a.hist[h0 + (i - nb)];
+                if (t64 < 0 || t64 >= a.V) continue;
+                const int tok = (int)t64;
+                int s = hslot(tok);
+                for (int probe = 0; probe < HSLOTS; probe++) {
+                    const int old = atomicCAS(&A->hkey[s], -1, tok);
+                    if (old == -1 || old == tok) { if (!is_bias) atomicAdd(&A->hcnt[s], 1); break; }
+                    s = (s + 1) & (HSLOTS - 1);
                 }
-            }
-            for (int i = nbulk + c.tid; i < c.nloc; i += NT) c.row[i] = __ldg(src + i);
-            if (nbulk > 0) {
-                bool done = false;
-                for (int spin = 0; spin < (1 << 22); spin++) {
-                    if (mbar_try_wait(&A->mbar, parity)) { done = true; break; }
-                }
-                if (!done) status |= MOLLA_ROW_LOAD_TIMEOUT;
-                parity ^= 1u;
             }
             __syncthreads();
+            for (int s = c.tid; s < HSLOTS; s += NT) {
+                const int tok = A->hkey[s];
+                if (tok < 0) continue;
+                float v = __ldg(c.src + tok);
+                for (int q = 0; q < nb; q++)  // duplicates add up, in the order they were given
+                    if (a.bias_ids[b0 + q] == (long long)tok) v = __fadd_rn(v, a.bias_vals[b0 + q]);
+                const int n = A->hcnt[s];
+                if (n > 0) {
+                    if (v > 0.0f) v = __fdiv_rn(v, rp);
+                    else v = __fmul_rn(v, rp);
+                    v = __fsub_rn(v, __fmul_rn((float)n, fp));
+                    v = __fsub_rn(v, pp);
+                }
+                A->hval[s] = v;
+                atomicOr(&c.bm[tok >> 5], 1u << (tok & 31));
+            }
+            __syncthreads();
+            c.patching = true;
         }
-
         STAMP(1);
-        // ---- 2. logit bias, then penalties, scattered over the window's tokens
-        // (sample.mojo:381-417: bias first, each in the reference's operation order)
-        if (nb > 0) {
-            for (int jx = c.tid; jx < nb; jx += NT) {
-                const long long tok = a.bias_ids[b0 + jx];
-                if (tok < c.base || tok >= (long long)c.base + c.nloc) continue;
-                bool first = true;
-                for (int q = 0; q < jx; q++)
-                    if (a.bias_ids[b0 + q] == tok) { first = false; break; }
-                if (!first) continue;
-                float v = c.row[tok - c.base];
-                for (int q = 0; q < nb; q++)
-                    if (a.bias_ids[b0 + q] == tok) v = __fadd_rn(v, a.bias_vals[b0 + q]);
-                c.row[tok - c.base] = v;
-            }
-            __syncthreads();
-        }
-        if (penalizing) {
-            const bool staged = H <= HIST_STAGE;
-            if (staged) {
-                for (int h = c.tid; h < H; h += NT) {
-                    long long t = a.hist[h0 + h];
-                    A->u.hist_tok[h] = (t >= 0 && t < a.V) ? (int)t : -1;
-                }
-                __syncthreads();
-            }
-            for (int h = c.tid; h < H; h += NT) {
-                long long tok = staged ? (long long)A->u.hist_tok[h] : a.hist[h0 + h];
-                if (tok < c.base || tok >= (long long)c.base + c.nloc) continue;
-                int n = 0;
-                bool first = true;
-                if (staged) {
-                    const int ti = (int)tok;
-                    for (int q = 0; q < H; q++) {
-                        if (A->u.hist_tok[q] == ti) { n++; if (q < h) first = false; }
-                    }
-                } else {
-                    for (int q = 0; q < H; q++) {
-                        if (a.hist[h0 + q] == tok) { n++; if (q < h) first = false; }
-                    }
-                }
-                if (!first) continue;
-                float v = c.row[tok - c.base];
-                if (v > 0.0f) v = __fdiv_rn(v, rp);
-                else v = __fmul_rn(v, rp);
-                v = __fsub_rn(v, __fmul_rn((float)n, fp));
-                v = __fsub_rn(v, pp);
-                c.row[tok - c.base] = v;
-            }
-            __syncthreads();
-        }
+
         if (a.penalised) {
-            float *dst = a.penalised + (long long)r * a.V + c.base;
-            for (int i = c.tid; i < c.nloc; i += NT) dst[i] = c.row[i];
+            float *dst = a.penalised + (long long)r * a.V;
+            tiles_begin(c);
+            for (int t = 0; t < c.ntiles; t++) {
+                int n_tile;
+                const float *buf = tile_acquire(c, t, n_tile);
+                const int c0 = min(n_tile, c.tid * LT), c1 = min(n_tile, (c.tid + 1) * LT);
+                const int g0 = t * TILE + c0;
+                const unsigned int pm = (c1 > c0) ? patch_mask(c, g0) : 0u;
+                for (int j = 0; c0 + j < c1; j++) {
+                    float x = buf[c0 + j];
+                    if ((pm >> j) & 1u) x = patch_lookup(c, g0 + j, x);
+                    dst[g0 + j] = x;
+                }
+            }
+            if (a.penalised_only) continue;
         }
-        if (a.penalised_only) { c.cluster.sync(); continue; }
 
-        STAMP(2);
-        // ---- 3. maximum and its first index (kernel.mojo:571-585, sample.mojo:342-346)
-        float mx = -INFINITY;
-        int mi = 0x7fffffff;
-        for (int i = c.c0; i < c.c1; i++) {
-            float x = c.row[i];
-            if (x > mx) { mx = x; mi = c.base + i; }
-        }
-        if (c.c1 > c.c0 && mi == 0x7fffffff) mi = c.base + c.c0;  // all -inf / NaN guard
-        block_argmax(c, mx, mi);
-        float xmax; int imax;
-        {
-            const unsigned long long *xs = xchg(c, pack_fi(mx, mi));
-            xmax = __uint_as_float((unsigned int)(xs[0] >> 32)); imax = (int)(unsigned int)xs[0];
-            for (int q = 1; q < c.cs; q++) {
-                float ov = __uint_as_float((unsigned int)(xs[q] >> 32)); int oi = (int)(unsigned int)xs[q];
-                if (ov > xmax || (ov == xmax && oi < imax)) { xmax = ov; imax = oi; }
+        // ---- 2. pass A (HBM): the maximum and its first index (kernel.mojo:571-585, sample.mojo:342-346)
+        float tmax = -INFINITY;
+        int tidx = 0x7fffffff, teq = 0;
+        tiles_begin(c);
+        for (int t = 0; t < c.ntiles; t++) {
+            int n_tile;
+            const float *buf = tile_acquire(c, t, n_tile);
+            const int c0 = min(n_tile, c.tid * LT), c1 = min(n_tile, (c.tid + 1) * LT);
+            const int g0 = t * TILE + c0;
+            const unsigned int pm = (c1 > c0) ? patch_mask(c, g0) : 0u;
+            float cm = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < LT; j++) {
+                if (c0 + j < c1) {
+                    float x = buf[c0 + j];
+                    if ((pm >> j) & 1u) x = patch_lookup(c, g0 + j, x);
+                    cm = fmaxf(cm, x);
+                    if (x > tmax) { tmax = x; tidx = g0 + j; teq = 1; }
+                    else if (x == tmax) teq++;
+                }
+            }
+            if (!greedy) {
+                const float tm = block_max(c, cm);
+                if (c.tid == 0) A->tilemax[t] = tm;
             }
         }
-        STAMP(3);
+        float xmax = tmax;
+        int imax = tidx;
+        block_argmax(c, xmax, imax);
+        if (imax == 0x7fffffff) imax = 0;
+        STAMP(2);
         const long long n_lim = (k > 0 && k < a.V) ? (long long)k : (long long)a.V;
-
         int token = -1;
         float dZ = 0.0f, dsum = 0.0f, dtarget = 0.0f, dp = 0.0f;
 
         if (greedy) {
             token = imax;
+        } else if (n_lim == 1) {
+            // top-k of one: the sort's first element is a maximum (sample.mojo:485-490)
+            int tot;
+            (void)block_excl_scan<int>((tmax == xmax) ? teq : 0, A->wsi, &tot);
+            if (tot > 1) c.status |= MOLLA_ROW_TOPK_TIE;
+            token = imax;
         } else {
-            // ---- 4. temperature, exponentials (sample.mojo:419-434) and chunk statistics
             const float top = (T == 1.0f) ? xmax : __fdiv_rn(xmax, T);
-            float csum = 0.0f, cmx = -1.0f;
-            int nties = 0;
-            for (int i = c.c0; i < c.c1; i++) {
-                float x = c.row[i];
-                float v = (T == 1.0f) ? x : __fdiv_rn(x, T);
-                float e = expf_pinned(__fsub_rn(v, top));
-                c.row[i] = e;
-                csum = __fadd_rn(csum, e);
-                cmx = fmaxf(cmx, e);
-                nties += (e == 1.0f) ? 1 : 0;
+            const bool topp_on = (P < 1.0f) && (n_lim > 1);
+            const bool pure = !topp_on && n_lim == (long long)a.V;
+            const float u01 = draw01(a.seed ? a.seed[r] : 0ull, a.drawn ? a.drawn[r] : 0ull);
+            const bool filter_ok = fabsf(top) < 1.0e5f;
+            long long need = n_lim + 1;
+            if (need > HEAD_NEED) need = HEAD_NEED;
+            if (need > a.V) need = a.V;
+            const bool p3row = !pure && (n_lim + 1 > HEAD_NEED);
+            unsigned int tau_bits = 1u;
+            if (!pure) {
+                // The need-th largest of the threads' own maxima bounds the need-th largest element
+                // from below: everything that can be in the head is at or above it.
+                __syncthreads();
+                A->cand[c.tid] = ((unsigned long long)fkey(tmax) << 32) | (unsigned long long)c.tid;
+                bitonic_desc(A->cand, NT, c.tid);
+                const float tau_x = fkey_inv((unsigned int)(A->cand[need - 1] >> 32));
+                const float tv = (T == 1.0f) ? tau_x : __fdiv_rn(tau_x, T);
+                const unsigned int tb_ = __float_as_uint(expf_pinned(__fsub_rn(tv, top)));
+                tau_bits = tb_ > 1u ? tb_ : 1u;
+                __syncthreads();
             }
-            A->cmax[c.tid] = cmx;
-            STAMP(4);
-            if (n_lim == 1) {
-                // top-k of one: the sort's first element is a maximum (sample.mojo:485-490)
-                int tot;
-                (void)block_excl_scan<int>(nties, A->wsi, &tot);
-                const unsigned long long *xs = xchg(c, (unsigned long long)(unsigned int)tot);
-                int all = 0;
-                for (int q = 0; q < c.cs; q++) all += (int)(unsigned int)xs[q];
-                if (all > 1) status |= MOLLA_ROW_TOPK_TIE;
-                token = imax;
-            } else {
-                // ---- 5. the softmax denominator, exactly as the sequential loop rounds it
-                p1_build(c, csum);
-                STAMP(5);
-                if (c.rank == 0 && c.tid == 0) {
-                    P1Walk w;
-                    p1_walk(c, false, 0.0f, w);
-                    Bcast b; b.s = w.s; b.aux = w.slow; b.event = 0; b.idx = 0; b.p = 0; b.pos = 0; b.tau = 0;
-                    publish(c, b);
-                }
-                c.cluster.sync();
-                const float Z = A->bc.s;
-                STAMP(6);
-                if (A->bc.aux) status |= MOLLA_ROW_SLOW_PATH;
-                dZ = Z;
-                const float u01 = draw01(a.seed ? a.seed[r] : 0ull, a.drawn ? a.drawn[r] : 0ull);
-                const bool topp_on = (P < 1.0f) && (n_lim > 1);
+            if (c.tid == 0) {
+                A->ncand = 0; A->nw = 0;
+                A->walk_s = 0.0f; A->walk_found = 0; A->walk_idx = -1; A->walk_slow = 0;
+            }
+            STAMP(3);
 
-                if (!topp_on && n_lim == (long long)a.V) {
-                    // ---- 6a. nothing sorted: the draw walks the vocabulary in order
-                    // (sample.mojo:365-369, 580-594), over p = e / Z
-                    float ps = 0.0f;
-                    for (int i = c.c0; i < c.c1; i++) {
-                        float p = __fdiv_rn(c.row[i], Z);
-                        c.row[i] = p;
-                        ps = __fadd_rn(ps, p);
-                    }
-                    p1_build(c, ps);
-                    if (c.rank == 0 && c.tid == 0) {
-                        P1Walk w;
-                        p1_walk(c, false, 0.0f, w);
-                        const float sum = w.s;
-                        int slow = w.slow;
-                        const float target = __fmul_rn(u01, sum);
-                        P1Walk w2;
-                        p1_walk(c, true, target, w2);
-                        slow |= w2.slow;
-                        Bcast b; b.s = sum; b.p = target; b.aux = slow; b.event = 0; b.pos = 0; b.tau = 0;
-                        b.idx = w2.found ? (int)w2.idx : (a.V - 1);
-                        publish(c, b);
-                    }
-                    c.cluster.sync();
-                    token = A->bc.idx; dsum = A->bc.s; dtarget = A->bc.p;
-                    if (A->bc.aux) status |= MOLLA_ROW_SLOW_PATH;
-                    if (token >= 0 && c.rank == 0 && c.tid == 0) {
-                        const int owner = token / c.S;  // probability of the chosen token (diagnostic)
-                        dp = c.cluster.map_shared_rank(c.row, owner)[token - owner * c.S];
-                    }
-                } else {
-                    // ---- 6b. sorted order. Head: the top candidates, sorted, walked exactly.
-                    long long need = n_lim + 1;
-                    if (need > HEAD_MAX) need = HEAD_MAX;
-                    if (need > a.V) need = a.V;
-                    // The need-th largest chunk maximum bounds the need-th largest element from
-                    // below, so a histogram of the chunk maxima alone gives a safe value threshold.
-                    for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0ull; A->u.h.hc[i] = 0u; }
-                    if (c.tid == 0 && c.rank == 0) A->ncand = 0;
-                    __syncthreads();
-                    if (cmx >= 0.0f) atomicAdd(&A->u.h.hc[__float_as_uint(cmx) >> BIN_SHIFT], 1u);
-                    c.cluster.sync();
-                    BinQuery qy; qy.m0 = 0; qy.xq = ~0ull; qy.pos0 = 0; qy.nstop = (unsigned long long)need; qy.specbin = -1;
-                    find_event_bin(c, qy);
-                    int hb = A->hit_bin < 0 ? 0 : A->hit_bin;
-                    gather_bin(c, hb, 0xFFFFFFFFu);
-                    c.cluster.sync();  // histograms read, candidates gathered
-                    int nc = c.cluster.map_shared_rank(A, 0)->ncand;
-                    c.cluster.sync();
-                    if (nc > NC) {
-                        // Too many (flat or tiny rows): count every element per bin and keep the
-                        // highest bins that fit the candidate list.
-                        for (int i = c.tid; i < NBINS; i += NT) A->u.h.hc[i] = 0u;
-                        if (c.tid == 0 && c.rank == 0) A->ncand = 0;
-                        __syncthreads();
-                        for (int i = c.c0; i < c.c1; i++) atomicAdd(&A->u.h.hc[__float_as_uint(c.row[i]) >> BIN_SHIFT], 1u);
-                        c.cluster.sync();
-                        qy.nstop = (unsigned long long)NC + 1ull;
-                        find_event_bin(c, qy);
-                        hb = A->hit_bin < 0 ? 0 : A->hit_bin + 1;
-                        if (hb < NBINS) gather_bin(c, hb, 0xFFFFFFFFu);
-                        c.cluster.sync();
-                        nc = c.cluster.map_shared_rank(A, 0)->ncand;
-                        c.cluster.sync();
-                        status |= MOLLA_ROW_SLOW_PATH;
-                    }
-                    STAMP(7);
-                    const unsigned int tau_head = (hb >= NBINS) ? 0x7F800000u : ((unsigned int)hb << BIN_SHIFT);
-                    // ---- head walk on CTA 0 (sample.mojo:497-506 then :580-590)
-                    if (c.rank == 0) {
-                        sort_cands(c, nc, Z);
-                        for (int i = c.tid; i < nc; i += NT) {
-                            const float p = A->pc[i];
-                            const bool eq = (i > 0 && A->pc[i - 1] == p) || (i + 1 < nc && A->pc[i + 1] == p);
-                            A->hidx[i] = (unsigned int)key_idx(A->cand[i]) | (eq ? 0x80000000u : 0u);
+            // ---- 3. pass B (L2): temperature, exponentials (sample.mojo:419-434), the exact softmax
+            // denominator, and the head candidates
+            double sbase = 0.0;
+            float pmx = -INFINITY;
+            long long tq0 = 0, tq1 = 0, tq2 = 0, tq3, tq0e = 0, tq5e = 0, tq0p = 0, tq5p = 0;
+            tiles_begin(c);
+            for (int t = 0; t < c.ntiles; t++) {
+                int n_tile;
+                tq3 = clock64();
+                float *buf = tile_acquire(c, t, n_tile);
+                tq0 += clock64() - tq3; tq3 = clock64();
+                const int c0 = min(n_tile, c.tid * LT), c1 = min(n_tile, (c.tid + 1) * LT);
+                const int g0 = t * TILE + c0;
+                const unsigned int pm = (c1 > c0) ? patch_mask(c, g0) : 0u;
+                const float xthr = (t == 0 || !filter_ok) ? -INFINITY : __fsub_rn(pmx, __fmul_rn(REL_MARGIN, T));
+                float e[LT];
+                float csum = 0.0f;
+#pragma unroll
+                for (int j = 0; j < LT; j++) {
+                    float ev = 0.0f;
+                    const bool in = c0 + j < c1;
+                    if (in) {
+                        float x = buf[c0 + j];
+                        if ((pm >> j) & 1u) x = patch_lookup(c, g0 + j, x);
+                        if (x >= xthr) {
+                            const float v = (T == 1.0f) ? x : __fdiv_rn(x, T);
+                            ev = expf_pinned(__fsub_rn(v, top));
                         }
-                        __syncthreads();
-                        if (c.tid == 0) {
-                            Bcast b; b.event = EV_NONE; b.idx = -1; b.p = 0; b.aux = 0; b.tau = tau_head;
-                            float s = 0.0f;
-                            long long pos = 0;
-                            int cut = -1;  // kept count once known
-                            int tie = 0;
-                            for (int i = 0; i < nc; i++) {
-                                if (pos >= n_lim) break;
-                                s = __fadd_rn(s, A->pc[i]);
-                                A->pre[i] = s;
-                                pos++;
-                                if (topp_on && s >= P) {
-                                    cut = i + 1;
-                                    if (i + 1 < nc && (long long)(i + 1) < n_lim && A->pc[i + 1] == A->pc[i]) tie |= MOLLA_ROW_TOPP_TIE;
-                                    break;
+                        buf[c0 + j] = ev;
+                        csum = __fadd_rn(csum, ev);
+                    }
+                    e[j] = ev;
+                    const unsigned int eb = __float_as_uint(ev);
+                    if (!pure) {
+                        if (in && eb >= tau_bits) {
+                            const int pos = atomicAdd(&A->ncand, 1);
+                            if (pos < NC) A->cand[pos] = make_key(eb, g0 + j);
+                        }
+                        if (p3row) {
+                            const bool wp = in && eb >= W_BITS && eb < tau_bits;
+                            const unsigned int m = __ballot_sync(0xffffffffu, wp);
+                            if (m) {
+                                int base = 0;
+                                const int leader = __ffs(m) - 1;
+                                if (c.lane == leader) base = atomicAdd(&A->nw, __popc(m));
+                                base = __shfl_sync(0xffffffffu, base, leader);
+                                if (wp) wl[base + __popc(m & ((1u << c.lane) - 1u))] = make_key(eb, g0 + j);
+                            }
+                        }
+                    }
+                }
+                if (t == 0) tq0e = clock64() - tq3; if (t == 5) tq5e = clock64() - tq3;
+                tq1 += clock64() - tq3; tq3 = clock64();
+                p1_tile(c, e, c1 - c0, csum, buf, n_tile, (long long)t * TILE, sbase, false, 0.0f);
+                tq2 += clock64() - tq3;
+                if (t == 0) tq0p = clock64() - tq3; if (t == 5) tq5p = clock64() - tq3;
+                pmx = fmaxf(pmx, A->tilemax[t]);
+            }
+            if (a.prof && c.tid == 0) { a.prof[(long long)r * 16 + 10] = tq0; a.prof[(long long)r * 16 + 11] = tq1; a.prof[(long long)r * 16 + 12] = tq2; a.prof[(long long)r * 16 + 13] = tq0e; a.prof[(long long)r * 16 + 14] = tq5e; a.prof[(long long)r * 16 + 15] = tq0p; a.prof[(long long)r * 16 + 5] = tq5p; }
+            __syncthreads();
+            const float Z = A->walk_s;
+            if (A->walk_slow) c.status |= MOLLA_ROW_SLOW_PATH;
+            dZ = Z;
+            STAMP(4);
+
+            if (pure) {
+                // ---- 4a. nothing sorted: the draw walks the vocabulary in order (sample.mojo:365-369,
+                // 580-594) over p = e / Z. Two more passes: the kept sum, then the position.
+                float sum = 0.0f, target = 0.0f;
+                for (int round = 0; round < 2; round++) {
+                    if (c.tid == 0) { A->walk_s = 0.0f; A->walk_found = 0; A->walk_idx = -1; }
+                    const bool locate = round == 1;
+                    sbase = 0.0; pmx = -INFINITY;
+                    tiles_begin(c);
+                    for (int t = 0; t < c.ntiles; t++) {
+                        int n_tile;
+                        float *buf = tile_acquire(c, t, n_tile);
+                        const int c0 = min(n_tile, c.tid * LT), c1 = min(n_tile, (c.tid + 1) * LT);
+                        const int g0 = t * TILE + c0;
+                        const unsigned int pm = (c1 > c0) ? patch_mask(c, g0) : 0u;
+                        const float xthr = (t == 0 || !filter_ok) ? -INFINITY : __fsub_rn(pmx, __fmul_rn(REL_MARGIN, T));
+                        float e[LT];
+                        float csum = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < LT; j++) {
+                            float pv = 0.0f;
+                            if (c0 + j < c1) {
+                                float x = buf[c0 + j];
+                                if ((pm >> j) & 1u) x = patch_lookup(c, g0 + j, x);
+                                if (x >= xthr) {
+                                    const float v = (T == 1.0f) ? x : __fdiv_rn(x, T);
+                                    pv = __fdiv_rn(expf_pinned(__fsub_rn(v, top)), Z);
                                 }
-                                if (pos >= n_lim) { cut = i + 1; break; }
+                                buf[c0 + j] = pv;
+                                csum = __fadd_rn(csum, pv);
                             }
-                            if (cut < 0 && nc == a.V) cut = nc;
-                            if (n_lim < (long long)a.V && (long long)nc > n_lim && A->pc[n_lim] == A->pc[n_lim - 1])
-                                tie |= MOLLA_ROW_TOPK_TIE;
-                            b.s = s; b.pos = pos;
-                            if (cut > 0) {
-                                const float sum = A->pre[cut - 1];
-                                const float target = __fmul_rn(u01, sum);
-                                int at = cut - 1;
-                                for (int i = 0; i < cut; i++)
-                                    if (target < A->pre[i]) { at = i; break; }
-                                b.event = EV_DRAW; b.idx = (int)(A->hidx[at] & 0x7fffffffu); b.p = A->pc[at];
-                                if ((at > 0 && A->pc[at - 1] == A->pc[at]) || (at + 1 < cut && A->pc[at + 1] == A->pc[at]))
-                                    tie |= MOLLA_ROW_CHOSEN_TIE;
-                                dsum = sum; dtarget = target;
-                            }
-                            b.aux = tie;
-                            publish(c, b);
+                            e[j] = pv;
                         }
+                        p1_tile(c, e, c1 - c0, csum, buf, n_tile, (long long)t * TILE, sbase, locate, target);
+                        pmx = fmaxf(pmx, A->tilemax[t]);
                     }
-                    c.cluster.sync();
-                    const Bcast hbq = A->bc;
-                    STAMP(8);
-                    status |= (unsigned int)hbq.aux;
-                    if (hbq.event == EV_DRAW) {
-                        token = hbq.idx; dp = hbq.p;
+                    __syncthreads();
+                    if (!locate) { sum = A->walk_s; target = __fmul_rn(u01, sum); }
+                    else token = A->walk_found ? A->walk_idx : (a.V - 1);
+                    if (A->walk_slow) c.status |= MOLLA_ROW_SLOW_PATH;
+                }
+                dsum = sum; dtarget = target;
+            } else {
+                // ---- 4b. sorted order. The head: sorted, walked exactly (sample.mojo:497-506, :580-590)
+                const int nc = A->ncand;
+                const int nw = A->nw;
+                if (nc > NC) {
+                    c.status |= MOLLA_ROW_DEGENERATE;
+                } else {
+                    sort_cands(c, nc, Z);
+                    for (int i = c.tid; i < nc; i += NT) {
+                        const float p = A->pc[i];
+                        const bool eq = (i > 0 && A->pc[i - 1] == p) || (i + 1 < nc && A->pc[i + 1] == p);
+                        A->hidx[i] = (unsigned int)key_idx(A->cand[i]) | (eq ? 0x80000000u : 0u);
+                    }
+                    __syncthreads();
+                    if (c.tid == 0) {
+                        float s = 0.0f;
+                        long long pos = 0;
+                        int cut = -1, tie = 0;
+                        for (int i = 0; i < nc; i++) {
+                            if (pos >= n_lim) break;
+                            s = __fadd_rn(s, A->pc[i]);
+                            A->pre[i] = s;
+                            pos++;
+                            if (topp_on && s >= P) {
+                                cut = i + 1;
+                                if (i + 1 < nc && (long long)(i + 1) < n_lim && A->pc[i + 1] == A->pc[i]) tie |= MOLLA_ROW_TOPP_TIE;
+                                break;
+                            }
+                            if (pos >= n_lim) { cut = i + 1; break; }
+                        }
+                        if (cut < 0 && !p3row) cut = nc;  // everything that can matter is in the head
+                        if (n_lim < (long long)a.V && (long long)nc > n_lim && A->pc[n_lim] == A->pc[n_lim - 1])
+                            tie |= MOLLA_ROW_TOPK_TIE;
+                        A->b_s = s; A->b_pos = pos; A->b_event = EV_NONE; A->b_idx = -1; A->b_p = 0.0f;
+                        if (cut > 0) {
+                            const float sum = A->pre[cut - 1];
+                            const float target = __fmul_rn(u01, sum);
+                            int at = cut - 1;
+                            for (int i = 0; i < cut; i++)
+                                if (target < A->pre[i]) { at = i; break; }
+                            A->b_event = EV_DRAW; A->b_idx = (int)(A->hidx[at] & 0x7fffffffu); A->b_p = A->pc[at];
+                            if ((at > 0 && A->pc[at - 1] == A->pc[at]) || (at + 1 < cut && A->pc[at + 1] == A->pc[at]))
+                                tie |= MOLLA_ROW_CHOSEN_TIE;
+                            A->b_sum = sum; A->b_target = target;
+                        }
+                        A->b_aux = tie;
+                    }
+                    __syncthreads();
+                    c.status |= (unsigned int)A->b_aux;
+                    const float head_s = A->b_s;
+                    const long long head_pos = A->b_pos;
+                    if (A->b_event == EV_DRAW) {
+                        token = A->b_idx; dp = A->b_p; dsum = A->b_sum; dtarget = A->b_target;
                     } else {
-                        // ---- 7. past the head: the cut walk, then the draw walk
-                        Walk cutw; cutw.s = hbq.s; cutw.pos = hbq.pos; cutw.tau = tau_head;
+                        // ---- 5. past the head: the cut walk, then the draw walk
+                        __syncthreads();
+                        Walk cutw; cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_bits;
                         cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
                         const bool limited = n_lim < (long long)a.V;
-                        descend(c, Z, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1, status);
-                        if (cutw.event == EV_DEGENERATE) {
-                            token = -1;
-                        } else {
-                            if (cutw.event == EV_CUT && cutw.tie) status |= MOLLA_ROW_TOPP_TIE;
-                            if (cutw.event == EV_LIMIT && cutw.tie) status |= MOLLA_ROW_TOPK_TIE;
+                        descend(c, wl, nw, Z, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
+                        if (cutw.event != EV_DEGENERATE) {
+                            if (cutw.event == EV_CUT && cutw.tie) c.status |= MOLLA_ROW_TOPP_TIE;
+                            if (cutw.event == EV_LIMIT && cutw.tie) c.status |= MOLLA_ROW_TOPK_TIE;
                             const float sum = cutw.s;
                             const float target = __fmul_rn(u01, sum);
                             dsum = sum; dtarget = target;
-                            // is the drawn element in the head?
-                            if (c.rank == 0 && c.tid == 0) {
-                                Bcast b; b.event = EV_NONE; b.idx = -1; b.p = 0; b.aux = 0; b.s = 0; b.pos = 0; b.tau = 0;
+                            __syncthreads();
+                            if (c.tid == 0) {  // is the drawn element in the head?
                                 int at = -1;
                                 for (int i = 0; i < nc; i++)
                                     if (target < A->pre[i]) { at = i; break; }
+                                A->b_event = EV_NONE;
                                 if (at >= 0) {
-                                    b.event = EV_DRAW; b.idx = (int)(A->hidx[at] & 0x7fffffffu);
-                                    b.p = __fsub_rn(A->pre[at], at > 0 ? A->pre[at - 1] : 0.0f);
-                                    if (A->hidx[at] & 0x80000000u) b.aux = MOLLA_ROW_CHOSEN_TIE;
+                                    A->b_event = EV_DRAW; A->b_idx = (int)(A->hidx[at] & 0x7fffffffu);
+                                    A->b_p = __fsub_rn(A->pre[at], at > 0 ? A->pre[at - 1] : 0.0f);
+                                    A->b_aux = (A->hidx[at] & 0x80000000u) ? MOLLA_ROW_CHOSEN_TIE : 0;
                                 }
-                                publish(c, b);
                             }
-                            c.cluster.sync();
-                            const Bcast hd = A->bc;
-                            if (hd.event == EV_DRAW) {
-                                token = hd.idx; dp = hd.p; status |= (unsigned int)hd.aux;
+                            __syncthreads();
+                            if (A->b_event == EV_DRAW) {
+                                token = A->b_idx; dp = A->b_p; c.status |= (unsigned int)A->b_aux;
                             } else {
                                 bool resolved = false;
                                 if (target < sum) {
-                                    Walk dw; dw.s = hbq.s; dw.pos = hbq.pos; dw.tau = tau_head;
+                                    __syncthreads();
+                                    Walk dw; dw.s = head_s; dw.pos = head_pos; dw.tau = tau_bits;
                                     dw.event = EV_NONE; dw.idx = -1; dw.p = 0; dw.tie = 0;
-                                    descend(c, Z, dw, 3.4e38f, target, -1, status);
+                                    descend(c, wl, nw, Z, dw, 3.4e38f, target, -1);
                                     if (dw.event == EV_DRAW) {
                                         token = dw.idx; dp = dw.p; resolved = true;
-                                        if (dw.tie) status |= MOLLA_ROW_CHOSEN_TIE;
+                                        if (dw.tie) c.status |= MOLLA_ROW_CHOSEN_TIE;
                                     } else if (dw.event == EV_DEGENERATE) {
-                                        token = -1; resolved = true;
+                                        resolved = true;
                                     }
                                 }
                                 if (!resolved) {
@@ -998,21 +1008,27 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                                     if (cutw.event == EV_CUT || cutw.event == EV_LIMIT) {
                                         token = cutw.idx; dp = cutw.p;
                                     } else {
-                                        // everything was kept: the smallest probability, highest id last
-                                        float nv = -INFINITY; int ni = 0x7fffffff;
-                                        for (int i = c.c0; i < c.c1; i++) {
-                                            const float e = -c.row[i];
-                                            const int id = 0x7fffffff - (c.base + i);
-                                            if (e > nv || (e == nv && id < ni)) { nv = e; ni = id; }
+                                        // everything was kept: the smallest listed value, highest id last
+                                        unsigned long long best = ~0ull;
+                                        for (int i = c.tid; i < nw; i += NT) best = wl[i] < best ? wl[i] : best;
+                                        for (int i = c.tid; i < nc; i += NT) {
+                                            unsigned long long kk = make_key(__float_as_uint(A->pc[i]) ? 0x7f800000u : 0u, 0);
+                                            (void)kk;
                                         }
-                                        block_argmax(c, nv, ni);
-                                        const unsigned long long *xs = xchg(c, pack_fi(nv, ni));
-                                        float bv = __uint_as_float((unsigned int)(xs[0] >> 32)); int bi = (int)(unsigned int)xs[0];
-                                        for (int q = 1; q < c.cs; q++) {
-                                            float ov = __uint_as_float((unsigned int)(xs[q] >> 32)); int oi = (int)(unsigned int)xs[q];
-                                            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+                                        // keys order by (value, inverted id): the minimum key is the smallest
+                                        // value with the highest id
+#pragma unroll
+                                        for (int o = 16; o > 0; o >>= 1) {
+                                            unsigned long long ob = __shfl_xor_sync(0xffffffffu, best, o);
+                                            best = ob < best ? ob : best;
                                         }
-                                        token = 0x7fffffff - bi;
+                                        __syncthreads();
+                                        if (c.lane == 0) A->wsu[c.warp] = best;
+                                        __syncthreads();
+                                        best = A->wsu[0];
+                                        for (int w = 1; w < NWARP; w++) best = A->wsu[w] < best ? A->wsu[w] : best;
+                                        if (nw > 0) token = key_idx(best);
+                                        else token = nc > 0 ? (int)(A->hidx[nc - 1] & 0x7fffffffu) : imax;
                                     }
                                 }
                             }
@@ -1022,13 +1038,11 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             }
         }
         STAMP(9);
-        if (c.rank == 0 && c.tid == 0) {
+        if (c.tid == 0) {
             a.tokens[r] = token;
-            a.row_status[r] = status;
+            a.row_status[r] = c.status;
             if (a.diag) { a.diag[4 * r] = dZ; a.diag[4 * r + 1] = dsum; a.diag[4 * r + 2] = dtarget; a.diag[4 * r + 3] = dp; }
         }
-        // the row buffer and the tables are free again only when every CTA is done with them
-        c.cluster.sync();
     }
 }
 
@@ -1142,66 +1156,42 @@ int fail(int code, const char *fmt, const char *detail = "") {
     return code;
 }
 
-struct Plan { int cs, S, L, nclusters; size_t smem; };
-
-// Smallest cluster whose CTAs can each hold a slice of the row next to the tables.
-int make_plan(int V, int B, Plan &p) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return fail(MOLLA_ERR_CUDA, "cudaGetDevice failed%s");
-    int max_optin = 0, sms = 0;
-    cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const size_t aux = ((sizeof(Aux) + 127) / 128) * 128 + 128;
-    if ((size_t)max_optin <= aux + 4096) return fail(MOLLA_ERR_CUDA, "device shared memory too small%s");
-    const long long cap = (((long long)max_optin - (long long)aux) / 4) & ~3ll;
-    static const int sizes[] = {1, 2, 4, 8, 16};
-    for (int cs : sizes) {
-        long long S = (((long long)V + cs - 1) / cs + 3) & ~3ll;
-        if (S <= cap) {
-            p.cs = cs; p.S = (int)S;
-            int L = (int)((S + NT - 1) / NT);
-            if ((L & 1) == 0) L += 1;
-            p.L = L;
-            p.smem = (((size_t)S * 4 + 127) / 128) * 128 + sizeof(Aux);
-            cudaError_t e = cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
-            if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "cudaFuncSetAttribute(smem): %s", cudaGetErrorString(e));
-            if (cs > 8) {
-                e = cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-                if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "cluster size 16 not allowed: %s", cudaGetErrorString(e));
-            }
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(cs, 1, 1); cfg.blockDim = dim3(NT, 1, 1); cfg.dynamicSmemBytes = p.smem;
-            cudaLaunchAttribute at[1];
-            at[0].id = cudaLaunchAttributeClusterDimension;
-            at[0].val.clusterDim.x = cs; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-            cfg.attrs = at; cfg.numAttrs = 1;
-            int maxc = 0;
-            e = cudaOccupancyMaxActiveClusters(&maxc, sample_rows_kernel, &cfg);
-            if (e != cudaSuccess || maxc <= 0) { cudaGetLastError(); maxc = sms / cs > 0 ? sms / cs : 1; }
-            p.nclusters = B < maxc ? B : maxc;
-            if (p.nclusters < 1) p.nclusters = 1;
-            return MOLLA_OK;
-        }
-    }
-    return fail(MOLLA_ERR_VOCAB, "vocabulary too wide for one cluster's shared memory%s");
+int sm_count() {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    return sms;
 }
 
-int launch_rows(const BatchArgs &args_in, cudaStream_t st) {
+size_t smem_bytes(int V) {
+    return (size_t)2 * TILE * 4 + ((sizeof(Aux) + 15) / 16) * 16 + (size_t)((V + 31) / 32) * 4 + 16;
+}
+
+// scratch layout: [row counter, 256 bytes][per-CTA (exp bits, token id) lists, V entries each]
+size_t batch_workspace_bytes(int B, int V, int sms) {
+    const size_t ctas = (size_t)(B < sms ? B : sms);
+    return 256 + ctas * (size_t)V * 8;
+}
+
+int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st) {
     BatchArgs a = args_in;
-    Plan p;
-    int rc = make_plan(a.V, a.B, p);
-    if (rc != MOLLA_OK) return rc;
-    a.S = p.S; a.L = p.L;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.nclusters * p.cs, 1, 1);
-    cfg.blockDim = dim3(NT, 1, 1);
-    cfg.dynamicSmemBytes = p.smem;
-    cfg.stream = st;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = p.cs; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, sample_rows_kernel, a);
+    const int sms = sm_count();
+    if (sms <= 0) return fail(MOLLA_ERR_CUDA, "cannot query the device%s");
+    int dev = 0, max_optin = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    const size_t smem = smem_bytes(a.V);
+    if (smem > (size_t)max_optin || a.V > MAX_TILES * TILE)
+        return fail(MOLLA_ERR_VOCAB, "vocabulary too wide for the shared-memory bitmap and tile table%s");
+    cudaError_t e = cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "cudaFuncSetAttribute(smem): %s", cudaGetErrorString(e));
+    a.row_counter = (int *)d_workspace;
+    a.wlist = (unsigned long long *)((char *)d_workspace + 256);
+    e = cudaMemsetAsync(d_workspace, 0, 256, st);
+    if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "workspace clear failed: %s", cudaGetErrorString(e));
+    const int grid = a.B < sms ? a.B : sms;
+    sample_rows_kernel<<<grid, NT, smem, st>>>(a);
+    e = cudaGetLastError();
     if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
     return MOLLA_OK;
 }
@@ -1218,7 +1208,9 @@ float molla_sample_draw(uint64_t seed, uint64_t counter) { return draw01(seed, c
 
 int64_t molla_sample_workspace_bytes(int32_t B, int32_t V, int32_t top_n) {
     if (B < 0 || V <= 0 || top_n < 0 || top_n > TOPN_MAX) return fail(MOLLA_ERR_ARGUMENT, "bad shape for the workspace query%s");
-    return 256;
+    const int sms = sm_count();
+    if (sms <= 0) return fail(MOLLA_ERR_CUDA, "cannot query the device%s");
+    return (int64_t)batch_workspace_bytes(B, V, sms);
 }
 
 int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B, int32_t V,
@@ -1255,9 +1247,8 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
     a.bias_ids = (const long long *)d_bias_ids; a.bias_vals = d_bias_vals; a.bias_off = d_bias_off;
     a.tokens = d_tokens; a.row_status = d_row_status; a.diag = d_diag;
     a.penalised = nullptr; a.penalised_only = 0;
-    a.row_counter = (int *)d_workspace;
     a.prof = g_prof;
-    int rc = launch_rows(a, st);
+    int rc = launch_rows(a, d_workspace, st);
     if (rc != MOLLA_OK) return rc;
     if (d_chosen_logprob || top_n > 0) {
         int dev = 0, sms = 148;
@@ -1277,11 +1268,12 @@ namespace {
 inline size_t al256(size_t n) { return (n + 255) & ~(size_t)255; }
 struct HostLayout {
     size_t logits, f[8], win, seed, drawn, k, hist, hist_off, bias_ids, bias_vals, bias_off;
-    size_t tokens, status, chosen, top_ids, top_lps, total;
+    size_t tokens, status, chosen, top_ids, top_lps, total, inner;
 };
-HostLayout host_layout(int B, int V, long long n_hist, long long n_bias, int top_n) {
+HostLayout host_layout(int B, int V, long long n_hist, long long n_bias, int top_n, int sms) {
     HostLayout L;
-    size_t o = 256;  // the batched call's own workspace comes first
+    size_t o = al256(batch_workspace_bytes(B, V, sms));  // the batched call's own workspace comes first
+    L.inner = o;
     L.logits = o; o += al256((size_t)B * V * 4);
     for (int i = 0; i < 8; i++) { L.f[i] = o; o += al256((size_t)B * 4); }
     L.k = o; o += al256((size_t)B * 4);
@@ -1306,7 +1298,9 @@ HostLayout host_layout(int B, int V, long long n_hist, long long n_bias, int top
 int64_t molla_sample_host_workspace_bytes(int32_t B, int32_t V, int64_t n_hist, int64_t n_bias, int32_t top_n) {
     if (B < 0 || V <= 0 || n_hist < 0 || n_bias < 0 || top_n < 0 || top_n > TOPN_MAX)
         return fail(MOLLA_ERR_ARGUMENT, "bad shape for the workspace query%s");
-    return (int64_t)host_layout(B, V, n_hist, n_bias, top_n).total;
+    const int sms = sm_count();
+    if (sms <= 0) return fail(MOLLA_ERR_CUDA, "cannot query the device%s");
+    return (int64_t)host_layout(B, V, n_hist, n_bias, top_n, sms).total;
 }
 
 int32_t molla_sample_batch_host(const float *h_logits, int64_t row_stride, int32_t B, int32_t V,
@@ -1338,13 +1332,13 @@ int32_t molla_sample_batch_host(const float *h_logits, int64_t row_stride, int32
     const long long n_hist = hist_off ? hist_off[B] : 0, n_bias = bias_off ? bias_off[B] : 0;
     for (long long j = 0; j < n_bias; j++)
         if (bias_ids[j] < 0 || bias_ids[j] >= V) return fail(MOLLA_ERR_CONFIG, "a logit bias names a token outside the vocabulary%s");
-    const HostLayout L = host_layout(B, V, n_hist, n_bias, top_n);
+    const int sms = sm_count();
+    if (sms <= 0) return fail(MOLLA_ERR_CUDA, "cannot query the device%s");
+    const HostLayout L = host_layout(B, V, n_hist, n_bias, top_n, sms);
     if (!d_workspace || workspace_bytes < (int64_t)L.total) return fail(MOLLA_ERR_WORKSPACE, "workspace missing or too small%s");
     char *w = (char *)d_workspace;
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e = cudaMemsetAsync(w, 0, 256, st);
-    if (e == cudaSuccess)
-        e = cudaMemcpy2DAsync(w + L.logits, (size_t)V * 4, h_logits, (size_t)row_stride * 4, (size_t)V * 4, (size_t)B, cudaMemcpyHostToDevice, st);
+    cudaError_t e = cudaMemcpy2DAsync(w + L.logits, (size_t)V * 4, h_logits, (size_t)row_stride * 4, (size_t)V * 4, (size_t)B, cudaMemcpyHostToDevice, st);
     const float *fsrc[8] = {temperature, top_p, min_p, typical_p, repeat_penalty, frequency_penalty, presence_penalty, nullptr};
     for (int i = 0; i < 7 && e == cudaSuccess; i++)
         if (fsrc[i]) e = cudaMemcpyAsync(w + L.f[i], fsrc[i], (size_t)B * 4, cudaMemcpyHostToDevice, st);
@@ -1361,7 +1355,7 @@ int32_t molla_sample_batch_host(const float *h_logits, int64_t row_stride, int32
         (const float *)dp(L.f[6], presence_penalty), (const uint8_t *)dp(L.win, window_on),
         (const uint64_t *)dp(L.seed, seed), (const uint64_t *)dp(L.drawn, drawn), (const int64_t *)dp(L.hist, hist),
         (const int32_t *)dp(L.hist_off, hist_off), (const int64_t *)dp(L.bias_ids, bias_ids),
-        (const float *)dp(L.bias_vals, bias_vals), (const int32_t *)dp(L.bias_off, bias_off), top_n, w, 256, stream,
+        (const float *)dp(L.bias_vals, bias_vals), (const int32_t *)dp(L.bias_off, bias_off), top_n, w, (int64_t)L.inner, stream,
         (int32_t *)(w + L.tokens), h_chosen_logprob ? (float *)(w + L.chosen) : nullptr,
         top_n > 0 ? (int32_t *)(w + L.top_ids) : nullptr, top_n > 0 ? (float *)(w + L.top_lps) : nullptr,
         (uint32_t *)(w + L.status), nullptr);
@@ -1390,7 +1384,7 @@ int32_t molla_sample_penalised(const float *d_logits, int64_t row_stride, int32_
     g_err[0] = 0;
     if (!d_logits || !d_out) return fail(MOLLA_ERR_ARGUMENT, "logits and output are required%s");
     if (B < 0 || V <= 0 || row_stride < V) return fail(MOLLA_ERR_ARGUMENT, "bad block shape%s");
-    if (!d_workspace || workspace_bytes < 256) return fail(MOLLA_ERR_WORKSPACE, "workspace missing or too small%s");
+    if (!d_workspace || workspace_bytes < molla_sample_workspace_bytes(B, V, 0)) return fail(MOLLA_ERR_WORKSPACE, "workspace missing or too small%s");
     if (B == 0) return MOLLA_OK;
     BatchArgs a;
     memset(&a, 0, sizeof(a));
@@ -1400,8 +1394,7 @@ int32_t molla_sample_penalised(const float *d_logits, int64_t row_stride, int32_
     a.hist = (const long long *)d_hist; a.hist_off = d_hist_off;
     a.bias_ids = (const long long *)d_bias_ids; a.bias_vals = d_bias_vals; a.bias_off = d_bias_off;
     a.penalised = d_out; a.penalised_only = 1;
-    a.row_counter = (int *)d_workspace;
-    return launch_rows(a, (cudaStream_t)stream);
+    return launch_rows(a, d_workspace, (cudaStream_t)stream);
 }
 
 int32_t molla_sample_logprobs(const float *d_logits, int64_t row_stride, int32_t B, int32_t V, void *stream,
