@@ -169,6 +169,12 @@ int32_t molla_sample_expf(const float *d_x, int64_t n, void *stream, float *d_ou
  * at the phase boundaries of each row (NULL switches it off again). */
 void molla_sample_debug_profile(void *d_stamps);
 
+/* Testing aid with no counterpart in the reference: when given a device buffer of
+ * B x cap int32, later molla_sample_batch calls write, for every row sampled with
+ * 1 < top_k < 128, the ids that survive top-k (`_top_k`, sample.mojo:485-490) in
+ * descending probability, padded with -1 (NULL switches it off again). */
+void molla_sample_debug_topk(void *d_ids, int32_t cap);
+
 /* cudaStreamSynchronize on `stream`, returning a status; then, if
  * `d_row_status` is given, nothing else is implied: rows report for themselves. */
 int32_t molla_sample_sync(void *stream);

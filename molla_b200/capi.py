@@ -31,7 +31,7 @@ EXPORTS = (
     "molla_sample_abi_version", "molla_sample_last_error", "molla_sample_draw",
     "molla_sample_workspace_bytes", "molla_sample_batch", "molla_sample_host_workspace_bytes",
     "molla_sample_batch_host", "molla_sample_penalised",
-    "molla_sample_logprobs", "molla_sample_expf", "molla_sample_sync", "molla_sample_debug_profile",
+    "molla_sample_logprobs", "molla_sample_expf", "molla_sample_sync", "molla_sample_debug_profile", "molla_sample_debug_topk",
 )
 
 
@@ -77,6 +77,8 @@ def lib():
     L.molla_sample_expf.argtypes = [vp, i64, vp, vp]
     L.molla_sample_debug_profile.restype = None
     L.molla_sample_debug_profile.argtypes = [vp]
+    L.molla_sample_debug_topk.restype = None
+    L.molla_sample_debug_topk.argtypes = [vp, i32]
     L.molla_sample_sync.restype = i32
     L.molla_sample_sync.argtypes = [vp]
     _lib = L

@@ -7,7 +7,7 @@
 
 namespace molla {
 
-constexpr int NT = 1024;     // threads per CTA
+constexpr int NT = 512;      // threads per CTA
 constexpr int NWARP = NT / 32;
 
 // ---- PRNG: the reference's splitmix64 finaliser and counter-based draw
@@ -99,15 +99,34 @@ __device__ __forceinline__ T block_excl_scan(T v, T *ws, T *total) {
     if (lane == 31) ws[warp] = inc;
     __syncthreads();
     if (warp == 0) {
-        T w = ws[lane];
+        T w = lane < NWARP ? ws[lane] : T(0);
         T wi = warp_incl_scan(w, lane);
-        ws[lane] = wi - w;
-        if (lane == 31) ws[NWARP] = wi;
+        if (lane < NWARP) ws[lane] = wi - w;
+        if (lane == NWARP - 1) ws[NWARP] = wi;
     }
     __syncthreads();
     T out = ws[warp] + (inc - v);
     *total = ws[NWARP];
     return out;
+}
+
+// Exclusive scan of two doubles at once (one pass of barriers for both).
+__device__ __forceinline__ void block_excl_scan2(double a, double b, double *ws /* 2*(NWARP+1) */, double &ea,
+                                                 double &eb, double &ta, double &tb) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    double ia = warp_incl_scan(a, lane), ib = warp_incl_scan(b, lane);
+    __syncthreads();
+    if (lane == 31) { ws[warp] = ia; ws[NWARP + 1 + warp] = ib; }
+    __syncthreads();
+    if (warp == 0) {
+        double wa = lane < NWARP ? ws[lane] : 0.0, wb = lane < NWARP ? ws[NWARP + 1 + lane] : 0.0;
+        double sa = warp_incl_scan(wa, lane), sb = warp_incl_scan(wb, lane);
+        if (lane < NWARP) { ws[lane] = sa - wa; ws[NWARP + 1 + lane] = sb - wb; }
+        if (lane == NWARP - 1) { ws[NWARP] = sa; ws[2 * NWARP + 1] = sb; }
+    }
+    __syncthreads();
+    ea = ws[warp] + (ia - a); eb = ws[NWARP + 1 + warp] + (ib - b);
+    ta = ws[NWARP]; tb = ws[2 * NWARP + 1];
 }
 
 // ---- mbarrier + bulk copy (TMA without a tensor map, never multicast) ---------

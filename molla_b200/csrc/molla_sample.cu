@@ -1,10 +1,12 @@
 // The token-sampling kernel and its C ABI (declared in include/molla_sample.h).
 //
-// One CTA owns one logit row at a time. The row is streamed through shared memory
-// in tiles staged by bulk asynchronous copies (TMA without a tensor map), twice:
-// pass A reads it from HBM and finds the maximum; pass B, a moment later, finds
-// the same bytes in L2 and does everything else. With one CTA per SM about 150
-// rows are in flight, which is less than the L2 holds, so HBM sees each logit once.
+// One CTA owns one logit row at a time and streams it twice through shared memory:
+// pass A reads it from HBM and finds the maximum; pass B, a moment later, finds the
+// same bytes in L2. With one CTA per SM about 150 rows are in flight, which is less
+// than the L2 holds, so HBM sees each logit once. In both passes every warp runs its
+// own pipeline: it owns a contiguous sixteenth of the row, fetches it piece by piece
+// with bulk asynchronous copies (TMA without a tensor map) into its own shared-memory
+// slots behind its own mbarriers, and never waits for another warp.
 //
 // The reference (src/molla/engine/sample.mojo) defines its result through
 // *sequential* fp32 sums: the softmax denominator is accumulated in vocabulary
@@ -12,6 +14,13 @@
 // (:497-506, :580-590). A parallel reduction rounds differently, and a different
 // last bit moves the top-p cut and the drawn token. So the kernel reproduces
 // those sums bit for bit instead of approximating them:
+//   * a term smaller than half an ulp of the running sum adds nothing at all. The
+//     running sum is never below the largest term before it, so a logit more than
+//     ~17.5 (in temperature-scaled units) below the running maximum cannot change
+//     any sum and can never be drawn. Pass B drops those (its only per-element work
+//     on them is one compare) and leaves the rest as one list, in vocabulary order,
+//     of (exp bits, token id) pairs: the "relevant list". Everything after pass B
+//     works on that list;
 //   * a running fp32 sum of non-negative terms stays inside one binade
 //     [2^j, 2^(j+1)) for long stretches; there `s + a` rounds to a multiple of
 //     ulp = 2^(j-23), so every term contributes the integer rne(a/ulp) and the
@@ -19,11 +28,7 @@
 //   * the few places where that fails - the running sum crossing into the next
 //     binade, a term that is large against the sum, a rounding tie whose
 //     direction depends on the parity of the sum - are found in parallel and
-//     replayed sequentially by one thread;
-//   * a term smaller than half an ulp of the running sum adds nothing at all.
-//     The running sum is never below the largest term before it, so a logit more
-//     than ~17.5 (in temperature-scaled units) below the running maximum cannot
-//     change any sum and can never be drawn: its exponential is not evaluated.
+//     replayed sequentially by one thread.
 // What cannot be reproduced is the order the reference's unstable heapsort
 // (:440-483) leaves equal probabilities in; rows where that order could matter
 // are marked in the row status (MOLLA_ROW_*_TIE) and equal probabilities are
@@ -41,19 +46,24 @@ using namespace molla;
 
 namespace {
 
-constexpr int LT = 11;              // elements per thread per tile (odd: conflict-free strides)
-constexpr int TILE = NT * LT;       // 11264 floats = 45056 bytes per tile
-constexpr int MAX_TILES = 64;       // V <= 720896
-constexpr int NBINS = 2048;         // histogram bins over the top bits of exp(v - max) in [0, 1]
-constexpr int BIN_SHIFT = 19;       // sign + 8 exponent + 4 mantissa bits
-constexpr int NC = 2048;            // candidate-list capacity (head list, gathered bins)
-constexpr int HEAD_NEED = 128;      // the sorted head covers top-k + 1 up to this many
-constexpr int HSLOTS = 2048;        // hash slots for penalised / biased tokens
-constexpr int PATCH_MAX = 1024;     // window + bias entries per row
-constexpr short SUS = -32768;       // chunk that must be replayed sequentially
+constexpr int LT = 11;               // elements per lane per piece (odd: conflict-free strides)
+constexpr int PIECE = 32 * LT;       // 352 floats = 1408 bytes: what one warp fetches at a time
+constexpr int NSTAGE = 4;            // pieces in flight per warp
+constexpr int MAX_PIECES = 128;      // per warp: V <= 16 * 128 * 352 = 720896
+constexpr int NBINS = 2048;          // histogram bins over the top bits of exp(v - max) in [0, 1]
+constexpr int BIN_SHIFT = 19;        // sign + 8 exponent + 4 mantissa bits
+constexpr int BPT = NBINS / NT;      // bins per thread in the bin search
+constexpr int NC = 2048;             // candidate-list capacity (gathered bins)
+constexpr int HEADC = 1024;          // head-list capacity
+constexpr int HEAD_NEED = 128;       // the sorted head covers top-k + 1 up to this many
+constexpr int HSLOTS = 2048;         // hash slots for penalised / biased tokens
+constexpr int PATCH_MAX = 1024;      // window + bias entries per row
+constexpr short SUS = -32768;        // chunk that must be replayed sequentially
 constexpr int TOPN_MAX = 20;
-constexpr float REL_MARGIN = 18.0f; // > 25.25*ln2 = 17.5: below this nothing can matter
-constexpr unsigned int W_BITS = 0x32800000u;  // 2^-26: what the descending walks can ever need
+constexpr float REL_MARGIN = 18.0f;  // > 25.25 ln 2 = 17.5: below this nothing can matter
+constexpr int STAGE_FLOATS = NWARP * NSTAGE * PIECE;       // 22528 floats = 90112 bytes
+constexpr int SLIST_CAP = STAGE_FLOATS / 2;                 // list entries that fit the stage area
+constexpr int ORDER_CAP = 4096;      // rows whose order is sorted by cost inside the kernel
 
 struct BatchArgs {
     const float *logits; long long row_stride; int B, V;
@@ -66,9 +76,12 @@ struct BatchArgs {
     int *tokens; unsigned int *row_status; float *diag;
     float *penalised;  // optional dump [B x V]
     int penalised_only;
+    int R;                       // floats per warp region (multiple of 4)
     int *row_counter;            // scratch: next row to hand out (zeroed before the launch)
-    unsigned long long *wlist;   // scratch: per-CTA list of (exp bits, token id), V entries each
+    const int *order;            // scratch: rows by decreasing cost (NULL = as given)
+    unsigned long long *wlist;   // scratch: per CTA, 2 x 16 x R list entries
     long long *prof;             // optional [B x 16] clock64 stamps per row (testing aid)
+    int *topk_out; int topk_cap; // optional [B x cap] ids of the sorted head after top-k (testing aid)
 };
 
 struct __align__(16) Aux {
@@ -85,31 +98,33 @@ struct __align__(16) Aux {
             unsigned long long hq[NBINS];
             unsigned int hc[NBINS];
         } h;
+        struct {                                 // the streaming passes only
+            float pmax[NWARP][MAX_PIECES];       // per warp, per piece: its maximum (pass A)
+            unsigned short ppos[NWARP][PIECE];   // per warp: positions of the piece's kept elements
+            float rmax[NWARP];                   // per warp: maximum of its region
+        } s;
     } u;
     unsigned long long cand[NC];
     float pc[NC];
-    float pre[NC];
-    unsigned int hidx[NC];  // head: token id, bit 31 = equal to a neighbour
+    float pre[HEADC];
+    unsigned int hidx[HEADC];  // head: token id, bit 31 = equal to a neighbour
     int hkey[HSLOTS];
     int hcnt[HSLOTS];
     float hval[HSLOTS];
-    float tilemax[MAX_TILES];
-    double wsd[NWARP + 1];
+    uint64_t mbar[NWARP][NSTAGE];
+    double wsd[2 * (NWARP + 1)];
     unsigned long long wsu[NWARP + 1];
     float wsf[NWARP + 1];
     int wsi[NWARP + 1];
-    uint64_t mbar[2];
+    int wcnt[NWARP + 1];             // per warp: entries it put on the list
     int nseg;
     int ncand;
-    int nw;
     int cur_row;
     int evt_thread;
     int specbin;
     int hit_bin; unsigned long long hit_qbefore; unsigned long long hit_cbefore;
     unsigned long long tot_q; unsigned long long tot_c;
-    // the sequential walker's state and results
     float walk_s; int walk_found; int walk_idx; int walk_slow;
-    // decisions published by thread 0
     float b_s; unsigned int b_tau; int b_event; int b_idx; float b_p; long long b_pos; int b_aux;
     float b_sum; float b_target;
 };
@@ -118,31 +133,22 @@ enum { EV_NONE = 0, EV_CUT = 1, EV_DRAW = 2, EV_LIMIT = 3, EV_EXHAUSTED = 4, EV_
 
 struct Ctx {
     int tid, lane, warp;
-    float *tb;            // two tile buffers
+    float *stage;         // NWARP x NSTAGE x PIECE floats
     unsigned int *bm;     // bitmap of patched tokens
     Aux *A;
-    int V, ntiles;
+    int V, R;
     bool patching;
     const float *src;     // this row in global memory
     bool aligned;
-    unsigned int par[2];  // mbarrier phase parity per buffer
     unsigned int status;
+    // this warp's region and pipeline
+    int rbeg, rlen, npieces;
+    unsigned int parbits;
 };
 
 #define STAMP(i) do { if (a.prof && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
 
 // ---- block collectives (NT threads) ----------------------------------------------
-__device__ __forceinline__ float block_max(Ctx &c, float v) {
-    v = warp_max(v);
-    __syncthreads();
-    if (c.lane == 0) c.A->wsf[c.warp] = v;
-    __syncthreads();
-    float r = c.A->wsf[0];
-#pragma unroll
-    for (int w = 1; w < NWARP; w++) r = fmaxf(r, c.A->wsf[w]);
-    return r;
-}
-
 __device__ __forceinline__ void block_argmax(Ctx &c, float &v, int &i) {
     warp_argmax(v, i);
     __syncthreads();
@@ -150,6 +156,7 @@ __device__ __forceinline__ void block_argmax(Ctx &c, float &v, int &i) {
     __syncthreads();
     float bv = c.A->wsf[0];
     int bi = c.A->wsi[0];
+#pragma unroll
     for (int w = 1; w < NWARP; w++) {
         float ov = c.A->wsf[w];
         int oi = c.A->wsi[w];
@@ -192,119 +199,189 @@ __device__ __forceinline__ unsigned long long make_key(unsigned int ebits, int i
     return ((unsigned long long)ebits << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)idx);
 }
 
-// ---- tile pipeline: tile t of the row lands in buffer t & 1 ------------------------
-__device__ __forceinline__ void tile_issue(Ctx &c, int t) {
-    // one thread; the buffer is free (a __syncthreads separates its last reader from here)
-    const int b = t & 1;
-    long long left = (long long)c.V - (long long)t * TILE;
-    const int n = (int)(left > TILE ? TILE : left);
-    const int nbulk = n & ~3;
+// ---- the warp's own pipeline: piece p of its region lands in slot p % NSTAGE --------
+__device__ __forceinline__ float *wslot(const Ctx &c, int p) {
+    return c.stage + (c.warp * NSTAGE + (p % NSTAGE)) * PIECE;
+}
+__device__ __forceinline__ int piece_len(const Ctx &c, int p) {
+    const int left = c.rlen - p * PIECE;
+    return left > PIECE ? PIECE : left;
+}
+// lane 0 only; the slot is free (a __syncwarp separates its last reader from here)
+__device__ __forceinline__ void piece_issue(Ctx &c, int p) {
+    if (!c.aligned || p >= c.npieces) return;
+    const int nbulk = piece_len(c, p) & ~3;
     if (nbulk <= 0) return;
+    uint64_t *bar = &c.A->mbar[c.warp][p % NSTAGE];
     fence_proxy_async();
-    mbar_expect_tx(&c.A->mbar[b], (uint32_t)nbulk * 4u);
-    const float *s = c.src + (long long)t * TILE;
-    float *d = c.tb + b * TILE;
-    const int PIECE = 4096;  // floats per bulk copy (16 KB)
-    for (int o = 0; o < nbulk; o += PIECE) {
-        int m = nbulk - o < PIECE ? nbulk - o : PIECE;
-        bulk_g2s(d + o, s + o, (uint32_t)m * 4u, &c.A->mbar[b]);
-    }
+    mbar_expect_tx(bar, (uint32_t)nbulk * 4u);
+    bulk_g2s(wslot(c, p), c.src + c.rbeg + (long long)p * PIECE, (uint32_t)nbulk * 4u, bar);
 }
-
-// Start a pass over the row: tile 0 is requested.
-__device__ __forceinline__ void tiles_begin(Ctx &c) {
-    __syncthreads();  // both buffers are free
-    if (c.aligned && c.tid == 0) tile_issue(c, 0);
+__device__ __forceinline__ void pieces_begin(Ctx &c) {
+    __syncwarp();
+    if (c.lane == 0)
+        for (int p = 0; p < NSTAGE - 1; p++) piece_issue(c, p);
 }
-
-// Make tile t available in shared memory (returns its buffer) and request tile t + 1.
-__device__ __forceinline__ float *tile_acquire(Ctx &c, int t, int &n_tile) {
-    const int b = t & 1;
-    long long left = (long long)c.V - (long long)t * TILE;
-    n_tile = (int)(left > TILE ? TILE : left);
-    float *buf = c.tb + b * TILE;
-    __syncthreads();  // everyone is done with the other buffer (tile t - 1)
+// Make piece p readable by the whole warp; returns its slot and length. Requests piece
+// p + NSTAGE - 1 into the slot the warp finished with in the previous iteration.
+__device__ __forceinline__ const float *piece_acquire(Ctx &c, int p, int &n) {
+    n = piece_len(c, p);
+    float *slot = wslot(c, p);
+    __syncwarp();  // the warp is done with the slot of piece p - 1
+    if (c.lane == 0) piece_issue(c, p + NSTAGE - 1);
+    const float *g = c.src + c.rbeg + (long long)p * PIECE;
     if (c.aligned) {
-        if (c.tid == 0 && t + 1 < c.ntiles) tile_issue(c, t + 1);
-        const int nbulk = n_tile & ~3;
-        for (int i = nbulk + c.tid; i < n_tile; i += NT) buf[i] = __ldg(c.src + (long long)t * TILE + i);
+        const int nbulk = n & ~3;
+        if (nbulk + c.lane < n) slot[nbulk + c.lane] = __ldg(g + nbulk + c.lane);
         if (nbulk > 0) {
+            const int s = p % NSTAGE;
             bool done = false;
             for (int spin = 0; spin < (1 << 22); spin++) {
-                if (mbar_try_wait(&c.A->mbar[b], c.par[b])) { done = true; break; }
+                if (mbar_try_wait(&c.A->mbar[c.warp][s], (c.parbits >> s) & 1u)) { done = true; break; }
             }
             if (!done) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
-            c.par[b] ^= 1u;
+            c.parbits ^= (1u << s);
         }
-        if (n_tile & 3) __syncthreads();
     } else {
-        const float *s = c.src + (long long)t * TILE;
-        for (int i = c.tid; i < n_tile; i += NT) buf[i] = __ldg(s + i);
-        __syncthreads();
+        for (int i = c.lane; i < n; i += 32) slot[i] = __ldg(g + i);
     }
-    return buf;
+    __syncwarp();
+    return slot;
 }
 
 // ---- patched tokens: bitmap over the vocabulary + a small hash of their values -----
 __device__ __forceinline__ int hslot(int tok) { return (int)(((unsigned int)tok * 2654435761u) >> 21); }
 
-__device__ __forceinline__ float patch_lookup(const Ctx &c, int tok, float x) {
+__device__ __forceinline__ float patch_lookup(const Aux *A, int tok, float x) {
     int s = hslot(tok);
     for (int probe = 0; probe < HSLOTS; probe++) {
-        int k = c.A->hkey[s];
-        if (k == tok) return c.A->hval[s];
+        const int k = A->hkey[s];
+        if (k == tok) return A->hval[s];
         if (k < 0) return x;
         s = (s + 1) & (HSLOTS - 1);
     }
     return x;
 }
-// bits j = 1 where element g0 + j (j < 32) is patched
+// bit j = 1 where element g0 + j (j < 32) is patched
 __device__ __forceinline__ unsigned int patch_mask(const Ctx &c, int g0) {
     if (!c.patching) return 0u;
     const int w = g0 >> 5, sh = g0 & 31;
     const int nwords = (c.V + 31) >> 5;
-    unsigned int lo = c.bm[w];
-    unsigned int hi = (w + 1 < nwords) ? c.bm[w + 1] : 0u;
+    const unsigned int lo = c.bm[w];
+    const unsigned int hi = (w + 1 < nwords) ? c.bm[w + 1] : 0u;
     return __funnelshift_r(lo, hi, sh);
+}
+// this lane's LT elements of a piece, with patches applied; past the end: -inf
+__device__ __forceinline__ void load_chunk(const Ctx &c, const float *slot, int n, int g0, float (&x)[LT]) {
+    const int l0 = c.lane * LT;
+    const unsigned int pm = (l0 < n) ? patch_mask(c, g0) : 0u;
+#pragma unroll
+    for (int j = 0; j < LT; j++) x[j] = (l0 + j < n) ? slot[l0 + j] : -INFINITY;
+    if (pm) {
+#pragma unroll
+        for (int j = 0; j < LT; j++)
+            if (((pm >> j) & 1u) && l0 + j < n) x[j] = patch_lookup(c.A, g0 + j, x[j]);
+    }
 }
 
 // =============================================================================
-// The exact sequential fp32 sum, one tile at a time (vocabulary order).
+// The exact sequential fp32 sum of the list's values, in list (= vocabulary) order.
 // =============================================================================
-// Every thread owns LT consecutive terms of the tile. From approximate prefix sums
-// each chunk guesses the binade(s) the true running sum can be in when it reaches
-// the chunk (a margin of 2^-12 covers the rounding drift of the true sum) and adds
-// up its terms' integer contributions for that binade (`pa`) and, when the guess
-// straddles a power of two, for the next one (`pb`). Chunks holding a rounding tie,
-// a term >= sum/4, or a span of more than two binades are replayed term by term.
-// Thread 0 then carries the exact sum across the tile from those tables.
+// Every thread owns L consecutive entries. From approximate prefix sums each chunk
+// guesses the binade(s) the true running sum can be in when it reaches the chunk (a
+// margin of 2^-12 covers the rounding drift of the true sum) and adds up its terms'
+// integer contributions for that binade (`pa`) and, when the guess straddles a power
+// of two, for the next one (`pb`). Chunks holding a rounding tie, a term >= sum/4, or
+// a span of more than two binades are replayed term by term. Thread 0 then carries
+// the exact sum across the list from those tables (`p1_walk`), optionally stopping at
+// the first entry whose running sum exceeds a target.
 struct Walker {
-    float s; int found; long long idx; int slow;
+    float s; int found; int at; int slow;
 };
 
-__device__ __forceinline__ void p1_sim(const float *buf, int i0, int i1, long long gbase, bool locate,
-                                       float target, Walker &w) {
+__device__ __forceinline__ float lval(const unsigned long long *lst, int i) {
+    return __uint_as_float((unsigned int)(lst[i] >> 32));
+}
+
+__device__ __forceinline__ void p1_sim(const unsigned long long *lst, int i0, int i1, bool locate, float target,
+                                       Walker &w) {
     float s = w.s;
     for (int i = i0; i < i1; i++) {
-        s = __fadd_rn(s, buf[i]);
-        if (locate && target < s) { w.found = 1; w.idx = gbase + i; break; }
+        s = __fadd_rn(s, lval(lst, i));
+        if (locate && target < s) { w.found = 1; w.at = i; break; }
     }
     w.s = s;
 }
 
-__device__ void p1_walk_tile(Ctx &c, const float *buf, int n_tile, long long gbase, bool locate, float target,
-                             Walker &w) {
+__device__ void p1_build(Ctx &c, const unsigned long long *lst, int n, int L) {
     Aux *A = c.A;
+    const float EPS = 1.0f / 4096.0f;
+    const int i0 = min(n, c.tid * L), i1 = min(n, (c.tid + 1) * L);
+    float csum = 0.0f;
+    for (int i = i0; i < i1; i++) csum = __fadd_rn(csum, lval(lst, i));
+    double tot;
+    const double sst = block_excl_scan<double>((double)csum, A->wsd, &tot);
+    short ja = SUS;
+    unsigned char dual = 0;
+    float da = 0.0f, db = 0.0f;
+    const float lo = (float)(sst * (1.0 - (double)EPS));
+    const float hi = (float)((sst + (double)csum) * (1.0 + (double)EPS));
+    if (lo > 0.0f && i1 > i0) {
+        const int jl = fexpo(lo), j2 = fexpo(hi);
+        if (j2 <= jl + 1 && jl >= -100 && j2 <= 100) {
+            bool bad = false;
+            const bool two = (j2 == jl + 1);
+            const float C1 = __fmul_rn(1.5f, fpow2(jl)), h1 = fpow2(jl - 24), b1 = fpow2(jl - 1);
+            const float C2 = __fmul_rn(1.5f, fpow2(jl + 1)), h2 = fpow2(jl - 23);
+            for (int i = i0; i < i1; i++) {
+                const float v = lval(lst, i);
+                const float q = __fsub_rn(__fadd_rn(v, C1), C1);
+                const float r = __fsub_rn(v, q);
+                bad |= (fabsf(r) == h1) | (v >= b1);
+                da = __fadd_rn(da, q);
+                const float q2 = __fsub_rn(__fadd_rn(v, C2), C2);
+                const float r2 = __fsub_rn(v, q2);
+                bad |= two & (fabsf(r2) == h2);
+                db = __fadd_rn(db, q2);
+            }
+            if (!bad) { ja = (short)jl; dual = two ? 1 : 0; }
+        }
+    }
+    if (ja == SUS) { da = 0.0f; db = 0.0f; dual = 0; }
+    A->u.p1.csum[c.tid] = (i1 > i0) ? csum : 0.0f;
+    A->u.p1.ja[c.tid] = ja;
+    A->u.p1.dual[c.tid] = dual;
+    double pa, pb, ta, tb;
+    block_excl_scan2((double)da, (double)(dual ? db : da), A->wsd, pa, pb, ta, tb);
+    A->u.p1.pa[c.tid] = pa;
+    A->u.p1.pb[c.tid] = pb;
+    if (c.tid == NT - 1) { A->u.p1.pa[NT] = ta; A->u.p1.pb[NT] = tb; }
+    __syncthreads();
+    // segment list: chunks where (binade guess, dual, replay) changes
+    const bool start = (c.tid == 0) || ja == SUS || A->u.p1.ja[c.tid - 1] != ja || A->u.p1.dual[c.tid - 1] != dual;
+    const unsigned int bal = __ballot_sync(0xffffffffu, start);
+    int wtot;
+    int wex = block_excl_scan<int>(c.lane == 0 ? __popc(bal) : 0, A->wsi, &wtot);
+    wex = __shfl_sync(0xffffffffu, wex, 0);
+    if (start) A->u.p1.seg[wex + __popc(bal & ((1u << c.lane) - 1u))] = (unsigned short)c.tid;
+    if (c.tid == 0) A->nseg = wtot;
+    __syncthreads();
+}
+
+// thread 0 only
+__device__ void p1_walk(Ctx &c, const unsigned long long *lst, int n, int L, bool locate, float target, Walker &w) {
+    Aux *A = c.A;
+    w.s = 0.0f; w.found = 0; w.at = -1; w.slow = 0;
     const int nseg = A->nseg;
     const double *PA = A->u.p1.pa, *PB = A->u.p1.pb;
     for (int si = 0; si < nseg && !(locate && w.found); si++) {
         const int t0 = A->u.p1.seg[si];
         const int t1 = (si + 1 < nseg) ? (int)A->u.p1.seg[si + 1] : NT;
         const int j = A->u.p1.ja[t0];
-        const int e0 = min(n_tile, t0 * LT), e1 = min(n_tile, t1 * LT);
-        if (e1 <= e0) continue;
+        const int e0 = min(n, t0 * L), e1 = min(n, t1 * L);
+        if (e1 <= e0) break;  // chunks past the end of the list are empty
         if (j == SUS) {
-            if (A->u.p1.csum[t0] != 0.0f) p1_sim(buf, e0, e1, gbase, locate, target, w);
+            if (A->u.p1.csum[t0] != 0.0f) p1_sim(lst, e0, e1, locate, target, w);
             continue;
         }
         const bool dual = A->u.p1.dual[t0] != 0;
@@ -326,7 +403,7 @@ __device__ void p1_walk_tile(Ctx &c, const float *buf, int n_tile, long long gba
                         else lo_ = mid + 1;
                     }
                     w.s = (float)((double)w.s + (P[lo_] - P[ta]));
-                    p1_sim(buf, min(n_tile, lo_ * LT), min(n_tile, (lo_ + 1) * LT), gbase, true, target, w);
+                    p1_sim(lst, min(n, lo_ * L), min(n, (lo_ + 1) * L), true, target, w);
                     return true;
                 }
                 w.s = (float)sn;
@@ -354,11 +431,11 @@ __device__ void p1_walk_tile(Ctx &c, const float *buf, int n_tile, long long gba
                     if (fine) {
                         ok = true;
                         if (!(locate && w.found)) {
-                            p1_sim(buf, min(n_tile, ts * LT), min(n_tile, (ts + 1) * LT), gbase, locate, target, w);
+                            p1_sim(lst, min(n, ts * L), min(n, (ts + 1) * L), locate, target, w);
                             if (!(locate && w.found) && ts + 1 < t1) {
                                 if (!(fexpo(w.s) == j + 1 && bulk(PB, ts + 1, t1, ldexp(1.0, j + 2)))) {
                                     w.slow = 1;
-                                    p1_sim(buf, min(n_tile, (ts + 1) * LT), e1, gbase, locate, target, w);
+                                    p1_sim(lst, min(n, (ts + 1) * L), e1, locate, target, w);
                                 }
                             }
                         }
@@ -368,80 +445,13 @@ __device__ void p1_walk_tile(Ctx &c, const float *buf, int n_tile, long long gba
         }
         if (!ok) {
             w.slow = 1;
-            p1_sim(buf, e0, e1, gbase, locate, target, w);
+            p1_sim(lst, e0, e1, locate, target, w);
         }
     }
-}
-
-// One tile of the sum. `e` are this thread's terms (zero past `nchunk`), already written
-// to `buf`; `sbase` is the approximate sum of everything before the tile.
-__device__ void p1_tile(Ctx &c, const float (&e)[LT], int nchunk, float csum, const float *buf, int n_tile,
-                        long long gbase, double &sbase, bool locate, float target) {
-    Aux *A = c.A;
-    const float EPS = 1.0f / 4096.0f;
-    double tot;
-    const double ex = block_excl_scan<double>((double)csum, A->wsd, &tot);
-    if (tot == 0.0) return;  // nothing in this tile can change the sum
-    const double sst = sbase + ex;
-    short ja = SUS;
-    unsigned char dual = 0;
-    float da = 0.0f, db = 0.0f;
-    const float lo = (float)(sst * (1.0 - (double)EPS));
-    const float hi = (float)((sst + (double)csum) * (1.0 + (double)EPS));
-    if (lo > 0.0f && nchunk > 0) {
-        const int jl = fexpo(lo), j2 = fexpo(hi);
-        if (j2 <= jl + 1 && jl >= -100 && j2 <= 100) {
-            bool bad = false;
-            const bool two = (j2 == jl + 1);
-            const float C1 = __fmul_rn(1.5f, fpow2(jl)), h1 = fpow2(jl - 24), b1 = fpow2(jl - 1);
-            const float C2 = __fmul_rn(1.5f, fpow2(jl + 1)), h2 = fpow2(jl - 23);
-#pragma unroll
-            for (int i = 0; i < LT; i++) {
-                const float v = e[i];
-                const float q = __fsub_rn(__fadd_rn(v, C1), C1);
-                const float r = __fsub_rn(v, q);
-                bad |= (fabsf(r) == h1) | (v >= b1);
-                da = __fadd_rn(da, q);
-                const float q2 = __fsub_rn(__fadd_rn(v, C2), C2);
-                const float r2 = __fsub_rn(v, q2);
-                bad |= two & (fabsf(r2) == h2);
-                db = __fadd_rn(db, q2);
-            }
-            if (!bad) { ja = (short)jl; dual = two ? 1 : 0; }
-        }
-    }
-    if (ja == SUS) { da = 0.0f; db = 0.0f; dual = 0; }
-    A->u.p1.csum[c.tid] = (nchunk > 0) ? csum : 0.0f;
-    A->u.p1.ja[c.tid] = ja;
-    A->u.p1.dual[c.tid] = dual;
-    double t2;
-    const double pa = block_excl_scan<double>((double)da, A->wsd, &t2);
-    A->u.p1.pa[c.tid] = pa;
-    if (c.tid == NT - 1) A->u.p1.pa[NT] = t2;
-    const double pb = block_excl_scan<double>((double)(dual ? db : da), A->wsd, &t2);
-    A->u.p1.pb[c.tid] = pb;
-    if (c.tid == NT - 1) A->u.p1.pb[NT] = t2;
-    __syncthreads();
-    // segment list: chunks where (binade guess, dual, replay) changes
-    const bool start = (c.tid == 0) || ja == SUS || A->u.p1.ja[c.tid - 1] != ja || A->u.p1.dual[c.tid - 1] != dual;
-    const unsigned int bal = __ballot_sync(0xffffffffu, start);
-    int wtot;
-    int wex = block_excl_scan<int>(c.lane == 0 ? __popc(bal) : 0, A->wsi, &wtot);
-    wex = __shfl_sync(0xffffffffu, wex, 0);
-    if (start) A->u.p1.seg[wex + __popc(bal & ((1u << c.lane) - 1u))] = (unsigned short)c.tid;
-    if (c.tid == 0) A->nseg = wtot;
-    __syncthreads();
-    if (c.tid == 0) {
-        Walker w; w.s = A->walk_s; w.found = A->walk_found; w.idx = A->walk_idx; w.slow = A->walk_slow;
-        p1_walk_tile(c, buf, n_tile, gbase, locate, target, w);
-        A->walk_s = w.s; A->walk_found = w.found; A->walk_idx = (int)w.idx; A->walk_slow = w.slow;
-    }
-    __syncthreads();
-    sbase += tot;
 }
 
 // =============================================================================
-// Histogram search: thread t owns bins NBINS-1-2t and NBINS-2-2t, so a scan over the
+// Histogram search: thread t owns bins NBINS-1-BPT*t-i (i < BPT), so a scan over the
 // threads runs through the bins in descending order.
 // =============================================================================
 struct BinQuery {
@@ -452,29 +462,33 @@ struct BinQuery {
 
 __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
     Aux *A = c.A;
-    const int bh = NBINS - 1 - 2 * c.tid, bl = bh - 1;
-    const unsigned long long qh = A->u.h.hq[bh], ql = A->u.h.hq[bl];
-    const unsigned long long ch = A->u.h.hc[bh], cl = A->u.h.hc[bl];
+    unsigned long long q[BPT], n[BPT], sq = 0, sn = 0;
+#pragma unroll
+    for (int i = 0; i < BPT; i++) {
+        const int b = NBINS - 1 - BPT * c.tid - i;
+        q[i] = A->u.h.hq[b]; n[i] = A->u.h.hc[b];
+        sq += q[i]; sn += n[i];
+    }
     unsigned long long tq, tc;
-    const unsigned long long eq = block_excl_scan<unsigned long long>(qh + ql, A->wsu, &tq);
-    const unsigned long long ec = block_excl_scan<unsigned long long>(ch + cl, A->wsu, &tc);
+    const unsigned long long eq = block_excl_scan<unsigned long long>(sq, A->wsu, &tq);
+    const unsigned long long ec = block_excl_scan<unsigned long long>(sn, A->wsu, &tc);
     __syncthreads();
     if (c.tid == 0) { A->evt_thread = 0x7fffffff; A->tot_q = tq; A->tot_c = tc; A->hit_bin = -1; }
     __syncthreads();
-    auto pred = [&](unsigned long long cq, unsigned long long cc, int bin) -> bool {
-        if (qy.xq != ~0ull && qy.m0 + cq >= qy.xq) return true;
-        if (qy.nstop != ~0ull && qy.pos0 + cc >= qy.nstop) return true;
-        if (bin <= qy.specbin) return true;
-        return false;
-    };
-    const bool ph = pred(eq + qh, ec + ch, bh);
-    const bool pl = pred(eq + qh + ql, ec + ch + cl, bl);
-    if (ph || pl) atomicMin(&A->evt_thread, c.tid);
-    __syncthreads();
-    if (A->evt_thread == c.tid) {
-        if (ph) { A->hit_bin = bh; A->hit_qbefore = eq; A->hit_cbefore = ec; }
-        else { A->hit_bin = bl; A->hit_qbefore = eq + qh; A->hit_cbefore = ec + ch; }
+    int hit = -1;
+    unsigned long long cq = eq, cc = ec, hq_before = 0, hc_before = 0;
+#pragma unroll
+    for (int i = 0; i < BPT; i++) {
+        const int b = NBINS - 1 - BPT * c.tid - i;
+        const unsigned long long q1 = cq + q[i], c1 = cc + n[i];
+        const bool pr = (qy.xq != ~0ull && qy.m0 + q1 >= qy.xq) || (qy.nstop != ~0ull && qy.pos0 + c1 >= qy.nstop) ||
+                        (b <= qy.specbin);
+        if (pr && hit < 0) { hit = b; hq_before = cq; hc_before = cc; }
+        cq = q1; cc = c1;
     }
+    if (hit >= 0) atomicMin(&A->evt_thread, c.tid);
+    __syncthreads();
+    if (A->evt_thread == c.tid) { A->hit_bin = hit; A->hit_qbefore = hq_before; A->hit_cbefore = hc_before; }
     __syncthreads();
 }
 
@@ -493,24 +507,55 @@ __device__ void sort_cands(Ctx &c, int n, float Z) {
 
 // =============================================================================
 // The descending walk past the sorted head (sample.mojo:492-506 and :580-590 on rows
-// whose nucleus is larger than the head), over the row's list `wl` of (exp bits,
-// token id) pairs. State: exact running sum `s`, elements consumed `pos`, and `tau`:
-// everything with exp bits >= tau is consumed. Each phase histograms what remains by
-// value bin with its integer contribution in the current binade, consumes whole bins
-// up to the first bin holding an event (the sum reaching x_ge, exceeding x_gt, leaving
-// the binade, a count limit, or an element needing sequential care), then gathers
-// that bin, sorts it and adds it element by element.
+// whose nucleus is larger than the head), over the row's relevant list. State: exact
+// running sum `s`, elements consumed `pos`, and `tau`: everything with exp bits >= tau
+// is consumed. Each phase histograms what remains by value bin with its integer
+// contribution in the current binade, consumes whole bins up to the first bin holding
+// an event (the sum reaching x_ge, exceeding x_gt, leaving the binade, a count limit,
+// or an element needing sequential care), then gathers that bin, sorts it and adds it
+// element by element.
 // =============================================================================
 struct Walk {
     float s; long long pos; unsigned int tau;
     int event; int idx; float p; int tie;
 };
 
-__device__ void descend(Ctx &c, const unsigned long long *wl, int nw, float Z, Walk &w, float x_ge, float x_gt,
+// index in list order of the (nth+1)-th entry whose exp bits equal `eb` and lie below `tau`
+__device__ int nth_equal(Ctx &c, const unsigned long long *lst, int nl, unsigned int eb, unsigned int tau, int nth) {
+    Aux *A = c.A;
+    const int L = (nl + NT - 1) / NT;
+    const int i0 = min(nl, c.tid * L), i1 = min(nl, (c.tid + 1) * L);
+    int cnt = 0;
+    for (int i = i0; i < i1; i++) cnt += ((unsigned int)(lst[i] >> 32) == eb && eb < tau) ? 1 : 0;
+    int tot;
+    const int ex = block_excl_scan<int>(cnt, A->wsi, &tot);
+    __syncthreads();
+    if (c.tid == 0) A->b_idx = -1;
+    __syncthreads();
+    if (nth >= ex && nth < ex + cnt) {
+        int seen = ex;
+        for (int i = i0; i < i1; i++) {
+            if ((unsigned int)(lst[i] >> 32) == eb) {
+                if (seen == nth) { A->b_idx = key_idx(lst[i]); break; }
+                seen++;
+            }
+        }
+    }
+    __syncthreads();
+    return A->b_idx;
+}
+
+__device__ void descend(Ctx &c, const unsigned long long *lst, int nl, float Z, Walk &w, float x_ge, float x_gt,
                         long long nstop) {
     Aux *A = c.A;
     const bool counting = nstop >= 0;
-    for (int phase = 0; phase < 4096; phase++) {
+    // Bins are 2048 ranges of exp bits. A bin holding more than the candidate buffer is split
+    // again (level 2: the next 11 bits; level 3: single values); a single value repeated more
+    // often than that is added one copy at a time.
+    int lvl = 1;
+    unsigned int lo = 0u;
+    int shift = BIN_SHIFT;
+    for (int phase = 0; phase < 8192; phase++) {
         __syncthreads();
         for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0ull; A->u.h.hc[i] = 0u; }
         if (c.tid == 0) { A->specbin = -1; A->ncand = 0; }
@@ -520,10 +565,10 @@ __device__ void descend(Ctx &c, const unsigned long long *wl, int nw, float Z, W
         const bool binade_ok = have_s && j >= -100 && j <= 100;
         const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1);
         const float inv_u = fpow2(23 - j);
-        for (int i = c.tid; i < nw; i += NT) {
-            const unsigned int eb = (unsigned int)(wl[i] >> 32);
-            if (eb >= w.tau) continue;
-            const int bin = (int)(eb >> BIN_SHIFT);
+        for (int i = c.tid; i < nl; i += NT) {
+            const unsigned int eb = (unsigned int)(lst[i] >> 32);
+            if (eb >= w.tau || eb < lo) continue;
+            const int bin = (int)((eb - lo) >> shift);
             if (!binade_ok) { atomicAdd(&A->u.h.hc[bin], 1u); continue; }
             const float p = __fdiv_rn(__uint_as_float(eb), Z);
             const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
@@ -561,28 +606,72 @@ __device__ void descend(Ctx &c, const unsigned long long *wl, int nw, float Z, W
         find_event_bin(c, qy);
         const int hb = A->hit_bin;
         if (hb < 0) {
+            // nothing left in this range triggers an event: consume it whole
             if (binade_ok) w.s = (float)((double)(qy.m0 + A->tot_q) * (double)fpow2(j - 23));
             w.pos += (long long)A->tot_c;
-            w.tau = 0;
-            w.event = EV_EXHAUSTED;
-            return;
+            if (lvl == 1) { w.tau = 0; w.event = EV_EXHAUSTED; return; }
+            w.tau = lo; lvl = 1; lo = 0u; shift = BIN_SHIFT;  // back to the coarse bins below this range
+            continue;
         }
         const unsigned long long qb = A->hit_qbefore, cb = A->hit_cbefore;
-        for (int i = c.tid; i < nw; i += NT) {
-            const unsigned long long key = wl[i];
+        const unsigned int blo = lo + ((unsigned int)hb << shift);
+        const unsigned long long bhi64 = (unsigned long long)lo + ((unsigned long long)(hb + 1) << shift);
+        const unsigned int bhi = bhi64 > 0xFFFFFFFFull ? 0xFFFFFFFFu : (unsigned int)bhi64;
+        for (int i = c.tid; i < nl; i += NT) {
+            const unsigned long long key = lst[i];
             const unsigned int eb = (unsigned int)(key >> 32);
-            if (eb < w.tau && (int)(eb >> BIN_SHIFT) == hb) {
+            if (eb < w.tau && eb >= blo && eb < bhi) {
                 int pos = atomicAdd(&A->ncand, 1);
                 if (pos < NC) A->cand[pos] = key;
             }
         }
         __syncthreads();
         const int nb = A->ncand;
-        if (nb > NC) { w.event = EV_DEGENERATE; c.status |= MOLLA_ROW_DEGENERATE; return; }
+        // what lies above the bin is consumed without an event either way
+        const float s_bin = binade_ok ? (float)((double)(qy.m0 + qb) * (double)fpow2(j - 23)) : w.s;
+        const long long pos_bin = w.pos + ((counting || !binade_ok) ? (long long)cb : 0);
+        if (nb > NC && lvl < 3) {
+            w.s = s_bin; w.pos = pos_bin;
+            w.tau = bhi < w.tau ? bhi : w.tau;
+            lo = blo; shift = (lvl == 1) ? 8 : 0; lvl++;
+            c.status |= MOLLA_ROW_SLOW_PATH;
+            continue;
+        }
+        if (nb > NC) {
+            // one value, more copies than the buffer holds: add them one at a time (thread 0), then
+            // find which copy, in token order, the event fell on
+            c.status |= MOLLA_ROW_SLOW_PATH;
+            const float pv = __fdiv_rn(__uint_as_float(blo), Z);
+            __syncthreads();
+            if (c.tid == 0) {
+                float s = s_bin;
+                long long pos = pos_bin;
+                int ev = EV_NONE, at = -1;
+                for (int i = 0; i < nb; i++) {
+                    s = __fadd_rn(s, pv);
+                    pos++;
+                    if (s >= x_ge) ev = EV_CUT;
+                    else if (x_gt < s) ev = EV_DRAW;
+                    else if (counting && pos >= nstop) ev = EV_LIMIT;
+                    if (ev != EV_NONE) { at = i; break; }
+                }
+                A->b_event = ev; A->b_s = s; A->b_pos = pos; A->b_aux = at;
+            }
+            __syncthreads();
+            const int ev = A->b_event, at = A->b_aux;
+            w.s = A->b_s; w.pos = A->b_pos;
+            if (ev != EV_NONE) {
+                const int id = nth_equal(c, lst, nl, blo, w.tau, at);
+                w.event = ev; w.idx = id; w.p = pv; w.tie = 1;
+                return;
+            }
+            w.tau = blo;
+            continue;
+        }
         sort_cands(c, nb, Z);
         if (c.tid == 0) {
-            float s = binade_ok ? (float)((double)(qy.m0 + qb) * (double)fpow2(j - 23)) : w.s;
-            long long pos = w.pos + ((counting || !binade_ok) ? (long long)cb : 0);
+            float s = s_bin;
+            long long pos = pos_bin;
             int ev = EV_NONE, at = -1;
             for (int i = 0; i < nb; i++) {
                 const float p = A->pc[i];
@@ -593,7 +682,7 @@ __device__ void descend(Ctx &c, const unsigned long long *wl, int nw, float Z, W
                 else if (counting && pos >= nstop) ev = EV_LIMIT;
                 if (ev != EV_NONE) { at = i; break; }
             }
-            A->b_event = ev; A->b_s = s; A->b_pos = pos; A->b_tau = (unsigned int)hb << BIN_SHIFT;
+            A->b_event = ev; A->b_s = s; A->b_pos = pos; A->b_tau = blo;
             if (at >= 0) {
                 const float p = A->pc[at];
                 A->b_idx = key_idx(A->cand[at]); A->b_p = p;
@@ -609,28 +698,63 @@ __device__ void descend(Ctx &c, const unsigned long long *wl, int nw, float Z, W
     c.status |= MOLLA_ROW_DEGENERATE;
 }
 
+// Rows differ in cost by an order of magnitude (a greedy row is one pass, a hot row keeps
+// most of its vocabulary). Handing out the dearest first keeps the last CTAs from running
+// long: this small kernel sorts the rows by a cost estimate.
+__global__ void __launch_bounds__(NT, 1) order_rows_kernel(const float *temperature, const int *top_k, int B, int *order) {
+    __shared__ unsigned long long keys[ORDER_CAP];
+    int n2 = 2;
+    while (n2 < B) n2 <<= 1;
+    for (int i = threadIdx.x; i < n2; i += NT) {
+        float cost = -1.0f;
+        if (i < B) {
+            const float T = temperature ? temperature[i] : 0.0f;
+            const int k = top_k ? top_k[i] : 0;
+            cost = (T > 0.0f && k != 1) ? T + ((k == 0 || k >= HEAD_NEED) ? 0.25f : 0.0f) : 0.0f;
+        }
+        keys[i] = ((unsigned long long)fkey(cost) << 32) | (unsigned long long)(0xFFFFu - (unsigned int)(i & 0xFFFF));
+    }
+    bitonic_desc(keys, n2, threadIdx.x);
+    for (int i = threadIdx.x; i < B; i += NT) order[i] = (int)(0xFFFFu - (unsigned int)(keys[i] & 0xFFFFull));
+}
+
 // =============================================================================
-// The kernel: persistent CTAs, each taking the next unsampled row.
+// The kernel: persistent CTAs, each taking the next row (dearest rows first).
 // =============================================================================
 __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constant__ BatchArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Ctx c;
     c.tid = threadIdx.x; c.lane = c.tid & 31; c.warp = c.tid >> 5;
-    c.tb = reinterpret_cast<float *>(smem_raw);
-    c.A = reinterpret_cast<Aux *>(smem_raw + 2 * TILE * 4);
-    c.bm = reinterpret_cast<unsigned int *>(smem_raw + 2 * TILE * 4 + ((sizeof(Aux) + 15) / 16) * 16);
-    c.V = a.V;
-    c.ntiles = (a.V + TILE - 1) / TILE;
-    c.par[0] = c.par[1] = 0;
+    c.stage = reinterpret_cast<float *>(smem_raw);
+    c.A = reinterpret_cast<Aux *>(smem_raw + STAGE_FLOATS * 4);
+    c.bm = reinterpret_cast<unsigned int *>(smem_raw + STAGE_FLOATS * 4 + ((sizeof(Aux) + 15) / 16) * 16);
+    c.V = a.V; c.R = a.R;
+    c.parbits = 0;
     Aux *A = c.A;
-    if (c.tid == 0) { mbar_init(&A->mbar[0], 1); mbar_init(&A->mbar[1], 1); fence_proxy_async(); }
+    if (c.lane == 0) {
+        for (int s = 0; s < NSTAGE; s++) mbar_init(&A->mbar[c.warp][s], 1);
+        fence_proxy_async();
+    }
     __syncthreads();
-    unsigned long long *wl = a.wlist ? a.wlist + (size_t)blockIdx.x * (size_t)a.V : nullptr;
+    {   // this warp's sixteenth of every row
+        long long beg = (long long)c.warp * a.R;
+        long long len = (long long)a.V - beg;
+        c.rbeg = (int)(beg < a.V ? beg : a.V);
+        c.rlen = (int)(len < 0 ? 0 : (len > a.R ? a.R : len));
+        c.npieces = (c.rlen + PIECE - 1) / PIECE;
+    }
+    unsigned long long *wl_seg = a.wlist + (size_t)blockIdx.x * 2 * NWARP * (size_t)a.R;   // per-warp segments
+    unsigned long long *wl_flat = wl_seg + (size_t)NWARP * (size_t)a.R;                   // contiguous copy
+    unsigned long long *slist = reinterpret_cast<unsigned long long *>(c.stage);           // list in shared memory
     const int nwords = (a.V + 31) >> 5;
 
     for (;;) {
         __syncthreads();
-        if (c.tid == 0) A->cur_row = atomicAdd(a.row_counter, 1);
+        if (c.tid == 0) {
+            int t = atomicAdd(a.row_counter, 1);
+            if (a.order && t < a.B) t = a.order[t];
+            A->cur_row = t;
+        }
         __syncthreads();
         const int r = A->cur_row;
         if (r >= a.B) break;
@@ -713,18 +837,16 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
 
         if (a.penalised) {
             float *dst = a.penalised + (long long)r * a.V;
-            tiles_begin(c);
-            for (int t = 0; t < c.ntiles; t++) {
-                int n_tile;
-                const float *buf = tile_acquire(c, t, n_tile);
-                const int c0 = min(n_tile, c.tid * LT), c1 = min(n_tile, (c.tid + 1) * LT);
-                const int g0 = t * TILE + c0;
-                const unsigned int pm = (c1 > c0) ? patch_mask(c, g0) : 0u;
-                for (int j = 0; c0 + j < c1; j++) {
-                    float x = buf[c0 + j];
-                    if ((pm >> j) & 1u) x = patch_lookup(c, g0 + j, x);
-                    dst[g0 + j] = x;
-                }
+            pieces_begin(c);
+            for (int p = 0; p < c.npieces; p++) {
+                int n;
+                const float *slot = piece_acquire(c, p, n);
+                const int g0 = c.rbeg + p * PIECE + c.lane * LT;
+                float x[LT];
+                load_chunk(c, slot, n, g0, x);
+#pragma unroll
+                for (int j = 0; j < LT; j++)
+                    if (c.lane * LT + j < n) dst[g0 + j] = x[j];
             }
             if (a.penalised_only) continue;
         }
@@ -732,28 +854,29 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         // ---- 2. pass A (HBM): the maximum and its first index (kernel.mojo:571-585, sample.mojo:342-346)
         float tmax = -INFINITY;
         int tidx = 0x7fffffff, teq = 0;
-        tiles_begin(c);
-        for (int t = 0; t < c.ntiles; t++) {
-            int n_tile;
-            const float *buf = tile_acquire(c, t, n_tile);
-            const int c0 = min(n_tile, c.tid * LT), c1 = min(n_tile, (c.tid + 1) * LT);
-            const int g0 = t * TILE + c0;
-            const unsigned int pm = (c1 > c0) ? patch_mask(c, g0) : 0u;
-            float cm = -INFINITY;
+        {
+            float rmx = -INFINITY;
+            pieces_begin(c);
+            for (int p = 0; p < c.npieces; p++) {
+                int n;
+                const float *slot = piece_acquire(c, p, n);
+                const int g0 = c.rbeg + p * PIECE + c.lane * LT;
+                float x[LT];
+                load_chunk(c, slot, n, g0, x);
+                float cm = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < LT; j++) {
-                if (c0 + j < c1) {
-                    float x = buf[c0 + j];
-                    if ((pm >> j) & 1u) x = patch_lookup(c, g0 + j, x);
-                    cm = fmaxf(cm, x);
-                    if (x > tmax) { tmax = x; tidx = g0 + j; teq = 1; }
-                    else if (x == tmax) teq++;
+                for (int j = 0; j < LT; j++) {
+                    cm = fmaxf(cm, x[j]);
+                    if (x[j] > tmax) { tmax = x[j]; tidx = g0 + j; teq = 1; }
+                    else if (x[j] == tmax && c.lane * LT + j < n) teq++;
+                }
+                if (!greedy) {
+                    cm = warp_max(cm);
+                    if (c.lane == 0) A->u.s.pmax[c.warp][p] = cm;
+                    rmx = fmaxf(rmx, cm);
                 }
             }
-            if (!greedy) {
-                const float tm = block_max(c, cm);
-                if (c.tid == 0) A->tilemax[t] = tm;
-            }
+            if (!greedy && c.lane == 0) A->u.s.rmax[c.warp] = rmx;
         }
         float xmax = tmax;
         int imax = tidx;
@@ -782,84 +905,92 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             if (need > HEAD_NEED) need = HEAD_NEED;
             if (need > a.V) need = a.V;
             const bool p3row = !pure && (n_lim + 1 > HEAD_NEED);
+
+            // The head of the sorted order holds the `need` largest. The need-th largest of the threads'
+            // own maxima bounds the need-th largest element from below, so everything at or above it is
+            // kept for the head whether or not it can matter to a sum.
+            float tau_x = INFINITY;
             unsigned int tau_bits = 1u;
             if (!pure) {
-                // The need-th largest of the threads' own maxima bounds the need-th largest element
-                // from below: everything that can be in the head is at or above it.
                 __syncthreads();
                 A->cand[c.tid] = ((unsigned long long)fkey(tmax) << 32) | (unsigned long long)c.tid;
                 bitonic_desc(A->cand, NT, c.tid);
-                const float tau_x = fkey_inv((unsigned int)(A->cand[need - 1] >> 32));
+                tau_x = fkey_inv((unsigned int)(A->cand[need - 1] >> 32));
                 const float tv = (T == 1.0f) ? tau_x : __fdiv_rn(tau_x, T);
                 const unsigned int tb_ = __float_as_uint(expf_pinned(__fsub_rn(tv, top)));
                 tau_bits = tb_ > 1u ? tb_ : 1u;
                 __syncthreads();
             }
-            if (c.tid == 0) {
-                A->ncand = 0; A->nw = 0;
-                A->walk_s = 0.0f; A->walk_found = 0; A->walk_idx = -1; A->walk_slow = 0;
-            }
-            STAMP(3);
 
-            // ---- 3. pass B (L2): temperature, exponentials (sample.mojo:419-434), the exact softmax
-            // denominator, and the head candidates
-            double sbase = 0.0;
-            float pmx = -INFINITY;
-            long long tq0 = 0, tq1 = 0, tq2 = 0, tq3, tq0e = 0, tq5e = 0, tq0p = 0, tq5p = 0;
-            tiles_begin(c);
-            for (int t = 0; t < c.ntiles; t++) {
-                int n_tile;
-                tq3 = clock64();
-                float *buf = tile_acquire(c, t, n_tile);
-                tq0 += clock64() - tq3; tq3 = clock64();
-                const int c0 = min(n_tile, c.tid * LT), c1 = min(n_tile, (c.tid + 1) * LT);
-                const int g0 = t * TILE + c0;
-                const unsigned int pm = (c1 > c0) ? patch_mask(c, g0) : 0u;
-                const float xthr = (t == 0 || !filter_ok) ? -INFINITY : __fsub_rn(pmx, __fmul_rn(REL_MARGIN, T));
-                float e[LT];
-                float csum = 0.0f;
+            // ---- 3. pass B (L2): keep what can matter, in vocabulary order, with its exponential
+            // (temperature and softmax numerator, sample.mojo:419-434)
+            float prev = -INFINITY;  // maximum of everything before this warp's region
+            for (int w = 0; w < c.warp; w++) prev = fmaxf(prev, A->u.s.rmax[w]);
+            int base = 0;
+            unsigned long long *myseg = wl_seg + (size_t)c.warp * (size_t)a.R;
+            long long tqa = 0, tqb = 0, tqc = 0, tq0;
+            pieces_begin(c);
+            for (int p = 0; p < c.npieces; p++) {
+                int n;
+                tq0 = clock64();
+                float *slot = const_cast<float *>(piece_acquire(c, p, n));
+                tqa += clock64() - tq0; tq0 = clock64();
+                const int g0 = c.rbeg + p * PIECE + c.lane * LT;
+                float x[LT];
+                load_chunk(c, slot, n, g0, x);
+                const float thr = fminf(filter_ok ? __fsub_rn(prev, __fmul_rn(REL_MARGIN, T)) : -INFINITY, tau_x);
+                int cnt = 0;
+#pragma unroll
+                for (int j = 0; j < LT; j++) cnt += (c.lane * LT + j < n && x[j] >= thr) ? 1 : 0;
+                const int incl = warp_incl_scan(cnt, c.lane);
+                const int total = __shfl_sync(0xffffffffu, incl, 31);
+                int off = incl - cnt;
+                __syncwarp();  // every lane has its elements in registers: compact in place
 #pragma unroll
                 for (int j = 0; j < LT; j++) {
-                    float ev = 0.0f;
-                    const bool in = c0 + j < c1;
-                    if (in) {
-                        float x = buf[c0 + j];
-                        if ((pm >> j) & 1u) x = patch_lookup(c, g0 + j, x);
-                        if (x >= xthr) {
-                            const float v = (T == 1.0f) ? x : __fdiv_rn(x, T);
-                            ev = expf_pinned(__fsub_rn(v, top));
-                        }
-                        buf[c0 + j] = ev;
-                        csum = __fadd_rn(csum, ev);
-                    }
-                    e[j] = ev;
-                    const unsigned int eb = __float_as_uint(ev);
-                    if (!pure) {
-                        if (in && eb >= tau_bits) {
-                            const int pos = atomicAdd(&A->ncand, 1);
-                            if (pos < NC) A->cand[pos] = make_key(eb, g0 + j);
-                        }
-                        if (p3row) {
-                            const bool wp = in && eb >= W_BITS && eb < tau_bits;
-                            const unsigned int m = __ballot_sync(0xffffffffu, wp);
-                            if (m) {
-                                int base = 0;
-                                const int leader = __ffs(m) - 1;
-                                if (c.lane == leader) base = atomicAdd(&A->nw, __popc(m));
-                                base = __shfl_sync(0xffffffffu, base, leader);
-                                if (wp) wl[base + __popc(m & ((1u << c.lane) - 1u))] = make_key(eb, g0 + j);
-                            }
-                        }
+                    if (c.lane * LT + j < n && x[j] >= thr) {
+                        slot[off] = x[j];
+                        A->u.s.ppos[c.warp][off] = (unsigned short)(c.lane * LT + j);
+                        off++;
                     }
                 }
-                if (t == 0) tq0e = clock64() - tq3; if (t == 5) tq5e = clock64() - tq3;
-                tq1 += clock64() - tq3; tq3 = clock64();
-                p1_tile(c, e, c1 - c0, csum, buf, n_tile, (long long)t * TILE, sbase, false, 0.0f);
-                tq2 += clock64() - tq3;
-                if (t == 0) tq0p = clock64() - tq3; if (t == 5) tq5p = clock64() - tq3;
-                pmx = fmaxf(pmx, A->tilemax[t]);
+                __syncwarp();
+                tqb += clock64() - tq0; tq0 = clock64();
+                for (int i = c.lane; i < total; i += 32) {
+                    const float xx = slot[i];
+                    const float v = (T == 1.0f) ? xx : __fdiv_rn(xx, T);
+                    const float e = expf_pinned(__fsub_rn(v, top));
+                    myseg[base + i] = make_key(__float_as_uint(e), c.rbeg + p * PIECE + (int)A->u.s.ppos[c.warp][i]);
+                }
+                base += total;
+                prev = fmaxf(prev, A->u.s.pmax[c.warp][p]);
+                tqc += clock64() - tq0;
             }
-            if (a.prof && c.tid == 0) { a.prof[(long long)r * 16 + 10] = tq0; a.prof[(long long)r * 16 + 11] = tq1; a.prof[(long long)r * 16 + 12] = tq2; a.prof[(long long)r * 16 + 13] = tq0e; a.prof[(long long)r * 16 + 14] = tq5e; a.prof[(long long)r * 16 + 15] = tq0p; a.prof[(long long)r * 16 + 5] = tq5p; }
+            if (a.prof && c.tid == 32 * 5) { a.prof[(long long)r * 16 + 10] = tqa; a.prof[(long long)r * 16 + 11] = tqb; a.prof[(long long)r * 16 + 12] = tqc; a.prof[(long long)r * 16 + 13] = base; }
+            if (c.lane == 0) A->wcnt[c.warp] = base;
+            __syncthreads();
+            // offsets of the warps' segments in the whole list
+            int nl = 0;
+            {
+                int offs = 0;
+                for (int w = 0; w < NWARP; w++) { if (w == c.warp) offs = nl; nl += A->wcnt[w]; }
+                // gather the segments into one array: shared memory if it fits, else global
+                unsigned long long *dstl = (nl <= SLIST_CAP) ? slist : wl_flat;
+                for (int i = c.lane; i < base; i += 32) dstl[offs + i] = myseg[i];
+            }
+            __syncthreads();
+            const unsigned long long *lst = (nl <= SLIST_CAP) ? slist : wl_flat;
+            STAMP(3);
+
+            // ---- 4. the softmax denominator, exactly as the sequential loop rounds it
+            int L = (nl + NT - 1) / NT;
+            if ((L & 1) == 0) L += 1;
+            p1_build(c, lst, nl, L);
+            if (c.tid == 0) {
+                Walker w;
+                p1_walk(c, lst, nl, L, false, 0.0f, w);
+                A->walk_s = w.s; A->walk_slow = w.slow;
+            }
             __syncthreads();
             const float Z = A->walk_s;
             if (A->walk_slow) c.status |= MOLLA_ROW_SLOW_PATH;
@@ -867,54 +998,59 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             STAMP(4);
 
             if (pure) {
-                // ---- 4a. nothing sorted: the draw walks the vocabulary in order (sample.mojo:365-369,
-                // 580-594) over p = e / Z. Two more passes: the kept sum, then the position.
-                float sum = 0.0f, target = 0.0f;
-                for (int round = 0; round < 2; round++) {
-                    if (c.tid == 0) { A->walk_s = 0.0f; A->walk_found = 0; A->walk_idx = -1; }
-                    const bool locate = round == 1;
-                    sbase = 0.0; pmx = -INFINITY;
-                    tiles_begin(c);
-                    for (int t = 0; t < c.ntiles; t++) {
-                        int n_tile;
-                        float *buf = tile_acquire(c, t, n_tile);
-                        const int c0 = min(n_tile, c.tid * LT), c1 = min(n_tile, (c.tid + 1) * LT);
-                        const int g0 = t * TILE + c0;
-                        const unsigned int pm = (c1 > c0) ? patch_mask(c, g0) : 0u;
-                        const float xthr = (t == 0 || !filter_ok) ? -INFINITY : __fsub_rn(pmx, __fmul_rn(REL_MARGIN, T));
-                        float e[LT];
-                        float csum = 0.0f;
-#pragma unroll
-                        for (int j = 0; j < LT; j++) {
-                            float pv = 0.0f;
-                            if (c0 + j < c1) {
-                                float x = buf[c0 + j];
-                                if ((pm >> j) & 1u) x = patch_lookup(c, g0 + j, x);
-                                if (x >= xthr) {
-                                    const float v = (T == 1.0f) ? x : __fdiv_rn(x, T);
-                                    pv = __fdiv_rn(expf_pinned(__fsub_rn(v, top)), Z);
-                                }
-                                buf[c0 + j] = pv;
-                                csum = __fadd_rn(csum, pv);
-                            }
-                            e[j] = pv;
-                        }
-                        p1_tile(c, e, c1 - c0, csum, buf, n_tile, (long long)t * TILE, sbase, locate, target);
-                        pmx = fmaxf(pmx, A->tilemax[t]);
-                    }
-                    __syncthreads();
-                    if (!locate) { sum = A->walk_s; target = __fmul_rn(u01, sum); }
-                    else token = A->walk_found ? A->walk_idx : (a.V - 1);
-                    if (A->walk_slow) c.status |= MOLLA_ROW_SLOW_PATH;
+                // ---- 5a. nothing sorted: the draw walks the vocabulary in order (sample.mojo:365-369,
+                // 580-594) over p = e / Z: the same machinery on the list of probabilities
+                unsigned long long *wlst = const_cast<unsigned long long *>(lst);
+                for (int i = c.tid; i < nl; i += NT) {
+                    const unsigned long long kk = wlst[i];
+                    const float pv = __fdiv_rn(key_val(kk), Z);
+                    wlst[i] = ((unsigned long long)__float_as_uint(pv) << 32) | (kk & 0xFFFFFFFFull);
                 }
-                dsum = sum; dtarget = target;
+                __syncthreads();
+                p1_build(c, lst, nl, L);
+                if (c.tid == 0) {
+                    Walker w;
+                    p1_walk(c, lst, nl, L, false, 0.0f, w);
+                    const float sum = w.s;
+                    const float target = __fmul_rn(u01, sum);
+                    Walker w2;
+                    p1_walk(c, lst, nl, L, true, target, w2);
+                    A->b_sum = sum; A->b_target = target;
+                    A->b_idx = w2.found ? key_idx(lst[w2.at]) : (nl > 0 ? key_idx(lst[nl - 1]) : imax);
+                    A->b_aux = (w.slow | w2.slow);
+                    A->b_event = w2.found;
+                }
+                __syncthreads();
+                token = A->b_idx; dsum = A->b_sum; dtarget = A->b_target;
+                if (A->b_aux) c.status |= MOLLA_ROW_SLOW_PATH;
+                if (!A->b_event) {
+                    // the walk fell off the end: the reference returns the last token of the vocabulary,
+                    // whether or not it could matter to any sum
+                    token = a.V - 1;
+                }
             } else {
-                // ---- 4b. sorted order. The head: sorted, walked exactly (sample.mojo:497-506, :580-590)
-                const int nc = A->ncand;
-                const int nw = A->nw;
-                if (nc > NC) {
-                    c.status |= MOLLA_ROW_DEGENERATE;
-                } else {
+                // ---- 5b. sorted order. The head: the need largest, sorted, walked exactly
+                // (sample.mojo:497-506, :580-590). The need-th largest of the threads' own maxima
+                // bounds the need-th largest element from below.
+                if (c.tid == 0) A->ncand = 0;
+                __syncthreads();
+                for (int i = c.tid; i < nl; i += NT) {
+                    const unsigned long long kk = lst[i];
+                    if ((unsigned int)(kk >> 32) >= tau_bits) {
+                        const int pos = atomicAdd(&A->ncand, 1);
+                        if (pos < NC) A->cand[pos] = kk;
+                    }
+                }
+                __syncthreads();
+                int nc = A->ncand;
+                unsigned int tau_head = tau_bits;
+                if (nc > HEADC) {
+                    // more equal-or-larger values than the head holds (flat or heavily tied rows):
+                    // no head, the descending walk takes everything from the top
+                    nc = 0; tau_head = 0xFFFFFFFFu;
+                    c.status |= MOLLA_ROW_SLOW_PATH;
+                }
+                {
                     sort_cands(c, nc, Z);
                     for (int i = c.tid; i < nc; i += NT) {
                         const float p = A->pc[i];
@@ -922,6 +1058,11 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         A->hidx[i] = (unsigned int)key_idx(A->cand[i]) | (eq ? 0x80000000u : 0u);
                     }
                     __syncthreads();
+                    if (a.topk_out) {
+                        for (int i = c.tid; i < a.topk_cap; i += NT)
+                            a.topk_out[(long long)r * a.topk_cap + i] =
+                                (i < nc && (long long)i < n_lim) ? (int)(A->hidx[i] & 0x7fffffffu) : -1;
+                    }
                     if (c.tid == 0) {
                         float s = 0.0f;
                         long long pos = 0;
@@ -938,7 +1079,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                             }
                             if (pos >= n_lim) { cut = i + 1; break; }
                         }
-                        if (cut < 0 && !p3row) cut = nc;  // everything that can matter is in the head
+                        if (cut < 0 && !p3row && tau_head == tau_bits) cut = nc;  // everything that can matter is in the head
                         if (n_lim < (long long)a.V && (long long)nc > n_lim && A->pc[n_lim] == A->pc[n_lim - 1])
                             tie |= MOLLA_ROW_TOPK_TIE;
                         A->b_s = s; A->b_pos = pos; A->b_event = EV_NONE; A->b_idx = -1; A->b_p = 0.0f;
@@ -962,12 +1103,12 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     if (A->b_event == EV_DRAW) {
                         token = A->b_idx; dp = A->b_p; dsum = A->b_sum; dtarget = A->b_target;
                     } else {
-                        // ---- 5. past the head: the cut walk, then the draw walk
+                        // ---- 6. past the head: the cut walk, then the draw walk
                         __syncthreads();
-                        Walk cutw; cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_bits;
+                        Walk cutw; cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
                         cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
                         const bool limited = n_lim < (long long)a.V;
-                        descend(c, wl, nw, Z, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
+                        descend(c, lst, nl, Z, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
                         if (cutw.event != EV_DEGENERATE) {
                             if (cutw.event == EV_CUT && cutw.tie) c.status |= MOLLA_ROW_TOPP_TIE;
                             if (cutw.event == EV_LIMIT && cutw.tie) c.status |= MOLLA_ROW_TOPK_TIE;
@@ -993,9 +1134,9 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                                 bool resolved = false;
                                 if (target < sum) {
                                     __syncthreads();
-                                    Walk dw; dw.s = head_s; dw.pos = head_pos; dw.tau = tau_bits;
+                                    Walk dw; dw.s = head_s; dw.pos = head_pos; dw.tau = tau_head;
                                     dw.event = EV_NONE; dw.idx = -1; dw.p = 0; dw.tie = 0;
-                                    descend(c, wl, nw, Z, dw, 3.4e38f, target, -1);
+                                    descend(c, lst, nl, Z, dw, 3.4e38f, target, -1);
                                     if (dw.event == EV_DRAW) {
                                         token = dw.idx; dp = dw.p; resolved = true;
                                         if (dw.tie) c.status |= MOLLA_ROW_CHOSEN_TIE;
@@ -1008,15 +1149,10 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                                     if (cutw.event == EV_CUT || cutw.event == EV_LIMIT) {
                                         token = cutw.idx; dp = cutw.p;
                                     } else {
-                                        // everything was kept: the smallest listed value, highest id last
+                                        // everything listed was kept: its smallest value, highest id last
+                                        // (keys order by value, then by inverted id)
                                         unsigned long long best = ~0ull;
-                                        for (int i = c.tid; i < nw; i += NT) best = wl[i] < best ? wl[i] : best;
-                                        for (int i = c.tid; i < nc; i += NT) {
-                                            unsigned long long kk = make_key(__float_as_uint(A->pc[i]) ? 0x7f800000u : 0u, 0);
-                                            (void)kk;
-                                        }
-                                        // keys order by (value, inverted id): the minimum key is the smallest
-                                        // value with the highest id
+                                        for (int i = c.tid; i < nl; i += NT) best = lst[i] < best ? lst[i] : best;
 #pragma unroll
                                         for (int o = 16; o > 0; o >>= 1) {
                                             unsigned long long ob = __shfl_xor_sync(0xffffffffu, best, o);
@@ -1027,8 +1163,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                                         __syncthreads();
                                         best = A->wsu[0];
                                         for (int w = 1; w < NWARP; w++) best = A->wsu[w] < best ? A->wsu[w] : best;
-                                        if (nw > 0) token = key_idx(best);
-                                        else token = nc > 0 ? (int)(A->hidx[nc - 1] & 0x7fffffffu) : imax;
+                                        token = nl > 0 ? key_idx(best) : imax;
                                     }
                                 }
                             }
@@ -1150,6 +1285,8 @@ __global__ void expf_kernel(const float *x, long long n, float *out) {
 // =============================================================================
 thread_local char g_err[512] = "";
 long long *g_prof = nullptr;
+int *g_topk = nullptr;
+int g_topk_cap = 0;
 
 int fail(int code, const char *fmt, const char *detail = "") {
     snprintf(g_err, sizeof(g_err), fmt, detail);
@@ -1164,13 +1301,17 @@ int sm_count() {
 }
 
 size_t smem_bytes(int V) {
-    return (size_t)2 * TILE * 4 + ((sizeof(Aux) + 15) / 16) * 16 + (size_t)((V + 31) / 32) * 4 + 16;
+    return (size_t)STAGE_FLOATS * 4 + ((sizeof(Aux) + 15) / 16) * 16 + (size_t)((V + 31) / 32) * 4 + 16;
 }
 
-// scratch layout: [row counter, 256 bytes][per-CTA (exp bits, token id) lists, V entries each]
+int region_floats(int V) { return (((V + NWARP - 1) / NWARP) + 3) & ~3; }
+
+// scratch layout: [row counter, 256 bytes][per CTA: 16 per-warp list segments + one contiguous
+// copy, each entry an (exp bits, token id) pair]
+constexpr size_t WS_HEADER = 256 + (size_t)ORDER_CAP * 4;
 size_t batch_workspace_bytes(int B, int V, int sms) {
     const size_t ctas = (size_t)(B < sms ? B : sms);
-    return 256 + ctas * (size_t)V * 8;
+    return WS_HEADER + ctas * 2 * (size_t)NWARP * (size_t)region_floats(V) * 8;
 }
 
 int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st) {
@@ -1181,15 +1322,22 @@ int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st) {
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     const size_t smem = smem_bytes(a.V);
-    if (smem > (size_t)max_optin || a.V > MAX_TILES * TILE)
+    a.R = region_floats(a.V);
+    if (smem > (size_t)max_optin || (a.R + PIECE - 1) / PIECE > MAX_PIECES)
         return fail(MOLLA_ERR_VOCAB, "vocabulary too wide for the shared-memory bitmap and tile table%s");
     cudaError_t e = cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "cudaFuncSetAttribute(smem): %s", cudaGetErrorString(e));
     a.row_counter = (int *)d_workspace;
-    a.wlist = (unsigned long long *)((char *)d_workspace + 256);
+    a.wlist = (unsigned long long *)((char *)d_workspace + WS_HEADER);
     e = cudaMemsetAsync(d_workspace, 0, 256, st);
     if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "workspace clear failed: %s", cudaGetErrorString(e));
     const int grid = a.B < sms ? a.B : sms;
+    a.order = nullptr;
+    if (!a.penalised_only && a.B > grid && a.B <= ORDER_CAP && a.temperature) {
+        int *order = (int *)((char *)d_workspace + 256);
+        order_rows_kernel<<<1, NT, 0, st>>>(a.temperature, a.top_k, a.B, order);
+        a.order = order;
+    }
     sample_rows_kernel<<<grid, NT, smem, st>>>(a);
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
@@ -1248,6 +1396,7 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
     a.tokens = d_tokens; a.row_status = d_row_status; a.diag = d_diag;
     a.penalised = nullptr; a.penalised_only = 0;
     a.prof = g_prof;
+    a.topk_out = g_topk; a.topk_cap = g_topk_cap;
     int rc = launch_rows(a, d_workspace, st);
     if (rc != MOLLA_OK) return rc;
     if (d_chosen_logprob || top_n > 0) {
@@ -1425,6 +1574,8 @@ int32_t molla_sample_expf(const float *d_x, int64_t n, void *stream, float *d_ou
 }
 
 void molla_sample_debug_profile(void *d_stamps) { g_prof = (long long *)d_stamps; }
+
+void molla_sample_debug_topk(void *d_ids, int32_t cap) { g_topk = (int *)d_ids; g_topk_cap = d_ids ? cap : 0; }
 
 int32_t molla_sample_sync(void *stream) {
     cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);

@@ -109,6 +109,10 @@ def sample_batch(logits: torch.Tensor, p: dict, top_n: int = 0, want_logprob: bo
         raise ValueError("logit rows must be contiguous")
     B, V = logits.shape
     dev = logits.device
+    if B == 0:  # nothing to sample: the C entry point would be handed null pointers
+        e = lambda *shape, dt=torch.float32: torch.empty(shape, dtype=dt, device=dev)
+        return dict(tokens=e(0, dt=torch.int32), row_status=e(0, dt=torch.int32), chosen_logprob=e(0),
+                    top_ids=e(0, top_n, dt=torch.int32), top_logprobs=e(0, top_n), diag=e(0, 4))
     if workspace is None:
         workspace = Workspace(B, V, top_n, dev)
     if out is None:

@@ -1,0 +1,399 @@
+"""Parity of the CUDA library with the CPU oracle, through the C ABI, on a B200.
+
+Bars (the north star's): penalised logits, greedy picks, the softmax denominator and
+top-k id sets bit-exact; logprobs within 1e-5 absolute; sampled tokens identical except
+rows the library itself marks as depending on the reference's unstable sort order
+(MOLLA_ROW_*_TIE) or that the oracle marks as lying within 1e-6 of a CDF boundary; every
+exception is counted and the unexplained count must be zero.
+"""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import golden_as_batch
+from molla_b200 import capi, sampler as S, workloads as W
+
+pytestmark = pytest.mark.gpu
+
+FIVE = np.array([math.log(8), math.log(4), math.log(2), 0, 0], dtype=np.float32)
+CLOSE = np.array([3.0, 2.9, 1.0, 0.0, -1.0], dtype=np.float32)
+LOGPROB_TOL = 1e-5  # absolute, fp32 (north star)
+
+
+def run_gpu(w, dev, top_n=0, want_logprob=False, stride=None, offset=0):
+    B, V = w["logits"].shape
+    if stride is None:
+        lg = torch.from_numpy(np.ascontiguousarray(w["logits"])).to(dev)
+    else:  # rows at an odd stride / unaligned base: the plain-load path
+        flat = torch.zeros(B * stride + offset + 8, dtype=torch.float32, device=dev)
+        lg = flat[offset:offset + B * stride].view(B, stride)[:, :V]
+        lg.copy_(torch.from_numpy(np.ascontiguousarray(w["logits"])))
+    p = S.upload_params(w, dev)
+    res = S.sample_batch(lg, p, top_n=top_n, want_logprob=want_logprob, want_diag=True)
+    torch.cuda.synchronize()
+    out = {k: (v.cpu().numpy() if v is not None else None) for k, v in res.items()}
+    out["row_status"] = out["row_status"].astype(np.uint32)
+    out["logits_t"], out["params_t"] = lg, p
+    return out
+
+
+def compare(w, dev, oracle, tag, top_n=0, stride=None, offset=0, max_exception_frac=0.05):
+    kw = {k: w[k] for k in W.SAMPLER_KEYS}
+    ref = oracle.pick_batch(w["logits"], **kw, want_penalised=True, kept_ids_cap=128)
+    got = run_gpu(w, dev, top_n=top_n, want_logprob=True, stride=stride, offset=offset)
+    st = got["row_status"]
+    assert not np.any(st & np.uint32(capi.ROW_ERROR_BITS)), (tag, np.unique(st))
+    # penalised logits: bit-exact
+    pen = S.penalised(got["logits_t"], got["params_t"]).cpu().numpy()
+    assert np.array_equal(pen.view(np.uint32), ref["penalised"].view(np.uint32)), tag
+    greedy = ~(w["temperature"] > 0)
+    assert np.array_equal(got["tokens"][greedy], ref["tokens"][greedy]), tag
+    sampled = (~greedy) & (w["top_k"] != 1)
+    # the softmax denominator: bit-exact
+    assert np.array_equal(got["diag"][sampled, 0].view(np.uint32), ref["z_sum"][sampled].view(np.uint32)), tag
+    mism = got["tokens"] != ref["tokens"]
+    tie = (st & np.uint32(capi.ROW_TIE_BITS)) != 0
+    otie = (ref["flags"] & (oracle.FLAG_TOPK_TIE | oracle.FLAG_TOPP_TIE | oracle.FLAG_CHOSEN_TIE)) != 0
+    edge = (ref["flags"] & oracle.FLAG_CDF_EDGE) != 0
+    unexplained = mism & ~tie & ~otie & ~edge
+    assert not unexplained.any(), (tag, np.nonzero(unexplained)[0][:8], got["tokens"][unexplained][:8],
+                                   ref["tokens"][unexplained][:8])
+    assert mism.sum() <= max(1, int(max_exception_frac * len(mism))), (tag, int(mism.sum()))
+    # where the tokens agree, the kept-mass sum and the draw target agree bit for bit
+    ok = sampled & ~mism & ~tie & ~otie
+    assert np.array_equal(got["diag"][ok, 1].view(np.uint32), ref["keep_sum"][ok].view(np.uint32)), tag
+    assert np.array_equal(got["diag"][ok, 2].view(np.uint32), ref["target"][ok].view(np.uint32)), tag
+    # logprobs of the raw logits
+    lp = oracle.logprobs_batch(w["logits"], tokens=got["tokens"], top_n=top_n)
+    assert np.max(np.abs(got["chosen_logprob"] - lp["chosen_logprob"])) <= LOGPROB_TOL, tag
+    if top_n:
+        assert np.array_equal(got["top_ids"], lp["top_ids"]), tag
+        assert np.max(np.abs(got["top_logprobs"] - lp["top_logprobs"])) <= LOGPROB_TOL, tag
+    return dict(rows=len(mism), mismatches=int(mism.sum()), tie_rows=int((tie | otie).sum()), cdf_edge=int(edge.sum()))
+
+
+def topk_sets(w, dev, cap=128):
+    B = w["logits"].shape[0]
+    buf = torch.full((B, cap), -1, dtype=torch.int32, device=dev)
+    capi.lib().molla_sample_debug_topk(C.c_void_p(buf.data_ptr()), cap)
+    try:
+        got = run_gpu(w, dev)
+    finally:
+        capi.lib().molla_sample_debug_topk(None, 0)
+    return buf.cpu().numpy(), got
+
+
+# ---- the pinned exponential ----------------------------------------------------------------
+
+def test_expf_is_bit_identical_to_the_oracle(dev, lib, oracle, golden):
+    xs = np.concatenate([golden["exp_x"], -np.random.default_rng(1).random(200000).astype(np.float32) * 104,
+                         np.float32([0, -1e-8, -3e-8, -104.0, -103.9, -87.5, -88.0, -120.0])]).astype(np.float32)
+    got = S.expf_device(torch.from_numpy(xs).to(dev)).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), oracle.expf(xs).view(np.uint32))
+    n = len(golden["exp_x"])
+    assert np.array_equal(got[:n].view(np.uint32), golden["exp_y"].view(np.uint32))
+
+
+# ---- golden vectors ------------------------------------------------------------------------
+
+def test_golden_vectors(dev, lib, golden):
+    for name in golden["names"]:
+        w, c = golden_as_batch(golden, str(name))
+        got = run_gpu(w, dev, want_logprob=False)
+        assert not np.any(got["row_status"] & np.uint32(capi.ROW_ERROR_BITS)), name
+        clean = (got["row_status"] & np.uint32(capi.ROW_TIE_BITS)) == 0
+        assert np.array_equal(got["tokens"][clean], c["tokens"][clean]), name
+        assert clean.sum() >= len(clean) - 1, name
+        if c["temperature"] > 0 and c["top_k"] != 1:
+            assert np.array_equal(got["diag"][:, 0].view(np.uint32), c["z_sum"].view(np.uint32)), name
+        pen = S.penalised(got["logits_t"], got["params_t"]).cpu().numpy()
+        assert np.array_equal(pen.view(np.uint32), c["penalised"].view(np.uint32)), name
+        lp = S.logprobs_block(got["logits_t"][:1]).cpu().numpy()[0]
+        assert np.max(np.abs(lp - c["logprobs"])) <= LOGPROB_TOL, name
+
+
+# ---- the reference's own test cases, through the Sampler interface ----------------------------
+
+def gpu_reachable(dev, logits, draws, **cfg):
+    w = W._base(draws, len(logits), 0)
+    w["logits"] = np.repeat(np.asarray(logits, np.float32)[None, :], draws, 0)
+    seed = cfg.pop("seed", 0)
+    w["seed"][:] = seed
+    w["drawn"] = np.arange(draws, dtype=np.uint64)
+    for k, v in cfg.items():
+        w[k][:] = v
+    got = run_gpu(w, dev)
+    assert not np.any(got["row_status"] & np.uint32(capi.ROW_ERROR_BITS))
+    return len(set(got["tokens"].tolist()))
+
+
+def test_reference_properties(dev, lib):
+    V = 5
+    mk = lambda **kw: S.Sampler(S.SamplerConfig(**kw), V, device=dev)
+    five = torch.from_numpy(FIVE).to(dev)
+    close = torch.from_numpy(CLOSE).to(dev)
+    # greedy (test_sample.mojo:72-106)
+    s = mk()
+    assert [s.pick(five) for _ in range(5)] == [0] * 5
+    assert mk().pick(torch.full((V,), 2.0, device=dev)) == 0
+    assert mk().pick(torch.tensor([800.0, 900.0, 100.0, 0.0, -900.0], device=dev)) == 1
+    # seeds (:109-148): the sequence both restatements of the reference give
+    s = mk(temperature=1.0, seed=20260901)
+    seq = [s.pick(five) for _ in range(20)]
+    assert seq == [0, 1, 4, 2, 1, 1, 1, 2, 0, 0, 3, 0, 3, 0, 2, 1, 1, 0, 1, 1]
+    s.reset()
+    assert [s.pick(five) for _ in range(20)] == seq
+    o = mk(temperature=1.0, seed=20260902)
+    assert [o.pick(five) for _ in range(20)] != seq
+    # counter (:151-197): a second sequence drawing in between changes nothing
+    mine, theirs = mk(temperature=1.0, seed=4242), mk(temperature=1.0, seed=777)
+    alone = mk(temperature=1.0, seed=4242)
+    ref = [alone.pick(five) for _ in range(12)]
+    out = []
+    for _ in range(12):
+        theirs.pick(five); out.append(mine.pick(five)); theirs.pick(five)
+    assert out == ref
+    # temperature, top-k, top-p (:200-292)
+    assert gpu_reachable(dev, FIVE, 200, temperature=0.01, seed=5) == 1
+    assert gpu_reachable(dev, FIVE, 200, temperature=100.0, seed=5) == V
+    assert gpu_reachable(dev, FIVE, 400, temperature=1.0, seed=5) == V
+    assert gpu_reachable(dev, FIVE, 200, temperature=1.0, seed=11, top_k=1) == 1
+    assert gpu_reachable(dev, FIVE, 400, temperature=1.0, seed=11, top_k=2) == 2
+    assert gpu_reachable(dev, FIVE, 400, temperature=1.0, seed=11, top_k=V + 10) == V
+    assert gpu_reachable(dev, FIVE, 200, temperature=1.0, seed=13, top_p=0.5) == 1
+    assert gpu_reachable(dev, FIVE, 400, temperature=1.0, seed=13, top_p=0.7) == 2
+    assert gpu_reachable(dev, FIVE, 600, temperature=1.0, seed=13, top_p=0.8) == 3
+    # penalties (:364-444)
+    assert mk().pick(close) == 0
+    s = mk(frequency_penalty=0.2)
+    assert (s.pick(close), s.pick(close)) == (0, 1)
+    s = mk(presence_penalty=0.2)
+    for _ in range(3):
+        s.observe(0)
+    assert s.pick(close) == 1
+    s = mk(repeat_penalty=1.5); s.observe(0); assert s.pick(close) == 1
+    s = mk(repeat_penalty=1.5)
+    for i in range(V):
+        s.observe(i)
+    assert s.pick(close) != 4
+    s = mk(frequency_penalty=0.2, repeat_last_n=0)
+    for _ in range(3):
+        s.observe(0)
+    assert s.pick(close) == 0
+    # bias (:447-521)
+    s = mk(); s.bias(2, 10.0); assert s.pick(five) == 2
+    s = mk(); s.bias(0, -100.0); assert s.pick(five) == 1
+    s = mk(); s.bias(2, 1.0); s.bias(2, 1.0); assert s.pick(five) == 2
+    s = mk(); s.bias(2, 1.0); assert s.pick(five) == 0
+    s = mk(temperature=2.0, seed=11)
+    for t in (0, 1, 3, 4):
+        s.bias(t, -100.0)
+    assert {s.pick(five) for _ in range(50)} == {2}
+    s = mk(frequency_penalty=11.0); s.bias(2, 10.0)
+    assert s.pick(five) == 2 and s.pick(five) != 2
+    # logprobs (:524-575)
+    s = mk(temperature=0.5, frequency_penalty=1.0, seed=23)
+    s.observe(0); s.observe(0)
+    out = s.logprobs(five).cpu().numpy()[0]
+    assert abs(np.exp(out).sum() - 1.0) <= 1e-5
+    assert np.allclose(out[:3], np.log([0.5, 0.25, 0.125]), atol=1e-5)
+    assert np.allclose(s.logprobs(five + 500.0).cpu().numpy()[0], out, atol=1e-4)
+    # errors (:578-645)
+    with pytest.raises(ValueError):
+        mk().pick(torch.zeros(7, device=dev))
+    with pytest.raises(ValueError):
+        mk().pick(five, row=3)
+    with pytest.raises(NotImplementedError):
+        mk(temperature=1.0, min_p=0.3).pick(five)
+
+
+def test_device_argmax_cases(dev, lib):
+    """tests/test_gpu_ops.mojo:365-407: planted maximum, all-equal tie, all-negative row."""
+    x = np.array([(i * 37 % 101) * 0.01 for i in range(777)], np.float32)
+    x[513] = 50.0
+    neg = np.array([-1000.0 - (i * 13) % 91 for i in range(777)], np.float32)
+    w = W._base(3, 777, 0)
+    w["logits"] = np.stack([x, np.ones(777, np.float32), neg])
+    got = run_gpu(w, dev)
+    assert got["tokens"].tolist() == [513, 0, int(np.argmax(neg))]
+
+
+# ---- the benchmark configurations -------------------------------------------------------------
+
+def test_config1(dev, lib, oracle):
+    r = compare(W.config1(), dev, oracle, "c1")
+    assert r["mismatches"] == 0
+
+
+def test_config2_with_top5_logprobs(dev, lib, oracle):
+    compare(W.config2(), dev, oracle, "c2", top_n=5)
+
+
+def test_config3_full(dev, lib, oracle):
+    r = compare(W.config3(), dev, oracle, "c3")
+    print("c3 exceptions:", r)
+
+
+def test_config4_reduced_rows(dev, lib, oracle):
+    compare(W.config4(B=96), dev, oracle, "c4")
+
+
+def test_topk_sets_are_bit_exact(dev, lib, oracle):
+    w = W.config3(seed=31, B=96)
+    ids, got = topk_sets(w, dev)
+    kw = {k: w[k] for k in W.SAMPLER_KEYS}
+    ref = oracle.pick_batch(w["logits"], **kw, kept_ids_cap=128)
+    checked = 0
+    for r in range(w["B"]):
+        k = int(w["top_k"][r])
+        if not (w["temperature"][r] > 0 and 1 < k < 128):
+            continue
+        if (ref["flags"][r] & (oracle.FLAG_TOPK_TIE | oracle.FLAG_KEPT_TIE)) or (got["row_status"][r] & capi.ROW_TIE_BITS):
+            continue  # which of two equal probabilities the sort keeps first is the sort's choice
+        assert ids[r, :k].tolist() == ref["kept_ids"][r, :k].tolist(), r
+        assert np.all(ids[r, k:] == -1)
+        checked += 1
+    assert checked >= 30
+
+
+# ---- edge cases ---------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("V", [5, 33, 1000, 11264, 11265, 22529, 32000])
+def test_vocabulary_sizes_and_tile_edges(dev, lib, oracle, V):
+    compare(W.config3(seed=100 + V, B=24, V=V, H=16), dev, oracle, f"V={V}", max_exception_frac=0.2)
+
+
+@pytest.mark.parametrize("stride_pad,offset", [(1, 0), (3, 1), (4, 2), (0, 3)])
+def test_unaligned_rows(dev, lib, oracle, stride_pad, offset):
+    w = W.config3(seed=7, B=12, V=12001, H=32)
+    compare(w, dev, oracle, "unaligned", stride=12001 + stride_pad, offset=offset, max_exception_frac=0.2)
+
+
+def test_extremes(dev, lib, oracle):
+    V = 4096
+    rng = np.random.default_rng(3)
+    base = (3.0 * rng.standard_normal(V)).astype(np.float32)
+    rows, cfg = [], []
+    def add(row, **kw):
+        rows.append(row.astype(np.float32)); cfg.append(kw)
+    add(np.full(V, 2.0), temperature=0.0)                                  # all equal, greedy -> 0
+    add(np.full(V, 2.0), temperature=1.0, top_k=8, seed=1)                  # all equal, sampled: ties flagged
+    add(np.concatenate([[800, 900, 100, 0, -900], base[5:] * 0]), temperature=0.0)
+    add(base * 100, temperature=1.0, seed=2)                               # huge spread
+    add(base, temperature=0.001, top_k=40, seed=3)                         # nearly greedy
+    add(base, temperature=50.0, top_p=0.999999, seed=4)                    # nearly flat, cut at the very end
+    add(base, temperature=1.0, top_p=1e-6, seed=5)                         # keeps one
+    add(base, temperature=1.0, top_k=V + 10, top_p=0.5, seed=6)            # top-k past the end is off
+    add(base, temperature=1.0, top_k=V - 1, seed=7)                        # all but one
+    add(base, temperature=1.3, seed=8)                                     # nothing sorted: vocabulary order
+    add(base - 1000.0, temperature=0.9, top_k=50, top_p=0.9, seed=9)       # all very negative
+    add(np.round(base * 2) / 2, temperature=1.0, top_k=20, seed=10)        # quantised: many exact ties
+    B = len(rows)
+    w = W._base(B, V, 0)
+    w["logits"] = np.stack(rows)
+    for i, kw in enumerate(cfg):
+        for k, v in kw.items():
+            w[k][i] = v
+    kwargs = {k: w[k] for k in W.SAMPLER_KEYS}
+    ref = oracle.pick_batch(w["logits"], **kwargs)
+    got = run_gpu(w, dev)
+    st = got["row_status"]
+    assert not np.any(st & np.uint32(capi.ROW_ERROR_BITS)), st
+    assert got["tokens"][0] == 0 and got["tokens"][2] == 1
+    tie = ((st & np.uint32(capi.ROW_TIE_BITS)) != 0) | ((ref["flags"] & 7) != 0)
+    assert np.array_equal(got["tokens"][~tie], ref["tokens"][~tie])
+    assert tie[1] and not tie[3]
+    sampled = w["temperature"] > 0
+    assert np.array_equal(got["diag"][sampled, 0].view(np.uint32), ref["z_sum"][sampled].view(np.uint32))
+
+
+def test_invalid_and_unsupported_rows_are_reported_not_run(dev, lib):
+    V = 64
+    w = W._base(6, V, 0)
+    w["logits"] = np.tile(np.linspace(0, 1, V, dtype=np.float32), (6, 1))
+    w["temperature"][:] = [1.0, -1.0, 1.0, 1.0, 1.0, 0.0]
+    w["top_p"][:] = [1.0, 1.0, 0.0, 1.0, 1.0, 1.0]
+    w["repeat_penalty"][:] = [1.0, 1.0, 1.0, 0.0, 1.0, 1.0]
+    w["min_p"][:] = [0, 0, 0, 0, 0.5, 0.5]
+    got = run_gpu(w, dev)
+    st = got["row_status"]
+    assert st[0] == 0 and got["tokens"][0] >= 0
+    for r in (1, 2, 3):
+        assert st[r] & capi.ROW_INVALID_CONFIG and got["tokens"][r] == -1
+    assert st[4] & capi.ROW_UNSUPPORTED and got["tokens"][4] == -1
+    assert st[5] == 0 and got["tokens"][5] == V - 1  # greedy ignores min_p, as the reference does
+
+
+def test_window_edge_cases(dev, lib, oracle):
+    V = 2000
+    w = W.config3(seed=11, B=8, V=V, H=40)
+    w["hist"][::7] = V + 5        # ids outside the vocabulary never match a candidate
+    w["hist"][3::11] = -1
+    w["window_on"][1] = 0         # repeat_last_n = 0 turns all three penalties off
+    w["temperature"][:] = 0.0
+    w["frequency_penalty"][:] = 0.7
+    w["presence_penalty"][:] = 0.2
+    compare(w, dev, oracle, "window")
+
+
+def test_empty_batch_and_single_row(dev, lib):
+    lg = torch.zeros((0, 16), dtype=torch.float32, device=dev)
+    res = S.sample_batch(lg, {})
+    assert res["tokens"].numel() == 0
+    one = torch.arange(16, dtype=torch.float32, device=dev)[None, :]
+    res = S.sample_batch(one, {})   # no settings at all: greedy defaults
+    torch.cuda.synchronize()
+    assert res["tokens"].cpu().tolist() == [15]
+
+
+# ---- properties at the benchmark's full size --------------------------------------------------
+
+def test_full_size_properties(dev, lib):
+    w = W.config3()
+    a = run_gpu(w, dev)
+    b = run_gpu(w, dev)
+    assert np.array_equal(a["tokens"], b["tokens"])  # same inputs, same tokens
+    perm = np.random.default_rng(0).permutation(w["B"])
+    wp = dict(w)
+    wp["logits"] = w["logits"][perm]
+    for k in ("temperature", "top_k", "top_p", "min_p", "typical_p", "repeat_penalty", "frequency_penalty",
+              "presence_penalty", "seed", "drawn", "window_on"):
+        wp[k] = w[k][perm]
+    off = w["hist_off"].astype(np.int64)
+    wp["hist"] = np.concatenate([w["hist"][off[i]:off[i + 1]] for i in perm])
+    wp["hist_off"] = np.concatenate([[0], np.cumsum([off[i + 1] - off[i] for i in perm])]).astype(np.int32)
+    c = run_gpu(wp, dev)
+    assert np.array_equal(c["tokens"], a["tokens"][perm])  # rows are independent of their neighbours
+    greedy = ~(w["temperature"] > 0)
+    pen = S.penalised(a["logits_t"], a["params_t"])
+    assert np.array_equal(a["tokens"][greedy], pen.argmax(dim=1).cpu().numpy()[greedy])
+    assert np.all((a["tokens"] >= 0) & (a["tokens"] < w["V"]))
+
+
+def test_host_buffer_entry_matches_device_entry(dev, lib):
+    w = W.config3(seed=21, B=40, V=30000, H=64)
+    w["top_n"] = 3
+    got = run_gpu(w, dev, top_n=3, want_logprob=True)
+    hb = S.HostBlock(w, dev, top_n=3, want_logprob=True)
+    S.sample_batch_host(hb)
+    assert np.array_equal(hb.tokens.numpy(), got["tokens"])
+    assert np.array_equal(hb.status.numpy().astype(np.uint32), got["row_status"])
+    assert np.array_equal(hb.chosen.numpy(), got["chosen_logprob"])
+    assert np.array_equal(hb.top_ids.numpy(), got["top_ids"])
+
+
+def test_pick_rows_is_the_batched_decode_step(dev, lib, oracle):
+    """Replaces the loop at batch.mojo:509-511: rows of one block, one sampler each."""
+    V, n = 3000, 6
+    rng = np.random.default_rng(5)
+    block = torch.from_numpy((3 * rng.standard_normal((n, V))).astype(np.float32)).to(dev)
+    cfgs = [S.SamplerConfig(temperature=0.8, top_k=30, seed=i, repeat_penalty=1.2) for i in range(n)]
+    batch = [S.Sampler(c, V, device=dev) for c in cfgs]
+    solo = [S.Sampler(c, V, device=dev) for c in cfgs]
+    for step in range(3):
+        toks = S.pick_rows(block, batch)
+        assert toks == [s.pick(block, row=i) for i, s in enumerate(solo)]
+        assert all(s.drawn == step + 1 for s in batch)
