@@ -60,7 +60,7 @@ constexpr int HSLOTS = 2048;         // hash slots for penalised / biased tokens
 constexpr int PATCH_MAX = 1024;      // window + bias entries per row
 constexpr short SUS = -32768;        // chunk that must be replayed sequentially
 constexpr int TOPN_MAX = 20;
-constexpr float REL_MARGIN = 18.0f;  // > 25.25 ln 2 = 17.5: below this nothing can matter
+constexpr float REL_MARGIN = 17.6f;  // > 25 ln 2 = 17.33: this far below ln(running sum) nothing can matter
 constexpr int STAGE_FLOATS = NWARP * NSTAGE * PIECE;       // 22528 floats = 90112 bytes
 constexpr int SLIST_CAP = STAGE_FLOATS / 2;                 // list entries that fit the stage area
 constexpr int ORDER_CAP = 4096;      // rows whose order is sorted by cost inside the kernel
@@ -95,7 +95,8 @@ struct __align__(16) Aux {
             unsigned short seg[NT];
         } p1;
         struct {
-            unsigned long long hq[NBINS];
+            unsigned int hq[NBINS];   // low words of the per-bin integer mass
+            unsigned int hqh[NBINS];  // carries out of the low words
             unsigned int hc[NBINS];
         } h;
         struct {                                 // the streaming passes only
@@ -117,6 +118,7 @@ struct __align__(16) Aux {
     float wsf[NWARP + 1];
     int wsi[NWARP + 1];
     int wcnt[NWARP + 1];             // per warp: entries it put on the list
+    int woff[NWARP + 1];             // their offsets in the whole list
     int nseg;
     int ncand;
     int cur_row;
@@ -284,6 +286,18 @@ __device__ __forceinline__ void load_chunk(const Ctx &c, const float *slot, int 
     }
 }
 
+// Block-strided loop over a list with four loads in flight per thread (the lists of hot rows
+// live in global memory; one dependent load per iteration would leave the loop latency-bound).
+template <class F>
+__device__ __forceinline__ void for_list(const unsigned long long *lst, int nl, int tid, F f) {
+    int i = tid;
+    for (; i + 3 * NT < nl; i += 4 * NT) {
+        const unsigned long long k0 = lst[i], k1 = lst[i + NT], k2 = lst[i + 2 * NT], k3 = lst[i + 3 * NT];
+        f(i, k0); f(i + NT, k1); f(i + 2 * NT, k2); f(i + 3 * NT, k3);
+    }
+    for (; i < nl; i += NT) f(i, lst[i]);
+}
+
 // =============================================================================
 // The exact sequential fp32 sum of the list's values, in list (= vocabulary) order.
 // =============================================================================
@@ -313,14 +327,14 @@ __device__ __forceinline__ void p1_sim(const unsigned long long *lst, int i0, in
     w.s = s;
 }
 
-__device__ void p1_build(Ctx &c, const unsigned long long *lst, int n, int L) {
+__device__ void p1_build(Ctx &c, const unsigned long long *lst, int n, int L, double sbase) {
     Aux *A = c.A;
     const float EPS = 1.0f / 4096.0f;
     const int i0 = min(n, c.tid * L), i1 = min(n, (c.tid + 1) * L);
     float csum = 0.0f;
     for (int i = i0; i < i1; i++) csum = __fadd_rn(csum, lval(lst, i));
     double tot;
-    const double sst = block_excl_scan<double>((double)csum, A->wsd, &tot);
+    const double sst = sbase + block_excl_scan<double>((double)csum, A->wsd, &tot);
     short ja = SUS;
     unsigned char dual = 0;
     float da = 0.0f, db = 0.0f;
@@ -368,10 +382,9 @@ __device__ void p1_build(Ctx &c, const unsigned long long *lst, int n, int L) {
     __syncthreads();
 }
 
-// thread 0 only
+// thread 0 only; continues from the state in `w`
 __device__ void p1_walk(Ctx &c, const unsigned long long *lst, int n, int L, bool locate, float target, Walker &w) {
     Aux *A = c.A;
-    w.s = 0.0f; w.found = 0; w.at = -1; w.slow = 0;
     const int nseg = A->nseg;
     const double *PA = A->u.p1.pa, *PB = A->u.p1.pb;
     for (int si = 0; si < nseg && !(locate && w.found); si++) {
@@ -450,6 +463,40 @@ __device__ void p1_walk(Ctx &c, const unsigned long long *lst, int n, int L, boo
     }
 }
 
+// The whole list, exactly: in one go when it sits in shared memory, else in blocks staged
+// there (`stage_lst`, SLIST_CAP entries) with the exact sum carried from block to block.
+// Result in A->walk_s (and A->walk_found / A->walk_idx = list position when locating).
+__device__ void p1_run(Ctx &c, const unsigned long long *lst, int nl, bool in_smem, unsigned long long *stage_lst,
+                       bool locate, float target) {
+    Aux *A = c.A;
+    __syncthreads();
+    if (c.tid == 0) { A->walk_s = 0.0f; A->walk_found = 0; A->walk_idx = -1; }
+    __syncthreads();
+    const int nblk = in_smem ? 1 : (nl + SLIST_CAP - 1) / SLIST_CAP;
+    for (int b = 0; b < nblk; b++) {
+        const unsigned long long *blk = lst;
+        int n = nl;
+        if (!in_smem) {
+            n = min(SLIST_CAP, nl - b * SLIST_CAP);
+            __syncthreads();
+            for_list(lst + (size_t)b * SLIST_CAP, n, c.tid, [&](int i, unsigned long long k) { stage_lst[i] = k; });
+            blk = stage_lst;
+        }
+        __syncthreads();
+        if (locate && A->walk_found) break;
+        int L = (n + NT - 1) / NT;
+        if ((L & 1) == 0) L += 1;
+        p1_build(c, blk, n, L, (double)A->walk_s);
+        if (c.tid == 0) {
+            Walker w; w.s = A->walk_s; w.found = 0; w.at = -1; w.slow = A->walk_slow;
+            p1_walk(c, blk, n, L, locate, target, w);
+            A->walk_s = w.s; A->walk_slow = w.slow;
+            if (w.found) { A->walk_found = 1; A->walk_idx = b * SLIST_CAP + w.at; }
+        }
+        __syncthreads();
+    }
+}
+
 // =============================================================================
 // Histogram search: thread t owns bins NBINS-1-BPT*t-i (i < BPT), so a scan over the
 // threads runs through the bins in descending order.
@@ -466,7 +513,7 @@ __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
 #pragma unroll
     for (int i = 0; i < BPT; i++) {
         const int b = NBINS - 1 - BPT * c.tid - i;
-        q[i] = A->u.h.hq[b]; n[i] = A->u.h.hc[b];
+        q[i] = (unsigned long long)A->u.h.hq[b] | ((unsigned long long)A->u.h.hqh[b] << 32); n[i] = A->u.h.hc[b];
         sq += q[i]; sn += n[i];
     }
     unsigned long long tq, tc;
@@ -492,16 +539,15 @@ __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
     __syncthreads();
 }
 
-// Sort the candidate list (descending value, ascending token id) and turn the
-// exponentials into probabilities p = e / Z (sample.mojo:437-438).
-__device__ void sort_cands(Ctx &c, int n, float Z) {
+// Sort the candidate list (descending probability, ascending token id).
+__device__ void sort_cands(Ctx &c, int n) {
     Aux *A = c.A;
     int n2 = 2;
     while (n2 < n) n2 <<= 1;
     __syncthreads();
     for (int i = n + c.tid; i < n2; i += NT) A->cand[i] = 0ull;
     bitonic_desc(A->cand, n2, c.tid);
-    for (int i = c.tid; i < n; i += NT) A->pc[i] = __fdiv_rn(key_val(A->cand[i]), Z);
+    for (int i = c.tid; i < n; i += NT) A->pc[i] = key_val(A->cand[i]);
     __syncthreads();
 }
 
@@ -545,7 +591,7 @@ __device__ int nth_equal(Ctx &c, const unsigned long long *lst, int nl, unsigned
     return A->b_idx;
 }
 
-__device__ void descend(Ctx &c, const unsigned long long *lst, int nl, float Z, Walk &w, float x_ge, float x_gt,
+__device__ void descend(Ctx &c, const unsigned long long *lst, int nl, Walk &w, float x_ge, float x_gt,
                         long long nstop) {
     Aux *A = c.A;
     const bool counting = nstop >= 0;
@@ -557,7 +603,7 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, float Z, 
     int shift = BIN_SHIFT;
     for (int phase = 0; phase < 8192; phase++) {
         __syncthreads();
-        for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0ull; A->u.h.hc[i] = 0u; }
+        for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0u; A->u.h.hqh[i] = 0u; A->u.h.hc[i] = 0u; }
         if (c.tid == 0) { A->specbin = -1; A->ncand = 0; }
         __syncthreads();
         const bool have_s = w.s > 0.0f;
@@ -565,23 +611,26 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, float Z, 
         const bool binade_ok = have_s && j >= -100 && j <= 100;
         const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1);
         const float inv_u = fpow2(23 - j);
-        for (int i = c.tid; i < nl; i += NT) {
-            const unsigned int eb = (unsigned int)(lst[i] >> 32);
-            if (eb >= w.tau || eb < lo) continue;
+        for_list(lst, nl, c.tid, [&](int, unsigned long long key) {
+            const unsigned int eb = (unsigned int)(key >> 32);
+            if (eb >= w.tau || eb < lo) return;
             const int bin = (int)((eb - lo) >> shift);
-            if (!binade_ok) { atomicAdd(&A->u.h.hc[bin], 1u); continue; }
-            const float p = __fdiv_rn(__uint_as_float(eb), Z);
+            if (!binade_ok) { atomicAdd(&A->u.h.hc[bin], 1u); return; }
+            const float p = __uint_as_float(eb);
             const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
             const float r = __fsub_rn(p, q);
             if (fabsf(r) == halfu || p >= bigthr) {
                 atomicMax(&A->specbin, bin);
                 if (counting) atomicAdd(&A->u.h.hc[bin], 1u);
-                continue;
+                return;
             }
             const unsigned int qu = __float2uint_rn(__fmul_rn(q, inv_u));
-            if (qu) atomicAdd(&A->u.h.hq[bin], (unsigned long long)qu);
+            if (qu) {
+                const unsigned int old = atomicAdd(&A->u.h.hq[bin], qu);
+                if (old + qu < old) atomicAdd(&A->u.h.hqh[bin], 1u);
+            }
             if (counting) atomicAdd(&A->u.h.hc[bin], 1u);
-        }
+        });
         __syncthreads();
         BinQuery qy;
         qy.specbin = A->specbin;
@@ -617,14 +666,13 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, float Z, 
         const unsigned int blo = lo + ((unsigned int)hb << shift);
         const unsigned long long bhi64 = (unsigned long long)lo + ((unsigned long long)(hb + 1) << shift);
         const unsigned int bhi = bhi64 > 0xFFFFFFFFull ? 0xFFFFFFFFu : (unsigned int)bhi64;
-        for (int i = c.tid; i < nl; i += NT) {
-            const unsigned long long key = lst[i];
+        for_list(lst, nl, c.tid, [&](int, unsigned long long key) {
             const unsigned int eb = (unsigned int)(key >> 32);
             if (eb < w.tau && eb >= blo && eb < bhi) {
                 int pos = atomicAdd(&A->ncand, 1);
                 if (pos < NC) A->cand[pos] = key;
             }
-        }
+        });
         __syncthreads();
         const int nb = A->ncand;
         // what lies above the bin is consumed without an event either way
@@ -641,7 +689,7 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, float Z, 
             // one value, more copies than the buffer holds: add them one at a time (thread 0), then
             // find which copy, in token order, the event fell on
             c.status |= MOLLA_ROW_SLOW_PATH;
-            const float pv = __fdiv_rn(__uint_as_float(blo), Z);
+            const float pv = __uint_as_float(blo);
             __syncthreads();
             if (c.tid == 0) {
                 float s = s_bin;
@@ -668,7 +716,7 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, float Z, 
             w.tau = blo;
             continue;
         }
-        sort_cands(c, nb, Z);
+        sort_cands(c, nb);
         if (c.tid == 0) {
             float s = s_bin;
             long long pos = pos_bin;
@@ -924,8 +972,30 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
 
             // ---- 3. pass B (L2): keep what can matter, in vocabulary order, with its exponential
             // (temperature and softmax numerator, sample.mojo:419-434)
-            float prev = -INFINITY;  // maximum of everything before this warp's region
-            for (int w = 0; w < c.warp; w++) prev = fmaxf(prev, A->u.s.rmax[w]);
+            // A lower bound on the running sum at every piece: each earlier piece adds at least the
+            // exponential of its own maximum. What is below half an ulp of that bound is dropped.
+            {
+                const int maxp = (a.R + PIECE - 1) / PIECE;
+                for (int idx = c.tid; idx < NWARP * maxp; idx += NT) {
+                    const int w = idx / maxp, p = idx - w * maxp;
+                    long long rl = (long long)a.V - (long long)w * a.R;
+                    const int rlen = (int)(rl < 0 ? 0 : (rl > a.R ? a.R : rl));
+                    if (p * PIECE < rlen) {
+                        const float x = A->u.s.pmax[w][p];
+                        const float v = (T == 1.0f) ? x : __fdiv_rn(x, T);
+                        A->u.s.pmax[w][p] = expf_pinned(__fsub_rn(v, top));
+                    }
+                }
+                __syncthreads();
+                float rs = 0.0f;
+                for (int p = c.lane; p < c.npieces; p += 32) rs += A->u.s.pmax[c.warp][p];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
+                if (c.lane == 0) A->u.s.rmax[c.warp] = rs;
+                __syncthreads();
+            }
+            float lb = 0.0f;  // bound on the sum of everything before this warp's current piece
+            for (int w = 0; w < c.warp; w++) lb += A->u.s.rmax[w];
             int base = 0;
             unsigned long long *myseg = wl_seg + (size_t)c.warp * (size_t)a.R;
             long long tqa = 0, tqb = 0, tqc = 0, tq0;
@@ -938,7 +1008,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 const int g0 = c.rbeg + p * PIECE + c.lane * LT;
                 float x[LT];
                 load_chunk(c, slot, n, g0, x);
-                const float thr = fminf(filter_ok ? __fsub_rn(prev, __fmul_rn(REL_MARGIN, T)) : -INFINITY, tau_x);
+                const float thr = fminf((filter_ok && lb > 0.0f) ? T * (top + logf(0.9f * lb) - REL_MARGIN) : -INFINITY, tau_x);
                 int cnt = 0;
 #pragma unroll
                 for (int j = 0; j < LT; j++) cnt += (c.lane * LT + j < n && x[j] >= thr) ? 1 : 0;
@@ -963,62 +1033,83 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     myseg[base + i] = make_key(__float_as_uint(e), c.rbeg + p * PIECE + (int)A->u.s.ppos[c.warp][i]);
                 }
                 base += total;
-                prev = fmaxf(prev, A->u.s.pmax[c.warp][p]);
+                lb += A->u.s.pmax[c.warp][p];
                 tqc += clock64() - tq0;
             }
             if (a.prof && c.tid == 32 * 5) { a.prof[(long long)r * 16 + 10] = tqa; a.prof[(long long)r * 16 + 11] = tqb; a.prof[(long long)r * 16 + 12] = tqc; a.prof[(long long)r * 16 + 13] = base; }
             if (c.lane == 0) A->wcnt[c.warp] = base;
             __syncthreads();
             // offsets of the warps' segments in the whole list
-            int nl = 0;
+            if (c.tid == 0) {
+                int o = 0;
+                for (int w = 0; w < NWARP; w++) { A->woff[w] = o; o += A->wcnt[w]; }
+                A->woff[NWARP] = o;
+            }
+            __syncthreads();
+            const int nl = A->woff[NWARP];
             {
-                int offs = 0;
-                for (int w = 0; w < NWARP; w++) { if (w == c.warp) offs = nl; nl += A->wcnt[w]; }
-                // gather the segments into one array: shared memory if it fits, else global
+                // gather the warps' segments into one array: shared memory if it fits, else global
                 unsigned long long *dstl = (nl <= SLIST_CAP) ? slist : wl_flat;
-                for (int i = c.lane; i < base; i += 32) dstl[offs + i] = myseg[i];
+                auto fetch = [&](int v) -> unsigned long long {
+                    int w = 0;
+#pragma unroll
+                    for (int q = 1; q < NWARP; q++) w += (v >= A->woff[q]) ? 1 : 0;
+                    return wl_seg[(size_t)w * (size_t)a.R + (size_t)(v - A->woff[w])];
+                };
+                int i = c.tid;
+                for (; i + 3 * NT < nl; i += 4 * NT) {
+                    const unsigned long long k0 = fetch(i), k1 = fetch(i + NT), k2 = fetch(i + 2 * NT), k3 = fetch(i + 3 * NT);
+                    dstl[i] = k0; dstl[i + NT] = k1; dstl[i + 2 * NT] = k2; dstl[i + 3 * NT] = k3;
+                }
+                for (; i < nl; i += NT) dstl[i] = fetch(i);
             }
             __syncthreads();
             const unsigned long long *lst = (nl <= SLIST_CAP) ? slist : wl_flat;
             STAMP(3);
 
             // ---- 4. the softmax denominator, exactly as the sequential loop rounds it
-            int L = (nl + NT - 1) / NT;
-            if ((L & 1) == 0) L += 1;
-            p1_build(c, lst, nl, L);
-            if (c.tid == 0) {
-                Walker w;
-                p1_walk(c, lst, nl, L, false, 0.0f, w);
-                A->walk_s = w.s; A->walk_slow = w.slow;
-            }
-            __syncthreads();
+            const bool in_smem = nl <= SLIST_CAP;
+            if (c.tid == 0) A->walk_slow = 0;
+            p1_run(c, lst, nl, in_smem, slist, false, 0.0f);
             const float Z = A->walk_s;
             if (A->walk_slow) c.status |= MOLLA_ROW_SLOW_PATH;
             dZ = Z;
             STAMP(4);
 
+            // probabilities p = e / Z (sample.mojo:437-438), once, in place; the head candidates are
+            // picked up on the way
+            const unsigned int tau_p = __float_as_uint(__fdiv_rn(__uint_as_float(tau_bits), Z));
+            const unsigned int tau_pb = tau_p > 1u ? tau_p : 1u;
+            __syncthreads();
+            if (c.tid == 0) A->ncand = 0;
+            __syncthreads();
+            {
+                unsigned long long *wlst = const_cast<unsigned long long *>(lst);
+                for_list(wlst, nl, c.tid, [&](int i, unsigned long long kk) {
+                    const unsigned int pb = __float_as_uint(__fdiv_rn(key_val(kk), Z));
+                    const unsigned long long nk = ((unsigned long long)pb << 32) | (kk & 0xFFFFFFFFull);
+                    wlst[i] = nk;
+                    if (!pure && pb >= tau_pb) {
+                        const int pos = atomicAdd(&A->ncand, 1);
+                        if (pos < HEADC) A->cand[pos] = nk;
+                    }
+                });
+            }
+            __syncthreads();
+
             if (pure) {
                 // ---- 5a. nothing sorted: the draw walks the vocabulary in order (sample.mojo:365-369,
-                // 580-594) over p = e / Z: the same machinery on the list of probabilities
-                unsigned long long *wlst = const_cast<unsigned long long *>(lst);
-                for (int i = c.tid; i < nl; i += NT) {
-                    const unsigned long long kk = wlst[i];
-                    const float pv = __fdiv_rn(key_val(kk), Z);
-                    wlst[i] = ((unsigned long long)__float_as_uint(pv) << 32) | (kk & 0xFFFFFFFFull);
-                }
+                // 580-594): the same exact-sum machinery on the list of probabilities
                 __syncthreads();
-                p1_build(c, lst, nl, L);
+                p1_run(c, lst, nl, in_smem, slist, false, 0.0f);
+                const float sum = A->walk_s;
+                const float target = __fmul_rn(u01, sum);
+                p1_run(c, lst, nl, in_smem, slist, true, target);
                 if (c.tid == 0) {
-                    Walker w;
-                    p1_walk(c, lst, nl, L, false, 0.0f, w);
-                    const float sum = w.s;
-                    const float target = __fmul_rn(u01, sum);
-                    Walker w2;
-                    p1_walk(c, lst, nl, L, true, target, w2);
                     A->b_sum = sum; A->b_target = target;
-                    A->b_idx = w2.found ? key_idx(lst[w2.at]) : (nl > 0 ? key_idx(lst[nl - 1]) : imax);
-                    A->b_aux = (w.slow | w2.slow);
-                    A->b_event = w2.found;
+                    A->b_event = A->walk_found;
+                    A->b_idx = A->walk_found ? key_idx(lst[A->walk_idx]) : imax;
+                    A->b_aux = A->walk_slow;
                 }
                 __syncthreads();
                 token = A->b_idx; dsum = A->b_sum; dtarget = A->b_target;
@@ -1032,18 +1123,8 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 // ---- 5b. sorted order. The head: the need largest, sorted, walked exactly
                 // (sample.mojo:497-506, :580-590). The need-th largest of the threads' own maxima
                 // bounds the need-th largest element from below.
-                if (c.tid == 0) A->ncand = 0;
-                __syncthreads();
-                for (int i = c.tid; i < nl; i += NT) {
-                    const unsigned long long kk = lst[i];
-                    if ((unsigned int)(kk >> 32) >= tau_bits) {
-                        const int pos = atomicAdd(&A->ncand, 1);
-                        if (pos < NC) A->cand[pos] = kk;
-                    }
-                }
-                __syncthreads();
                 int nc = A->ncand;
-                unsigned int tau_head = tau_bits;
+                unsigned int tau_head = tau_pb;
                 if (nc > HEADC) {
                     // more equal-or-larger values than the head holds (flat or heavily tied rows):
                     // no head, the descending walk takes everything from the top
@@ -1051,7 +1132,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     c.status |= MOLLA_ROW_SLOW_PATH;
                 }
                 {
-                    sort_cands(c, nc, Z);
+                    sort_cands(c, nc);
                     for (int i = c.tid; i < nc; i += NT) {
                         const float p = A->pc[i];
                         const bool eq = (i > 0 && A->pc[i - 1] == p) || (i + 1 < nc && A->pc[i + 1] == p);
@@ -1079,7 +1160,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                             }
                             if (pos >= n_lim) { cut = i + 1; break; }
                         }
-                        if (cut < 0 && !p3row && tau_head == tau_bits) cut = nc;  // everything that can matter is in the head
+                        if (cut < 0 && !p3row && tau_head == tau_pb) cut = nc;  // everything that can matter is in the head
                         if (n_lim < (long long)a.V && (long long)nc > n_lim && A->pc[n_lim] == A->pc[n_lim - 1])
                             tie |= MOLLA_ROW_TOPK_TIE;
                         A->b_s = s; A->b_pos = pos; A->b_event = EV_NONE; A->b_idx = -1; A->b_p = 0.0f;
@@ -1108,7 +1189,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         Walk cutw; cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
                         cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
                         const bool limited = n_lim < (long long)a.V;
-                        descend(c, lst, nl, Z, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
+                        descend(c, lst, nl, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
                         if (cutw.event != EV_DEGENERATE) {
                             if (cutw.event == EV_CUT && cutw.tie) c.status |= MOLLA_ROW_TOPP_TIE;
                             if (cutw.event == EV_LIMIT && cutw.tie) c.status |= MOLLA_ROW_TOPK_TIE;
@@ -1136,7 +1217,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                                     __syncthreads();
                                     Walk dw; dw.s = head_s; dw.pos = head_pos; dw.tau = tau_head;
                                     dw.event = EV_NONE; dw.idx = -1; dw.p = 0; dw.tie = 0;
-                                    descend(c, lst, nl, Z, dw, 3.4e38f, target, -1);
+                                    descend(c, lst, nl, dw, 3.4e38f, target, -1);
                                     if (dw.event == EV_DRAW) {
                                         token = dw.idx; dp = dw.p; resolved = true;
                                         if (dw.tie) c.status |= MOLLA_ROW_CHOSEN_TIE;
