@@ -176,7 +176,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     capi.lib()  # fail loudly here if the library is missing
 
-    w = workload(rank)
+    w = workload(rank, args.rows)
     B, V = w["logits"].shape
     p = S.upload_params(w, dev)
     host_logits = torch.from_numpy(w["logits"])
@@ -214,25 +214,27 @@ def run_ours(args):
     bad_rows = int(np.sum((status & np.uint32(capi.ROW_ERROR_BITS)) != 0))
 
     # end to end through the host-buffer entry point: pinned host block in, host tokens out
-    hb = S.HostBlock(w, dev)
-    for _ in range(2):
-        S.sample_batch_host(hb)
-    barrier()
-    e2e_steps = max(3, min(args.steps, 10))
-    t0 = time.perf_counter()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    for _ in range(e2e_steps):
-        S.sample_batch_host(hb)
-    e3.record()
-    barrier()
-    e2e_ms = max(e2.elapsed_time(e3), 1e3 * (time.perf_counter() - t0))
+    e2e_ms, e2e_steps, hb = None, 0, None
+    if not args.kernel_only:
+        hb = S.HostBlock(w, dev)
+        for _ in range(2):
+            S.sample_batch_host(hb)
+        barrier()
+        e2e_steps = max(3, min(args.steps, 10))
+        t0 = time.perf_counter()
+        e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e2.record()
+        for _ in range(e2e_steps):
+            S.sample_batch_host(hb)
+        e3.record()
+        barrier()
+        e2e_ms = max(e2.elapsed_time(e3), 1e3 * (time.perf_counter() - t0))
     clk = clocks.stop() if rank == 0 else None
 
     if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms, e2e_ms or 0.0], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+        ms, e2e_ms = float(t[0]), (float(t[1]) if e2e_ms is not None else None)
         b = torch.tensor([bad_rows], device=dev)
         dist.all_reduce(b)
         bad_rows = int(b[0])
@@ -254,7 +256,7 @@ def run_ours(args):
             traffic = json.load(open(os.path.join(ROOT, "profiles", "traffic.json"))).get("sample_rows_kernel_c3_bytes")
         except Exception:
             pass
-        cpu = cpu_baseline(w) if world == 1 else None
+        cpu = cpu_baseline(w) if (world == 1 and not args.kernel_only) else None
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -266,9 +268,10 @@ def run_ours(args):
                          "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                          "frac_of_8TBs_nominal": achieved / 8000.0, "algorithmic_bytes_per_launch": abytes,
                          "kernel": "sample_rows_kernel", "avg_launch_ms": ms_step},
-            "e2e": {"value": world * B * e2e_steps / (e2e_ms / 1e3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": hb.h2d_bytes, "d2h_bytes_per_step": hb.d2h_bytes,
-                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
+            "e2e": None if e2e_ms is None else {
+                "value": world * B * e2e_steps / (e2e_ms / 1e3), "unit": "tokens/s",
+                "h2d_bytes_per_step": hb.h2d_bytes, "d2h_bytes_per_step": hb.d2h_bytes,
+                "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
             "gpu_launches": args.steps,
             "clocks": clk,
         }
@@ -286,6 +289,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=B_ROWS, help="rows per GPU (smaller cases for profiler captures)")
+    ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
