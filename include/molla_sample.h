@@ -119,6 +119,46 @@ int32_t molla_sample_batch(
     int32_t *d_top_ids, float *d_top_logprobs, uint32_t *d_row_status, float *d_diag);
 
 /*
+ * The same sampling call for callers that must not allocate device memory. It has no
+ * counterpart in the reference.
+ *
+ * Some hosts of this library cannot call cudaMalloc where they sample: a decode loop whose
+ * memory was carved up once at start-up and handed out from a fixed arena, a plugin that
+ * runs inside another runtime's allocator and may not go round it, a step that has to keep
+ * the device heap untouched between two points. molla_sample_batch asks such a caller for a
+ * workspace it has no way to obtain. This entry point brings its own: a fixed array of
+ * MOLLA_NOALLOC_SCRATCH_BYTES bytes that is part of the library's device image, so every GPU
+ * that loads the library gives up that much memory until the process ends, whether or not
+ * this function is ever called. Inputs and outputs are still the caller's buffers, with
+ * the meaning they have in molla_sample_batch (there is no d_diag).
+ *
+ * Limits: V <= MOLLA_NOALLOC_MAX_VOCAB and B <= MOLLA_NOALLOC_MAX_ROWS, otherwise
+ * MOLLA_ERR_WORKSPACE and nothing is launched. The array holds the working lists of only a
+ * few thread blocks at large vocabularies (about 13 at V = 151936), so the call is slower
+ * than molla_sample_batch; results are the same.
+ *
+ * The first call on each device looks up the array's device address (with that device
+ * current); make that first call before starting any stream capture. Every call on a device
+ * uses the same array and leaves its contents behind; what has to start at zero is cleared
+ * on the stream at the start of each call. Two calls that overlap on one GPU (different
+ * streams, or different host threads) race on the array: run them one after the other.
+ * The function calls no cudaMalloc, cudaFree or allocating library routine.
+ */
+#define MOLLA_NOALLOC_SCRATCH_BYTES (32u << 20)
+#define MOLLA_NOALLOC_MAX_VOCAB 262144
+#define MOLLA_NOALLOC_MAX_ROWS 4096
+int32_t molla_sample_batch_noalloc(
+    const float *d_logits, int64_t row_stride, int32_t B, int32_t V,
+    const float *d_temperature, const int32_t *d_top_k, const float *d_top_p,
+    const float *d_min_p, const float *d_typical_p, const float *d_repeat_penalty,
+    const float *d_frequency_penalty, const float *d_presence_penalty,
+    const uint8_t *d_window_on, const uint64_t *d_seed, const uint64_t *d_drawn,
+    const int64_t *d_hist, const int32_t *d_hist_off, const int64_t *d_bias_ids,
+    const float *d_bias_vals, const int32_t *d_bias_off, int32_t top_n, void *stream,
+    int32_t *d_tokens, float *d_chosen_logprob, int32_t *d_top_ids, float *d_top_logprobs,
+    uint32_t *d_row_status);
+
+/*
  * The same call for a caller whose logits are in host memory, which is where the
  * reference's decode loop has them after `copy_out` (src/molla/engine/batch.mojo:
  * 504-508, `Buffer` of src/molla/nn/tensor.mojo:270-296): every argument that is a

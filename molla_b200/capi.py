@@ -16,6 +16,8 @@ LIB_PATH = os.environ.get("MOLLA_SAMPLE_LIB", os.path.join(_HERE, "lib", "libmol
 OK = 0
 ERR_ARGUMENT, ERR_VOCAB, ERR_WORKSPACE, ERR_CONFIG = -1, -2, -3, -4
 ERR_CUDA, ERR_DEVICE = 1, 2
+NOALLOC_MAX_VOCAB = 262144
+NOALLOC_MAX_ROWS = 4096
 ROW_INVALID_CONFIG = 0x001
 ROW_UNSUPPORTED = 0x002
 ROW_TOPK_TIE = 0x004
@@ -30,7 +32,7 @@ ROW_ERROR_BITS = ROW_INVALID_CONFIG | ROW_UNSUPPORTED | ROW_LOAD_TIMEOUT | ROW_D
 EXPORTS = (
     "molla_sample_abi_version", "molla_sample_last_error", "molla_sample_draw",
     "molla_sample_workspace_bytes", "molla_sample_batch", "molla_sample_host_workspace_bytes",
-    "molla_sample_batch_host", "molla_sample_penalised",
+    "molla_sample_batch_host", "molla_sample_batch_noalloc", "molla_sample_penalised",
     "molla_sample_logprobs", "molla_sample_expf", "molla_sample_sync", "molla_sample_debug_profile", "molla_sample_debug_topk",
 )
 
@@ -69,6 +71,8 @@ def lib():
     L.molla_sample_host_workspace_bytes.argtypes = [i32, i32, i64, i64, i32]
     L.molla_sample_batch_host.restype = i32
     L.molla_sample_batch_host.argtypes = [vp, i64, i32, i32] + [vp] * 16 + [i32, vp, i64, vp] + [vp] * 5
+    L.molla_sample_batch_noalloc.restype = i32
+    L.molla_sample_batch_noalloc.argtypes = [vp, i64, i32, i32] + [vp] * 16 + [i32, vp] + [vp] * 5
     L.molla_sample_penalised.restype = i32
     L.molla_sample_penalised.argtypes = [vp, i64, i32, i32] + [vp] * 9 + [vp, i64, vp, vp]
     L.molla_sample_logprobs.restype = i32

@@ -1365,6 +1365,12 @@ __global__ void expf_kernel(const float *x, long long n, float *out) {
 // Host side of the C ABI
 // =============================================================================
 thread_local char g_err[512] = "";
+
+// Scratch of the entry point that allocates nothing. It lives in the library's device image:
+// every GPU that loads the library sets these bytes aside until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[MOLLA_NOALLOC_SCRATCH_BYTES];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+void *g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};  // device address of the array, per device ordinal
 long long *g_prof = nullptr;
 int *g_topk = nullptr;
 int g_topk_cap = 0;
@@ -1395,7 +1401,7 @@ size_t batch_workspace_bytes(int B, int V, int sms) {
     return WS_HEADER + ctas * 2 * (size_t)NWARP * (size_t)region_floats(V) * 8;
 }
 
-int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st) {
+int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, int max_ctas = 0x7fffffff) {
     BatchArgs a = args_in;
     const int sms = sm_count();
     if (sms <= 0) return fail(MOLLA_ERR_CUDA, "cannot query the device%s");
@@ -1412,7 +1418,8 @@ int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st) {
     a.wlist = (unsigned long long *)((char *)d_workspace + WS_HEADER);
     e = cudaMemsetAsync(d_workspace, 0, 256, st);
     if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "workspace clear failed: %s", cudaGetErrorString(e));
-    const int grid = a.B < sms ? a.B : sms;
+    int grid = a.B < sms ? a.B : sms;
+    if (grid > max_ctas) grid = max_ctas;
     a.order = nullptr;
     if (!a.penalised_only && a.B > grid && a.B <= ORDER_CAP && a.temperature) {
         int *order = (int *)((char *)d_workspace + 256);
@@ -1488,6 +1495,74 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
         logprob_kernel<<<grid, NT, 0, st>>>(d_logits, row_stride, B, V, d_tokens, top_n, d_chosen_logprob,
                                             d_top_ids, d_top_logprobs, nullptr);
         cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
+    }
+    return MOLLA_OK;
+}
+
+int32_t molla_sample_batch_noalloc(const float *d_logits, int64_t row_stride, int32_t B, int32_t V,
+                                   const float *d_temperature, const int32_t *d_top_k, const float *d_top_p,
+                                   const float *d_min_p, const float *d_typical_p, const float *d_repeat_penalty,
+                                   const float *d_frequency_penalty, const float *d_presence_penalty,
+                                   const uint8_t *d_window_on, const uint64_t *d_seed, const uint64_t *d_drawn,
+                                   const int64_t *d_hist, const int32_t *d_hist_off, const int64_t *d_bias_ids,
+                                   const float *d_bias_vals, const int32_t *d_bias_off, int32_t top_n, void *stream,
+                                   int32_t *d_tokens, float *d_chosen_logprob, int32_t *d_top_ids,
+                                   float *d_top_logprobs, uint32_t *d_row_status) {
+    g_err[0] = 0;
+    if (!d_logits || !d_tokens || !d_row_status) return fail(MOLLA_ERR_ARGUMENT, "logits, tokens and row status are required%s");
+    if (B < 0 || V <= 0 || row_stride < V) return fail(MOLLA_ERR_ARGUMENT, "bad block shape%s");
+    if (top_n < 0 || top_n > TOPN_MAX) return fail(MOLLA_ERR_ARGUMENT, "top_n out of range%s");
+    if (top_n > 0 && (!d_top_ids || !d_top_logprobs)) return fail(MOLLA_ERR_ARGUMENT, "top_n needs its output arrays%s");
+    if ((d_hist == nullptr) != (d_hist_off == nullptr)) return fail(MOLLA_ERR_ARGUMENT, "history ids and offsets go together%s");
+    if ((d_bias_ids == nullptr) != (d_bias_off == nullptr) || (d_bias_ids && !d_bias_vals))
+        return fail(MOLLA_ERR_ARGUMENT, "bias ids, values and offsets go together%s");
+    if (V > MOLLA_NOALLOC_MAX_VOCAB)
+        return fail(MOLLA_ERR_WORKSPACE, "the built-in scratch holds rows of at most MOLLA_NOALLOC_MAX_VOCAB logits%s");
+    if (B > MOLLA_NOALLOC_MAX_ROWS)
+        return fail(MOLLA_ERR_WORKSPACE, "the built-in scratch serves at most MOLLA_NOALLOC_MAX_ROWS rows per call%s");
+    if (B == 0) return MOLLA_OK;
+    // how many CTAs' lists the fixed array holds for this vocabulary (at least one, by the limit above)
+    const size_t per_cta = 2 * (size_t)NWARP * (size_t)region_floats(V) * 8;
+    const size_t room = (size_t)MOLLA_NOALLOC_SCRATCH_BYTES - WS_HEADER;
+    const int max_ctas = (int)(room / per_cta);
+    if (max_ctas < 1) return fail(MOLLA_ERR_WORKSPACE, "the built-in scratch is too small for this vocabulary%s");
+    // Set-up, once per device: in host code the array's name is only a handle. The address the
+    // kernels can use comes from cudaGetSymbolAddress with that device current.
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return fail(MOLLA_ERR_ARGUMENT, "device ordinal out of range%s");
+    if (!g_noalloc_addr[dev]) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress((void **)&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || !ptr) return fail(MOLLA_ERR_CUDA, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        g_noalloc_addr[dev] = ptr;
+    }
+    void *ws = g_noalloc_addr[dev];
+    cudaStream_t st = (cudaStream_t)stream;
+    BatchArgs a;
+    memset(&a, 0, sizeof(a));
+    a.logits = d_logits; a.row_stride = row_stride; a.B = B; a.V = V;
+    a.temperature = d_temperature; a.top_k = d_top_k; a.top_p = d_top_p; a.min_p = d_min_p;
+    a.typical_p = d_typical_p; a.repeat_penalty = d_repeat_penalty;
+    a.frequency_penalty = d_frequency_penalty; a.presence_penalty = d_presence_penalty;
+    a.window_on = d_window_on;
+    a.seed = (const unsigned long long *)d_seed; a.drawn = (const unsigned long long *)d_drawn;
+    a.hist = (const long long *)d_hist; a.hist_off = d_hist_off;
+    a.bias_ids = (const long long *)d_bias_ids; a.bias_vals = d_bias_vals; a.bias_off = d_bias_off;
+    a.tokens = d_tokens; a.row_status = d_row_status; a.diag = nullptr;
+    // launch_rows clears the row counter at the head of the scratch (the one part that must start
+    // at zero); the row order and the lists behind it are written before they are read
+    int rc = launch_rows(a, ws, st, max_ctas);
+    if (rc != MOLLA_OK) return rc;
+    if (d_chosen_logprob || top_n > 0) {
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        int grid = B < sms ? B : sms;
+        logprob_kernel<<<grid, NT, 0, st>>>(d_logits, row_stride, B, V, d_tokens, top_n, d_chosen_logprob,
+                                            d_top_ids, d_top_logprobs, nullptr);
+        e = cudaGetLastError();
         if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
     }
     return MOLLA_OK;
