@@ -56,6 +56,7 @@ extern "C" {
 #define MOLLA_ROW_LOAD_TIMEOUT 0x020u   /* a bounded wait on the row load ran out; result invalid */
 #define MOLLA_ROW_SLOW_PATH 0x040u      /* informational: a sequential fallback ran for this row */
 #define MOLLA_ROW_DEGENERATE 0x080u     /* more equal values than the candidate buffer holds; token = -1 */
+#define MOLLA_ROW_SHARD_OVERFLOW 0x100u /* vocab-sharded form: a shard's list outgrew the exchange buffer */
 
 /* Replaces nothing in the reference; lets a binding check what it loaded. */
 int32_t molla_sample_abi_version(void);
@@ -117,6 +118,61 @@ int32_t molla_sample_batch(
     const float *d_bias_vals, const int32_t *d_bias_off, int32_t top_n, void *d_workspace,
     int64_t workspace_bytes, void *stream, int32_t *d_tokens, float *d_chosen_logprob,
     int32_t *d_top_ids, float *d_top_logprobs, uint32_t *d_row_status, float *d_diag);
+
+/*
+ * Vocab-sharded form, for a tensor-parallel LM head: GPU g holds columns
+ * [col0, col0 + V_local) of every row of a vocabulary of V_global. The reference has no
+ * multi-GPU mode (docs/roadmap.md:74,80); the result is defined as `Sampler.pick`
+ * (src/molla/engine/sample.mojo:295-359) on the unsharded row, and is reproduced bit for
+ * bit because the list of logits that can matter to any of the reference's sums, kept in
+ * vocabulary order, is a sufficient statistic of a row.
+ *
+ *   stage_a   per shard: maximum, first index, ties, region maxima and the largest
+ *             per-thread maxima of the slice -> d_summary [B x summary_words] floats
+ *   (all-gather the summaries: [world][B][summary_words])
+ *   merge     per shard: folds them into d_global [B x 4] (global maximum, head threshold,
+ *             a bound on the softmax sum before this shard's columns, global argmax) and
+ *             answers greedy and top-k = 1 rows straight into d_tokens / d_row_status
+ *   stage_b   per shard: the slice's list of (exp bits << 32 | ~token id) entries with
+ *             global token ids -> d_list [B x list_cap], d_count [B] (-1 = outgrew list_cap)
+ *   (all-gather lists and counts: [world][B][list_cap], [world][B], shards in column order)
+ *   stage_c   on every GPU alike: penalties are already in the lists; exact softmax sum,
+ *             top-k, top-p and the draw on the concatenated list -> d_tokens, d_row_status
+ *
+ * The collectives are the caller's (NCCL all-gather over NVLink); at most 16 shards.
+ * Per-row arrays are the full batch's on every shard, windows and bias lists with global
+ * token ids. Workspaces: molla_sample_workspace_bytes(B, V_local, 0) for stages a and b,
+ * molla_sample_workspace_bytes(B, V_global, 0) for stage c.
+ */
+int32_t molla_sample_shard_summary_words(void);
+int32_t molla_sample_shard_stage_a(
+    const float *d_logits, int64_t row_stride, int32_t B, int32_t V_local, int32_t col0,
+    int32_t V_global, const float *d_temperature, const int32_t *d_top_k, const float *d_top_p,
+    const float *d_min_p, const float *d_typical_p, const float *d_repeat_penalty,
+    const float *d_frequency_penalty, const float *d_presence_penalty,
+    const uint8_t *d_window_on, const int64_t *d_hist, const int32_t *d_hist_off,
+    const int64_t *d_bias_ids, const float *d_bias_vals, const int32_t *d_bias_off,
+    void *d_workspace, int64_t workspace_bytes, void *stream, float *d_summary);
+int32_t molla_sample_shard_merge(
+    int32_t B, int32_t V_global, int32_t world, int32_t rank, const float *d_temperature,
+    const int32_t *d_top_k, const float *d_gathered_summaries, void *stream, float *d_global,
+    int32_t *d_tokens, uint32_t *d_row_status);
+int32_t molla_sample_shard_stage_b(
+    const float *d_logits, int64_t row_stride, int32_t B, int32_t V_local, int32_t col0,
+    int32_t V_global, const float *d_temperature, const int32_t *d_top_k, const float *d_top_p,
+    const float *d_min_p, const float *d_typical_p, const float *d_repeat_penalty,
+    const float *d_frequency_penalty, const float *d_presence_penalty,
+    const uint8_t *d_window_on, const int64_t *d_hist, const int32_t *d_hist_off,
+    const int64_t *d_bias_ids, const float *d_bias_vals, const int32_t *d_bias_off,
+    const float *d_global, int32_t list_cap, void *d_workspace, int64_t workspace_bytes,
+    void *stream, uint64_t *d_list, int32_t *d_count);
+int32_t molla_sample_shard_stage_c(
+    int32_t B, int32_t V_global, const float *d_temperature, const int32_t *d_top_k,
+    const float *d_top_p, const float *d_min_p, const float *d_typical_p,
+    const uint64_t *d_seed, const uint64_t *d_drawn, const float *d_global, int32_t world,
+    int32_t list_cap, const uint64_t *d_lists, const int32_t *d_counts, void *d_workspace,
+    int64_t workspace_bytes, void *stream, int32_t *d_tokens, uint32_t *d_row_status,
+    float *d_diag);
 
 /*
  * The same sampling call for callers that must not allocate device memory. It has no

@@ -26,13 +26,15 @@ ROW_CHOSEN_TIE = 0x010
 ROW_LOAD_TIMEOUT = 0x020
 ROW_SLOW_PATH = 0x040
 ROW_DEGENERATE = 0x080
+ROW_SHARD_OVERFLOW = 0x100
 ROW_TIE_BITS = ROW_TOPK_TIE | ROW_TOPP_TIE | ROW_CHOSEN_TIE
-ROW_ERROR_BITS = ROW_INVALID_CONFIG | ROW_UNSUPPORTED | ROW_LOAD_TIMEOUT | ROW_DEGENERATE
+ROW_ERROR_BITS = ROW_INVALID_CONFIG | ROW_UNSUPPORTED | ROW_LOAD_TIMEOUT | ROW_DEGENERATE | ROW_SHARD_OVERFLOW
 
 EXPORTS = (
     "molla_sample_abi_version", "molla_sample_last_error", "molla_sample_draw",
     "molla_sample_workspace_bytes", "molla_sample_batch", "molla_sample_host_workspace_bytes",
-    "molla_sample_batch_host", "molla_sample_batch_noalloc", "molla_sample_penalised",
+    "molla_sample_batch_host", "molla_sample_batch_noalloc", "molla_sample_shard_summary_words",
+    "molla_sample_shard_stage_a", "molla_sample_shard_merge", "molla_sample_shard_stage_b", "molla_sample_shard_stage_c", "molla_sample_penalised",
     "molla_sample_logprobs", "molla_sample_expf", "molla_sample_sync", "molla_sample_debug_profile", "molla_sample_debug_topk",
 )
 
@@ -73,6 +75,16 @@ def lib():
     L.molla_sample_batch_host.argtypes = [vp, i64, i32, i32] + [vp] * 16 + [i32, vp, i64, vp] + [vp] * 5
     L.molla_sample_batch_noalloc.restype = i32
     L.molla_sample_batch_noalloc.argtypes = [vp, i64, i32, i32] + [vp] * 16 + [i32, vp] + [vp] * 5
+    L.molla_sample_shard_summary_words.restype = i32
+    L.molla_sample_shard_summary_words.argtypes = []
+    L.molla_sample_shard_stage_a.restype = i32
+    L.molla_sample_shard_stage_a.argtypes = [vp, i64, i32, i32, i32, i32] + [vp] * 14 + [vp, i64, vp, vp]
+    L.molla_sample_shard_merge.restype = i32
+    L.molla_sample_shard_merge.argtypes = [i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp]
+    L.molla_sample_shard_stage_b.restype = i32
+    L.molla_sample_shard_stage_b.argtypes = [vp, i64, i32, i32, i32, i32] + [vp] * 14 + [vp, i32, vp, i64, vp, vp, vp]
+    L.molla_sample_shard_stage_c.restype = i32
+    L.molla_sample_shard_stage_c.argtypes = [i32, i32] + [vp] * 8 + [i32, i32, vp, vp, vp, i64, vp, vp, vp, vp]
     L.molla_sample_penalised.restype = i32
     L.molla_sample_penalised.argtypes = [vp, i64, i32, i32] + [vp] * 9 + [vp, i64, vp, vp]
     L.molla_sample_logprobs.restype = i32

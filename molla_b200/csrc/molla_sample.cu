@@ -63,6 +63,7 @@ constexpr int TOPN_MAX = 20;
 constexpr float REL_MARGIN = 17.6f;  // > 25 ln 2 = 17.33: this far below ln(running sum) nothing can matter
 constexpr int STAGE_FLOATS = NWARP * NSTAGE * PIECE;       // 22528 floats = 90112 bytes
 constexpr int SLIST_CAP = STAGE_FLOATS / 2;                 // list entries that fit the stage area
+constexpr int SA_WORDS = 3 + NWARP + HEAD_NEED + 1;  // max, argmax, ties, region maxima, top thread maxima
 constexpr int ORDER_CAP = 4096;      // rows whose order is sorted by cost inside the kernel
 
 struct BatchArgs {
@@ -82,6 +83,13 @@ struct BatchArgs {
     unsigned long long *wlist;   // scratch: per CTA, 2 x 16 x R list entries
     long long *prof;             // optional [B x 16] clock64 stamps per row (testing aid)
     int *topk_out; int topk_cap; // optional [B x cap] ids of the sorted head after top-k (testing aid)
+    // vocab-sharded form: this GPU holds columns [col0, col0 + V) of a vocabulary of Vg
+    int mode;                    // 0 whole pipeline; 1, 2, 3 the stages around the two all-gathers
+    int col0, Vg;
+    float *sa_out;               // stage 1 out: [B x SA_WORDS] summary of the slice
+    const float *sb_in;          // stages 2, 3 in: [B x 4] global max, head threshold, sum bound before the slice, global argmax
+    unsigned long long *sb_list; int *sb_count; int list_cap;     // stage 2 out: the slice's list
+    const unsigned long long *sc_list; const int *sc_count; int world;  // stage 3 in: [world][B][cap], [world][B]
 };
 
 struct __align__(16) Aux {
@@ -746,6 +754,58 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, Walk &w, 
     c.status |= MOLLA_ROW_DEGENERATE;
 }
 
+// Between the two all-gathers of the vocab-sharded form: one thread per row folds the shards'
+// stage-1 summaries into what stage 2 needs (the global maximum, the head threshold, a bound on
+// the softmax sum before this shard's columns) and answers the rows that need nothing more.
+__global__ void shard_merge_kernel(int B, int Vg, int world, int rank, const float *temperature, const int *top_k,
+                                   const float *gathered /*[world][B][SA_WORDS]*/, float *global4, int *tokens,
+                                   unsigned int *status) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= B) return;
+    const float T = temperature ? temperature[r] : 0.0f;
+    const int k = top_k ? top_k[r] : 0;
+    float xmax = -INFINITY; int imax = 0, eq = 0;
+    for (int w = 0; w < world; w++) {
+        const float *s = gathered + ((long long)w * B + r) * SA_WORDS;
+        if (s[0] > xmax) { xmax = s[0]; imax = __float_as_int(s[1]); eq = __float_as_int(s[2]); }
+        else if (s[0] == xmax) eq += __float_as_int(s[2]);
+    }
+    const bool greedy = !(T > 0.0f);
+    const long long n_lim = (k > 0 && k < Vg) ? (long long)k : (long long)Vg;
+    long long need = n_lim + 1;
+    if (need > HEAD_NEED) need = HEAD_NEED;
+    if (need > Vg) need = Vg;
+    // the need-th largest of the union of the shards' sorted lists (a merge by one thread)
+    int ptr[16];
+    for (int w = 0; w < 16; w++) ptr[w] = 0;
+    float tau = -INFINITY;
+    for (long long step = 0; step < need; step++) {
+        float best = -INFINITY; int bw = -1;
+        for (int w = 0; w < world; w++) {
+            if (ptr[w] >= HEAD_NEED) continue;
+            const float v = gathered[((long long)w * B + r) * SA_WORDS + 3 + NWARP + ptr[w]];
+            if (bw < 0 || v > best) { best = v; bw = w; }
+        }
+        if (bw < 0) { tau = -INFINITY; break; }
+        tau = best; ptr[bw]++;
+    }
+    float lb = 0.0f;
+    if (!greedy) {
+        const float top = (T == 1.0f) ? xmax : __fdiv_rn(xmax, T);
+        for (int w = 0; w < rank; w++)
+            for (int q = 0; q < NWARP; q++) {
+                const float m = gathered[((long long)w * B + r) * SA_WORDS + 3 + q];
+                const float v = (T == 1.0f) ? m : __fdiv_rn(m, T);
+                lb += expf_pinned(__fsub_rn(v, top));
+            }
+    }
+    global4[4 * r] = xmax; global4[4 * r + 1] = tau; global4[4 * r + 2] = lb; global4[4 * r + 3] = __int_as_float(imax);
+    if ((greedy || n_lim == 1) && tokens && status && xmax > -INFINITY) {
+        tokens[r] = imax;
+        status[r] = (!greedy && eq > 1) ? MOLLA_ROW_TOPK_TIE : 0u;
+    }
+}
+
 // Rows differ in cost by an order of magnitude (a greedy row is one pass, a hot row keeps
 // most of its vocabulary). Handing out the dearest first keeps the last CTAs from running
 // long: this small kernel sorts the rows by a cost estimate.
@@ -825,14 +885,16 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                            (typ > 0.0f && typ <= 1.0f) && (rp > 0.0f) && H >= 0 && nb >= 0;
         const bool greedy = !(T > 0.0f);
         const bool penalizing = won && H > 0 && (rp != 1.0f || fp != 0.0f || pp != 0.0f);
-        const int npatch = (penalizing ? H : 0) + nb;
+        const int npatch = (a.mode == 3) ? 0 : (penalizing ? H : 0) + nb;
         if (!a.penalised_only) {
             if (!valid) c.status |= MOLLA_ROW_INVALID_CONFIG;
             else if (!greedy && (minp > 0.0f || typ < 1.0f)) c.status |= MOLLA_ROW_UNSUPPORTED;
         }
         if (npatch > PATCH_MAX) c.status |= MOLLA_ROW_UNSUPPORTED;
         if (c.status) {
-            if (c.tid == 0 && !a.penalised_only) {
+            if (a.mode == 1 && c.tid == 0) { float *o = a.sa_out + (long long)r * SA_WORDS; o[0] = -INFINITY; o[1] = __int_as_float(0); o[2] = __int_as_float(0); }
+            if (a.mode == 2 && c.tid == 0) a.sb_count[r] = 0;
+            if (c.tid == 0 && !a.penalised_only && a.tokens) {
                 a.tokens[r] = -1; a.row_status[r] = c.status;
                 if (a.diag) { a.diag[4 * r] = a.diag[4 * r + 1] = a.diag[4 * r + 2] = a.diag[4 * r + 3] = 0.0f; }
             }
@@ -851,7 +913,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             __syncthreads();
             for (int i = c.tid; i < npatch; i += NT) {
                 const bool is_bias = i < nb;
-                const long long t64 = is_bias ? a.bias_ids[b0 + i] : a.hist[h0 + (i - nb)];
+                const long long t64 = (is_bias ? a.bias_ids[b0 + i] : a.hist[h0 + (i - nb)]) - a.col0;
                 if (t64 < 0 || t64 >= a.V) continue;
                 const int tok = (int)t64;
                 int s = hslot(tok);
@@ -867,7 +929,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 if (tok < 0) continue;
                 float v = __ldg(c.src + tok);
                 for (int q = 0; q < nb; q++)  // duplicates add up, in the order they were given
-                    if (a.bias_ids[b0 + q] == (long long)tok) v = __fadd_rn(v, a.bias_vals[b0 + q]);
+                    if (a.bias_ids[b0 + q] == (long long)tok + a.col0) v = __fadd_rn(v, a.bias_vals[b0 + q]);
                 const int n = A->hcnt[s];
                 if (n > 0) {
                     if (v > 0.0f) v = __fdiv_rn(v, rp);
@@ -902,7 +964,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         // ---- 2. pass A (HBM): the maximum and its first index (kernel.mojo:571-585, sample.mojo:342-346)
         float tmax = -INFINITY;
         int tidx = 0x7fffffff, teq = 0;
-        {
+        if (a.mode != 3) {
             float rmx = -INFINITY;
             pieces_begin(c);
             for (int p = 0; p < c.npieces; p++) {
@@ -915,23 +977,41 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
 #pragma unroll
                 for (int j = 0; j < LT; j++) {
                     cm = fmaxf(cm, x[j]);
-                    if (x[j] > tmax) { tmax = x[j]; tidx = g0 + j; teq = 1; }
+                    if (x[j] > tmax) { tmax = x[j]; tidx = g0 + j + a.col0; teq = 1; }
                     else if (x[j] == tmax && c.lane * LT + j < n) teq++;
                 }
-                if (!greedy) {
+                if (!greedy || a.mode == 1) {
                     cm = warp_max(cm);
                     if (c.lane == 0) A->u.s.pmax[c.warp][p] = cm;
                     rmx = fmaxf(rmx, cm);
                 }
             }
-            if (!greedy && c.lane == 0) A->u.s.rmax[c.warp] = rmx;
+            if ((!greedy || a.mode == 1) && c.lane == 0) A->u.s.rmax[c.warp] = rmx;
         }
         float xmax = tmax;
         int imax = tidx;
-        block_argmax(c, xmax, imax);
+        if (a.mode != 3) block_argmax(c, xmax, imax);
         if (imax == 0x7fffffff) imax = 0;
         STAMP(2);
-        const long long n_lim = (k > 0 && k < a.V) ? (long long)k : (long long)a.V;
+        if (a.mode == 1) {
+            // stage 1 of the sharded form: what the other shards need to know about this slice
+            int tot;
+            (void)block_excl_scan<int>((tmax == xmax) ? teq : 0, A->wsi, &tot);
+            float *o = a.sa_out + (long long)r * SA_WORDS;
+            __syncthreads();
+            A->cand[c.tid] = ((unsigned long long)fkey(tmax) << 32) | (unsigned long long)c.tid;
+            bitonic_desc(A->cand, NT, c.tid);
+            if (c.tid < HEAD_NEED) o[3 + NWARP + c.tid] = fkey_inv((unsigned int)(A->cand[c.tid] >> 32));
+            if (c.tid < NWARP) o[3 + c.tid] = A->u.s.rmax[c.tid];
+            if (c.tid == 0) { o[0] = xmax; o[1] = __int_as_float(imax); o[2] = __int_as_float(tot); o[SA_WORDS - 1] = 0.0f; }
+            continue;
+        }
+        if (a.mode >= 2) { xmax = a.sb_in[4 * r]; imax = __float_as_int(a.sb_in[4 * r + 3]); }
+        const long long n_lim = (k > 0 && k < a.Vg) ? (long long)k : (long long)a.Vg;
+        if (a.mode >= 2 && (greedy || n_lim == 1)) {  // the first all-gather already answered these rows
+            if (a.mode == 2 && c.tid == 0) a.sb_count[r] = 0;
+            continue;
+        }
         int token = -1;
         float dZ = 0.0f, dsum = 0.0f, dtarget = 0.0f, dp = 0.0f;
 
@@ -946,12 +1026,12 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         } else {
             const float top = (T == 1.0f) ? xmax : __fdiv_rn(xmax, T);
             const bool topp_on = (P < 1.0f) && (n_lim > 1);
-            const bool pure = !topp_on && n_lim == (long long)a.V;
+            const bool pure = !topp_on && n_lim == (long long)a.Vg;
             const float u01 = draw01(a.seed ? a.seed[r] : 0ull, a.drawn ? a.drawn[r] : 0ull);
             const bool filter_ok = fabsf(top) < 1.0e5f;
             long long need = n_lim + 1;
             if (need > HEAD_NEED) need = HEAD_NEED;
-            if (need > a.V) need = a.V;
+            if (need > a.Vg) need = a.Vg;
             const bool p3row = !pure && (n_lim + 1 > HEAD_NEED);
 
             // The head of the sorted order holds the `need` largest. The need-th largest of the threads'
@@ -961,9 +1041,13 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             unsigned int tau_bits = 1u;
             if (!pure) {
                 __syncthreads();
-                A->cand[c.tid] = ((unsigned long long)fkey(tmax) << 32) | (unsigned long long)c.tid;
-                bitonic_desc(A->cand, NT, c.tid);
-                tau_x = fkey_inv((unsigned int)(A->cand[need - 1] >> 32));
+                if (a.mode >= 2) {
+                    tau_x = a.sb_in[4 * r + 1];
+                } else {
+                    A->cand[c.tid] = ((unsigned long long)fkey(tmax) << 32) | (unsigned long long)c.tid;
+                    bitonic_desc(A->cand, NT, c.tid);
+                    tau_x = fkey_inv((unsigned int)(A->cand[need - 1] >> 32));
+                }
                 const float tv = (T == 1.0f) ? tau_x : __fdiv_rn(tau_x, T);
                 const unsigned int tb_ = __float_as_uint(expf_pinned(__fsub_rn(tv, top)));
                 tau_bits = tb_ > 1u ? tb_ : 1u;
@@ -974,6 +1058,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             // (temperature and softmax numerator, sample.mojo:419-434)
             // A lower bound on the running sum at every piece: each earlier piece adds at least the
             // exponential of its own maximum. What is below half an ulp of that bound is dropped.
+            if (a.mode != 3) {
             {
                 const int maxp = (a.R + PIECE - 1) / PIECE;
                 for (int idx = c.tid; idx < NWARP * maxp; idx += NT) {
@@ -994,7 +1079,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 if (c.lane == 0) A->u.s.rmax[c.warp] = rs;
                 __syncthreads();
             }
-            float lb = 0.0f;  // bound on the sum of everything before this warp's current piece
+            float lb = (a.mode == 2) ? a.sb_in[4 * r + 2] : 0.0f;  // bound on the sum of everything before this warp's current piece
             for (int w = 0; w < c.warp; w++) lb += A->u.s.rmax[w];
             int base = 0;
             unsigned long long *myseg = wl_seg + (size_t)c.warp * (size_t)a.R;
@@ -1030,7 +1115,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     const float xx = slot[i];
                     const float v = (T == 1.0f) ? xx : __fdiv_rn(xx, T);
                     const float e = expf_pinned(__fsub_rn(v, top));
-                    myseg[base + i] = make_key(__float_as_uint(e), c.rbeg + p * PIECE + (int)A->u.s.ppos[c.warp][i]);
+                    myseg[base + i] = make_key(__float_as_uint(e), a.col0 + c.rbeg + p * PIECE + (int)A->u.s.ppos[c.warp][i]);
                 }
                 base += total;
                 lb += A->u.s.pmax[c.warp][p];
@@ -1038,6 +1123,11 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             }
             if (a.prof && c.tid == 32 * 5) { a.prof[(long long)r * 16 + 10] = tqa; a.prof[(long long)r * 16 + 11] = tqb; a.prof[(long long)r * 16 + 12] = tqc; a.prof[(long long)r * 16 + 13] = base; }
             if (c.lane == 0) A->wcnt[c.warp] = base;
+            } else if (c.tid < NWARP) {
+                // stage 3: the segments are the shards' lists, already in vocabulary order
+                int n = (c.tid < a.world) ? a.sc_count[(long long)c.tid * a.B + r] : 0;
+                A->wcnt[c.tid] = n < 0 ? 0 : (n > a.list_cap ? a.list_cap : n);
+            }
             __syncthreads();
             // offsets of the warps' segments in the whole list
             if (c.tid == 0) {
@@ -1050,20 +1140,33 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             {
                 // gather the warps' segments into one array: shared memory if it fits, else global
                 unsigned long long *dstl = (nl <= SLIST_CAP) ? slist : wl_flat;
+                if (a.mode == 2) dstl = a.sb_list + (long long)r * a.list_cap;  // the slice's list goes to the all-gather
+                const int nmove = (a.mode == 2 && nl > a.list_cap) ? 0 : nl;
                 auto fetch = [&](int v) -> unsigned long long {
                     int w = 0;
 #pragma unroll
                     for (int q = 1; q < NWARP; q++) w += (v >= A->woff[q]) ? 1 : 0;
+                    if (a.mode == 3) return a.sc_list[((size_t)w * a.B + r) * (size_t)a.list_cap + (size_t)(v - A->woff[w])];
                     return wl_seg[(size_t)w * (size_t)a.R + (size_t)(v - A->woff[w])];
                 };
                 int i = c.tid;
-                for (; i + 3 * NT < nl; i += 4 * NT) {
+                for (; i + 3 * NT < nmove; i += 4 * NT) {
                     const unsigned long long k0 = fetch(i), k1 = fetch(i + NT), k2 = fetch(i + 2 * NT), k3 = fetch(i + 3 * NT);
                     dstl[i] = k0; dstl[i + NT] = k1; dstl[i + 2 * NT] = k2; dstl[i + 3 * NT] = k3;
                 }
-                for (; i < nl; i += NT) dstl[i] = fetch(i);
+                for (; i < nmove; i += NT) dstl[i] = fetch(i);
             }
             __syncthreads();
+            if (a.mode == 3 && c.tid == 0) {
+                for (int w = 0; w < a.world; w++) {
+                    const int n = a.sc_count[(long long)w * a.B + r];
+                    if (n < 0 || n > a.list_cap) c.status |= MOLLA_ROW_SHARD_OVERFLOW;
+                }
+            }
+            if (a.mode == 2) {
+                if (c.tid == 0) a.sb_count[r] = (nl > a.list_cap) ? -1 : nl;  // -1: the slice's list outgrew the exchange buffer
+                continue;
+            }
             const unsigned long long *lst = (nl <= SLIST_CAP) ? slist : wl_flat;
             STAMP(3);
 
@@ -1117,7 +1220,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 if (!A->b_event) {
                     // the walk fell off the end: the reference returns the last token of the vocabulary,
                     // whether or not it could matter to any sum
-                    token = a.V - 1;
+                    token = a.Vg - 1;
                 }
             } else {
                 // ---- 5b. sorted order. The head: the need largest, sorted, walked exactly
@@ -1161,7 +1264,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                             if (pos >= n_lim) { cut = i + 1; break; }
                         }
                         if (cut < 0 && !p3row && tau_head == tau_pb) cut = nc;  // everything that can matter is in the head
-                        if (n_lim < (long long)a.V && (long long)nc > n_lim && A->pc[n_lim] == A->pc[n_lim - 1])
+                        if (n_lim < (long long)a.Vg && (long long)nc > n_lim && A->pc[n_lim] == A->pc[n_lim - 1])
                             tie |= MOLLA_ROW_TOPK_TIE;
                         A->b_s = s; A->b_pos = pos; A->b_event = EV_NONE; A->b_idx = -1; A->b_p = 0.0f;
                         if (cut > 0) {
@@ -1188,7 +1291,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         __syncthreads();
                         Walk cutw; cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
                         cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
-                        const bool limited = n_lim < (long long)a.V;
+                        const bool limited = n_lim < (long long)a.Vg;
                         descend(c, lst, nl, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
                         if (cutw.event != EV_DEGENERATE) {
                             if (cutw.event == EV_CUT && cutw.tie) c.status |= MOLLA_ROW_TOPP_TIE;
@@ -1410,6 +1513,7 @@ int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, in
     cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
     const size_t smem = smem_bytes(a.V);
     a.R = region_floats(a.V);
+    if (a.mode == 0) { a.Vg = a.V; a.col0 = 0; }
     if (smem > (size_t)max_optin || (a.R + PIECE - 1) / PIECE > MAX_PIECES)
         return fail(MOLLA_ERR_VOCAB, "vocabulary too wide for the shared-memory bitmap and tile table%s");
     cudaError_t e = cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -1566,6 +1670,104 @@ int32_t molla_sample_batch_noalloc(const float *d_logits, int64_t row_stride, in
         if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
     }
     return MOLLA_OK;
+}
+
+// ---- vocab-sharded form ------------------------------------------------------------
+namespace {
+BatchArgs shard_args(const float *d_logits, int64_t row_stride, int32_t B, int32_t V, const float *t, const int32_t *k,
+                     const float *p, const float *minp, const float *typ, const float *rp, const float *fp,
+                     const float *pp, const uint8_t *won, const uint64_t *seed, const uint64_t *drawn,
+                     const int64_t *hist, const int32_t *hist_off, const int64_t *bias_ids, const float *bias_vals,
+                     const int32_t *bias_off) {
+    BatchArgs a;
+    memset(&a, 0, sizeof(a));
+    a.logits = d_logits; a.row_stride = row_stride; a.B = B; a.V = V;
+    a.temperature = t; a.top_k = k; a.top_p = p; a.min_p = minp; a.typical_p = typ; a.repeat_penalty = rp;
+    a.frequency_penalty = fp; a.presence_penalty = pp; a.window_on = won;
+    a.seed = (const unsigned long long *)seed; a.drawn = (const unsigned long long *)drawn;
+    a.hist = (const long long *)hist; a.hist_off = hist_off;
+    a.bias_ids = (const long long *)bias_ids; a.bias_vals = bias_vals; a.bias_off = bias_off;
+    return a;
+}
+}  // namespace
+
+int32_t molla_sample_shard_summary_words(void) { return SA_WORDS; }
+
+int32_t molla_sample_shard_stage_a(const float *d_logits, int64_t row_stride, int32_t B, int32_t V_local, int32_t col0,
+                                   int32_t V_global, const float *d_temperature, const int32_t *d_top_k,
+                                   const float *d_top_p, const float *d_min_p, const float *d_typical_p,
+                                   const float *d_repeat_penalty, const float *d_frequency_penalty,
+                                   const float *d_presence_penalty, const uint8_t *d_window_on, const int64_t *d_hist,
+                                   const int32_t *d_hist_off, const int64_t *d_bias_ids, const float *d_bias_vals,
+                                   const int32_t *d_bias_off, void *d_workspace, int64_t workspace_bytes, void *stream,
+                                   float *d_summary) {
+    g_err[0] = 0;
+    if (!d_logits || !d_summary || B < 0 || V_local <= 0 || row_stride < V_local || col0 < 0 ||
+        (long long)col0 + V_local > V_global)
+        return fail(MOLLA_ERR_ARGUMENT, "bad arguments to the sharded stage 1%s");
+    if (!d_workspace || workspace_bytes < molla_sample_workspace_bytes(B, V_local, 0)) return fail(MOLLA_ERR_WORKSPACE, "workspace missing or too small%s");
+    if (B == 0) return MOLLA_OK;
+    BatchArgs a = shard_args(d_logits, row_stride, B, V_local, d_temperature, d_top_k, d_top_p, d_min_p, d_typical_p,
+                             d_repeat_penalty, d_frequency_penalty, d_presence_penalty, d_window_on, nullptr, nullptr,
+                             d_hist, d_hist_off, d_bias_ids, d_bias_vals, d_bias_off);
+    a.mode = 1; a.col0 = col0; a.Vg = V_global; a.sa_out = d_summary;
+    return launch_rows(a, d_workspace, (cudaStream_t)stream);
+}
+
+int32_t molla_sample_shard_merge(int32_t B, int32_t V_global, int32_t world, int32_t rank, const float *d_temperature,
+                                 const int32_t *d_top_k, const float *d_gathered_summaries, void *stream,
+                                 float *d_global, int32_t *d_tokens, uint32_t *d_row_status) {
+    g_err[0] = 0;
+    if (B < 0 || V_global <= 0 || world < 1 || world > NWARP || rank < 0 || rank >= world || !d_gathered_summaries || !d_global)
+        return fail(MOLLA_ERR_ARGUMENT, "bad arguments to the sharded merge (at most 16 shards)%s");
+    if (B == 0) return MOLLA_OK;
+    shard_merge_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(B, V_global, world, rank, d_temperature, d_top_k,
+                                                                       d_gathered_summaries, d_global, d_tokens, d_row_status);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "merge launch failed: %s", cudaGetErrorString(e));
+    return MOLLA_OK;
+}
+
+int32_t molla_sample_shard_stage_b(const float *d_logits, int64_t row_stride, int32_t B, int32_t V_local, int32_t col0,
+                                   int32_t V_global, const float *d_temperature, const int32_t *d_top_k,
+                                   const float *d_top_p, const float *d_min_p, const float *d_typical_p,
+                                   const float *d_repeat_penalty, const float *d_frequency_penalty,
+                                   const float *d_presence_penalty, const uint8_t *d_window_on, const int64_t *d_hist,
+                                   const int32_t *d_hist_off, const int64_t *d_bias_ids, const float *d_bias_vals,
+                                   const int32_t *d_bias_off, const float *d_global, int32_t list_cap, void *d_workspace,
+                                   int64_t workspace_bytes, void *stream, uint64_t *d_list, int32_t *d_count) {
+    g_err[0] = 0;
+    if (!d_logits || !d_global || !d_list || !d_count || B < 0 || V_local <= 0 || row_stride < V_local || list_cap < 1 ||
+        col0 < 0 || (long long)col0 + V_local > V_global)
+        return fail(MOLLA_ERR_ARGUMENT, "bad arguments to the sharded stage 2%s");
+    if (!d_workspace || workspace_bytes < molla_sample_workspace_bytes(B, V_local, 0)) return fail(MOLLA_ERR_WORKSPACE, "workspace missing or too small%s");
+    if (B == 0) return MOLLA_OK;
+    BatchArgs a = shard_args(d_logits, row_stride, B, V_local, d_temperature, d_top_k, d_top_p, d_min_p, d_typical_p,
+                             d_repeat_penalty, d_frequency_penalty, d_presence_penalty, d_window_on, nullptr, nullptr,
+                             d_hist, d_hist_off, d_bias_ids, d_bias_vals, d_bias_off);
+    a.mode = 2; a.col0 = col0; a.Vg = V_global; a.sb_in = d_global;
+    a.sb_list = (unsigned long long *)d_list; a.sb_count = d_count; a.list_cap = list_cap;
+    return launch_rows(a, d_workspace, (cudaStream_t)stream);
+}
+
+int32_t molla_sample_shard_stage_c(int32_t B, int32_t V_global, const float *d_temperature, const int32_t *d_top_k,
+                                   const float *d_top_p, const float *d_min_p, const float *d_typical_p,
+                                   const uint64_t *d_seed, const uint64_t *d_drawn, const float *d_global, int32_t world,
+                                   int32_t list_cap, const uint64_t *d_lists, const int32_t *d_counts, void *d_workspace,
+                                   int64_t workspace_bytes, void *stream, int32_t *d_tokens, uint32_t *d_row_status,
+                                   float *d_diag) {
+    g_err[0] = 0;
+    if (!d_global || !d_lists || !d_counts || !d_tokens || !d_row_status || B < 0 || V_global <= 0 || world < 1 ||
+        world > NWARP || list_cap < 1)
+        return fail(MOLLA_ERR_ARGUMENT, "bad arguments to the sharded stage 3 (at most 16 shards)%s");
+    if (!d_workspace || workspace_bytes < molla_sample_workspace_bytes(B, V_global, 0)) return fail(MOLLA_ERR_WORKSPACE, "workspace missing or too small%s");
+    if (B == 0) return MOLLA_OK;
+    BatchArgs a = shard_args(nullptr, V_global, B, V_global, d_temperature, d_top_k, d_top_p, d_min_p, d_typical_p, nullptr,
+                             nullptr, nullptr, nullptr, d_seed, d_drawn, nullptr, nullptr, nullptr, nullptr, nullptr);
+    a.mode = 3; a.col0 = 0; a.Vg = V_global; a.sb_in = d_global; a.world = world; a.list_cap = list_cap;
+    a.sc_list = (const unsigned long long *)d_lists; a.sc_count = d_counts;
+    a.tokens = d_tokens; a.row_status = d_row_status; a.diag = d_diag;
+    return launch_rows(a, d_workspace, (cudaStream_t)stream);
 }
 
 // ---- host-buffer form ---------------------------------------------------------

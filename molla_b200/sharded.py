@@ -1,0 +1,111 @@
+"""Row-sharded and vocab-sharded sampling over several GPUs of one node.
+
+Row-sharded: rows are independent (per-sequence sampler state and a counter-based RNG,
+src/molla/engine/sample.mojo:30-37,157-163), so every rank samples its own contiguous block
+of rows with no collective (`row_range`).
+
+Vocab-sharded (a tensor-parallel LM head): rank g holds columns [g*Vs, (g+1)*Vs) of every
+row. Three library stages with two all-gathers between them (`sample_vocab_sharded`); the
+collectives go through `torch.distributed` (NCCL over NVLink on GPUs), or through any
+callable with the same contract, which is how one GPU stands in for several in the tests.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import capi
+from .sampler import Workspace, _ptr, _stream_ptr
+
+
+def row_range(rank: int, world: int, B: int) -> tuple[int, int]:
+    """Contiguous rows [lo, hi) of rank `rank`; the first B % world ranks take one more."""
+    base, extra = divmod(B, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def dist_all_gather(group=None):
+    """An all-gather callable over a torch.distributed group: tensor -> [world, *tensor.shape]."""
+    import torch.distributed as dist
+
+    def gather(t: torch.Tensor) -> torch.Tensor:
+        world = dist.get_world_size(group)
+        out = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.contiguous(), group=group)
+        return out
+
+    return gather
+
+
+class VocabShard:
+    """One rank's part of a vocab-sharded sampling step."""
+
+    def __init__(self, B: int, V_local: int, col0: int, V_global: int, rank: int, world: int, device,
+                 list_cap: int | None = None):
+        if world > 16:
+            raise ValueError("at most 16 vocabulary shards")
+        self.B, self.Vl, self.col0, self.Vg = B, V_local, col0, V_global
+        # Before a row's largest logits have gone by, the running softmax sum is small and nearly every
+        # logit can still move its last bit, so a shard's list can be as long as its slice: that is the
+        # capacity that never overflows. A smaller one trades exchange volume for MOLLA_ROW_SHARD_OVERFLOW.
+        if list_cap is None:
+            list_cap = V_local
+        self.rank, self.world, self.dev, self.cap = rank, world, torch.device(device), list_cap
+        self.words = capi.lib().molla_sample_shard_summary_words()
+        self.ws_local = Workspace(B, V_local, 0, self.dev)
+        self.ws_global = Workspace(B, V_global, 0, self.dev)
+        f32, i32, i64 = torch.float32, torch.int32, torch.int64
+        self.summary = torch.empty((B, self.words), dtype=f32, device=self.dev)
+        self.global4 = torch.empty((B, 4), dtype=f32, device=self.dev)
+        self.lst = torch.empty((B, list_cap), dtype=i64, device=self.dev)
+        self.count = torch.empty(B, dtype=i32, device=self.dev)
+        self.tokens = torch.full((B,), -1, dtype=i32, device=self.dev)
+        self.status = torch.zeros(B, dtype=i32, device=self.dev)
+
+    def _row_args(self, p):
+        g = p.get
+        return [_ptr(g("temperature")), _ptr(g("top_k")), _ptr(g("top_p")), _ptr(g("min_p")), _ptr(g("typical_p")),
+                _ptr(g("repeat_penalty")), _ptr(g("frequency_penalty")), _ptr(g("presence_penalty")),
+                _ptr(g("window_on")), _ptr(g("hist")), _ptr(g("hist_off")), _ptr(g("bias_ids")),
+                _ptr(g("bias_vals")), _ptr(g("bias_off"))]
+
+    def stage_a(self, logits: torch.Tensor, p: dict) -> torch.Tensor:
+        capi.check(capi.lib().molla_sample_shard_stage_a(
+            _ptr(logits), logits.stride(0), self.B, self.Vl, self.col0, self.Vg, *self._row_args(p),
+            _ptr(self.ws_local.buf), self.ws_local.bytes, _stream_ptr(self.dev), _ptr(self.summary)))
+        return self.summary
+
+    def merge(self, gathered: torch.Tensor, p: dict) -> torch.Tensor:
+        g = p.get
+        capi.check(capi.lib().molla_sample_shard_merge(
+            self.B, self.Vg, self.world, self.rank, _ptr(g("temperature")), _ptr(g("top_k")),
+            _ptr(gathered.contiguous()), _stream_ptr(self.dev), _ptr(self.global4), _ptr(self.tokens),
+            _ptr(self.status)))
+        return self.global4
+
+    def stage_b(self, logits: torch.Tensor, p: dict):
+        capi.check(capi.lib().molla_sample_shard_stage_b(
+            _ptr(logits), logits.stride(0), self.B, self.Vl, self.col0, self.Vg, *self._row_args(p),
+            _ptr(self.global4), self.cap, _ptr(self.ws_local.buf), self.ws_local.bytes, _stream_ptr(self.dev),
+            _ptr(self.lst), _ptr(self.count)))
+        return self.lst, self.count
+
+    def stage_c(self, lists: torch.Tensor, counts: torch.Tensor, p: dict, diag: torch.Tensor | None = None):
+        g = p.get
+        capi.check(capi.lib().molla_sample_shard_stage_c(
+            self.B, self.Vg, _ptr(g("temperature")), _ptr(g("top_k")), _ptr(g("top_p")), _ptr(g("min_p")),
+            _ptr(g("typical_p")), _ptr(g("seed")), _ptr(g("drawn")), _ptr(self.global4), self.world, self.cap,
+            _ptr(lists.contiguous()), _ptr(counts.contiguous()), _ptr(self.ws_global.buf), self.ws_global.bytes,
+            _stream_ptr(self.dev), _ptr(self.tokens), _ptr(self.status), _ptr(diag)))
+        return self.tokens, self.status
+
+
+def sample_vocab_sharded(shard: VocabShard, logits: torch.Tensor, p: dict, all_gather, diag=None):
+    """One sampling step on this rank's columns. `all_gather(t)` must return [world, *t.shape]
+    with the shards in column order. Every rank ends with the same tokens."""
+    gathered = all_gather(shard.stage_a(logits, p))
+    shard.merge(gathered, p)
+    lst, cnt = shard.stage_b(logits, p)
+    return shard.stage_c(all_gather(lst), all_gather(cnt), p, diag)
