@@ -33,7 +33,10 @@ def dist_all_gather(group=None):
     def gather(t: torch.Tensor) -> torch.Tensor:
         world = dist.get_world_size(group)
         out = torch.empty((world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
-        dist.all_gather_into_tensor(out, t.contiguous(), group=group)
+        if dist.get_backend(group) == "nccl":
+            dist.all_gather_into_tensor(out, t.contiguous(), group=group)
+        else:  # gloo (CPU tests): the list form
+            dist.all_gather(list(out.unbind(0)), t.contiguous(), group=group)
         return out
 
     return gather
