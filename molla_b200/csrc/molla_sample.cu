@@ -1058,6 +1058,8 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             // (temperature and softmax numerator, sample.mojo:419-434)
             // A lower bound on the running sum at every piece: each earlier piece adds at least the
             // exponential of its own maximum. What is below half an ulp of that bound is dropped.
+            const bool head_in_pass = (a.mode == 0) && !pure;  // the head's candidates are picked up on the way
+            if (c.tid == 0) A->ncand = 0;
             if (a.mode != 3) {
             {
                 const int maxp = (a.R + PIECE - 1) / PIECE;
@@ -1093,7 +1095,10 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 const int g0 = c.rbeg + p * PIECE + c.lane * LT;
                 float x[LT];
                 load_chunk(c, slot, n, g0, x);
-                const float thr = fminf((filter_ok && lb > 0.0f) ? T * (top + logf(0.9f * lb) - REL_MARGIN) : -INFINITY, tau_x);
+                // below top - 105 the exponential is exactly zero whatever came before
+                const float thr_rel = (filter_ok && lb > 0.0f) ? T * (top + logf(0.9f * lb) - REL_MARGIN) : -INFINITY;
+                const float thr_zero = filter_ok ? T * (top - 105.0f) : -INFINITY;
+                const float thr = fminf(fmaxf(thr_rel, thr_zero), tau_x);
                 int cnt = 0;
 #pragma unroll
                 for (int j = 0; j < LT; j++) cnt += (c.lane * LT + j < n && x[j] >= thr) ? 1 : 0;
@@ -1115,7 +1120,12 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     const float xx = slot[i];
                     const float v = (T == 1.0f) ? xx : __fdiv_rn(xx, T);
                     const float e = expf_pinned(__fsub_rn(v, top));
-                    myseg[base + i] = make_key(__float_as_uint(e), a.col0 + c.rbeg + p * PIECE + (int)A->u.s.ppos[c.warp][i]);
+                    const unsigned long long key = make_key(__float_as_uint(e), a.col0 + c.rbeg + p * PIECE + (int)A->u.s.ppos[c.warp][i]);
+                    myseg[base + i] = key;
+                    if (head_in_pass && __float_as_uint(e) >= tau_bits) {
+                        const int pos = atomicAdd(&A->ncand, 1);
+                        if (pos < HEADC) A->cand[pos] = key;
+                    }
                 }
                 base += total;
                 lb += A->u.s.pmax[c.warp][p];
@@ -1179,26 +1189,41 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             dZ = Z;
             STAMP(4);
 
-            // probabilities p = e / Z (sample.mojo:437-438), once, in place; the head candidates are
-            // picked up on the way
+            // probabilities p = e / Z (sample.mojo:437-438). The head's candidates came out of pass B
+            // and are converted on their own; the list itself is converted (once, in place) only for
+            // rows that have to walk it.
             const unsigned int tau_p = __float_as_uint(__fdiv_rn(__uint_as_float(tau_bits), Z));
             const unsigned int tau_pb = tau_p > 1u ? tau_p : 1u;
-            __syncthreads();
-            if (c.tid == 0) A->ncand = 0;
-            __syncthreads();
-            {
+            bool mark_head = head_in_pass;  // the head was taken in pass B: its entries are consumed
+            auto convert_list = [&](bool gather_head) {
+                __syncthreads();
+                if (gather_head && c.tid == 0) A->ncand = 0;
+                __syncthreads();
                 unsigned long long *wlst = const_cast<unsigned long long *>(lst);
                 for_list(wlst, nl, c.tid, [&](int i, unsigned long long kk) {
-                    const unsigned int pb = __float_as_uint(__fdiv_rn(key_val(kk), Z));
+                    unsigned int pb = __float_as_uint(__fdiv_rn(key_val(kk), Z));
+                    // entries the head took in pass B (by their exponential) are marked as consumed
+                    if (!gather_head && mark_head && (unsigned int)(kk >> 32) >= tau_bits) pb = 0xFFFFFFFFu;
                     const unsigned long long nk = ((unsigned long long)pb << 32) | (kk & 0xFFFFFFFFull);
                     wlst[i] = nk;
-                    if (!pure && pb >= tau_pb) {
+                    if (gather_head && pb >= tau_pb) {
                         const int pos = atomicAdd(&A->ncand, 1);
                         if (pos < HEADC) A->cand[pos] = nk;
                     }
                 });
+                __syncthreads();
+            };
+            bool list_is_p = false;
+            if (pure || !head_in_pass) { convert_list(!pure); list_is_p = true; }
+            else {
+                __syncthreads();
+                const int nh = min(A->ncand, HEADC);
+                for (int i = c.tid; i < nh; i += NT) {
+                    const unsigned long long kk = A->cand[i];
+                    A->cand[i] = ((unsigned long long)__float_as_uint(__fdiv_rn(key_val(kk), Z)) << 32) | (kk & 0xFFFFFFFFull);
+                }
+                __syncthreads();
             }
-            __syncthreads();
 
             if (pure) {
                 // ---- 5a. nothing sorted: the draw walks the vocabulary in order (sample.mojo:365-369,
@@ -1227,11 +1252,12 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 // (sample.mojo:497-506, :580-590). The need-th largest of the threads' own maxima
                 // bounds the need-th largest element from below.
                 int nc = A->ncand;
-                unsigned int tau_head = tau_pb;
+                unsigned int tau_head = head_in_pass ? 0xFFFFFFFFu : tau_pb;
+                bool head_overflow = false;
                 if (nc > HEADC) {
                     // more equal-or-larger values than the head holds (flat or heavily tied rows):
                     // no head, the descending walk takes everything from the top
-                    nc = 0; tau_head = 0xFFFFFFFFu;
+                    nc = 0; tau_head = 0xFFFFFFFFu; head_overflow = true; mark_head = false;
                     c.status |= MOLLA_ROW_SLOW_PATH;
                 }
                 {
@@ -1263,7 +1289,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                             }
                             if (pos >= n_lim) { cut = i + 1; break; }
                         }
-                        if (cut < 0 && !p3row && tau_head == tau_pb) cut = nc;  // everything that can matter is in the head
+                        if (cut < 0 && !p3row && !head_overflow) cut = nc;  // everything that can matter is in the head
                         if (n_lim < (long long)a.Vg && (long long)nc > n_lim && A->pc[n_lim] == A->pc[n_lim - 1])
                             tie |= MOLLA_ROW_TOPK_TIE;
                         A->b_s = s; A->b_pos = pos; A->b_event = EV_NONE; A->b_idx = -1; A->b_p = 0.0f;
@@ -1288,6 +1314,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         token = A->b_idx; dp = A->b_p; dsum = A->b_sum; dtarget = A->b_target;
                     } else {
                         // ---- 6. past the head: the cut walk, then the draw walk
+                        if (!list_is_p) { convert_list(false); list_is_p = true; }
                         __syncthreads();
                         Walk cutw; cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
                         cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
