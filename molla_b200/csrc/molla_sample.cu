@@ -135,6 +135,8 @@ struct __align__(16) Aux {
     int hit_bin; unsigned long long hit_qbefore; unsigned long long hit_cbefore;
     unsigned long long tot_q; unsigned long long tot_c;
     float walk_s; int walk_found; int walk_idx; int walk_slow;
+    unsigned int spec_bits[NBINS / 32];  // bins holding an element that needs sequential care
+    float blk_s[44];                 // exact running sum at the start of every staged block
     float b_s; unsigned int b_tau; int b_event; int b_idx; float b_p; long long b_pos; int b_aux;
     float b_sum; float b_target;
 };
@@ -154,6 +156,7 @@ struct Ctx {
     // this warp's region and pipeline
     int rbeg, rlen, npieces;
     unsigned int parbits;
+    int nphase;           // histogram phases run by the descending walks of this row (profiling aid)
 };
 
 #define STAMP(i) do { if (a.prof && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
@@ -321,26 +324,90 @@ struct Walker {
     float s; int found; int at; int slow;
 };
 
-__device__ __forceinline__ float lval(const unsigned long long *lst, int i) {
-    return __uint_as_float((unsigned int)(lst[i] >> 32));
-}
+// value accessors: a list of (value bits << 32 | ~id) keys, or bare value bits
+struct ValKeys {
+    const unsigned long long *p;
+    __device__ __forceinline__ float operator()(int i) const { return __uint_as_float((unsigned int)(p[i] >> 32)); }
+};
+struct ValBits {
+    const unsigned int *p;
+    __device__ __forceinline__ float operator()(int i) const { return __uint_as_float(p[i]); }
+};
 
-__device__ __forceinline__ void p1_sim(const unsigned long long *lst, int i0, int i1, bool locate, float target,
+// A row's list as the later phases see it: a copy in shared memory when it is small, else the
+// segments pass B wrote (one per warp, each in vocabulary order, `stride` entries apart).
+struct LView {
+    const unsigned long long *flat;  // shared-memory copy, or nullptr
+    unsigned long long *seg;
+    size_t stride;
+    const int *woff;                 // NWARP + 1 segment offsets into the whole list
+    int n;
+    __device__ __forceinline__ unsigned long long *slot(int v) const {
+        if (flat) return const_cast<unsigned long long *>(flat) + v;
+        int w = 0;
+#pragma unroll
+        for (int q = 1; q < NWARP; q++) w += (v >= woff[q]) ? 1 : 0;
+        return seg + (size_t)w * stride + (size_t)(v - woff[w]);
+    }
+    __device__ __forceinline__ unsigned long long at(int v) const { return *slot(v); }
+    // f(index in the whole list, key, where the key lives); four loads in flight per thread
+    // the same over the entries [v0, v1) only
+    template <class F>
+    __device__ __forceinline__ void for_range(int tid, int v0, int v1, F f) const {
+        const int nseg = flat ? 1 : NWARP;
+        for (int w = 0; w < nseg; w++) {
+            const unsigned long long *b = flat ? flat : seg + (size_t)w * stride;
+            const int o = flat ? 0 : woff[w];
+            const int m = flat ? n : woff[w + 1] - o;
+            const int lo = max(v0 - o, 0), hi = min(v1 - o, m);
+            int i = lo + tid;
+            for (; i + 3 * NT < hi; i += 4 * NT) {
+                const unsigned long long k0 = b[i], k1 = b[i + NT], k2 = b[i + 2 * NT], k3 = b[i + 3 * NT];
+                f(o + i, k0); f(o + i + NT, k1); f(o + i + 2 * NT, k2); f(o + i + 3 * NT, k3);
+            }
+            for (; i < hi; i += NT) f(o + i, b[i]);
+        }
+    }
+    // f(index in the whole list, key, where the key lives). A list in segments is walked with one
+    // warp per segment (pass B left sixteen of similar length); eight loads in flight per thread.
+    template <class F>
+    __device__ __forceinline__ void for_each(int tid, F f) const {
+        unsigned long long *b;
+        int o, m, i, step;
+        if (flat) { b = const_cast<unsigned long long *>(flat); o = 0; m = n; i = tid; step = NT; }
+        else {
+            const int w = tid >> 5;
+            b = seg + (size_t)w * stride; o = woff[w]; m = woff[w + 1] - o; i = tid & 31; step = 32;
+        }
+        for (; i + 7 * step < m; i += 8 * step) {
+            unsigned long long k[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) k[q] = b[i + q * step];
+#pragma unroll
+            for (int q = 0; q < 8; q++) f(o + i + q * step, k[q], b + i + q * step);
+        }
+        for (; i < m; i += step) f(o + i, b[i], b + i);
+    }
+};
+
+template <class V>
+__device__ __forceinline__ void p1_sim(V lst, int i0, int i1, bool locate, float target,
                                        Walker &w) {
     float s = w.s;
     for (int i = i0; i < i1; i++) {
-        s = __fadd_rn(s, lval(lst, i));
+        s = __fadd_rn(s, lst(i));
         if (locate && target < s) { w.found = 1; w.at = i; break; }
     }
     w.s = s;
 }
 
-__device__ void p1_build(Ctx &c, const unsigned long long *lst, int n, int L, double sbase) {
+template <class V>
+__device__ void p1_build(Ctx &c, V lst, int n, int L, double sbase) {
     Aux *A = c.A;
     const float EPS = 1.0f / 4096.0f;
     const int i0 = min(n, c.tid * L), i1 = min(n, (c.tid + 1) * L);
     float csum = 0.0f;
-    for (int i = i0; i < i1; i++) csum = __fadd_rn(csum, lval(lst, i));
+    for (int i = i0; i < i1; i++) csum = __fadd_rn(csum, lst(i));
     double tot;
     const double sst = sbase + block_excl_scan<double>((double)csum, A->wsd, &tot);
     short ja = SUS;
@@ -356,7 +423,7 @@ __device__ void p1_build(Ctx &c, const unsigned long long *lst, int n, int L, do
             const float C1 = __fmul_rn(1.5f, fpow2(jl)), h1 = fpow2(jl - 24), b1 = fpow2(jl - 1);
             const float C2 = __fmul_rn(1.5f, fpow2(jl + 1)), h2 = fpow2(jl - 23);
             for (int i = i0; i < i1; i++) {
-                const float v = lval(lst, i);
+                const float v = lst(i);
                 const float q = __fsub_rn(__fadd_rn(v, C1), C1);
                 const float r = __fsub_rn(v, q);
                 bad |= (fabsf(r) == h1) | (v >= b1);
@@ -391,7 +458,8 @@ __device__ void p1_build(Ctx &c, const unsigned long long *lst, int n, int L, do
 }
 
 // thread 0 only; continues from the state in `w`
-__device__ void p1_walk(Ctx &c, const unsigned long long *lst, int n, int L, bool locate, float target, Walker &w) {
+template <class V>
+__device__ void p1_walk(Ctx &c, V lst, int n, int L, bool locate, float target, Walker &w) {
     Aux *A = c.A;
     const int nseg = A->nseg;
     const double *PA = A->u.p1.pa, *PB = A->u.p1.pb;
@@ -471,38 +539,65 @@ __device__ void p1_walk(Ctx &c, const unsigned long long *lst, int n, int L, boo
     }
 }
 
-// The whole list, exactly: in one go when it sits in shared memory, else in blocks staged
-// there (`stage_lst`, SLIST_CAP entries) with the exact sum carried from block to block.
+// The whole list, exactly: in one go when it sits in shared memory, else in blocks of bare
+// values staged there (`vals`, VBLK entries) with the exact sum carried from block to block.
+// The sum at every block start is remembered, so a second run that only has to find where
+// the running sum passes `target` rebuilds a single block.
 // Result in A->walk_s (and A->walk_found / A->walk_idx = list position when locating).
-__device__ void p1_run(Ctx &c, const unsigned long long *lst, int nl, bool in_smem, unsigned long long *stage_lst,
-                       bool locate, float target) {
+constexpr int VBLK = STAGE_FLOATS;  // values per staged block
+constexpr int MAX_VBLK = 40;
+
+template <class V>
+__device__ void p1_block(Ctx &c, V vals, int n, int base, bool locate, float target) {
+    Aux *A = c.A;
+    int L = (n + NT - 1) / NT;
+    if ((L & 1) == 0) L += 1;
+    p1_build(c, vals, n, L, (double)A->walk_s);
+    if (c.tid == 0) {
+        Walker w; w.s = A->walk_s; w.found = 0; w.at = -1; w.slow = A->walk_slow;
+        p1_walk(c, vals, n, L, locate, target, w);
+        A->walk_s = w.s; A->walk_slow = w.slow;
+        if (w.found) { A->walk_found = 1; A->walk_idx = base + w.at; }
+    }
+    __syncthreads();
+}
+
+__device__ void p1_run(Ctx &c, const LView &lv, unsigned int *vals, bool locate, float target) {
     Aux *A = c.A;
     __syncthreads();
     if (c.tid == 0) { A->walk_s = 0.0f; A->walk_found = 0; A->walk_idx = -1; }
     __syncthreads();
-    const int nblk = in_smem ? 1 : (nl + SLIST_CAP - 1) / SLIST_CAP;
-    for (int b = 0; b < nblk; b++) {
-        const unsigned long long *blk = lst;
-        int n = nl;
-        if (!in_smem) {
-            n = min(SLIST_CAP, nl - b * SLIST_CAP);
-            __syncthreads();
-            for_list(lst + (size_t)b * SLIST_CAP, n, c.tid, [&](int i, unsigned long long k) { stage_lst[i] = k; });
-            blk = stage_lst;
+    if (lv.flat) {
+        p1_block(c, ValKeys{lv.flat}, lv.n, 0, locate, target);
+        return;
+    }
+    const int nblk = (lv.n + VBLK - 1) / VBLK;
+    int b0 = 0, b1 = nblk;
+    if (locate && nblk <= MAX_VBLK) {
+        // the block whose end value is the first to exceed the target (sums remembered by the last full run)
+        b0 = nblk;
+        for (int b = 0; b < nblk; b++)
+            if (target < A->blk_s[b + 1]) { b0 = b; break; }
+        if (b0 == nblk) return;  // never exceeded
+        b1 = b0 + 1;
+        __syncthreads();
+        if (c.tid == 0) A->walk_s = A->blk_s[b0];
+        __syncthreads();
+    }
+    for (int b = b0; b < b1; b++) {
+        const int n = min(VBLK, lv.n - b * VBLK);
+        __syncthreads();
+        if (!locate && c.tid == 0 && b < MAX_VBLK) A->blk_s[b] = A->walk_s;
+        {
+            const int o = b * VBLK;
+            lv.for_range(c.tid, o, o + n, [&](int v, unsigned long long k) { vals[v - o] = (unsigned int)(k >> 32); });
         }
         __syncthreads();
         if (locate && A->walk_found) break;
-        int L = (n + NT - 1) / NT;
-        if ((L & 1) == 0) L += 1;
-        p1_build(c, blk, n, L, (double)A->walk_s);
-        if (c.tid == 0) {
-            Walker w; w.s = A->walk_s; w.found = 0; w.at = -1; w.slow = A->walk_slow;
-            p1_walk(c, blk, n, L, locate, target, w);
-            A->walk_s = w.s; A->walk_slow = w.slow;
-            if (w.found) { A->walk_found = 1; A->walk_idx = b * SLIST_CAP + w.at; }
-        }
-        __syncthreads();
+        p1_block(c, ValBits{vals}, n, b * VBLK, locate, target);
     }
+    if (!locate && c.tid == 0 && nblk <= MAX_VBLK) A->blk_s[nblk] = A->walk_s;
+    __syncthreads();
 }
 
 // =============================================================================
@@ -513,6 +608,8 @@ struct BinQuery {
     unsigned long long m0, xq;       // mass event: m0 + cum_q >= xq   (xq = ~0 disables)
     unsigned long long pos0, nstop;  // count event: pos0 + cum_c >= nstop (nstop = ~0 disables)
     int specbin;                     // stop at this bin (-1 disables)
+    int bin_hi;                      // only bins below this one count (NBINS = all)
+    const unsigned int *spec_bits;   // or: stop at any bin whose bit is set here (nullptr = use specbin)
 };
 
 __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
@@ -521,7 +618,9 @@ __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
 #pragma unroll
     for (int i = 0; i < BPT; i++) {
         const int b = NBINS - 1 - BPT * c.tid - i;
-        q[i] = (unsigned long long)A->u.h.hq[b] | ((unsigned long long)A->u.h.hqh[b] << 32); n[i] = A->u.h.hc[b];
+        const bool live = b < qy.bin_hi;
+        q[i] = live ? ((unsigned long long)A->u.h.hq[b] | ((unsigned long long)A->u.h.hqh[b] << 32)) : 0ull;
+        n[i] = live ? A->u.h.hc[b] : 0u;
         sq += q[i]; sn += n[i];
     }
     unsigned long long tq, tc;
@@ -537,7 +636,7 @@ __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
         const int b = NBINS - 1 - BPT * c.tid - i;
         const unsigned long long q1 = cq + q[i], c1 = cc + n[i];
         const bool pr = (qy.xq != ~0ull && qy.m0 + q1 >= qy.xq) || (qy.nstop != ~0ull && qy.pos0 + c1 >= qy.nstop) ||
-                        (b <= qy.specbin);
+                        (qy.spec_bits ? (b < qy.bin_hi && ((qy.spec_bits[b >> 5] >> (b & 31)) & 1u)) : (b <= qy.specbin));
         if (pr && hit < 0) { hit = b; hq_before = cq; hc_before = cc; }
         cq = q1; cc = c1;
     }
@@ -559,6 +658,115 @@ __device__ void sort_cands(Ctx &c, int n) {
     __syncthreads();
 }
 
+// Adds the sorted candidates pc[0..nb) to the running sum `s0` in order, exactly as the
+// reference's loops do (sample.mojo:497-506, 585-590), and stops at the first event: the sum
+// reaching x_ge, exceeding x_gt, or the count reaching nstop. Where the sum stays in one
+// binade the additions are integers and the first event is found with a block scan; a
+// candidate that takes the sum across a power of two is added by itself and the scan resumes
+// behind it; a rounding tie or a candidate >= sum/4 sends the rest to one thread.
+// Results: A->b_event, b_s, b_pos, and for an event b_idx (token), b_p, b_aux (tie).
+__device__ void walk_sorted(Ctx &c, int nb, float s0, long long pos0, float x_ge, float x_gt, bool counting,
+                            long long nstop) {
+    Aux *A = c.A;
+    constexpr int EPT = NC / NT;
+    __syncthreads();
+    if (c.tid == 0) { A->b_s = s0; A->b_event = EV_NONE; A->b_aux = -1; A->b_idx = 0; }
+    __syncthreads();
+    for (int round = 0; round < 256; round++) {
+        const int st = A->b_idx;      // candidates before st are consumed
+        const float s = A->b_s;
+        if (A->b_event != EV_NONE || st >= nb) break;
+        const bool have_s = s > 0.0f;
+        const int j = have_s ? fexpo(s) : 0;
+        const bool ok = have_s && j >= -100 && j <= 100;
+        const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1), inv_u = fpow2(23 - j);
+        unsigned int q[EPT];
+        bool special = !ok;
+#pragma unroll
+        for (int e = 0; e < EPT; e++) {
+            const int i = st + c.tid * EPT + e;
+            q[e] = 0u;
+            if (i < nb && ok) {
+                const float p = A->pc[i];
+                const float qf = __fsub_rn(__fadd_rn(p, Cm), Cm);
+                const float r = __fsub_rn(p, qf);
+                if (fabsf(r) == halfu || p >= bigthr) special = true;
+                q[e] = __float2uint_rn(__fmul_rn(qf, inv_u));
+            }
+        }
+        if (__syncthreads_or(special ? 1 : 0)) {
+            // one thread, one addition at a time, from st to the first event or the end
+            if (c.tid == 0) {
+                float acc = s;
+                long long pos = pos0 + st;
+                int ev = EV_NONE, at = -1;
+                for (int i = st; i < nb; i++) {
+                    acc = __fadd_rn(acc, A->pc[i]);
+                    pos++;
+                    if (acc >= x_ge) ev = EV_CUT;
+                    else if (x_gt < acc) ev = EV_DRAW;
+                    else if (counting && pos >= nstop) ev = EV_LIMIT;
+                    if (ev != EV_NONE) { at = i; break; }
+                }
+                A->b_s = acc; A->b_event = ev; A->b_aux = at; A->b_idx = nb;
+            }
+            __syncthreads();
+            break;
+        }
+        unsigned long long loc = 0;
+#pragma unroll
+        for (int e = 0; e < EPT; e++) loc += q[e];
+        unsigned long long tot;
+        const unsigned long long ex = block_excl_scan<unsigned long long>(loc, A->wsu, &tot);
+        const unsigned long long m0 = (unsigned long long)((double)s * (double)inv_u);
+        unsigned long long X = 1ull << 24;
+        if (x_ge < 3.0e38f) { double t = ceil((double)x_ge * (double)inv_u); if (t < (double)X) X = t <= 0.0 ? 0ull : (unsigned long long)t; }
+        if (x_gt < 3.0e38f) { double t = floor((double)x_gt * (double)inv_u) + 1.0; if (t < (double)X) X = t <= 0.0 ? 0ull : (unsigned long long)t; }
+        __syncthreads();
+        if (c.tid == 0) A->evt_thread = 0x7fffffff;
+        __syncthreads();
+        unsigned long long m = m0 + ex, mb_first = 0;
+        int first = -1;
+#pragma unroll
+        for (int e = 0; e < EPT; e++) {
+            const int i = st + c.tid * EPT + e;
+            const unsigned long long mb = m;
+            m += q[e];
+            if (i < nb && first < 0 && (m >= X || (counting && pos0 + i + 1 >= nstop))) { first = i; mb_first = mb; }
+        }
+        if (first >= 0) atomicMin(&A->evt_thread, first);
+        __syncthreads();
+        const int hit = A->evt_thread;
+        if (hit == 0x7fffffff) {
+            if (c.tid == 0) { A->b_s = (float)((double)(m0 + tot) * (double)fpow2(j - 23)); A->b_idx = nb; }
+            __syncthreads();
+            break;
+        }
+        if (first == hit) {
+            // the true addition at the candidate the integers point at decides what happened there
+            const float sb = (float)((double)mb_first * (double)fpow2(j - 23));
+            const float acc = __fadd_rn(sb, A->pc[hit]);
+            int ev = EV_NONE;
+            if (acc >= x_ge) ev = EV_CUT;
+            else if (x_gt < acc) ev = EV_DRAW;
+            else if (counting && pos0 + hit + 1 >= nstop) ev = EV_LIMIT;
+            A->b_s = acc; A->b_event = ev; A->b_aux = (ev != EV_NONE) ? hit : -1; A->b_idx = hit + 1;
+        }
+        __syncthreads();
+    }
+    if (c.tid == 0) {
+        const int at = A->b_aux;
+        const int consumed = (A->b_event != EV_NONE) ? at + 1 : nb;
+        A->b_pos = pos0 + consumed;
+        if (A->b_event != EV_NONE) {
+            const float p = A->pc[at];
+            A->b_idx = key_idx(A->cand[at]); A->b_p = p;
+            A->b_aux = ((at > 0 && A->pc[at - 1] == p) || (at + 1 < nb && A->pc[at + 1] == p)) ? 1 : 0;
+        }
+    }
+    __syncthreads();
+}
+
 // =============================================================================
 // The descending walk past the sorted head (sample.mojo:492-506 and :580-590 on rows
 // whose nucleus is larger than the head), over the row's relevant list. State: exact
@@ -575,12 +783,13 @@ struct Walk {
 };
 
 // index in list order of the (nth+1)-th entry whose exp bits equal `eb` and lie below `tau`
-__device__ int nth_equal(Ctx &c, const unsigned long long *lst, int nl, unsigned int eb, unsigned int tau, int nth) {
+__device__ int nth_equal(Ctx &c, const LView &lv, unsigned int eb, unsigned int tau, int nth) {
+    const int nl = lv.n;
     Aux *A = c.A;
     const int L = (nl + NT - 1) / NT;
     const int i0 = min(nl, c.tid * L), i1 = min(nl, (c.tid + 1) * L);
     int cnt = 0;
-    for (int i = i0; i < i1; i++) cnt += ((unsigned int)(lst[i] >> 32) == eb && eb < tau) ? 1 : 0;
+    for (int i = i0; i < i1; i++) cnt += ((unsigned int)(lv.at(i) >> 32) == eb && eb < tau) ? 1 : 0;
     int tot;
     const int ex = block_excl_scan<int>(cnt, A->wsi, &tot);
     __syncthreads();
@@ -589,8 +798,9 @@ __device__ int nth_equal(Ctx &c, const unsigned long long *lst, int nl, unsigned
     if (nth >= ex && nth < ex + cnt) {
         int seen = ex;
         for (int i = i0; i < i1; i++) {
-            if ((unsigned int)(lst[i] >> 32) == eb) {
-                if (seen == nth) { A->b_idx = key_idx(lst[i]); break; }
+            const unsigned long long kk = lv.at(i);
+            if ((unsigned int)(kk >> 32) == eb) {
+                if (seen == nth) { A->b_idx = key_idx(kk); break; }
                 seen++;
             }
         }
@@ -599,7 +809,7 @@ __device__ int nth_equal(Ctx &c, const unsigned long long *lst, int nl, unsigned
     return A->b_idx;
 }
 
-__device__ void descend(Ctx &c, const unsigned long long *lst, int nl, Walk &w, float x_ge, float x_gt,
+__device__ void descend(Ctx &c, const LView &lv, Walk &w, float x_ge, float x_gt,
                         long long nstop) {
     Aux *A = c.A;
     const bool counting = nstop >= 0;
@@ -610,6 +820,7 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, Walk &w, 
     unsigned int lo = 0u;
     int shift = BIN_SHIFT;
     for (int phase = 0; phase < 8192; phase++) {
+        c.nphase++;
         __syncthreads();
         for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0u; A->u.h.hqh[i] = 0u; A->u.h.hc[i] = 0u; }
         if (c.tid == 0) { A->specbin = -1; A->ncand = 0; }
@@ -619,7 +830,7 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, Walk &w, 
         const bool binade_ok = have_s && j >= -100 && j <= 100;
         const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1);
         const float inv_u = fpow2(23 - j);
-        for_list(lst, nl, c.tid, [&](int, unsigned long long key) {
+        lv.for_each(c.tid, [&](int, unsigned long long key, unsigned long long *) {
             const unsigned int eb = (unsigned int)(key >> 32);
             if (eb >= w.tau || eb < lo) return;
             const int bin = (int)((eb - lo) >> shift);
@@ -641,7 +852,7 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, Walk &w, 
         });
         __syncthreads();
         BinQuery qy;
-        qy.specbin = A->specbin;
+        qy.specbin = A->specbin; qy.bin_hi = NBINS; qy.spec_bits = nullptr;
         qy.pos0 = (unsigned long long)w.pos;
         qy.nstop = counting ? (unsigned long long)nstop : ~0ull;
         qy.m0 = 0; qy.xq = ~0ull;
@@ -674,7 +885,7 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, Walk &w, 
         const unsigned int blo = lo + ((unsigned int)hb << shift);
         const unsigned long long bhi64 = (unsigned long long)lo + ((unsigned long long)(hb + 1) << shift);
         const unsigned int bhi = bhi64 > 0xFFFFFFFFull ? 0xFFFFFFFFu : (unsigned int)bhi64;
-        for_list(lst, nl, c.tid, [&](int, unsigned long long key) {
+        lv.for_each(c.tid, [&](int, unsigned long long key, unsigned long long *) {
             const unsigned int eb = (unsigned int)(key >> 32);
             if (eb < w.tau && eb >= blo && eb < bhi) {
                 int pos = atomicAdd(&A->ncand, 1);
@@ -717,7 +928,7 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, Walk &w, 
             const int ev = A->b_event, at = A->b_aux;
             w.s = A->b_s; w.pos = A->b_pos;
             if (ev != EV_NONE) {
-                const int id = nth_equal(c, lst, nl, blo, w.tau, at);
+                const int id = nth_equal(c, lv, blo, w.tau, at);
                 w.event = ev; w.idx = id; w.p = pv; w.tie = 1;
                 return;
             }
@@ -725,26 +936,8 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, Walk &w, 
             continue;
         }
         sort_cands(c, nb);
-        if (c.tid == 0) {
-            float s = s_bin;
-            long long pos = pos_bin;
-            int ev = EV_NONE, at = -1;
-            for (int i = 0; i < nb; i++) {
-                const float p = A->pc[i];
-                s = __fadd_rn(s, p);
-                pos++;
-                if (s >= x_ge) ev = EV_CUT;
-                else if (x_gt < s) ev = EV_DRAW;
-                else if (counting && pos >= nstop) ev = EV_LIMIT;
-                if (ev != EV_NONE) { at = i; break; }
-            }
-            A->b_event = ev; A->b_s = s; A->b_pos = pos; A->b_tau = blo;
-            if (at >= 0) {
-                const float p = A->pc[at];
-                A->b_idx = key_idx(A->cand[at]); A->b_p = p;
-                A->b_aux = ((at > 0 && A->pc[at - 1] == p) || (at + 1 < nb && A->pc[at + 1] == p)) ? 1 : 0;
-            }
-        }
+        walk_sorted(c, nb, s_bin, pos_bin, x_ge, x_gt, counting, nstop);
+        if (c.tid == 0) A->b_tau = blo;
         __syncthreads();
         w.s = A->b_s; w.pos = A->b_pos; w.tau = A->b_tau;
         if (A->b_event != EV_NONE) { w.event = A->b_event; w.idx = A->b_idx; w.p = A->b_p; w.tie = A->b_aux; return; }
@@ -752,6 +945,149 @@ __device__ void descend(Ctx &c, const unsigned long long *lst, int nl, Walk &w, 
     }
     w.event = EV_DEGENERATE;
     c.status |= MOLLA_ROW_DEGENERATE;
+}
+
+// =============================================================================
+// The same walk for long lists, which live in global memory: every pass over them costs
+// tens of microseconds, so the list is first sorted into its 2048 value bins (a counting
+// sort: bin counts taken while the probabilities were written, one scatter pass). After
+// that a bin is a contiguous slice, the per-bin integer masses of a binade come from one
+// coalesced pass with warp-aggregated atomics and stay valid until the running sum leaves
+// the binade, and walking a bin touches only that bin.
+// =============================================================================
+struct Buckets {
+    unsigned long long *arr;   // the list ordered by bin, highest bin first (global memory)
+    unsigned int *off;         // [NBINS] entries in higher bins (shared memory)
+    unsigned int *cnt;         // [NBINS] entries per bin
+    unsigned int *cur;         // [NBINS] scatter cursors
+    int total;
+    bool built;
+    int mass_j;                // binade the masses in u.h.hq were computed for (INT_MIN: none)
+    int mass_hi;               // ... over the bins below this one
+    // where the masses were last built: a later walk that starts at or after this point reuses them
+    float ck_s; long long ck_pos; int ck_hi;
+};
+
+__device__ void buckets_build(Ctx &c, const LView &lv, Buckets &bk, unsigned int tau) {
+    Aux *A = c.A;
+    // bk.cnt holds the per-bin counts of the entries below tau (taken during the conversion pass)
+    unsigned int n[BPT], sn = 0;
+#pragma unroll
+    for (int i = 0; i < BPT; i++) { n[i] = bk.cnt[NBINS - 1 - BPT * c.tid - i]; sn += n[i]; }
+    unsigned int tot;
+    unsigned int ex = block_excl_scan<unsigned int>(sn, reinterpret_cast<unsigned int *>(A->wsi), &tot);
+#pragma unroll
+    for (int i = 0; i < BPT; i++) {
+        const int b = NBINS - 1 - BPT * c.tid - i;
+        bk.off[b] = ex; bk.cur[b] = ex; ex += n[i];
+    }
+    __syncthreads();
+    lv.for_each(c.tid, [&](int, unsigned long long key, unsigned long long *) {
+        const unsigned int pb = (unsigned int)(key >> 32);
+        if (pb >= tau) return;
+        const unsigned int pos = atomicAdd(&bk.cur[pb >> BIN_SHIFT], 1u);
+        bk.arr[pos] = key;
+    });
+    __syncthreads();
+    bk.total = (int)tot; bk.built = true; bk.mass_j = -0x7fffffff; bk.mass_hi = 0;
+}
+
+// integer masses of the bins below `hi` for binade j, and the bins that need sequential care
+__device__ void buckets_masses(Ctx &c, Buckets &bk, int j, int hi) {
+    Aux *A = c.A;
+    __syncthreads();
+    for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0u; A->u.h.hqh[i] = 0u; A->u.h.hc[i] = bk.cnt[i]; }
+    for (int i = c.tid; i < NBINS / 32; i += NT) A->spec_bits[i] = 0u;
+    __syncthreads();
+    const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1), inv_u = fpow2(23 - j);
+    const int p0 = (hi >= NBINS) ? 0 : (int)(bk.off[hi - 1]);
+    const int n = bk.total;
+    // every warp walks whole groups of 32 consecutive entries, so the ballots below are warp-wide
+    for (int base0 = p0 + (c.tid & ~31); base0 < n; base0 += 4 * NT) {
+        unsigned long long kk[4];
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const int i = base0 + g * NT + c.lane;
+            kk[g] = (i < n) ? bk.arr[i] : 0ull;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const int i = base0 + g * NT + c.lane;
+            if (base0 + g * NT >= n) break;  // warp-uniform
+            const bool in = i < n;
+            const unsigned int pb = (unsigned int)(kk[g] >> 32);
+            const int bin = (int)(pb >> BIN_SHIFT);
+            const float p = __uint_as_float(pb);
+            const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
+            const float r = __fsub_rn(p, q);
+            const bool special = in && (fabsf(r) == halfu || p >= bigthr);
+            const unsigned int qu = (in && !special) ? __float2uint_rn(__fmul_rn(q, inv_u)) : 0u;
+            if (special) atomicOr(&A->spec_bits[bin >> 5], 1u << (bin & 31));
+            // neighbours in the sorted array mostly share a bin: one atomic per bin per warp
+            const unsigned int peers = __match_any_sync(0xffffffffu, in ? bin : -1);
+            const unsigned int sum = __reduce_add_sync(peers, qu);
+            if (in && sum && c.lane == __ffs(peers) - 1) {
+                const unsigned int old = atomicAdd(&A->u.h.hq[bin], sum);
+                if (old + sum < old) atomicAdd(&A->u.h.hqh[bin], 1u);
+            }
+        }
+    }
+    __syncthreads();
+    bk.mass_j = j; bk.mass_hi = hi;
+}
+
+// Returns false if it met something it leaves to the general walk (no usable binade yet, or a
+// bin larger than the candidate buffer); `w` then holds the exact state to continue from.
+__device__ bool descend_buckets(Ctx &c, Buckets &bk, Walk &w, int &hi, float x_ge, float x_gt, long long nstop,
+                                bool may_reuse) {
+    Aux *A = c.A;
+    const bool counting = nstop >= 0;
+    for (int phase = 0; phase < 8192; phase++) {
+        c.nphase++;
+        if (hi <= 0) { w.tau = 0; w.event = EV_EXHAUSTED; return true; }
+        if (!(w.s > 0.0f)) return false;
+        const int j = fexpo(w.s);
+        if (j < -100 || j > 100) return false;
+        const float inv_u = fpow2(23 - j);
+        if (!(may_reuse && bk.mass_j == j && bk.mass_hi >= hi)) {
+            buckets_masses(c, bk, j, hi);
+            bk.ck_s = w.s; bk.ck_pos = w.pos; bk.ck_hi = hi;
+        }
+        may_reuse = true;
+        BinQuery qy;
+        qy.specbin = -1; qy.bin_hi = hi; qy.spec_bits = A->spec_bits;
+        qy.pos0 = (unsigned long long)w.pos;
+        qy.nstop = counting ? (unsigned long long)nstop : ~0ull;
+        qy.m0 = (unsigned long long)((double)w.s * (double)inv_u);
+        unsigned long long xq = 1ull << 24;
+        if (x_ge < 3.0e38f) { double t = ceil((double)x_ge * (double)inv_u); if (t < (double)xq) xq = (t <= 0.0) ? 0ull : (unsigned long long)t; }
+        if (x_gt < 3.0e38f) { double t = floor((double)x_gt * (double)inv_u) + 1.0; if (t < (double)xq) xq = (t <= 0.0) ? 0ull : (unsigned long long)t; }
+        qy.xq = xq;
+        find_event_bin(c, qy);
+        const int hb = A->hit_bin;
+        if (hb < 0) {
+            w.s = (float)((double)(qy.m0 + A->tot_q) * (double)fpow2(j - 23));
+            w.pos += (long long)A->tot_c;
+            w.tau = 0; hi = 0;
+            w.event = EV_EXHAUSTED;
+            return true;
+        }
+        const unsigned long long qb = A->hit_qbefore, cb = A->hit_cbefore;
+        const float s_bin = (float)((double)(qy.m0 + qb) * (double)fpow2(j - 23));
+        const long long pos_bin = w.pos + (long long)cb;
+        const int nb = (int)bk.cnt[hb];
+        if (nb > NC) {  // a crowded bin: the general walk splits it further
+            w.s = s_bin; w.pos = pos_bin; w.tau = (unsigned int)(hb + 1) << BIN_SHIFT; hi = hb + 1;
+            return false;
+        }
+        __syncthreads();
+        for (int i = c.tid; i < nb; i += NT) A->cand[i] = bk.arr[bk.off[hb] + i];
+        sort_cands(c, nb);
+        walk_sorted(c, nb, s_bin, pos_bin, x_ge, x_gt, counting, nstop);
+        w.s = A->b_s; w.pos = A->b_pos; w.tau = (unsigned int)hb << BIN_SHIFT; hi = hb;
+        if (A->b_event != EV_NONE) { w.event = A->b_event; w.idx = A->b_idx; w.p = A->b_p; w.tie = A->b_aux; return true; }
+    }
+    return false;
 }
 
 // Between the two all-gathers of the vocab-sharded form: one thread per row folds the shards'
@@ -866,7 +1202,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         __syncthreads();
         const int r = A->cur_row;
         if (r >= a.B) break;
-        c.status = 0;
+        c.status = 0; c.nphase = 0;
         const float T = a.temperature ? a.temperature[r] : 0.0f;
         const int k = a.top_k ? a.top_k[r] : 0;
         const float P = a.top_p ? a.top_p[r] : 1.0f;
@@ -1151,7 +1487,9 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 // gather the warps' segments into one array: shared memory if it fits, else global
                 unsigned long long *dstl = (nl <= SLIST_CAP) ? slist : wl_flat;
                 if (a.mode == 2) dstl = a.sb_list + (long long)r * a.list_cap;  // the slice's list goes to the all-gather
-                const int nmove = (a.mode == 2 && nl > a.list_cap) ? 0 : nl;
+                // a long list of the ordinary form stays where pass B wrote it (the view walks the segments)
+                const bool stays = (a.mode == 0 && nl > SLIST_CAP);
+                const int nmove = (stays || (a.mode == 2 && nl > a.list_cap)) ? 0 : nl;
                 auto fetch = [&](int v) -> unsigned long long {
                     int w = 0;
 #pragma unroll
@@ -1177,13 +1515,21 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 if (c.tid == 0) a.sb_count[r] = (nl > a.list_cap) ? -1 : nl;  // -1: the slice's list outgrew the exchange buffer
                 continue;
             }
-            const unsigned long long *lst = (nl <= SLIST_CAP) ? slist : wl_flat;
+            LView lv;
+            lv.n = nl; lv.woff = A->woff;
+            if (nl <= SLIST_CAP) { lv.flat = slist; lv.seg = nullptr; lv.stride = 0; }
+            else if (a.mode == 0) { lv.flat = nullptr; lv.seg = wl_seg; lv.stride = (size_t)a.R; }
+            else {  // stage 3: the shards' lists were copied into one global array
+                if (c.tid <= NWARP) A->woff[c.tid] = (c.tid == 0) ? 0 : nl;
+                __syncthreads();
+                lv.flat = nullptr; lv.seg = wl_flat; lv.stride = 0;
+            }
             STAMP(3);
 
             // ---- 4. the softmax denominator, exactly as the sequential loop rounds it
-            const bool in_smem = nl <= SLIST_CAP;
             if (c.tid == 0) A->walk_slow = 0;
-            p1_run(c, lst, nl, in_smem, slist, false, 0.0f);
+            unsigned int *vstage = reinterpret_cast<unsigned int *>(c.stage);
+            p1_run(c, lv, vstage, false, 0.0f);
             const float Z = A->walk_s;
             if (A->walk_slow) c.status |= MOLLA_ROW_SLOW_PATH;
             dZ = Z;
@@ -1195,17 +1541,19 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             const unsigned int tau_p = __float_as_uint(__fdiv_rn(__uint_as_float(tau_bits), Z));
             const unsigned int tau_pb = tau_p > 1u ? tau_p : 1u;
             bool mark_head = head_in_pass;  // the head was taken in pass B: its entries are consumed
+            unsigned int *bin_counts = nullptr;  // set: the conversion pass also counts entries per value bin
+            unsigned int count_below = 0u;
             auto convert_list = [&](bool gather_head) {
                 __syncthreads();
                 if (gather_head && c.tid == 0) A->ncand = 0;
                 __syncthreads();
-                unsigned long long *wlst = const_cast<unsigned long long *>(lst);
-                for_list(wlst, nl, c.tid, [&](int i, unsigned long long kk) {
+                lv.for_each(c.tid, [&](int, unsigned long long kk, unsigned long long *where) {
                     unsigned int pb = __float_as_uint(__fdiv_rn(key_val(kk), Z));
                     // entries the head took in pass B (by their exponential) are marked as consumed
                     if (!gather_head && mark_head && (unsigned int)(kk >> 32) >= tau_bits) pb = 0xFFFFFFFFu;
                     const unsigned long long nk = ((unsigned long long)pb << 32) | (kk & 0xFFFFFFFFull);
-                    wlst[i] = nk;
+                    *where = nk;
+                    if (bin_counts && pb < count_below) atomicAdd(&bin_counts[pb >> BIN_SHIFT], 1u);
                     if (gather_head && pb >= tau_pb) {
                         const int pos = atomicAdd(&A->ncand, 1);
                         if (pos < HEADC) A->cand[pos] = nk;
@@ -1225,18 +1573,21 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 __syncthreads();
             }
 
+            STAMP(5);
             if (pure) {
                 // ---- 5a. nothing sorted: the draw walks the vocabulary in order (sample.mojo:365-369,
                 // 580-594): the same exact-sum machinery on the list of probabilities
                 __syncthreads();
-                p1_run(c, lst, nl, in_smem, slist, false, 0.0f);
+                p1_run(c, lv, vstage, false, 0.0f);
+                STAMP(6);
                 const float sum = A->walk_s;
                 const float target = __fmul_rn(u01, sum);
-                p1_run(c, lst, nl, in_smem, slist, true, target);
+                p1_run(c, lv, vstage, true, target);
+                STAMP(7);
                 if (c.tid == 0) {
                     A->b_sum = sum; A->b_target = target;
                     A->b_event = A->walk_found;
-                    A->b_idx = A->walk_found ? key_idx(lst[A->walk_idx]) : imax;
+                    A->b_idx = A->walk_found ? key_idx(lv.at(A->walk_idx)) : imax;
                     A->b_aux = A->walk_slow;
                 }
                 __syncthreads();
@@ -1314,12 +1665,31 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         token = A->b_idx; dp = A->b_p; dsum = A->b_sum; dtarget = A->b_target;
                     } else {
                         // ---- 6. past the head: the cut walk, then the draw walk
+                        STAMP(6);
+                        // long lists (global memory) are first sorted into their value bins
+                        Buckets bk;
+                        bk.arr = wl_flat; bk.off = reinterpret_cast<unsigned int *>(A->hkey);
+                        bk.cur = reinterpret_cast<unsigned int *>(A->hcnt); bk.cnt = reinterpret_cast<unsigned int *>(A->hval);
+                        bk.built = false; bk.total = 0; bk.mass_j = -0x7fffffff; bk.mass_hi = 0; bk.ck_s = 0.0f; bk.ck_pos = 0; bk.ck_hi = NBINS;
+                        const bool use_bk = (a.mode == 0) && !lv.flat && !list_is_p;
+                        if (use_bk) {
+                            __syncthreads();
+                            for (int i = c.tid; i < NBINS; i += NT) bk.cnt[i] = 0u;
+                            bin_counts = bk.cnt; count_below = tau_head;
+                        }
                         if (!list_is_p) { convert_list(false); list_is_p = true; }
+                        bin_counts = nullptr;
+                        if (use_bk) buckets_build(c, lv, bk, tau_head);
+                        STAMP(7);
                         __syncthreads();
                         Walk cutw; cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
                         cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
                         const bool limited = n_lim < (long long)a.Vg;
-                        descend(c, lst, nl, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
+                        {
+                            int hi = NBINS;
+                            const bool done = use_bk && descend_buckets(c, bk, cutw, hi, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1, false);
+                            if (!done) descend(c, lv, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
+                        }
                         if (cutw.event != EV_DEGENERATE) {
                             if (cutw.event == EV_CUT && cutw.tie) c.status |= MOLLA_ROW_TOPP_TIE;
                             if (cutw.event == EV_LIMIT && cutw.tie) c.status |= MOLLA_ROW_TOPK_TIE;
@@ -1347,7 +1717,17 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                                     __syncthreads();
                                     Walk dw; dw.s = head_s; dw.pos = head_pos; dw.tau = tau_head;
                                     dw.event = EV_NONE; dw.idx = -1; dw.p = 0; dw.tie = 0;
-                                    descend(c, lst, nl, dw, 3.4e38f, target, -1);
+                                    bool ddone = false;
+                                    if (use_bk) {
+                                        int hi = NBINS;
+                                        // everything before the point the masses were last built at sums to
+                                        // bk.ck_s: if that does not exceed the target, start there and reuse them
+                                        if (bk.mass_j != -0x7fffffff && !(target < bk.ck_s) && bk.ck_hi < NBINS) {
+                                            dw.s = bk.ck_s; dw.pos = bk.ck_pos; hi = bk.ck_hi; dw.tau = (unsigned int)hi << BIN_SHIFT;
+                                        }
+                                        ddone = descend_buckets(c, bk, dw, hi, 3.4e38f, target, -1, true);
+                                    }
+                                    if (!ddone) descend(c, lv, dw, 3.4e38f, target, -1);
                                     if (dw.event == EV_DRAW) {
                                         token = dw.idx; dp = dw.p; resolved = true;
                                         if (dw.tie) c.status |= MOLLA_ROW_CHOSEN_TIE;
@@ -1363,7 +1743,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                                         // everything listed was kept: its smallest value, highest id last
                                         // (keys order by value, then by inverted id)
                                         unsigned long long best = ~0ull;
-                                        for (int i = c.tid; i < nl; i += NT) best = lst[i] < best ? lst[i] : best;
+                                        lv.for_each(c.tid, [&](int, unsigned long long kk, unsigned long long *) { best = kk < best ? kk : best; });
 #pragma unroll
                                         for (int o = 16; o > 0; o >>= 1) {
                                             unsigned long long ob = __shfl_xor_sync(0xffffffffu, best, o);
@@ -1384,6 +1764,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             }
         }
         STAMP(9);
+        if (a.prof && c.tid == 0) a.prof[(long long)r * 16 + 8] = c.nphase;
         if (c.tid == 0) {
             a.tokens[r] = token;
             a.row_status[r] = c.status;
