@@ -361,9 +361,12 @@ struct LView {
             const int m = flat ? n : woff[w + 1] - o;
             const int lo = max(v0 - o, 0), hi = min(v1 - o, m);
             int i = lo + tid;
-            for (; i + 3 * NT < hi; i += 4 * NT) {
-                const unsigned long long k0 = b[i], k1 = b[i + NT], k2 = b[i + 2 * NT], k3 = b[i + 3 * NT];
-                f(o + i, k0); f(o + i + NT, k1); f(o + i + 2 * NT, k2); f(o + i + 3 * NT, k3);
+            for (; i + 7 * NT < hi; i += 8 * NT) {
+                unsigned long long k[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) k[q] = b[i + q * NT];
+#pragma unroll
+                for (int q = 0; q < 8; q++) f(o + i + q * NT, k[q]);
             }
             for (; i < hi; i += NT) f(o + i, b[i]);
         }
@@ -394,7 +397,19 @@ template <class V>
 __device__ __forceinline__ void p1_sim(V lst, int i0, int i1, bool locate, float target,
                                        Walker &w) {
     float s = w.s;
-    for (int i = i0; i < i1; i++) {
+    int i = i0;
+    for (; i + 8 <= i1; i += 8) {  // the loads do not depend on the running sum: fetch eight, then add
+        float v[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) v[q] = lst(i + q);
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            s = __fadd_rn(s, v[q]);
+            if (locate && !w.found && target < s) { w.found = 1; w.at = i + q; }
+        }
+        if (locate && w.found) { w.s = s; return; }
+    }
+    for (; i < i1; i++) {
         s = __fadd_rn(s, lst(i));
         if (locate && target < s) { w.found = 1; w.at = i; break; }
     }
@@ -1452,16 +1467,27 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 }
                 __syncwarp();
                 tqb += clock64() - tq0; tq0 = clock64();
-                for (int i = c.lane; i < total; i += 32) {
-                    const float xx = slot[i];
-                    const float v = (T == 1.0f) ? xx : __fdiv_rn(xx, T);
-                    const float e = expf_pinned(__fsub_rn(v, top));
-                    const unsigned long long key = make_key(__float_as_uint(e), a.col0 + c.rbeg + p * PIECE + (int)A->u.s.ppos[c.warp][i]);
-                    myseg[base + i] = key;
-                    if (head_in_pass && __float_as_uint(e) >= tau_bits) {
-                        const int pos = atomicAdd(&A->ncand, 1);
-                        if (pos < HEADC) A->cand[pos] = key;
+                {
+                    const int gbase = a.col0 + c.rbeg + p * PIECE;
+                    auto value = [&](int i) -> float {
+                        const float xx = slot[i];
+                        const float v = (T == 1.0f) ? xx : __fdiv_rn(xx, T);
+                        return expf_pinned(__fsub_rn(v, top));
+                    };
+                    auto emit = [&](int i, float e) {
+                        const unsigned long long key = make_key(__float_as_uint(e), gbase + (int)A->u.s.ppos[c.warp][i]);
+                        myseg[base + i] = key;
+                        if (head_in_pass && __float_as_uint(e) >= tau_bits) {
+                            const int pos = atomicAdd(&A->ncand, 1);
+                            if (pos < HEADC) A->cand[pos] = key;
+                        }
+                    };
+                    int i = c.lane;
+                    for (; i + 96 < total; i += 128) {  // four independent evaluations in flight
+                        const float e0 = value(i), e1 = value(i + 32), e2 = value(i + 64), e3 = value(i + 96);
+                        emit(i, e0); emit(i + 32, e1); emit(i + 64, e2); emit(i + 96, e3);
                     }
+                    for (; i < total; i += 32) emit(i, value(i));
                 }
                 base += total;
                 lb += A->u.s.pmax[c.warp][p];
