@@ -103,8 +103,8 @@ struct __align__(16) Aux {
             unsigned short seg[NT];
         } p1;
         struct {
-            unsigned int hq[NBINS];   // low words of the per-bin integer mass
-            unsigned int hqh[NBINS];  // carries out of the low words
+            unsigned int hq[NBINS];   // per bin: sum of the low bits of the integer contributions
+            unsigned int hqh[NBINS];  // ... and of their high bits
             unsigned int hc[NBINS];
         } h;
         struct {                                 // the streaming passes only
@@ -157,6 +157,7 @@ struct Ctx {
     int rbeg, rlen, npieces;
     unsigned int parbits;
     int nphase;           // histogram phases run by the descending walks of this row (profiling aid)
+    long long tmass;      // cycles spent building bin masses (profiling aid)
 };
 
 #define STAMP(i) do { if (a.prof && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
@@ -619,12 +620,18 @@ __device__ void p1_run(Ctx &c, const LView &lv, unsigned int *vals, bool locate,
 // Histogram search: thread t owns bins NBINS-1-BPT*t-i (i < BPT), so a scan over the
 // threads runs through the bins in descending order.
 // =============================================================================
+// A bin's integer mass is kept as two sums, of the low MASS_SPLIT bits of each contribution and of
+// the rest: contributions are below 2^27 (32 elements of less than 2^22 units each) and a bin holds
+// fewer than 2^20 elements, so neither sum can wrap, and the additions need no return value.
+constexpr int MASS_SPLIT = 11;
+constexpr unsigned int MASS_LO_MASK = (1u << MASS_SPLIT) - 1u;
 struct BinQuery {
     unsigned long long m0, xq;       // mass event: m0 + cum_q >= xq   (xq = ~0 disables)
     unsigned long long pos0, nstop;  // count event: pos0 + cum_c >= nstop (nstop = ~0 disables)
     int specbin;                     // stop at this bin (-1 disables)
     int bin_hi;                      // only bins below this one count (NBINS = all)
     const unsigned int *spec_bits;   // or: stop at any bin whose bit is set here (nullptr = use specbin)
+    const unsigned int *hq, *hqh, *hc;  // per bin: integer mass (low MASS_SPLIT bits summed, the rest summed) and count
 };
 
 __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
@@ -634,8 +641,8 @@ __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
     for (int i = 0; i < BPT; i++) {
         const int b = NBINS - 1 - BPT * c.tid - i;
         const bool live = b < qy.bin_hi;
-        q[i] = live ? ((unsigned long long)A->u.h.hq[b] | ((unsigned long long)A->u.h.hqh[b] << 32)) : 0ull;
-        n[i] = live ? A->u.h.hc[b] : 0u;
+        q[i] = live ? ((unsigned long long)qy.hq[b] + ((unsigned long long)qy.hqh[b] << MASS_SPLIT)) : 0ull;
+        n[i] = live ? qy.hc[b] : 0u;
         sq += q[i]; sn += n[i];
     }
     unsigned long long tq, tc;
@@ -859,15 +866,16 @@ __device__ void descend(Ctx &c, const LView &lv, Walk &w, float x_ge, float x_gt
                 return;
             }
             const unsigned int qu = __float2uint_rn(__fmul_rn(q, inv_u));
-            if (qu) {
-                const unsigned int old = atomicAdd(&A->u.h.hq[bin], qu);
-                if (old + qu < old) atomicAdd(&A->u.h.hqh[bin], 1u);
+            if (qu) {  // two halves, so that neither counter can wrap and no atomic has to return a value
+                atomicAdd(&A->u.h.hq[bin], qu & MASS_LO_MASK);
+                if (qu >> MASS_SPLIT) atomicAdd(&A->u.h.hqh[bin], qu >> MASS_SPLIT);
             }
             if (counting) atomicAdd(&A->u.h.hc[bin], 1u);
         });
         __syncthreads();
         BinQuery qy;
         qy.specbin = A->specbin; qy.bin_hi = NBINS; qy.spec_bits = nullptr;
+        qy.hq = A->u.h.hq; qy.hqh = A->u.h.hqh; qy.hc = A->u.h.hc;
         qy.pos0 = (unsigned long long)w.pos;
         qy.nstop = counting ? (unsigned long long)nstop : ~0ull;
         qy.m0 = 0; qy.xq = ~0ull;
@@ -970,6 +978,18 @@ __device__ void descend(Ctx &c, const LView &lv, Walk &w, float x_ge, float x_gt
 // coalesced pass with warp-aggregated atomics and stay valid until the running sum leaves
 // the binade, and walking a bin touches only that bin.
 // =============================================================================
+// Value bins of the bucketed list: 64 per binade over the 32 binades below 1 (probabilities
+// further down share bin 0), so that even a flat row spreads over hundreds of bins.
+constexpr int BK_SHIFT = 17;
+constexpr int BK_BASE = (127 - 32) << 6;
+__device__ __forceinline__ int bk_bin(unsigned int pbits) {
+    const int b = (int)(pbits >> BK_SHIFT) - BK_BASE;
+    return min(max(b, 0), NBINS - 1);
+}
+__device__ __forceinline__ unsigned int bk_lo(int bin) {  // smallest value bits of a bin
+    return bin <= 0 ? 0u : (unsigned int)(bin + BK_BASE) << BK_SHIFT;
+}
+
 struct Buckets {
     unsigned long long *arr;   // the list ordered by bin, highest bin first (global memory)
     unsigned int *off;         // [NBINS] entries in higher bins (shared memory)
@@ -977,7 +997,8 @@ struct Buckets {
     unsigned int *cur;         // [NBINS] scatter cursors
     int total;
     bool built;
-    int mass_j;                // binade the masses in u.h.hq were computed for (INT_MIN: none)
+    unsigned int *sets;        // MASS_SETS x (NBINS low words, NBINS carries, NBINS/32 care bits) (shared memory)
+    int mass_j;                // set k holds the masses in units of binade mass_j + k (INT_MIN: none)
     int mass_hi;               // ... over the bins below this one
     // where the masses were last built: a later walk that starts at or after this point reuses them
     float ck_s; long long ck_pos; int ck_hi;
@@ -1000,55 +1021,79 @@ __device__ void buckets_build(Ctx &c, const LView &lv, Buckets &bk, unsigned int
     lv.for_each(c.tid, [&](int, unsigned long long key, unsigned long long *) {
         const unsigned int pb = (unsigned int)(key >> 32);
         if (pb >= tau) return;
-        const unsigned int pos = atomicAdd(&bk.cur[pb >> BIN_SHIFT], 1u);
+        const unsigned int pos = atomicAdd(&bk.cur[bk_bin(pb)], 1u);
         bk.arr[pos] = key;
     });
     __syncthreads();
     bk.total = (int)tot; bk.built = true; bk.mass_j = -0x7fffffff; bk.mass_hi = 0;
 }
 
-// integer masses of the bins below `hi` for binade j, and the bins that need sequential care
+// Integer masses of the bins below `hi` in the units of MASS_SETS consecutive binades starting
+// at j, and per binade the bins that need sequential care: one pass over the sorted array
+// serves a walk whose running sum doubles up to MASS_SETS - 1 times.
+constexpr int MASS_SETS = 3;
+constexpr int MASS_SET_WORDS = 2 * NBINS + NBINS / 32;
 __device__ void buckets_masses(Ctx &c, Buckets &bk, int j, int hi) {
-    Aux *A = c.A;
+    const long long t0 = clock64();
     __syncthreads();
-    for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0u; A->u.h.hqh[i] = 0u; A->u.h.hc[i] = bk.cnt[i]; }
-    for (int i = c.tid; i < NBINS / 32; i += NT) A->spec_bits[i] = 0u;
+    for (int i = c.tid; i < MASS_SETS * MASS_SET_WORDS; i += NT) bk.sets[i] = 0u;
     __syncthreads();
-    const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1), inv_u = fpow2(23 - j);
     const int p0 = (hi >= NBINS) ? 0 : (int)(bk.off[hi - 1]);
     const int n = bk.total;
-    // every warp walks whole groups of 32 consecutive entries, so the ballots below are warp-wide
-    for (int base0 = p0 + (c.tid & ~31); base0 < n; base0 += 4 * NT) {
-        unsigned long long kk[4];
+    const float Cm0 = __fmul_rn(1.5f, fpow2(j)), half0 = fpow2(j - 24), big0 = fpow2(j - 1);
+    // every warp walks whole groups of 64 consecutive entries (two per lane, one 16-byte load), so
+    // the votes below are warp-wide; eight loads in flight per thread
+    const ulonglong2 *arr2 = reinterpret_cast<const ulonglong2 *>(bk.arr);
+    const int pair0 = p0 >> 1, npair = (n + 1) >> 1;
+    for (int base0 = pair0 + (c.tid & ~31); base0 < npair; base0 += 8 * NT) {
+        ulonglong2 kk[8];
 #pragma unroll
-        for (int g = 0; g < 4; g++) {
+        for (int g = 0; g < 8; g++) {
             const int i = base0 + g * NT + c.lane;
-            kk[g] = (i < n) ? bk.arr[i] : 0ull;
+            kk[g] = (i < npair) ? arr2[i] : make_ulonglong2(0ull, 0ull);
         }
 #pragma unroll
-        for (int g = 0; g < 4; g++) {
+        for (int g = 0; g < 8; g++) {
             const int i = base0 + g * NT + c.lane;
-            if (base0 + g * NT >= n) break;  // warp-uniform
-            const bool in = i < n;
-            const unsigned int pb = (unsigned int)(kk[g] >> 32);
-            const int bin = (int)(pb >> BIN_SHIFT);
-            const float p = __uint_as_float(pb);
-            const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
-            const float r = __fsub_rn(p, q);
-            const bool special = in && (fabsf(r) == halfu || p >= bigthr);
-            const unsigned int qu = (in && !special) ? __float2uint_rn(__fmul_rn(q, inv_u)) : 0u;
-            if (special) atomicOr(&A->spec_bits[bin >> 5], 1u << (bin & 31));
-            // neighbours in the sorted array mostly share a bin: one atomic per bin per warp
-            const unsigned int peers = __match_any_sync(0xffffffffu, in ? bin : -1);
-            const unsigned int sum = __reduce_add_sync(peers, qu);
-            if (in && sum && c.lane == __ffs(peers) - 1) {
-                const unsigned int old = atomicAdd(&A->u.h.hq[bin], sum);
-                if (old + sum < old) atomicAdd(&A->u.h.hqh[bin], 1u);
+            if (base0 + g * NT >= npair) break;  // warp-uniform
+            const bool in0 = 2 * i >= p0 && 2 * i < n, in1 = 2 * i + 1 >= p0 && 2 * i + 1 < n;
+            const unsigned int pb0 = (unsigned int)(kk[g].x >> 32), pb1 = (unsigned int)(kk[g].y >> 32);
+            const int b0 = bk_bin(pb0), b1 = bk_bin(pb1);
+            const float v0 = __uint_as_float(pb0), v1 = __uint_as_float(pb1);
+            // neighbours in the sorted array mostly share a bin: then one atomic per warp
+            const int bin0 = __shfl_sync(0xffffffffu, in0 ? b0 : b1, 0);
+            const bool same = __all_sync(0xffffffffu, (!in0 || b0 == bin0) && (!in1 || b1 == bin0));
+#pragma unroll
+            for (int k = 0; k < MASS_SETS; k++) {
+                // p + 1.5 * 2^(j+k) rounds p to the binade's unit; below 2^(j+k-1) the rounded
+                // multiple sits in the low 22 mantissa bits of that sum
+                const float sc = (float)(1 << k);  // exact scalings
+                const float Cm = __fmul_rn(Cm0, sc), hk = __fmul_rn(half0, sc), bgk = __fmul_rn(big0, sc);
+                unsigned int *set = bk.sets + k * MASS_SET_WORDS;
+                const float t0 = __fadd_rn(v0, Cm), t1 = __fadd_rn(v1, Cm);
+                const float r0 = __fsub_rn(v0, __fsub_rn(t0, Cm)), r1 = __fsub_rn(v1, __fsub_rn(t1, Cm));
+                const unsigned int tb0 = __float_as_uint(t0), tb1 = __float_as_uint(t1);
+                const bool sp0 = in0 && (fabsf(r0) == hk || v0 >= bgk || !(tb0 & 0x400000u));
+                const bool sp1 = in1 && (fabsf(r1) == hk || v1 >= bgk || !(tb1 & 0x400000u));
+                const unsigned int q0 = (in0 && !sp0) ? (tb0 & 0x3fffffu) : 0u, q1 = (in1 && !sp1) ? (tb1 & 0x3fffffu) : 0u;
+                if (sp0) atomicOr(&set[2 * NBINS + (b0 >> 5)], 1u << (b0 & 31));
+                if (sp1) atomicOr(&set[2 * NBINS + (b1 >> 5)], 1u << (b1 & 31));
+                if (same) {
+                    const unsigned int sum = __reduce_add_sync(0xffffffffu, q0 + q1);
+                    if (c.lane == 0 && sum) {
+                        atomicAdd(&set[bin0], sum & MASS_LO_MASK);
+                        if (sum >> MASS_SPLIT) atomicAdd(&set[NBINS + bin0], sum >> MASS_SPLIT);
+                    }
+                } else {
+                    if (q0) { atomicAdd(&set[b0], q0 & MASS_LO_MASK); if (q0 >> MASS_SPLIT) atomicAdd(&set[NBINS + b0], q0 >> MASS_SPLIT); }
+                    if (q1) { atomicAdd(&set[b1], q1 & MASS_LO_MASK); if (q1 >> MASS_SPLIT) atomicAdd(&set[NBINS + b1], q1 >> MASS_SPLIT); }
+                }
             }
         }
     }
     __syncthreads();
     bk.mass_j = j; bk.mass_hi = hi;
+    c.tmass += clock64() - t0;
 }
 
 // Returns false if it met something it leaves to the general walk (no usable binade yet, or a
@@ -1064,13 +1109,15 @@ __device__ bool descend_buckets(Ctx &c, Buckets &bk, Walk &w, int &hi, float x_g
         const int j = fexpo(w.s);
         if (j < -100 || j > 100) return false;
         const float inv_u = fpow2(23 - j);
-        if (!(may_reuse && bk.mass_j == j && bk.mass_hi >= hi)) {
+        if (!(may_reuse && bk.mass_j != -0x7fffffff && j >= bk.mass_j && j < bk.mass_j + MASS_SETS && bk.mass_hi >= hi)) {
             buckets_masses(c, bk, j, hi);
             bk.ck_s = w.s; bk.ck_pos = w.pos; bk.ck_hi = hi;
         }
         may_reuse = true;
+        const unsigned int *set = bk.sets + (j - bk.mass_j) * MASS_SET_WORDS;
         BinQuery qy;
-        qy.specbin = -1; qy.bin_hi = hi; qy.spec_bits = A->spec_bits;
+        qy.specbin = -1; qy.bin_hi = hi; qy.spec_bits = set + 2 * NBINS;
+        qy.hq = set; qy.hqh = set + NBINS; qy.hc = bk.cnt;
         qy.pos0 = (unsigned long long)w.pos;
         qy.nstop = counting ? (unsigned long long)nstop : ~0ull;
         qy.m0 = (unsigned long long)((double)w.s * (double)inv_u);
@@ -1092,14 +1139,14 @@ __device__ bool descend_buckets(Ctx &c, Buckets &bk, Walk &w, int &hi, float x_g
         const long long pos_bin = w.pos + (long long)cb;
         const int nb = (int)bk.cnt[hb];
         if (nb > NC) {  // a crowded bin: the general walk splits it further
-            w.s = s_bin; w.pos = pos_bin; w.tau = (unsigned int)(hb + 1) << BIN_SHIFT; hi = hb + 1;
+            w.s = s_bin; w.pos = pos_bin; w.tau = bk_lo(hb + 1); hi = hb + 1;
             return false;
         }
         __syncthreads();
         for (int i = c.tid; i < nb; i += NT) A->cand[i] = bk.arr[bk.off[hb] + i];
         sort_cands(c, nb);
         walk_sorted(c, nb, s_bin, pos_bin, x_ge, x_gt, counting, nstop);
-        w.s = A->b_s; w.pos = A->b_pos; w.tau = (unsigned int)hb << BIN_SHIFT; hi = hb;
+        w.s = A->b_s; w.pos = A->b_pos; w.tau = bk_lo(hb); hi = hb;
         if (A->b_event != EV_NONE) { w.event = A->b_event; w.idx = A->b_idx; w.p = A->b_p; w.tie = A->b_aux; return true; }
     }
     return false;
@@ -1217,7 +1264,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         __syncthreads();
         const int r = A->cur_row;
         if (r >= a.B) break;
-        c.status = 0; c.nphase = 0;
+        c.status = 0; c.nphase = 0; c.tmass = 0;
         const float T = a.temperature ? a.temperature[r] : 0.0f;
         const int k = a.top_k ? a.top_k[r] : 0;
         const float P = a.top_p ? a.top_p[r] : 1.0f;
@@ -1579,7 +1626,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     if (!gather_head && mark_head && (unsigned int)(kk >> 32) >= tau_bits) pb = 0xFFFFFFFFu;
                     const unsigned long long nk = ((unsigned long long)pb << 32) | (kk & 0xFFFFFFFFull);
                     *where = nk;
-                    if (bin_counts && pb < count_below) atomicAdd(&bin_counts[pb >> BIN_SHIFT], 1u);
+                    if (bin_counts && pb < count_below) atomicAdd(&bin_counts[bk_bin(pb)], 1u);
                     if (gather_head && pb >= tau_pb) {
                         const int pos = atomicAdd(&A->ncand, 1);
                         if (pos < HEADC) A->cand[pos] = nk;
@@ -1696,6 +1743,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         Buckets bk;
                         bk.arr = wl_flat; bk.off = reinterpret_cast<unsigned int *>(A->hkey);
                         bk.cur = reinterpret_cast<unsigned int *>(A->hcnt); bk.cnt = reinterpret_cast<unsigned int *>(A->hval);
+                        bk.sets = reinterpret_cast<unsigned int *>(c.stage);  // idle while the list is a global view
                         bk.built = false; bk.total = 0; bk.mass_j = -0x7fffffff; bk.mass_hi = 0; bk.ck_s = 0.0f; bk.ck_pos = 0; bk.ck_hi = NBINS;
                         const bool use_bk = (a.mode == 0) && !lv.flat && !list_is_p;
                         if (use_bk) {
@@ -1749,7 +1797,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                                         // everything before the point the masses were last built at sums to
                                         // bk.ck_s: if that does not exceed the target, start there and reuse them
                                         if (bk.mass_j != -0x7fffffff && !(target < bk.ck_s) && bk.ck_hi < NBINS) {
-                                            dw.s = bk.ck_s; dw.pos = bk.ck_pos; hi = bk.ck_hi; dw.tau = (unsigned int)hi << BIN_SHIFT;
+                                            dw.s = bk.ck_s; dw.pos = bk.ck_pos; hi = bk.ck_hi; dw.tau = bk_lo(hi);
                                         }
                                         ddone = descend_buckets(c, bk, dw, hi, 3.4e38f, target, -1, true);
                                     }
@@ -1790,7 +1838,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             }
         }
         STAMP(9);
-        if (a.prof && c.tid == 0) a.prof[(long long)r * 16 + 8] = c.nphase;
+        if (a.prof && c.tid == 0) { a.prof[(long long)r * 16 + 8] = c.nphase; a.prof[(long long)r * 16 + 14] = c.tmass; }
         if (c.tid == 0) {
             a.tokens[r] = token;
             a.row_status[r] = c.status;
