@@ -163,4 +163,21 @@ __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Atomics on shared memory through a pointer whose address space the compiler cannot see
+// (it would otherwise fall back to generic-address atomics, which are far slower).
+__device__ __forceinline__ void sred_add(unsigned int *p, unsigned int v) {
+    asm volatile("red.shared.add.u32 [%0], %1;" ::"r"((unsigned int)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sred_or(unsigned int *p, unsigned int v) {
+    asm volatile("red.shared.or.b32 [%0], %1;" ::"r"((unsigned int)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sred_max(int *p, int v) {
+    asm volatile("red.shared.max.s32 [%0], %1;" ::"r"((unsigned int)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ int satom_add(int *p, int v) {
+    int old;
+    asm volatile("atom.shared.add.u32 %0, [%1], %2;" : "=r"(old) : "r"((unsigned int)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+    return old;
+}
+
 }  // namespace molla

@@ -351,46 +351,63 @@ struct LView {
         return seg + (size_t)w * stride + (size_t)(v - woff[w]);
     }
     __device__ __forceinline__ unsigned long long at(int v) const { return *slot(v); }
-    // f(index in the whole list, key, where the key lives); four loads in flight per thread
-    // the same over the entries [v0, v1) only
+    // f(index in the whole list, key) over the entries [v0, v1): the whole block on one segment
+    // after the other, 16-byte loads (two entries), eight in flight per thread
     template <class F>
     __device__ __forceinline__ void for_range(int tid, int v0, int v1, F f) const {
-        const int nseg = flat ? 1 : NWARP;
+        const bool one = flat || stride == 0;
+        const int nseg = one ? 1 : NWARP;
         for (int w = 0; w < nseg; w++) {
             const unsigned long long *b = flat ? flat : seg + (size_t)w * stride;
-            const int o = flat ? 0 : woff[w];
-            const int m = flat ? n : woff[w + 1] - o;
+            const int o = one ? 0 : woff[w];
+            const int m = one ? n : woff[w + 1] - o;
             const int lo = max(v0 - o, 0), hi = min(v1 - o, m);
-            int i = lo + tid;
-            for (; i + 7 * NT < hi; i += 8 * NT) {
-                unsigned long long k[8];
+            if (hi <= lo) continue;
+            const int lo2 = (lo + 1) & ~1, hi2 = hi & ~1;
+            if (tid == 0 && (lo & 1)) f(o + lo, b[lo]);
+            if (tid == 32 && (hi & 1) && hi - 1 >= lo2) f(o + hi - 1, b[hi - 1]);
+            const ulonglong2 *b2 = reinterpret_cast<const ulonglong2 *>(b);
+            const int p1 = hi2 >> 1;
+            int i = (lo2 >> 1) + tid;
+            for (; i + 7 * NT < p1; i += 8 * NT) {
+                ulonglong2 k[8];
 #pragma unroll
-                for (int q = 0; q < 8; q++) k[q] = b[i + q * NT];
+                for (int q = 0; q < 8; q++) k[q] = b2[i + q * NT];
 #pragma unroll
-                for (int q = 0; q < 8; q++) f(o + i + q * NT, k[q]);
+                for (int q = 0; q < 8; q++) { f(o + 2 * (i + q * NT), k[q].x); f(o + 2 * (i + q * NT) + 1, k[q].y); }
             }
-            for (; i < hi; i += NT) f(o + i, b[i]);
+            for (; i < p1; i += NT) { const ulonglong2 k = b2[i]; f(o + 2 * i, k.x); f(o + 2 * i + 1, k.y); }
         }
     }
     // f(index in the whole list, key, where the key lives). A list in segments is walked with one
-    // warp per segment (pass B left sixteen of similar length); eight loads in flight per thread.
+    // warp per segment (pass B left sixteen of similar length); 16-byte loads, eight in flight.
     template <class F>
     __device__ __forceinline__ void for_each(int tid, F f) const {
         unsigned long long *b;
-        int o, m, i, step;
-        if (flat) { b = const_cast<unsigned long long *>(flat); o = 0; m = n; i = tid; step = NT; }
+        int o, m, t, step;
+        if (flat || stride == 0) { b = flat ? const_cast<unsigned long long *>(flat) : seg; o = 0; m = n; t = tid; step = NT; }
         else {
             const int w = tid >> 5;
-            b = seg + (size_t)w * stride; o = woff[w]; m = woff[w + 1] - o; i = tid & 31; step = 32;
+            b = seg + (size_t)w * stride; o = woff[w]; m = woff[w + 1] - o; t = tid & 31; step = 32;
         }
-        for (; i + 7 * step < m; i += 8 * step) {
-            unsigned long long k[8];
+        const ulonglong2 *b2 = reinterpret_cast<const ulonglong2 *>(b);
+        const int mp = m >> 1;
+        int i = t;
+        for (; i + 7 * step < mp; i += 8 * step) {
+            ulonglong2 k[8];
 #pragma unroll
-            for (int q = 0; q < 8; q++) k[q] = b[i + q * step];
+            for (int q = 0; q < 8; q++) k[q] = b2[i + q * step];
 #pragma unroll
-            for (int q = 0; q < 8; q++) f(o + i + q * step, k[q], b + i + q * step);
+            for (int q = 0; q < 8; q++) {
+                const int e = 2 * (i + q * step);
+                f(o + e, k[q].x, b + e); f(o + e + 1, k[q].y, b + e + 1);
+            }
         }
-        for (; i < m; i += step) f(o + i, b[i], b + i);
+        for (; i < mp; i += step) {
+            const ulonglong2 k = b2[i];
+            f(o + 2 * i, k.x, b + 2 * i); f(o + 2 * i + 1, k.y, b + 2 * i + 1);
+        }
+        if ((m & 1) && t == 0) f(o + m - 1, b[m - 1], b + m - 1);
     }
 };
 
@@ -856,21 +873,21 @@ __device__ void descend(Ctx &c, const LView &lv, Walk &w, float x_ge, float x_gt
             const unsigned int eb = (unsigned int)(key >> 32);
             if (eb >= w.tau || eb < lo) return;
             const int bin = (int)((eb - lo) >> shift);
-            if (!binade_ok) { atomicAdd(&A->u.h.hc[bin], 1u); return; }
+            if (!binade_ok) { sred_add(&A->u.h.hc[bin], 1u); return; }
             const float p = __uint_as_float(eb);
             const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
             const float r = __fsub_rn(p, q);
             if (fabsf(r) == halfu || p >= bigthr) {
-                atomicMax(&A->specbin, bin);
-                if (counting) atomicAdd(&A->u.h.hc[bin], 1u);
+                sred_max(&A->specbin, bin);
+                if (counting) sred_add(&A->u.h.hc[bin], 1u);
                 return;
             }
             const unsigned int qu = __float2uint_rn(__fmul_rn(q, inv_u));
             if (qu) {  // two halves, so that neither counter can wrap and no atomic has to return a value
-                atomicAdd(&A->u.h.hq[bin], qu & MASS_LO_MASK);
-                if (qu >> MASS_SPLIT) atomicAdd(&A->u.h.hqh[bin], qu >> MASS_SPLIT);
+                sred_add(&A->u.h.hq[bin], qu & MASS_LO_MASK);
+                if (qu >> MASS_SPLIT) sred_add(&A->u.h.hqh[bin], qu >> MASS_SPLIT);
             }
-            if (counting) atomicAdd(&A->u.h.hc[bin], 1u);
+            if (counting) sred_add(&A->u.h.hc[bin], 1u);
         });
         __syncthreads();
         BinQuery qy;
@@ -911,7 +928,7 @@ __device__ void descend(Ctx &c, const LView &lv, Walk &w, float x_ge, float x_gt
         lv.for_each(c.tid, [&](int, unsigned long long key, unsigned long long *) {
             const unsigned int eb = (unsigned int)(key >> 32);
             if (eb < w.tau && eb >= blo && eb < bhi) {
-                int pos = atomicAdd(&A->ncand, 1);
+                int pos = satom_add(&A->ncand, 1);
                 if (pos < NC) A->cand[pos] = key;
             }
         });
@@ -972,14 +989,15 @@ __device__ void descend(Ctx &c, const LView &lv, Walk &w, float x_ge, float x_gt
 
 // =============================================================================
 // The same walk for long lists, which live in global memory: every pass over them costs
-// tens of microseconds, so the list is first sorted into its 2048 value bins (a counting
-// sort: bin counts taken while the probabilities were written, one scatter pass). After
-// that a bin is a contiguous slice, the per-bin integer masses of a binade come from one
-// coalesced pass with warp-aggregated atomics and stay valid until the running sum leaves
-// the binade, and walking a bin touches only that bin.
+// tens of microseconds. The pass that turns the list's exponentials into probabilities
+// also adds every entry's integer contribution to its value bin, in the units of
+// MASS_SETS consecutive binades starting at the one the running sum is in after the head
+// (`masses_add`). Those tables serve the cut walk and the draw walk alike (both run
+// through the same prefix sums), so a walk costs one filtered pass per bin it has to
+// look into: the bin where the sum leaves a binade, and the bin of the event itself.
 // =============================================================================
-// Value bins of the bucketed list: 64 per binade over the 32 binades below 1 (probabilities
-// further down share bin 0), so that even a flat row spreads over hundreds of bins.
+// Value bins: 64 per binade over the 32 binades below 1 (probabilities further down share
+// bin 0), so that even a flat row spreads over hundreds of bins.
 constexpr int BK_SHIFT = 17;
 constexpr int BK_BASE = (127 - 32) << 6;
 __device__ __forceinline__ int bk_bin(unsigned int pbits) {
@@ -990,116 +1008,63 @@ __device__ __forceinline__ unsigned int bk_lo(int bin) {  // smallest value bits
     return bin <= 0 ? 0u : (unsigned int)(bin + BK_BASE) << BK_SHIFT;
 }
 
-struct Buckets {
-    unsigned long long *arr;   // the list ordered by bin, highest bin first (global memory)
-    unsigned int *off;         // [NBINS] entries in higher bins (shared memory)
-    unsigned int *cnt;         // [NBINS] entries per bin
-    unsigned int *cur;         // [NBINS] scatter cursors
-    int total;
-    bool built;
-    unsigned int *sets;        // MASS_SETS x (NBINS low words, NBINS carries, NBINS/32 care bits) (shared memory)
-    int mass_j;                // set k holds the masses in units of binade mass_j + k (INT_MIN: none)
-    int mass_hi;               // ... over the bins below this one
-    // where the masses were last built: a later walk that starts at or after this point reuses them
-    float ck_s; long long ck_pos; int ck_hi;
+constexpr int MASS_SETS = 3;
+constexpr int MASS_SET_WORDS = 2 * NBINS + NBINS / 32;  // low sums, high sums, care bits
+constexpr int MASS_CK = 4;
+
+struct MassTable {
+    unsigned int *cnt;    // [NBINS] entries per bin (shared memory)
+    unsigned int *sets;   // MASS_SETS x MASS_SET_WORDS (shared memory)
+    int j0;               // set k is in the units of binade j0 + k
+    unsigned int tau0;    // only entries with value bits below this are in the tables
+    float Cm0, half0, big0;
+};
+// bins a walk consumed whole: the exact state before and after, for the walk that follows
+struct MassCk {
+    int n;
+    int bin[MASS_CK]; float s_in[MASS_CK], s_out[MASS_CK]; long long pos_in[MASS_CK], pos_out[MASS_CK];
 };
 
-__device__ void buckets_build(Ctx &c, const LView &lv, Buckets &bk, unsigned int tau) {
-    Aux *A = c.A;
-    // bk.cnt holds the per-bin counts of the entries below tau (taken during the conversion pass)
-    unsigned int n[BPT], sn = 0;
-#pragma unroll
-    for (int i = 0; i < BPT; i++) { n[i] = bk.cnt[NBINS - 1 - BPT * c.tid - i]; sn += n[i]; }
-    unsigned int tot;
-    unsigned int ex = block_excl_scan<unsigned int>(sn, reinterpret_cast<unsigned int *>(A->wsi), &tot);
-#pragma unroll
-    for (int i = 0; i < BPT; i++) {
-        const int b = NBINS - 1 - BPT * c.tid - i;
-        bk.off[b] = ex; bk.cur[b] = ex; ex += n[i];
-    }
+__device__ __forceinline__ void masses_begin(Ctx &c, MassTable &mt, int j0, unsigned int tau0) {
     __syncthreads();
-    lv.for_each(c.tid, [&](int, unsigned long long key, unsigned long long *) {
-        const unsigned int pb = (unsigned int)(key >> 32);
-        if (pb >= tau) return;
-        const unsigned int pos = atomicAdd(&bk.cur[bk_bin(pb)], 1u);
-        bk.arr[pos] = key;
-    });
+    for (int i = c.tid; i < MASS_SETS * MASS_SET_WORDS; i += NT) mt.sets[i] = 0u;
+    for (int i = c.tid; i < NBINS; i += NT) mt.cnt[i] = 0u;
+    mt.j0 = j0; mt.tau0 = tau0;
+    mt.Cm0 = __fmul_rn(1.5f, fpow2(j0)); mt.half0 = fpow2(j0 - 24); mt.big0 = fpow2(j0 - 1);
     __syncthreads();
-    bk.total = (int)tot; bk.built = true; bk.mass_j = -0x7fffffff; bk.mass_hi = 0;
 }
 
-// Integer masses of the bins below `hi` in the units of MASS_SETS consecutive binades starting
-// at j, and per binade the bins that need sequential care: one pass over the sorted array
-// serves a walk whose running sum doubles up to MASS_SETS - 1 times.
-constexpr int MASS_SETS = 3;
-constexpr int MASS_SET_WORDS = 2 * NBINS + NBINS / 32;
-__device__ void buckets_masses(Ctx &c, Buckets &bk, int j, int hi) {
-    const long long t0 = clock64();
-    __syncthreads();
-    for (int i = c.tid; i < MASS_SETS * MASS_SET_WORDS; i += NT) bk.sets[i] = 0u;
-    __syncthreads();
-    const int p0 = (hi >= NBINS) ? 0 : (int)(bk.off[hi - 1]);
-    const int n = bk.total;
-    const float Cm0 = __fmul_rn(1.5f, fpow2(j)), half0 = fpow2(j - 24), big0 = fpow2(j - 1);
-    // every warp walks whole groups of 64 consecutive entries (two per lane, one 16-byte load), so
-    // the votes below are warp-wide; eight loads in flight per thread
-    const ulonglong2 *arr2 = reinterpret_cast<const ulonglong2 *>(bk.arr);
-    const int pair0 = p0 >> 1, npair = (n + 1) >> 1;
-    for (int base0 = pair0 + (c.tid & ~31); base0 < npair; base0 += 8 * NT) {
-        ulonglong2 kk[8];
+// one entry's contribution to its bin in every set
+__device__ __forceinline__ void masses_add(const MassTable &mt, unsigned int pb) {
+    if (pb >= mt.tau0) return;
+    const int bin = bk_bin(pb);
+    sred_add(&mt.cnt[bin], 1u);
+    const float v = __uint_as_float(pb);
 #pragma unroll
-        for (int g = 0; g < 8; g++) {
-            const int i = base0 + g * NT + c.lane;
-            kk[g] = (i < npair) ? arr2[i] : make_ulonglong2(0ull, 0ull);
-        }
-#pragma unroll
-        for (int g = 0; g < 8; g++) {
-            const int i = base0 + g * NT + c.lane;
-            if (base0 + g * NT >= npair) break;  // warp-uniform
-            const bool in0 = 2 * i >= p0 && 2 * i < n, in1 = 2 * i + 1 >= p0 && 2 * i + 1 < n;
-            const unsigned int pb0 = (unsigned int)(kk[g].x >> 32), pb1 = (unsigned int)(kk[g].y >> 32);
-            const int b0 = bk_bin(pb0), b1 = bk_bin(pb1);
-            const float v0 = __uint_as_float(pb0), v1 = __uint_as_float(pb1);
-            // neighbours in the sorted array mostly share a bin: then one atomic per warp
-            const int bin0 = __shfl_sync(0xffffffffu, in0 ? b0 : b1, 0);
-            const bool same = __all_sync(0xffffffffu, (!in0 || b0 == bin0) && (!in1 || b1 == bin0));
-#pragma unroll
-            for (int k = 0; k < MASS_SETS; k++) {
-                // p + 1.5 * 2^(j+k) rounds p to the binade's unit; below 2^(j+k-1) the rounded
-                // multiple sits in the low 22 mantissa bits of that sum
-                const float sc = (float)(1 << k);  // exact scalings
-                const float Cm = __fmul_rn(Cm0, sc), hk = __fmul_rn(half0, sc), bgk = __fmul_rn(big0, sc);
-                unsigned int *set = bk.sets + k * MASS_SET_WORDS;
-                const float t0 = __fadd_rn(v0, Cm), t1 = __fadd_rn(v1, Cm);
-                const float r0 = __fsub_rn(v0, __fsub_rn(t0, Cm)), r1 = __fsub_rn(v1, __fsub_rn(t1, Cm));
-                const unsigned int tb0 = __float_as_uint(t0), tb1 = __float_as_uint(t1);
-                const bool sp0 = in0 && (fabsf(r0) == hk || v0 >= bgk || !(tb0 & 0x400000u));
-                const bool sp1 = in1 && (fabsf(r1) == hk || v1 >= bgk || !(tb1 & 0x400000u));
-                const unsigned int q0 = (in0 && !sp0) ? (tb0 & 0x3fffffu) : 0u, q1 = (in1 && !sp1) ? (tb1 & 0x3fffffu) : 0u;
-                if (sp0) atomicOr(&set[2 * NBINS + (b0 >> 5)], 1u << (b0 & 31));
-                if (sp1) atomicOr(&set[2 * NBINS + (b1 >> 5)], 1u << (b1 & 31));
-                if (same) {
-                    const unsigned int sum = __reduce_add_sync(0xffffffffu, q0 + q1);
-                    if (c.lane == 0 && sum) {
-                        atomicAdd(&set[bin0], sum & MASS_LO_MASK);
-                        if (sum >> MASS_SPLIT) atomicAdd(&set[NBINS + bin0], sum >> MASS_SPLIT);
-                    }
-                } else {
-                    if (q0) { atomicAdd(&set[b0], q0 & MASS_LO_MASK); if (q0 >> MASS_SPLIT) atomicAdd(&set[NBINS + b0], q0 >> MASS_SPLIT); }
-                    if (q1) { atomicAdd(&set[b1], q1 & MASS_LO_MASK); if (q1 >> MASS_SPLIT) atomicAdd(&set[NBINS + b1], q1 >> MASS_SPLIT); }
-                }
-            }
+    for (int k = 0; k < MASS_SETS; k++) {
+        // v + 1.5 * 2^(j0+k) rounds v to the binade's unit; below 2^(j0+k-1) the rounded multiple
+        // sits in the low 22 mantissa bits of that sum
+        const float sc = (float)(1 << k);  // exact scalings
+        const float Cm = __fmul_rn(mt.Cm0, sc);
+        const float t = __fadd_rn(v, Cm);
+        const float r = __fsub_rn(v, __fsub_rn(t, Cm));
+        const unsigned int tb = __float_as_uint(t);
+        unsigned int *set = mt.sets + k * MASS_SET_WORDS;
+        if (fabsf(r) == __fmul_rn(mt.half0, sc) || v >= __fmul_rn(mt.big0, sc) || !(tb & 0x400000u)) {
+            sred_or(&set[2 * NBINS + (bin >> 5)], 1u << (bin & 31));  // a rounding tie or a large term
+        } else {
+            const unsigned int q = tb & 0x3fffffu;
+            if (q & MASS_LO_MASK) sred_add(&set[bin], q & MASS_LO_MASK);
+            if (q >> MASS_SPLIT) sred_add(&set[NBINS + bin], q >> MASS_SPLIT);
         }
     }
-    __syncthreads();
-    bk.mass_j = j; bk.mass_hi = hi;
-    c.tmass += clock64() - t0;
 }
 
-// Returns false if it met something it leaves to the general walk (no usable binade yet, or a
-// bin larger than the candidate buffer); `w` then holds the exact state to continue from.
-__device__ bool descend_buckets(Ctx &c, Buckets &bk, Walk &w, int &hi, float x_ge, float x_gt, long long nstop,
-                                bool may_reuse) {
+// Returns false if it met something it leaves to the general walk (a running sum outside the
+// tables' binades, or a bin larger than the candidate buffer); `w` then holds the exact state
+// to continue from.
+__device__ bool descend_masses(Ctx &c, const LView &lv, const MassTable &mt, MassCk &ck, Walk &w, int &hi, float x_ge, float x_gt,
+                               long long nstop) {
     Aux *A = c.A;
     const bool counting = nstop >= 0;
     for (int phase = 0; phase < 8192; phase++) {
@@ -1107,17 +1072,12 @@ __device__ bool descend_buckets(Ctx &c, Buckets &bk, Walk &w, int &hi, float x_g
         if (hi <= 0) { w.tau = 0; w.event = EV_EXHAUSTED; return true; }
         if (!(w.s > 0.0f)) return false;
         const int j = fexpo(w.s);
-        if (j < -100 || j > 100) return false;
+        if (j < mt.j0 || j >= mt.j0 + MASS_SETS || j < -100 || j > 100) return false;
         const float inv_u = fpow2(23 - j);
-        if (!(may_reuse && bk.mass_j != -0x7fffffff && j >= bk.mass_j && j < bk.mass_j + MASS_SETS && bk.mass_hi >= hi)) {
-            buckets_masses(c, bk, j, hi);
-            bk.ck_s = w.s; bk.ck_pos = w.pos; bk.ck_hi = hi;
-        }
-        may_reuse = true;
-        const unsigned int *set = bk.sets + (j - bk.mass_j) * MASS_SET_WORDS;
+        const unsigned int *set = mt.sets + (j - mt.j0) * MASS_SET_WORDS;
         BinQuery qy;
         qy.specbin = -1; qy.bin_hi = hi; qy.spec_bits = set + 2 * NBINS;
-        qy.hq = set; qy.hqh = set + NBINS; qy.hc = bk.cnt;
+        qy.hq = set; qy.hqh = set + NBINS; qy.hc = mt.cnt;
         qy.pos0 = (unsigned long long)w.pos;
         qy.nstop = counting ? (unsigned long long)nstop : ~0ull;
         qy.m0 = (unsigned long long)((double)w.s * (double)inv_u);
@@ -1137,17 +1097,43 @@ __device__ bool descend_buckets(Ctx &c, Buckets &bk, Walk &w, int &hi, float x_g
         const unsigned long long qb = A->hit_qbefore, cb = A->hit_cbefore;
         const float s_bin = (float)((double)(qy.m0 + qb) * (double)fpow2(j - 23));
         const long long pos_bin = w.pos + (long long)cb;
-        const int nb = (int)bk.cnt[hb];
+        const int nb = (int)mt.cnt[hb];
         if (nb > NC) {  // a crowded bin: the general walk splits it further
-            w.s = s_bin; w.pos = pos_bin; w.tau = bk_lo(hb + 1); hi = hb + 1;
+            w.s = s_bin; w.pos = pos_bin; w.tau = min(bk_lo(hb + 1), mt.tau0); hi = hb + 1;
             return false;
         }
+        // a bin an earlier walk went through whole, from the same state: if this walk's event does
+        // not fall inside it either (prefix sums only grow), take the state behind it
+        bool skipped = false;
+        for (int q = 0; q < ck.n; q++) {
+            if (ck.bin[q] == hb && ck.s_in[q] == s_bin && ck.pos_in[q] == pos_bin && !(ck.s_out[q] >= x_ge) &&
+                !(x_gt < ck.s_out[q]) && !(counting && ck.pos_out[q] >= nstop)) {
+                w.s = ck.s_out[q]; w.pos = ck.pos_out[q]; w.tau = bk_lo(hb); hi = hb;
+                skipped = true;
+                break;
+            }
+        }
+        if (skipped) continue;
         __syncthreads();
-        for (int i = c.tid; i < nb; i += NT) A->cand[i] = bk.arr[bk.off[hb] + i];
+        if (c.tid == 0) A->ncand = 0;
+        __syncthreads();
+        const unsigned int tau0 = mt.tau0;
+        lv.for_each(c.tid, [&](int, unsigned long long key, unsigned long long *) {
+            const unsigned int pb = (unsigned int)(key >> 32);
+            if (pb < tau0 && bk_bin(pb) == hb) {
+                const int pos = satom_add(&A->ncand, 1);
+                if (pos < NC) A->cand[pos] = key;
+            }
+        });
+        __syncthreads();
         sort_cands(c, nb);
         walk_sorted(c, nb, s_bin, pos_bin, x_ge, x_gt, counting, nstop);
         w.s = A->b_s; w.pos = A->b_pos; w.tau = bk_lo(hb); hi = hb;
         if (A->b_event != EV_NONE) { w.event = A->b_event; w.idx = A->b_idx; w.p = A->b_p; w.tie = A->b_aux; return true; }
+        if (ck.n < MASS_CK) {
+            const int q = ck.n++;
+            ck.bin[q] = hb; ck.s_in[q] = s_bin; ck.pos_in[q] = pos_bin; ck.s_out[q] = w.s; ck.pos_out[q] = w.pos;
+        }
     }
     return false;
 }
@@ -1614,8 +1600,9 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             const unsigned int tau_p = __float_as_uint(__fdiv_rn(__uint_as_float(tau_bits), Z));
             const unsigned int tau_pb = tau_p > 1u ? tau_p : 1u;
             bool mark_head = head_in_pass;  // the head was taken in pass B: its entries are consumed
-            unsigned int *bin_counts = nullptr;  // set: the conversion pass also counts entries per value bin
-            unsigned int count_below = 0u;
+            bool mass_on = false;  // set: the conversion pass also fills the bin mass tables
+            MassTable mt;
+            mt.cnt = nullptr; mt.sets = nullptr; mt.j0 = 0; mt.tau0 = 0u; mt.Cm0 = mt.half0 = mt.big0 = 0.0f;
             auto convert_list = [&](bool gather_head) {
                 __syncthreads();
                 if (gather_head && c.tid == 0) A->ncand = 0;
@@ -1626,7 +1613,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     if (!gather_head && mark_head && (unsigned int)(kk >> 32) >= tau_bits) pb = 0xFFFFFFFFu;
                     const unsigned long long nk = ((unsigned long long)pb << 32) | (kk & 0xFFFFFFFFull);
                     *where = nk;
-                    if (bin_counts && pb < count_below) atomicAdd(&bin_counts[bk_bin(pb)], 1u);
+                    if (mass_on) masses_add(mt, pb);
                     if (gather_head && pb >= tau_pb) {
                         const int pos = atomicAdd(&A->ncand, 1);
                         if (pos < HEADC) A->cand[pos] = nk;
@@ -1740,20 +1727,15 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         // ---- 6. past the head: the cut walk, then the draw walk
                         STAMP(6);
                         // long lists (global memory) are first sorted into their value bins
-                        Buckets bk;
-                        bk.arr = wl_flat; bk.off = reinterpret_cast<unsigned int *>(A->hkey);
-                        bk.cur = reinterpret_cast<unsigned int *>(A->hcnt); bk.cnt = reinterpret_cast<unsigned int *>(A->hval);
-                        bk.sets = reinterpret_cast<unsigned int *>(c.stage);  // idle while the list is a global view
-                        bk.built = false; bk.total = 0; bk.mass_j = -0x7fffffff; bk.mass_hi = 0; bk.ck_s = 0.0f; bk.ck_pos = 0; bk.ck_hi = NBINS;
-                        const bool use_bk = (a.mode == 0) && !lv.flat && !list_is_p;
-                        if (use_bk) {
-                            __syncthreads();
-                            for (int i = c.tid; i < NBINS; i += NT) bk.cnt[i] = 0u;
-                            bin_counts = bk.cnt; count_below = tau_head;
-                        }
+                        // long lists (global memory): per-bin integer masses come out of the conversion pass
+                        MassCk ck;
+                        ck.n = 0;
+                        mt.cnt = reinterpret_cast<unsigned int *>(A->hval);
+                        mt.sets = reinterpret_cast<unsigned int *>(c.stage);  // idle while the list is a global view
+                        const bool use_mt = (a.mode == 0) && !lv.flat && !list_is_p && head_s > 0.0f;
+                        if (use_mt) { masses_begin(c, mt, fexpo(head_s), tau_head); mass_on = true; }
                         if (!list_is_p) { convert_list(false); list_is_p = true; }
-                        bin_counts = nullptr;
-                        if (use_bk) buckets_build(c, lv, bk, tau_head);
+                        mass_on = false;
                         STAMP(7);
                         __syncthreads();
                         Walk cutw; cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
@@ -1761,7 +1743,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         const bool limited = n_lim < (long long)a.Vg;
                         {
                             int hi = NBINS;
-                            const bool done = use_bk && descend_buckets(c, bk, cutw, hi, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1, false);
+                            const bool done = use_mt && descend_masses(c, lv, mt, ck, cutw, hi, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
                             if (!done) descend(c, lv, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
                         }
                         if (cutw.event != EV_DEGENERATE) {
@@ -1792,14 +1774,9 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                                     Walk dw; dw.s = head_s; dw.pos = head_pos; dw.tau = tau_head;
                                     dw.event = EV_NONE; dw.idx = -1; dw.p = 0; dw.tie = 0;
                                     bool ddone = false;
-                                    if (use_bk) {
+                                    if (use_mt) {
                                         int hi = NBINS;
-                                        // everything before the point the masses were last built at sums to
-                                        // bk.ck_s: if that does not exceed the target, start there and reuse them
-                                        if (bk.mass_j != -0x7fffffff && !(target < bk.ck_s) && bk.ck_hi < NBINS) {
-                                            dw.s = bk.ck_s; dw.pos = bk.ck_pos; hi = bk.ck_hi; dw.tau = bk_lo(hi);
-                                        }
-                                        ddone = descend_buckets(c, bk, dw, hi, 3.4e38f, target, -1, true);
+                                        ddone = descend_masses(c, lv, mt, ck, dw, hi, 3.4e38f, target, -1);
                                     }
                                     if (!ddone) descend(c, lv, dw, 3.4e38f, target, -1);
                                     if (dw.event == EV_DRAW) {
