@@ -159,8 +159,39 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
         "l"(src), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
 }
+// The same copy, telling L2 that the lines will not be read again (their last use).
+__device__ __forceinline__ void bulk_g2s_last_use(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::
+            "r"(smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// Loads and stores of data that is read again soon (a row's list between its passes): L2 is
+// asked to keep these lines in preference to the streamed logits.
+__device__ __forceinline__ uint64_t l2_keep_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ uint64_t l2_normal_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ ulonglong2 ldg_keep(const ulonglong2 *p, uint64_t policy) {
+    ulonglong2 v;
+    asm volatile("ld.global.L2::cache_hint.v2.u64 {%0, %1}, [%2], %3;" : "=l"(v.x), "=l"(v.y) : "l"(p), "l"(policy));
+    return v;
+}
+__device__ __forceinline__ void stg_keep(unsigned long long *p, unsigned long long v, uint64_t policy) {
+    asm volatile("st.global.L2::cache_hint.u64 [%0], %1, %2;" ::"l"(p), "l"(v), "l"(policy) : "memory");
 }
 
 // Atomics on shared memory through a pointer whose address space the compiler cannot see

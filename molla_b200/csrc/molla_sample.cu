@@ -66,6 +66,10 @@ constexpr int SLIST_CAP = STAGE_FLOATS / 2;                 // list entries that
 constexpr int SA_WORDS = 3 + NWARP + HEAD_NEED + 1;  // max, argmax, ties, region maxima, top thread maxima
 constexpr int ORDER_CAP = 4096;      // rows whose order is sorted by cost inside the kernel
 
+// Tell the compiler which address space a pointer is in (functions it does not inline would
+// otherwise use generic loads, stores and atomics on shared memory).
+#define IN_SHARED(ptr) __builtin_assume(__isShared(ptr))
+
 struct BatchArgs {
     const float *logits; long long row_stride; int B, V;
     const float *temperature; const int *top_k; const float *top_p; const float *min_p;
@@ -82,6 +86,7 @@ struct BatchArgs {
     const int *order;            // scratch: rows by decreasing cost (NULL = as given)
     unsigned long long *wlist;   // scratch: per CTA, 2 x 16 x R list entries
     long long *prof;             // optional [B x 16] clock64 stamps per row (testing aid)
+    int knobs;                   // experiment switches (testing aid; 0 in production)
     int *topk_out; int topk_cap; // optional [B x cap] ids of the sorted head after top-k (testing aid)
     // vocab-sharded form: this GPU holds columns [col0, col0 + V) of a vocabulary of Vg
     int mode;                    // 0 whole pipeline; 1, 2, 3 the stages around the two all-gathers
@@ -152,12 +157,13 @@ struct Ctx {
     bool patching;
     const float *src;     // this row in global memory
     bool aligned;
+    bool last_read;       // the pass being streamed is the last one over this row: L2 need not keep it
     unsigned int status;
     // this warp's region and pipeline
     int rbeg, rlen, npieces;
     unsigned int parbits;
     int nphase;           // histogram phases run by the descending walks of this row (profiling aid)
-    long long tmass;      // cycles spent building bin masses (profiling aid)
+    long long tmass, tbuild;  // cycles thread 0 spent in the exact sum's serial walk / waiting for its tables (profiling aid)
 };
 
 #define STAMP(i) do { if (a.prof && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
@@ -181,6 +187,7 @@ __device__ __forceinline__ void block_argmax(Ctx &c, float &v, int &i) {
 
 // bitonic sort, descending, of n2 (power of two) keys in shared memory
 __device__ void bitonic_desc(unsigned long long *k, int n2, int tid) {
+    IN_SHARED(k);
     for (int size = 2; size <= n2; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
             __syncthreads();
@@ -229,7 +236,8 @@ __device__ __forceinline__ void piece_issue(Ctx &c, int p) {
     uint64_t *bar = &c.A->mbar[c.warp][p % NSTAGE];
     fence_proxy_async();
     mbar_expect_tx(bar, (uint32_t)nbulk * 4u);
-    bulk_g2s(wslot(c, p), c.src + c.rbeg + (long long)p * PIECE, (uint32_t)nbulk * 4u, bar);
+    if (c.last_read) bulk_g2s_last_use(wslot(c, p), c.src + c.rbeg + (long long)p * PIECE, (uint32_t)nbulk * 4u, bar);
+    else bulk_g2s(wslot(c, p), c.src + c.rbeg + (long long)p * PIECE, (uint32_t)nbulk * 4u, bar);
 }
 __device__ __forceinline__ void pieces_begin(Ctx &c) {
     __syncwarp();
@@ -288,7 +296,7 @@ __device__ __forceinline__ unsigned int patch_mask(const Ctx &c, int g0) {
 // this lane's LT elements of a piece, with patches applied; past the end: -inf
 __device__ __forceinline__ void load_chunk(const Ctx &c, const float *slot, int n, int g0, float (&x)[LT]) {
     const int l0 = c.lane * LT;
-    const unsigned int pm = (l0 < n) ? patch_mask(c, g0) : 0u;
+    const unsigned int pm = (l0 < n) ? (patch_mask(c, g0) & ((1u << LT) - 1u)) : 0u;
 #pragma unroll
     for (int j = 0; j < LT; j++) x[j] = (l0 + j < n) ? slot[l0 + j] : -INFINITY;
     if (pm) {
@@ -325,14 +333,14 @@ struct Walker {
     float s; int found; int at; int slow;
 };
 
-// value accessors: a list of (value bits << 32 | ~id) keys, or bare value bits
+// value accessors (shared memory): a list of (value bits << 32 | ~id) keys, or bare value bits
 struct ValKeys {
     const unsigned long long *p;
-    __device__ __forceinline__ float operator()(int i) const { return __uint_as_float((unsigned int)(p[i] >> 32)); }
+    __device__ __forceinline__ float operator()(int i) const { IN_SHARED(p); return __uint_as_float((unsigned int)(p[i] >> 32)); }
 };
 struct ValBits {
     const unsigned int *p;
-    __device__ __forceinline__ float operator()(int i) const { return __uint_as_float(p[i]); }
+    __device__ __forceinline__ float operator()(int i) const { IN_SHARED(p); return __uint_as_float(p[i]); }
 };
 
 // A row's list as the later phases see it: a copy in shared memory when it is small, else the
@@ -343,6 +351,7 @@ struct LView {
     size_t stride;
     const int *woff;                 // NWARP + 1 segment offsets into the whole list
     int n;
+    uint64_t keep;                   // L2 policy for loads from a list in global memory
     __device__ __forceinline__ unsigned long long *slot(int v) const {
         if (flat) return const_cast<unsigned long long *>(flat) + v;
         int w = 0;
@@ -368,15 +377,17 @@ struct LView {
             if (tid == 32 && (hi & 1) && hi - 1 >= lo2) f(o + hi - 1, b[hi - 1]);
             const ulonglong2 *b2 = reinterpret_cast<const ulonglong2 *>(b);
             const int p1 = hi2 >> 1;
-            int i = (lo2 >> 1) + tid;
-            for (; i + 7 * NT < p1; i += 8 * NT) {
+            // (every round issues its eight loads before it uses one, the last round included:
+            // a range is often only a round or two long)
+            for (int i = (lo2 >> 1) + tid; i < p1; i += 8 * NT) {
                 ulonglong2 k[8];
 #pragma unroll
-                for (int q = 0; q < 8; q++) k[q] = b2[i + q * NT];
+                for (int q = 0; q < 8; q++)
+                    k[q] = (i + q * NT < p1) ? (flat ? b2[i + q * NT] : ldg_keep(b2 + i + q * NT, keep)) : make_ulonglong2(0ull, 0ull);
 #pragma unroll
-                for (int q = 0; q < 8; q++) { f(o + 2 * (i + q * NT), k[q].x); f(o + 2 * (i + q * NT) + 1, k[q].y); }
+                for (int q = 0; q < 8; q++)
+                    if (i + q * NT < p1) { f(o + 2 * (i + q * NT), k[q].x); f(o + 2 * (i + q * NT) + 1, k[q].y); }
             }
-            for (; i < p1; i += NT) { const ulonglong2 k = b2[i]; f(o + 2 * i, k.x); f(o + 2 * i + 1, k.y); }
         }
     }
     // f(index in the whole list, key, where the key lives). A list in segments is walked with one
@@ -396,7 +407,7 @@ struct LView {
         for (; i + 7 * step < mp; i += 8 * step) {
             ulonglong2 k[8];
 #pragma unroll
-            for (int q = 0; q < 8; q++) k[q] = b2[i + q * step];
+            for (int q = 0; q < 8; q++) k[q] = flat ? b2[i + q * step] : ldg_keep(b2 + i + q * step, keep);
 #pragma unroll
             for (int q = 0; q < 8; q++) {
                 const int e = 2 * (i + q * step);
@@ -404,7 +415,7 @@ struct LView {
             }
         }
         for (; i < mp; i += step) {
-            const ulonglong2 k = b2[i];
+            const ulonglong2 k = flat ? b2[i] : ldg_keep(b2 + i, keep);
             f(o + 2 * i, k.x, b + 2 * i); f(o + 2 * i + 1, k.y, b + 2 * i + 1);
         }
         if ((m & 1) && t == 0) f(o + m - 1, b[m - 1], b + m - 1);
@@ -437,10 +448,19 @@ __device__ __forceinline__ void p1_sim(V lst, int i0, int i1, bool locate, float
 template <class V>
 __device__ void p1_build(Ctx &c, V lst, int n, int L, double sbase) {
     Aux *A = c.A;
+    IN_SHARED(A);
     const float EPS = 1.0f / 4096.0f;
     const int i0 = min(n, c.tid * L), i1 = min(n, (c.tid + 1) * L);
     float csum = 0.0f;
-    for (int i = i0; i < i1; i++) csum = __fadd_rn(csum, lst(i));
+    {   // only an estimate is needed here: four partial sums shorten the dependency chain
+        float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;
+        int i = i0;
+        for (; i + 4 <= i1; i += 4) {
+            c0 = __fadd_rn(c0, lst(i)); c1 = __fadd_rn(c1, lst(i + 1)); c2 = __fadd_rn(c2, lst(i + 2)); c3 = __fadd_rn(c3, lst(i + 3));
+        }
+        for (; i < i1; i++) c0 = __fadd_rn(c0, lst(i));
+        csum = __fadd_rn(__fadd_rn(c0, c1), __fadd_rn(c2, c3));
+    }
     double tot;
     const double sst = sbase + block_excl_scan<double>((double)csum, A->wsd, &tot);
     short ja = SUS;
@@ -455,17 +475,24 @@ __device__ void p1_build(Ctx &c, V lst, int n, int L, double sbase) {
             const bool two = (j2 == jl + 1);
             const float C1 = __fmul_rn(1.5f, fpow2(jl)), h1 = fpow2(jl - 24), b1 = fpow2(jl - 1);
             const float C2 = __fmul_rn(1.5f, fpow2(jl + 1)), h2 = fpow2(jl - 23);
-            for (int i = i0; i < i1; i++) {
+            // the terms are multiples of the binade's unit and their sum stays below 2^24 units, so
+            // these additions are exact in any order: two accumulators each
+            float da1 = 0.0f, db1 = 0.0f;
+            auto term = [&](int i, float &xa, float &xb) {
                 const float v = lst(i);
                 const float q = __fsub_rn(__fadd_rn(v, C1), C1);
                 const float r = __fsub_rn(v, q);
                 bad |= (fabsf(r) == h1) | (v >= b1);
-                da = __fadd_rn(da, q);
+                xa = __fadd_rn(xa, q);
                 const float q2 = __fsub_rn(__fadd_rn(v, C2), C2);
                 const float r2 = __fsub_rn(v, q2);
                 bad |= two & (fabsf(r2) == h2);
-                db = __fadd_rn(db, q2);
-            }
+                xb = __fadd_rn(xb, q2);
+            };
+            int i = i0;
+            for (; i + 2 <= i1; i += 2) { term(i, da, db); term(i + 1, da1, db1); }
+            if (i < i1) term(i, da, db);
+            da = __fadd_rn(da, da1); db = __fadd_rn(db, db1);
             if (!bad) { ja = (short)jl; dual = two ? 1 : 0; }
         }
     }
@@ -494,6 +521,7 @@ __device__ void p1_build(Ctx &c, V lst, int n, int L, double sbase) {
 template <class V>
 __device__ void p1_walk(Ctx &c, V lst, int n, int L, bool locate, float target, Walker &w) {
     Aux *A = c.A;
+    IN_SHARED(A);
     const int nseg = A->nseg;
     const double *PA = A->u.p1.pa, *PB = A->u.p1.pb;
     for (int si = 0; si < nseg && !(locate && w.found); si++) {
@@ -583,9 +611,12 @@ constexpr int MAX_VBLK = 40;
 template <class V>
 __device__ void p1_block(Ctx &c, V vals, int n, int base, bool locate, float target) {
     Aux *A = c.A;
+    IN_SHARED(A);
     int L = (n + NT - 1) / NT;
     if ((L & 1) == 0) L += 1;
+    const long long tq0 = clock64();
     p1_build(c, vals, n, L, (double)A->walk_s);
+    c.tbuild += clock64() - tq0;
     if (c.tid == 0) {
         Walker w; w.s = A->walk_s; w.found = 0; w.at = -1; w.slow = A->walk_slow;
         p1_walk(c, vals, n, L, locate, target, w);
@@ -596,7 +627,9 @@ __device__ void p1_block(Ctx &c, V vals, int n, int base, bool locate, float tar
 }
 
 __device__ void p1_run(Ctx &c, const LView &lv, unsigned int *vals, bool locate, float target) {
+    IN_SHARED(vals);
     Aux *A = c.A;
+    IN_SHARED(A);
     __syncthreads();
     if (c.tid == 0) { A->walk_s = 0.0f; A->walk_found = 0; A->walk_idx = -1; }
     __syncthreads();
@@ -621,11 +654,13 @@ __device__ void p1_run(Ctx &c, const LView &lv, unsigned int *vals, bool locate,
         const int n = min(VBLK, lv.n - b * VBLK);
         __syncthreads();
         if (!locate && c.tid == 0 && b < MAX_VBLK) A->blk_s[b] = A->walk_s;
+        const long long tq0 = clock64();
         {
             const int o = b * VBLK;
             lv.for_range(c.tid, o, o + n, [&](int v, unsigned long long k) { vals[v - o] = (unsigned int)(k >> 32); });
         }
         __syncthreads();
+        c.tmass += clock64() - tq0;
         if (locate && A->walk_found) break;
         p1_block(c, ValBits{vals}, n, b * VBLK, locate, target);
     }
@@ -653,6 +688,7 @@ struct BinQuery {
 
 __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
     Aux *A = c.A;
+    IN_SHARED(A);
     unsigned long long q[BPT], n[BPT], sq = 0, sn = 0;
 #pragma unroll
     for (int i = 0; i < BPT; i++) {
@@ -688,6 +724,7 @@ __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
 // Sort the candidate list (descending probability, ascending token id).
 __device__ void sort_cands(Ctx &c, int n) {
     Aux *A = c.A;
+    IN_SHARED(A);
     int n2 = 2;
     while (n2 < n) n2 <<= 1;
     __syncthreads();
@@ -707,6 +744,7 @@ __device__ void sort_cands(Ctx &c, int n) {
 __device__ void walk_sorted(Ctx &c, int nb, float s0, long long pos0, float x_ge, float x_gt, bool counting,
                             long long nstop) {
     Aux *A = c.A;
+    IN_SHARED(A);
     constexpr int EPT = NC / NT;
     __syncthreads();
     if (c.tid == 0) { A->b_s = s0; A->b_event = EV_NONE; A->b_aux = -1; A->b_idx = 0; }
@@ -825,6 +863,7 @@ struct Walk {
 __device__ int nth_equal(Ctx &c, const LView &lv, unsigned int eb, unsigned int tau, int nth) {
     const int nl = lv.n;
     Aux *A = c.A;
+    IN_SHARED(A);
     const int L = (nl + NT - 1) / NT;
     const int i0 = min(nl, c.tid * L), i1 = min(nl, (c.tid + 1) * L);
     int cnt = 0;
@@ -851,6 +890,7 @@ __device__ int nth_equal(Ctx &c, const LView &lv, unsigned int eb, unsigned int 
 __device__ void descend(Ctx &c, const LView &lv, Walk &w, float x_ge, float x_gt,
                         long long nstop) {
     Aux *A = c.A;
+    IN_SHARED(A);
     const bool counting = nstop >= 0;
     // Bins are 2048 ranges of exp bits. A bin holding more than the candidate buffer is split
     // again (level 2: the next 11 bits; level 3: single values); a single value repeated more
@@ -1066,6 +1106,7 @@ __device__ __forceinline__ void masses_add(const MassTable &mt, unsigned int pb)
 __device__ bool descend_masses(Ctx &c, const LView &lv, const MassTable &mt, MassCk &ck, Walk &w, int &hi, float x_ge, float x_gt,
                                long long nstop) {
     Aux *A = c.A;
+    IN_SHARED(A);
     const bool counting = nstop >= 0;
     for (int phase = 0; phase < 8192; phase++) {
         c.nphase++;
@@ -1223,6 +1264,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
     c.V = a.V; c.R = a.R;
     c.parbits = 0;
     Aux *A = c.A;
+    IN_SHARED(A);
     if (c.lane == 0) {
         for (int s = 0; s < NSTAGE; s++) mbar_init(&A->mbar[c.warp][s], 1);
         fence_proxy_async();
@@ -1239,6 +1281,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
     unsigned long long *wl_flat = wl_seg + (size_t)NWARP * (size_t)a.R;                   // contiguous copy
     unsigned long long *slist = reinterpret_cast<unsigned long long *>(c.stage);           // list in shared memory
     const int nwords = (a.V + 31) >> 5;
+    const uint64_t keep_policy = (a.knobs & 4) ? l2_normal_policy() : l2_keep_policy();
 
     for (;;) {
         __syncthreads();
@@ -1250,7 +1293,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         __syncthreads();
         const int r = A->cur_row;
         if (r >= a.B) break;
-        c.status = 0; c.nphase = 0; c.tmass = 0;
+        c.status = 0; c.last_read = false; c.nphase = 0; c.tmass = 0; c.tbuild = 0;
         const float T = a.temperature ? a.temperature[r] : 0.0f;
         const int k = a.top_k ? a.top_k[r] : 0;
         const float P = a.top_p ? a.top_p[r] : 1.0f;
@@ -1357,15 +1400,31 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 const int g0 = c.rbeg + p * PIECE + c.lane * LT;
                 float x[LT];
                 load_chunk(c, slot, n, g0, x);
-                float cm = -INFINITY;
+                // the chunk's maximum first (a short tree); only a chunk that reaches the running
+                // maximum, which is rare after the first few pieces, is looked at element by element
+                float cm;
+                {
+                    float m[LT];
 #pragma unroll
-                for (int j = 0; j < LT; j++) {
-                    cm = fmaxf(cm, x[j]);
-                    if (x[j] > tmax) { tmax = x[j]; tidx = g0 + j + a.col0; teq = 1; }
-                    else if (x[j] == tmax && c.lane * LT + j < n) teq++;
+                    for (int j = 0; j < LT; j++) m[j] = x[j];
+#pragma unroll
+                    for (int w = 1; w < LT; w <<= 1)
+#pragma unroll
+                        for (int j = 0; j + w < LT; j += 2 * w) m[j] = fmaxf(m[j], m[j + w]);
+                    cm = m[0];
+                }
+                if (cm >= tmax) {
+                    if (cm > tmax) { tmax = cm; teq = 0; tidx = 0x7fffffff; }
+#pragma unroll
+                    for (int j = 0; j < LT; j++) {
+                        if (x[j] == tmax && c.lane * LT + j < n) {
+                            if (tidx == 0x7fffffff) tidx = g0 + j + a.col0;
+                            teq++;
+                        }
+                    }
                 }
                 if (!greedy || a.mode == 1) {
-                    cm = warp_max(cm);
+                    cm = fkey_inv(__reduce_max_sync(0xffffffffu, fkey(cm)));
                     if (c.lane == 0) A->u.s.pmax[c.warp][p] = cm;
                     rmx = fmaxf(rmx, cm);
                 }
@@ -1470,6 +1529,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             int base = 0;
             unsigned long long *myseg = wl_seg + (size_t)c.warp * (size_t)a.R;
             long long tqa = 0, tqb = 0, tqc = 0, tq0;
+            c.last_read = !(a.knobs & 2);
             pieces_begin(c);
             for (int p = 0; p < c.npieces; p++) {
                 int n;
@@ -1509,9 +1569,9 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     };
                     auto emit = [&](int i, float e) {
                         const unsigned long long key = make_key(__float_as_uint(e), gbase + (int)A->u.s.ppos[c.warp][i]);
-                        myseg[base + i] = key;
+                        stg_keep(myseg + base + i, key, keep_policy);
                         if (head_in_pass && __float_as_uint(e) >= tau_bits) {
-                            const int pos = atomicAdd(&A->ncand, 1);
+                            const int pos = satom_add(&A->ncand, 1);
                             if (pos < HEADC) A->cand[pos] = key;
                         }
                     };
@@ -1575,7 +1635,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 continue;
             }
             LView lv;
-            lv.n = nl; lv.woff = A->woff;
+            lv.n = nl; lv.woff = A->woff; lv.keep = keep_policy;
             if (nl <= SLIST_CAP) { lv.flat = slist; lv.seg = nullptr; lv.stride = 0; }
             else if (a.mode == 0) { lv.flat = nullptr; lv.seg = wl_seg; lv.stride = (size_t)a.R; }
             else {  // stage 3: the shards' lists were copied into one global array
@@ -1612,7 +1672,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     // entries the head took in pass B (by their exponential) are marked as consumed
                     if (!gather_head && mark_head && (unsigned int)(kk >> 32) >= tau_bits) pb = 0xFFFFFFFFu;
                     const unsigned long long nk = ((unsigned long long)pb << 32) | (kk & 0xFFFFFFFFull);
-                    *where = nk;
+                    if (lv.flat) *where = nk; else stg_keep(where, nk, keep_policy);
                     if (mass_on) masses_add(mt, pb);
                     if (gather_head && pb >= tau_pb) {
                         const int pos = atomicAdd(&A->ncand, 1);
@@ -1815,7 +1875,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             }
         }
         STAMP(9);
-        if (a.prof && c.tid == 0) { a.prof[(long long)r * 16 + 8] = c.nphase; a.prof[(long long)r * 16 + 14] = c.tmass; }
+        if (a.prof && c.tid == 0) { a.prof[(long long)r * 16 + 8] = c.nphase; a.prof[(long long)r * 16 + 14] = c.tmass; a.prof[(long long)r * 16 + 15] = c.tbuild; }
         if (c.tid == 0) {
             a.tokens[r] = token;
             a.row_status[r] = c.status;
@@ -1934,6 +1994,7 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[MOLLA_NOALLOC_S
 constexpr int NOALLOC_MAX_DEVICES = 64;
 void *g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};  // device address of the array, per device ordinal
 long long *g_prof = nullptr;
+int g_knobs = 0;
 int *g_topk = nullptr;
 int g_topk_cap = 0;
 
@@ -2047,6 +2108,7 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
     a.tokens = d_tokens; a.row_status = d_row_status; a.diag = d_diag;
     a.penalised = nullptr; a.penalised_only = 0;
     a.prof = g_prof;
+    a.knobs = g_knobs;
     a.topk_out = g_topk; a.topk_cap = g_topk_cap;
     int rc = launch_rows(a, d_workspace, st);
     if (rc != MOLLA_OK) return rc;
@@ -2391,6 +2453,7 @@ int32_t molla_sample_expf(const float *d_x, int64_t n, void *stream, float *d_ou
 }
 
 void molla_sample_debug_profile(void *d_stamps) { g_prof = (long long *)d_stamps; }
+void molla_sample_debug_knobs(int k) { g_knobs = k; }
 
 void molla_sample_debug_topk(void *d_ids, int32_t cap) { g_topk = (int *)d_ids; g_topk_cap = d_ids ? cap : 0; }
 
