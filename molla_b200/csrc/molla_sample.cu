@@ -1315,7 +1315,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         const int npatch = (a.mode == 3) ? 0 : (penalizing ? H : 0) + nb;
         if (!a.penalised_only) {
             if (!valid) c.status |= MOLLA_ROW_INVALID_CONFIG;
-            else if (!greedy && (minp > 0.0f || typ < 1.0f)) c.status |= MOLLA_ROW_UNSUPPORTED;
+            else if (!greedy && typ < 1.0f) c.status |= MOLLA_ROW_UNSUPPORTED;
         }
         if (npatch > PATCH_MAX) c.status |= MOLLA_ROW_UNSUPPORTED;
         if (c.status) {
@@ -1659,6 +1659,45 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             // rows that have to walk it.
             const unsigned int tau_p = __float_as_uint(__fdiv_rn(__uint_as_float(tau_bits), Z));
             const unsigned int tau_pb = tau_p > 1u ? tau_p : 1u;
+
+            // min-p (sample.mojo:508-523): candidates below `largest probability * min_p` go; what is
+            // left keeps its order. The largest probability is exp(0) / Z. On a sorted row the survivors
+            // are a prefix, so the filter is one more bound on how many the walk may keep; on an
+            // unsorted row the others' probabilities become zero, which no running sum can see.
+            long long n_use = n_lim;
+            unsigned int minp_pbits = 0u;   // probability bits of the floor (0: off)
+            if (minp > 0.0f) {
+                const float p_top = __fdiv_rn(expf_pinned(__fsub_rn(top, top)), Z);
+                const float floor_p = __fmul_rn(p_top, minp);
+                minp_pbits = __float_as_uint(floor_p);
+                // everything pass B dropped has a probability below 2.2e-8: a floor under that could
+                // keep candidates the list no longer holds
+                if (!(floor_p >= 2.2e-8f)) {
+                    c.status |= MOLLA_ROW_UNSUPPORTED;
+                } else if (!pure) {
+                    // the smallest exponential whose probability reaches the floor (e / Z is monotone in e)
+                    unsigned int lo_b = 0u, hi_b = 0x3F800000u;  // fdiv(hi) >= floor: p_top itself is e = 1
+                    for (int it = 0; it < 32 && lo_b < hi_b; it++) {
+                        const unsigned int mid = lo_b + ((hi_b - lo_b) >> 1);
+                        if (__fdiv_rn(__uint_as_float(mid), Z) >= floor_p) hi_b = mid; else lo_b = mid + 1u;
+                    }
+                    const unsigned int e_floor = hi_b;
+                    int cnt_ge = 0;
+                    lv.for_each(c.tid, [&](int, unsigned long long kk, unsigned long long *) { cnt_ge += ((unsigned int)(kk >> 32) >= e_floor) ? 1 : 0; });
+                    int n_ge;
+                    (void)block_excl_scan<int>(cnt_ge, A->wsi, &n_ge);
+                    __syncthreads();
+                    if (n_ge < 1) n_ge = 1;  // never empties
+                    if ((long long)n_ge < n_use) n_use = n_ge;
+                }
+            }
+            if (c.status & MOLLA_ROW_UNSUPPORTED) {
+                if (c.tid == 0) {
+                    a.tokens[r] = -1; a.row_status[r] = c.status;
+                    if (a.diag) { a.diag[4 * r] = Z; a.diag[4 * r + 1] = a.diag[4 * r + 2] = a.diag[4 * r + 3] = 0.0f; }
+                }
+                continue;
+            }
             bool mark_head = head_in_pass;  // the head was taken in pass B: its entries are consumed
             bool mass_on = false;  // set: the conversion pass also fills the bin mass tables
             MassTable mt;
@@ -1671,6 +1710,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     unsigned int pb = __float_as_uint(__fdiv_rn(key_val(kk), Z));
                     // entries the head took in pass B (by their exponential) are marked as consumed
                     if (!gather_head && mark_head && (unsigned int)(kk >> 32) >= tau_bits) pb = 0xFFFFFFFFu;
+                    if (pure && pb < minp_pbits) pb = 0u;
                     const unsigned long long nk = ((unsigned long long)pb << 32) | (kk & 0xFFFFFFFFull);
                     if (lv.flat) *where = nk; else stg_keep(where, nk, keep_policy);
                     if (mass_on) masses_add(mt, pb);
@@ -1717,6 +1757,20 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     // the walk fell off the end: the reference returns the last token of the vocabulary,
                     // whether or not it could matter to any sum
                     token = a.Vg - 1;
+                    if (minp_pbits) {  // ... the last one min-p left
+                        int last = -1;
+                        lv.for_each(c.tid, [&](int, unsigned long long kk, unsigned long long *) {
+                            if ((unsigned int)(kk >> 32) >= minp_pbits) last = max(last, key_idx(kk));
+                        });
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
+                        __syncthreads();
+                        if (c.lane == 0) A->wsi[c.warp] = last;
+                        __syncthreads();
+                        for (int w = 0; w < NWARP; w++) last = max(last, A->wsi[w]);
+                        __syncthreads();
+                        token = last >= 0 ? last : imax;
+                    }
                 }
             } else {
                 // ---- 5b. sorted order. The head: the need largest, sorted, walked exactly
@@ -1742,26 +1796,26 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     if (a.topk_out) {
                         for (int i = c.tid; i < a.topk_cap; i += NT)
                             a.topk_out[(long long)r * a.topk_cap + i] =
-                                (i < nc && (long long)i < n_lim) ? (int)(A->hidx[i] & 0x7fffffffu) : -1;
+                                (i < nc && (long long)i < n_use) ? (int)(A->hidx[i] & 0x7fffffffu) : -1;
                     }
                     if (c.tid == 0) {
                         float s = 0.0f;
                         long long pos = 0;
                         int cut = -1, tie = 0;
                         for (int i = 0; i < nc; i++) {
-                            if (pos >= n_lim) break;
+                            if (pos >= n_use) break;
                             s = __fadd_rn(s, A->pc[i]);
                             A->pre[i] = s;
                             pos++;
                             if (topp_on && s >= P) {
                                 cut = i + 1;
-                                if (i + 1 < nc && (long long)(i + 1) < n_lim && A->pc[i + 1] == A->pc[i]) tie |= MOLLA_ROW_TOPP_TIE;
+                                if (i + 1 < nc && (long long)(i + 1) < n_use && A->pc[i + 1] == A->pc[i]) tie |= MOLLA_ROW_TOPP_TIE;
                                 break;
                             }
-                            if (pos >= n_lim) { cut = i + 1; break; }
+                            if (pos >= n_use) { cut = i + 1; break; }
                         }
                         if (cut < 0 && !p3row && !head_overflow) cut = nc;  // everything that can matter is in the head
-                        if (n_lim < (long long)a.Vg && (long long)nc > n_lim && A->pc[n_lim] == A->pc[n_lim - 1])
+                        if (n_use < (long long)a.Vg && (long long)nc > n_use && A->pc[n_use] == A->pc[n_use - 1])
                             tie |= MOLLA_ROW_TOPK_TIE;
                         A->b_s = s; A->b_pos = pos; A->b_event = EV_NONE; A->b_idx = -1; A->b_p = 0.0f;
                         if (cut > 0) {
@@ -1800,11 +1854,11 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         __syncthreads();
                         Walk cutw; cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
                         cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
-                        const bool limited = n_lim < (long long)a.Vg;
+                        const bool limited = n_use < (long long)a.Vg;
                         {
                             int hi = NBINS;
-                            const bool done = use_mt && descend_masses(c, lv, mt, ck, cutw, hi, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
-                            if (!done) descend(c, lv, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_lim : -1);
+                            const bool done = use_mt && descend_masses(c, lv, mt, ck, cutw, hi, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_use : -1);
+                            if (!done) descend(c, lv, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_use : -1);
                         }
                         if (cutw.event != EV_DEGENERATE) {
                             if (cutw.event == EV_CUT && cutw.tie) c.status |= MOLLA_ROW_TOPP_TIE;

@@ -207,7 +207,11 @@ def test_reference_properties(dev, lib):
     with pytest.raises(ValueError):
         mk().pick(five, row=3)
     with pytest.raises(NotImplementedError):
-        mk(temperature=1.0, min_p=0.3).pick(five)
+        mk(temperature=1.0, typical_p=0.4).pick(five)
+    # min-p (:305-329): 0.3 leaves two of the five, 0.2 three, and a flat row keeps everything
+    assert gpu_reachable(dev, FIVE, 400, temperature=1.0, seed=17, min_p=0.3) == 2
+    assert gpu_reachable(dev, FIVE, 600, temperature=1.0, seed=17, min_p=0.2) == 3
+    assert gpu_reachable(dev, [1.0] * V, 400, temperature=1.0, seed=17, min_p=0.9) == V
 
 
 def test_device_argmax_cases(dev, lib):
@@ -219,6 +223,27 @@ def test_device_argmax_cases(dev, lib):
     w["logits"] = np.stack([x, np.ones(777, np.float32), neg])
     got = run_gpu(w, dev)
     assert got["tokens"].tolist() == [513, 0, int(np.argmax(neg))]
+
+
+def test_min_p_against_the_oracle(dev, lib, oracle):
+    """sample.mojo:508-523 after every combination of the earlier filters, vocabulary order included."""
+    B = 96
+    w = W.config3(seed=21, B=B, V=20000, H=48)
+    rng = np.random.default_rng(5)
+    w["min_p"][:] = rng.choice(np.float32([0.0, 0.01, 0.05, 0.1, 0.3, 0.9]), size=B)
+    w["top_k"][::3] = 0
+    w["top_p"][::3] = 1.0      # a third of the rows unsorted: what min-p leaves keeps vocabulary order
+    w["top_p"][1::6] = 1.0     # top-k and min-p only
+    w["temperature"][5::8] = 1.5
+    r = compare(w, dev, oracle, "min_p", max_exception_frac=0.1)
+    assert r["rows"] == B
+    # a long list (the walk past the head on the list in global memory) with a small floor
+    w = W.config3(seed=22, B=12, V=151936, H=32)
+    w["temperature"][:] = 1.4
+    w["top_k"][:] = 0
+    w["top_p"][:] = np.float32([0.9, 0.99, 1.0] * 4)
+    w["min_p"][:] = np.float32([0.002, 0.0005, 0.01, 0.05] * 3)
+    compare(w, dev, oracle, "min_p long", max_exception_frac=0.2)
 
 
 # ---- the benchmark configurations -------------------------------------------------------------
@@ -317,7 +342,8 @@ def test_invalid_and_unsupported_rows_are_reported_not_run(dev, lib):
     w["temperature"][:] = [1.0, -1.0, 1.0, 1.0, 1.0, 0.0]
     w["top_p"][:] = [1.0, 1.0, 0.0, 1.0, 1.0, 1.0]
     w["repeat_penalty"][:] = [1.0, 1.0, 1.0, 0.0, 1.0, 1.0]
-    w["min_p"][:] = [0, 0, 0, 0, 0.5, 0.5]
+    w["min_p"][:] = [0, 0, 0, 0, 0, 0.5]
+    w["typical_p"][4] = 0.5
     got = run_gpu(w, dev)
     st = got["row_status"]
     assert st[0] == 0 and got["tokens"][0] >= 0
