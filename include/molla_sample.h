@@ -260,6 +260,15 @@ int32_t molla_sample_logprobs(const float *d_logits, int64_t row_stride, int32_t
  * (`exp` of the Mojo standard library, imported at sample.mojo:40). For tests. */
 int32_t molla_sample_expf(const float *d_x, int64_t n, void *stream, float *d_out);
 
+/* log(x) exactly as the typical-p filter evaluates it (`log` of the Mojo standard
+ * library at sample.mojo:541,550), element-wise on the device. For tests. */
+int32_t molla_sample_logf(const float *d_x, int64_t n, void *stream, float *d_out);
+
+/* Testing aid with no counterpart in the reference: experiment switches of the row kernel
+ * (bit 1: no last-use hint on the second pass over a row; bit 2: no keep hint on list
+ * traffic). 0, the default, is the production behaviour. */
+void molla_sample_debug_knobs(int32_t knobs);
+
 /* Testing aid with no counterpart in the reference: when given a device buffer of
  * B x 16 int64, later molla_sample_batch calls from any thread record clock64() stamps
  * at the phase boundaries of each row (NULL switches it off again). */

@@ -35,7 +35,7 @@ EXPORTS = (
     "molla_sample_workspace_bytes", "molla_sample_batch", "molla_sample_host_workspace_bytes",
     "molla_sample_batch_host", "molla_sample_batch_noalloc", "molla_sample_shard_summary_words",
     "molla_sample_shard_stage_a", "molla_sample_shard_merge", "molla_sample_shard_stage_b", "molla_sample_shard_stage_c", "molla_sample_penalised",
-    "molla_sample_logprobs", "molla_sample_expf", "molla_sample_sync", "molla_sample_debug_profile", "molla_sample_debug_topk",
+    "molla_sample_logprobs", "molla_sample_expf", "molla_sample_logf", "molla_sample_debug_knobs", "molla_sample_sync", "molla_sample_debug_profile", "molla_sample_debug_topk",
 )
 
 
@@ -91,6 +91,10 @@ def lib():
     L.molla_sample_logprobs.argtypes = [vp, i64, i32, i32, vp, vp]
     L.molla_sample_expf.restype = i32
     L.molla_sample_expf.argtypes = [vp, i64, vp, vp]
+    L.molla_sample_logf.restype = i32
+    L.molla_sample_logf.argtypes = [vp, i64, vp, vp]
+    L.molla_sample_debug_knobs.restype = None
+    L.molla_sample_debug_knobs.argtypes = [i32]
     L.molla_sample_debug_profile.restype = None
     L.molla_sample_debug_profile.argtypes = [vp]
     L.molla_sample_debug_topk.restype = None

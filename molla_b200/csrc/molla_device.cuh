@@ -58,6 +58,34 @@ __device__ __forceinline__ float expf_pinned(float x) {
     return scale2(p, n);
 }
 
+// The typical-p filter's logarithm: the same operations in the same order as the CPU oracle's
+// molla_oracle_logf, each rounded once, so the bits agree. Within 2 ulp of the true logarithm.
+__device__ __forceinline__ float logf_pinned(float x) {
+    if (x != x || x < 0.0f) return __int_as_float(0x7fc00000);
+    if (x == 0.0f) return __int_as_float(0xff800000);
+    if (x == __int_as_float(0x7f800000)) return x;
+    unsigned int u = __float_as_uint(x);
+    int e = 0;
+    if (u < 0x00800000u) { u = __float_as_uint(__fmul_rn(x, 16777216.0f)); e = -24; }
+    e += (int)(u >> 23) - 127;
+    float m = __uint_as_float((u & 0x007fffffu) | 0x3f800000u);
+    if (m > 1.41421354f) { m = __fmul_rn(m, 0.5f); e += 1; }
+    const float f = __fsub_rn(m, 1.0f);
+    const float s = __fdiv_rn(f, __fadd_rn(2.0f, f));
+    const float z = __fmul_rn(s, s);
+    float R = 2.0f / 11.0f;
+    R = __fmaf_rn(R, z, 2.0f / 9.0f);
+    R = __fmaf_rn(R, z, 2.0f / 7.0f);
+    R = __fmaf_rn(R, z, 2.0f / 5.0f);
+    R = __fmaf_rn(R, z, 2.0f / 3.0f);
+    R = __fmul_rn(R, z);
+    const float lm = __fmaf_rn(-s, __fsub_rn(f, R), f);
+    const float LN2_HI = 0.693145751953125f;
+    const float LN2_LO = 1.428606765330187e-06f;
+    const float dk = (float)e;
+    return __fmaf_rn(dk, LN2_HI, __fmaf_rn(dk, LN2_LO, lm));
+}
+
 __device__ __forceinline__ int fexpo(float x) {  // floor(log2 x) of a positive normal float
     return (int)((__float_as_uint(x) >> 23) & 0xFF) - 127;
 }

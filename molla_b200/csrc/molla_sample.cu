@@ -1179,6 +1179,83 @@ __device__ bool descend_masses(Ctx &c, const LView &lv, const MassTable &mt, Mas
     return false;
 }
 
+// =============================================================================
+// Typical-p (sample.mojo:525-567) on a kept set that lies inside the sorted head: m
+// probabilities pc[0..m), descending, ids in hidx. Entropy H = -sum p log p, added up
+// in that order in fp32; distance |-log p - H|; stable order by distance; the smallest
+// prefix whose probabilities add up to typ; then the draw of sample.mojo:569-594 over
+// that prefix in that order. The sums run on one thread (m is at most the head's 1024).
+// Results: A->b_idx (token), b_p, b_sum, b_target, b_aux (tie bits).
+// =============================================================================
+__device__ void typical_head(Ctx &c, int m, float typ, float u01) {
+    Aux *A = c.A;
+    IN_SHARED(A);
+    float *lg = reinterpret_cast<float *>(A->cand);             // log p
+    float *tt = lg + HEADC;                                     // p * log p
+    unsigned long long *keys = reinterpret_cast<unsigned long long *>(&A->u);  // HEADC sort keys
+    __syncthreads();
+    for (int i = c.tid; i < m; i += NT) {
+        const float p = A->pc[i];
+        const float l = (p > 0.0f) ? logf_pinned(p) : 0.0f;
+        lg[i] = l;
+        tt[i] = __fmul_rn(p, l);
+    }
+    __syncthreads();
+    if (c.tid == 0) {
+        float ent = 0.0f;
+        for (int i = 0; i < m; i++)
+            if (A->pc[i] > 0.0f) ent = __fsub_rn(ent, tt[i]);
+        A->b_s = ent;
+    }
+    __syncthreads();
+    const float ent = A->b_s;
+    int n2 = 2;
+    while (n2 < m) n2 <<= 1;
+    for (int i = c.tid; i < n2; i += NT) {
+        unsigned long long key = 0ull;
+        if (i < m) {
+            const float sur = (A->pc[i] > 0.0f) ? -lg[i] : 0.0f;
+            const float d = fabsf(__fsub_rn(sur, ent));
+            // descending keys = ascending distance, and among equal distances ascending position (stable)
+            key = ((unsigned long long)(~__float_as_uint(d)) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)i);
+        }
+        keys[i] = key;
+    }
+    bitonic_desc(keys, n2, c.tid);
+    if (c.tid == 0) {
+        float s = 0.0f;
+        int kept = m;
+        for (int j = 0; j < m; j++) {
+            const int i = (int)(0xFFFFFFFFu - (unsigned int)(keys[j] & 0xFFFFFFFFull));
+            s = __fadd_rn(s, A->pc[i]);
+            A->pre[j] = s;
+            if (s >= typ) { kept = j + 1; break; }
+        }
+        const float sum = A->pre[kept - 1];
+        int at = kept - 1;
+        float target = 0.0f;
+        if (sum <= 0.0f) at = 0;  // sample.mojo:583-584
+        else {
+            target = __fmul_rn(u01, sum);
+            for (int j = 0; j < kept; j++)
+                if (target < A->pre[j]) { at = j; break; }
+        }
+        const int i_at = (int)(0xFFFFFFFFu - (unsigned int)(keys[at] & 0xFFFFFFFFull));
+        int tie = 0;
+        if (A->hidx[i_at] & 0x80000000u) tie |= MOLLA_ROW_CHOSEN_TIE;
+        // the last one kept and the first one dropped equally probable: which of them the
+        // reference keeps depends on the order its sort left them in
+        if (kept < m) {
+            const int i_last = (int)(0xFFFFFFFFu - (unsigned int)(keys[kept - 1] & 0xFFFFFFFFull));
+            const int i_next = (int)(0xFFFFFFFFu - (unsigned int)(keys[kept] & 0xFFFFFFFFull));
+            if (A->pc[i_last] == A->pc[i_next]) tie |= MOLLA_ROW_TOPP_TIE;
+        }
+        A->b_idx = (int)(A->hidx[i_at] & 0x7fffffffu); A->b_p = A->pc[i_at];
+        A->b_sum = sum; A->b_target = target; A->b_aux = tie;
+    }
+    __syncthreads();
+}
+
 // Between the two all-gathers of the vocab-sharded form: one thread per row folds the shards'
 // stage-1 summaries into what stage 2 needs (the global maximum, the head threshold, a bound on
 // the softmax sum before this shard's columns) and answers the rows that need nothing more.
@@ -1315,7 +1392,8 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         const int npatch = (a.mode == 3) ? 0 : (penalizing ? H : 0) + nb;
         if (!a.penalised_only) {
             if (!valid) c.status |= MOLLA_ROW_INVALID_CONFIG;
-            else if (!greedy && typ < 1.0f) c.status |= MOLLA_ROW_UNSUPPORTED;
+            // typical-p is done on rows an earlier filter sorted and cut to a set inside the sorted head
+            else if (!greedy && typ < 1.0f && !((k > 0 && k < a.Vg) || P < 1.0f)) c.status |= MOLLA_ROW_UNSUPPORTED;
         }
         if (npatch > PATCH_MAX) c.status |= MOLLA_ROW_UNSUPPORTED;
         if (c.status) {
@@ -1665,6 +1743,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             // are a prefix, so the filter is one more bound on how many the walk may keep; on an
             // unsorted row the others' probabilities become zero, which no running sum can see.
             long long n_use = n_lim;
+            const bool typ_on = typ < 1.0f;
             unsigned int minp_pbits = 0u;   // probability bits of the floor (0: off)
             if (minp > 0.0f) {
                 const float p_top = __fdiv_rn(expf_pinned(__fsub_rn(top, top)), Z);
@@ -1818,7 +1897,9 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         if (n_use < (long long)a.Vg && (long long)nc > n_use && A->pc[n_use] == A->pc[n_use - 1])
                             tie |= MOLLA_ROW_TOPK_TIE;
                         A->b_s = s; A->b_pos = pos; A->b_event = EV_NONE; A->b_idx = -1; A->b_p = 0.0f;
-                        if (cut > 0) {
+                        if (typ_on) {
+                            A->ncand = cut;  // the typical-p filter takes over from here
+                        } else if (cut > 0) {
                             const float sum = A->pre[cut - 1];
                             const float target = __fmul_rn(u01, sum);
                             int at = cut - 1;
@@ -1835,7 +1916,16 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     c.status |= (unsigned int)A->b_aux;
                     const float head_s = A->b_s;
                     const long long head_pos = A->b_pos;
-                    if (A->b_event == EV_DRAW) {
+                    if (typ_on) {
+                        const int m = A->ncand;
+                        if (m <= 0) {
+                            c.status |= MOLLA_ROW_UNSUPPORTED;  // what the earlier filters left reaches past the head
+                        } else {
+                            typical_head(c, m, typ, u01);
+                            token = A->b_idx; dp = A->b_p; dsum = A->b_sum; dtarget = A->b_target;
+                            c.status |= (unsigned int)A->b_aux;
+                        }
+                    } else if (A->b_event == EV_DRAW) {
                         token = A->b_idx; dp = A->b_p; dsum = A->b_sum; dtarget = A->b_target;
                     } else {
                         // ---- 6. past the head: the cut walk, then the draw walk
@@ -2035,6 +2125,11 @@ __global__ void __launch_bounds__(NT, 1) logprob_kernel(const float *logits, lon
 __global__ void expf_kernel(const float *x, long long n, float *out) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = expf_pinned(x[i]);
+}
+
+__global__ void logf_kernel(const float *x, long long n, float *out) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = logf_pinned(x[i]);
 }
 
 // =============================================================================
@@ -2506,8 +2601,19 @@ int32_t molla_sample_expf(const float *d_x, int64_t n, void *stream, float *d_ou
     return MOLLA_OK;
 }
 
+int32_t molla_sample_logf(const float *d_x, int64_t n, void *stream, float *d_out) {
+    g_err[0] = 0;
+    if (!d_x || !d_out || n < 0) return fail(MOLLA_ERR_ARGUMENT, "bad arguments to logf%s");
+    if (n == 0) return MOLLA_OK;
+    long long blocks = (n + 255) / 256;
+    logf_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(d_x, n, d_out);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logf launch failed: %s", cudaGetErrorString(e));
+    return MOLLA_OK;
+}
+
 void molla_sample_debug_profile(void *d_stamps) { g_prof = (long long *)d_stamps; }
-void molla_sample_debug_knobs(int k) { g_knobs = k; }
+void molla_sample_debug_knobs(int32_t k) { g_knobs = k; }
 
 void molla_sample_debug_topk(void *d_ids, int32_t cap) { g_topk = (int *)d_ids; g_topk_cap = d_ids ? cap : 0; }
 

@@ -230,6 +230,12 @@ def expf_device(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def logf_device(x: torch.Tensor) -> torch.Tensor:
+    out = torch.empty_like(x)
+    capi.check(capi.lib().molla_sample_logf(_ptr(x), x.numel(), _stream_ptr(x.device), _ptr(out)))
+    return out
+
+
 _PARAM_DTYPES = dict(
     temperature=np.float32, top_k=np.int32, top_p=np.float32, min_p=np.float32,
     typical_p=np.float32, repeat_penalty=np.float32, frequency_penalty=np.float32,
@@ -389,7 +395,8 @@ def pick_rows(logits: torch.Tensor, samplers: Sequence[Sampler], rows: Iterable[
     for s, t, st in zip(samplers, toks, stat):
         s.last_status = st & 0xFFFFFFFF
         if st & capi.ROW_UNSUPPORTED:
-            raise NotImplementedError("min_p and typical_p are not implemented on the device")
+            raise NotImplementedError("this combination of settings is not implemented on the device "
+                                      "(typical_p needs top_k or top_p to leave a set inside the sorted head)")
         if st & capi.ROW_ERROR_BITS:
             raise capi.MollaSampleError(capi.ERR_DEVICE, f"row status {st:#x}")
         s._took(t)

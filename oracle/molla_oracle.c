@@ -103,6 +103,46 @@ static inline float exp_sel(float x, int mode) {
     return mode == 1 ? expf(x) : molla_oracle_expf(x);
 }
 
+/* The natural logarithm the typical-p filter uses (sample.mojo:541,550 call the Mojo
+ * standard library's `log`, whose bits are not available here): fp32, x = 2^e * m with m in
+ * [sqrt(1/2), sqrt(2)), f = m - 1, s = f / (2 + f), log m = f - s * (f - R(s^2)) with the
+ * odd series of atanh for R. Only add, multiply, divide and fmaf, each rounded once, so the
+ * CUDA kernel (`logf_pinned`) returns the same bits. Within 2 ulp of the true logarithm. */
+float molla_oracle_logf(float x) {
+    if (x != x || x < 0.0f) return NAN;
+    if (x == 0.0f) return -INFINITY;
+    if (x == INFINITY) return x;
+    union { float f; uint32_t u; } v;
+    v.f = x;
+    int e = 0;
+    if (v.u < 0x00800000u) { v.f = x * 16777216.0f; e = -24; }  /* subnormal: scale up, exactly */
+    e += (int)(v.u >> 23) - 127;
+    v.u = (v.u & 0x007fffffu) | 0x3f800000u;                    /* m in [1, 2) */
+    if (v.f > 1.41421354f) { v.f = v.f * 0.5f; e += 1; }
+    const float f = v.f - 1.0f;                                 /* exact */
+    const float s = f / (2.0f + f);
+    const float z = s * s;
+    float R = 2.0f / 11.0f;
+    R = fmaf(R, z, 2.0f / 9.0f);
+    R = fmaf(R, z, 2.0f / 7.0f);
+    R = fmaf(R, z, 2.0f / 5.0f);
+    R = fmaf(R, z, 2.0f / 3.0f);
+    R = R * z;
+    const float lm = fmaf(-s, f - R, f);
+    const float LN2_HI = 0.693145751953125f;       /* 0x3f317200: e * LN2_HI is exact for |e| < 2^9 */
+    const float LN2_LO = 1.428606765330187e-06f;   /* ln2 - LN2_HI */
+    const float dk = (float)e;
+    return fmaf(dk, LN2_HI, fmaf(dk, LN2_LO, lm));
+}
+
+static inline float log_sel(float x, int mode) {
+    return mode == 1 ? logf(x) : molla_oracle_logf(x);
+}
+
+void molla_oracle_logf_array(const float *x, int64_t n, float *out) {
+    for (int64_t i = 0; i < n; i++) out[i] = molla_oracle_logf(x[i]);
+}
+
 /* ---- argmax: kernel.mojo:571-585 ---------------------------------------- */
 
 int64_t molla_oracle_argmax(const float *x, int64_t at, int64_t n) {
@@ -331,11 +371,11 @@ static void typical_(sampler_t *s) {
     if (p >= 1.0f || s->kept <= 1) return;
     float entropy = 0.0f;
     for (int64_t i = 0; i < s->kept; i++)
-        if (s->vals[i] > 0) entropy -= s->vals[i] * logf(s->vals[i]);
+        if (s->vals[i] > 0) entropy -= s->vals[i] * log_sel(s->vals[i], s->exp_mode);
     float *distance = (float *)malloc(sizeof(float) * (size_t)s->kept);
     for (int64_t i = 0; i < s->kept; i++) {
         float surprise = 0.0f;
-        if (s->vals[i] > 0) surprise = -logf(s->vals[i]);
+        if (s->vals[i] > 0) surprise = -log_sel(s->vals[i], s->exp_mode);
         float d = surprise - entropy;
         distance[i] = d >= 0 ? d : -d;
     }

@@ -48,6 +48,8 @@ def lib():
         L.molla_oracle_draw.argtypes = [C.c_uint64, C.c_uint64]
         L.molla_oracle_expf.restype = C.c_float
         L.molla_oracle_expf.argtypes = [C.c_float]
+        L.molla_oracle_logf_array.restype = None
+        L.molla_oracle_logf_array.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
         L.molla_oracle_argmax.restype = C.c_int64
         L.molla_oracle_argmax.argtypes = [C.c_void_p, C.c_int64, C.c_int64]
         L.molla_oracle_logprobs.restype = None
@@ -73,6 +75,14 @@ def expf(x) -> np.ndarray:
     f = lib().molla_oracle_expf
     for i in range(x.size):
         out[i] = f(C.c_float(float(x[i])))
+    return out
+
+
+def logf(x) -> np.ndarray:
+    """The pinned fp32 logarithm of the typical-p filter, elementwise."""
+    x = np.ascontiguousarray(x, dtype=np.float32).ravel()
+    out = np.empty_like(x)
+    lib().molla_oracle_logf_array(x.ctypes.data_as(C.c_void_p), x.size, out.ctypes.data_as(C.c_void_p))
     return out
 
 

@@ -156,3 +156,17 @@ def test_workload_generators_are_seeded():
     assert np.all(w["temperature"][::16] == 0) and set(np.unique(w["top_k"])) <= {0, 1, 20, 50, 100}
     s = W.slice_rows(w, 8, 16)
     assert s["B"] == 8 and np.array_equal(s["logits"], w["logits"][8:16]) and s["hist_off"][0] == 0
+
+
+def test_pinned_logf_is_within_an_ulp_of_the_true_logarithm(oracle):
+    """The typical-p filter's logarithm (sample.mojo:541,550 take it from the Mojo standard library,
+    whose bits cannot be had here): the oracle's own, checked against float64."""
+    rng = np.random.default_rng(4)
+    xs = np.concatenate([rng.random(100000), np.exp(rng.uniform(-87, 80, 100000)),
+                         [1.0, 0.5, 2.0, 1e-38, 1e-45, 0.70710677, 1.4142135, 1.4142137]]).astype(np.float32)
+    got = oracle.logf(xs)
+    ref = np.log(xs.astype(np.float64))
+    err = np.abs(got - ref) / np.maximum(np.spacing(np.abs(ref).astype(np.float32)), 1e-45)
+    assert err.max() <= 1.0
+    assert oracle.logf(np.float32([1.0]))[0] == 0.0
+    assert np.isneginf(oracle.logf(np.float32([0.0]))[0]) and np.isnan(oracle.logf(np.float32([-1.0]))[0])
