@@ -52,6 +52,13 @@ def cases():
                    (1000, dict(temperature=1.0, top_k=120, top_p=0.97, seed=12, repeat_last_n=16, frequency_penalty=0.1)),
                    (1501, dict(temperature=1.5, top_p=0.95, seed=14))):
         out.append((f"gen_V{V}_s{cfg['seed']}", logits_row(rng, V), cfg, [], 6))
+    # min-p (test_sample.mojo:305-329 for the five-logit fixture), sorted and unsorted rows
+    out.append(("five_minp03", five, dict(temperature=1.0, min_p=0.3, seed=17), [], 12))
+    out.append(("five_minp02", five, dict(temperature=1.0, min_p=0.2, seed=17), [], 12))
+    for V, cfg in ((600, dict(temperature=0.9, top_k=40, min_p=0.05, seed=21)),
+                   (257, dict(temperature=1.2, min_p=0.02, seed=22)),
+                   (1000, dict(temperature=1.1, top_p=0.95, min_p=0.1, seed=23, repeat_penalty=1.15))):
+        out.append((f"minp_V{V}_s{cfg['seed']}", logits_row(rng, V), cfg, [], 6))
     return out
 
 
@@ -77,7 +84,8 @@ def main():
         store[f"{name}/cfg"] = np.array([cfg.get("temperature", 0.0), cfg.get("top_k", 0), cfg.get("top_p", 1.0),
                                          cfg.get("repeat_penalty", 1.0), cfg.get("frequency_penalty", 0.0),
                                          cfg.get("presence_penalty", 0.0), cfg.get("repeat_last_n", 64),
-                                         cfg.get("seed", 0)], dtype=np.float64)
+                                         cfg.get("seed", 0), cfg.get("min_p", 0.0), cfg.get("typical_p", 1.0)],
+                                        dtype=np.float64)
         store[f"{name}/bias_ids"] = np.array([b[0] for b in bias], dtype=np.int64)
         store[f"{name}/bias_vals"] = np.array([b[1] for b in bias], dtype=F)
         store[f"{name}/tokens"] = np.array(toks, dtype=np.int32)

@@ -61,7 +61,7 @@ def golden_case(g, name):
     return dict(
         logits=g[f"{name}/logits"], temperature=np.float32(cfg[0]), top_k=int(cfg[1]), top_p=np.float32(cfg[2]),
         repeat_penalty=np.float32(cfg[3]), frequency_penalty=np.float32(cfg[4]), presence_penalty=np.float32(cfg[5]),
-        repeat_last_n=int(cfg[6]), seed=int(cfg[7]), bias_ids=g[f"{name}/bias_ids"], bias_vals=g[f"{name}/bias_vals"],
+        repeat_last_n=int(cfg[6]), seed=int(cfg[7]), min_p=np.float32(cfg[8]), typical_p=np.float32(cfg[9]), bias_ids=g[f"{name}/bias_ids"], bias_vals=g[f"{name}/bias_vals"],
         tokens=g[f"{name}/tokens"], z_sum=g[f"{name}/z_sum"], penalised=g[f"{name}/penalised"],
         drawn=g[f"{name}/drawn"], windows=g[f"{name}/windows"], window_len=g[f"{name}/window_len"],
         logprobs=g[f"{name}/logprobs"])
@@ -75,7 +75,7 @@ def golden_as_batch(g, name):
     w = dict(B=steps, V=V, logits=np.repeat(c["logits"][None, :], steps, 0))
     full = lambda v, dt: np.full(steps, v, dtype=dt)
     w.update(temperature=full(c["temperature"], np.float32), top_k=full(c["top_k"], np.int32),
-             top_p=full(c["top_p"], np.float32), min_p=full(0, np.float32), typical_p=full(1, np.float32),
+             top_p=full(c["top_p"], np.float32), min_p=full(c["min_p"], np.float32), typical_p=full(c["typical_p"], np.float32),
              repeat_penalty=full(c["repeat_penalty"], np.float32),
              frequency_penalty=full(c["frequency_penalty"], np.float32),
              presence_penalty=full(c["presence_penalty"], np.float32),
