@@ -49,7 +49,8 @@ extern "C" {
  * (src/molla/engine/sample.mojo:440-483); the library then orders equal
  * probabilities by token id and says so. */
 #define MOLLA_ROW_INVALID_CONFIG 0x001u /* row skipped, token = -1 (rules of sample.mojo:140-154) */
-#define MOLLA_ROW_UNSUPPORTED 0x002u    /* min_p / typical_p requested: not implemented, token = -1 */
+#define MOLLA_ROW_UNSUPPORTED 0x002u    /* token = -1: typical_p on a row no top_k / top_p sorted or whose kept set reaches past the
+                                         * sorted head (1024 candidates); a min_p floor under 2.2e-8; more than 1024 window + bias entries */
 #define MOLLA_ROW_TOPK_TIE 0x004u       /* the top-k boundary splits a run of equal probabilities */
 #define MOLLA_ROW_TOPP_TIE 0x008u       /* the top-p cut splits a run of equal probabilities */
 #define MOLLA_ROW_CHOSEN_TIE 0x010u     /* the chosen token shares its probability with another kept one */

@@ -16,7 +16,7 @@
 // those sums bit for bit instead of approximating them:
 //   * a term smaller than half an ulp of the running sum adds nothing at all. The
 //     running sum is never below the largest term before it, so a logit more than
-//     ~17.5 (in temperature-scaled units) below the running maximum cannot change
+//     17.6 (in temperature-scaled units) below the logarithm of the running sum cannot change
 //     any sum and can never be drawn. Pass B drops those (its only per-element work
 //     on them is one compare) and leaves the rest as one list, in vocabulary order,
 //     of (exp bits, token id) pairs: the "relevant list". Everything after pass B
