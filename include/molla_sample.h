@@ -121,6 +121,45 @@ int32_t molla_sample_batch(
     int32_t *d_top_ids, float *d_top_logprobs, uint32_t *d_row_status, float *d_diag);
 
 /*
+ * The decode-step form: what `DeviceBatch.step` would call once the sampler state lives on the
+ * device (src/molla/engine/batch.mojo:421-520), so that a step needs no host round trip before
+ * the next forward pass. Compared with molla_sample_batch:
+ *
+ *   - batch row r reads logit row d_rows[r] of the block the forward pass left on the device
+ *     (`DeviceScratch.logits`, rows picked by `rows[]`, src/molla/nn/gpu_block.mojo:1676-1680);
+ *     d_rows NULL = row r;
+ *   - final_softcap > 0 applies `cap * tanh(x / cap)` to every logit as it is read, i.e. the
+ *     separate in-place pass of gpu_block.mojo:1568-1571 / gpu_ops.mojo:302-317 is fused into
+ *     the first read (the block itself is not written); logprobs are of the capped logits, as
+ *     they would be after that pass;
+ *   - settings and state are stored per sampler slot (one per live sequence, n_slots of them)
+ *     and batch row r uses slot d_slots[r] (NULL = r): every d_* settings array, d_seed,
+ *     d_bias_off (n_slots + 1 offsets) and the state arrays are indexed by slot. No slot may
+ *     appear twice in one call;
+ *   - the state is `Sampler`'s (sample.mojo:157-212): d_ring [n_slots x ring_cap] int64 token
+ *     windows with d_ring_head, d_ring_filled and d_ring_len (repeat_last_n of the slot, at most
+ *     ring_cap <= 1024; 0 turns the penalties off), and d_drawn, the draw counters. After a
+ *     successful pick the kernel does what `_took` does (sample.mojo:361-363, 246-258): the
+ *     token enters the window, the counter advances. A row that fails leaves its slot as it was;
+ *   - d_stopped [B] (optional) is set where the pick equals d_stop_token[slot] (the end-of-
+ *     sequence test of batch.mojo:512-519); d_stop_token NULL or -1 = no stop token.
+ *
+ * A new sequence takes a slot by writing its settings and zeroing head, filled and drawn
+ * (`reset`, sample.mojo:239-244). Everything else is as in molla_sample_batch.
+ */
+int32_t molla_sample_decode_step(
+    const float *d_logits, int64_t row_stride, int32_t n_logit_rows, int32_t V,
+    const int32_t *d_rows, const int32_t *d_slots, int32_t B, int32_t n_slots, float final_softcap,
+    const float *d_temperature, const int32_t *d_top_k, const float *d_top_p, const float *d_min_p,
+    const float *d_typical_p, const float *d_repeat_penalty, const float *d_frequency_penalty,
+    const float *d_presence_penalty, const uint64_t *d_seed, uint64_t *d_drawn, int64_t *d_ring,
+    int32_t ring_cap, int32_t *d_ring_head, int32_t *d_ring_filled, const int32_t *d_ring_len,
+    const int64_t *d_stop_token, const int64_t *d_bias_ids, const float *d_bias_vals,
+    const int32_t *d_bias_off, int32_t top_n, void *d_workspace, int64_t workspace_bytes, void *stream,
+    int32_t *d_tokens, uint8_t *d_stopped, float *d_chosen_logprob, int32_t *d_top_ids,
+    float *d_top_logprobs, uint32_t *d_row_status);
+
+/*
  * Vocab-sharded form, for a tensor-parallel LM head: GPU g holds columns
  * [col0, col0 + V_local) of every row of a vocabulary of V_global. The reference has no
  * multi-GPU mode (docs/roadmap.md:74,80); the result is defined as `Sampler.pick`

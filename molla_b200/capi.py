@@ -35,7 +35,7 @@ EXPORTS = (
     "molla_sample_workspace_bytes", "molla_sample_batch", "molla_sample_host_workspace_bytes",
     "molla_sample_batch_host", "molla_sample_batch_noalloc", "molla_sample_shard_summary_words",
     "molla_sample_shard_stage_a", "molla_sample_shard_merge", "molla_sample_shard_stage_b", "molla_sample_shard_stage_c", "molla_sample_penalised",
-    "molla_sample_logprobs", "molla_sample_expf", "molla_sample_logf", "molla_sample_debug_knobs", "molla_sample_sync", "molla_sample_debug_profile", "molla_sample_debug_topk",
+    "molla_sample_decode_step", "molla_sample_logprobs", "molla_sample_expf", "molla_sample_logf", "molla_sample_debug_knobs", "molla_sample_sync", "molla_sample_debug_profile", "molla_sample_debug_topk",
 )
 
 
@@ -69,6 +69,9 @@ def lib():
     L.molla_sample_workspace_bytes.argtypes = [i32, i32, i32]
     L.molla_sample_batch.restype = i32
     L.molla_sample_batch.argtypes = [vp, i64, i32, i32] + [vp] * 16 + [i32, vp, i64, vp] + [vp] * 6
+    L.molla_sample_decode_step.restype = i32
+    L.molla_sample_decode_step.argtypes = ([vp, i64, i32, i32, vp, vp, i32, i32, f32] + [vp] * 8 + [vp, vp, vp, i32, vp, vp, vp, vp]
+                                           + [vp, vp, vp, i32, vp, i64, vp] + [vp] * 6)
     L.molla_sample_host_workspace_bytes.restype = i64
     L.molla_sample_host_workspace_bytes.argtypes = [i32, i32, i64, i64, i32]
     L.molla_sample_batch_host.restype = i32

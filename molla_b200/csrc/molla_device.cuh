@@ -86,6 +86,17 @@ __device__ __forceinline__ float logf_pinned(float x) {
     return __fmaf_rn(dk, LN2_HI, __fmaf_rn(dk, LN2_LO, lm));
 }
 
+// The final-logit softcap `cap * tanh(x / cap)` as the reference's device kernel evaluates it
+// (src/molla/nn/gpu_ops.mojo:302-317 with `_tanh`, :607-623: one exponential of a non-positive
+// argument), on the pinned exponential.
+__device__ __forceinline__ float softcap_pinned(float x, float cap) {
+    const float t = __fdiv_rn(x, cap);
+    const float v = (t >= 0.0f) ? t : -t;
+    const float e = expf_pinned(__fmul_rn(-2.0f, v));
+    const float r = __fdiv_rn(__fsub_rn(1.0f, e), __fadd_rn(1.0f, e));
+    return __fmul_rn(cap, (t >= 0.0f) ? r : -r);
+}
+
 __device__ __forceinline__ int fexpo(float x) {  // floor(log2 x) of a positive normal float
     return (int)((__float_as_uint(x) >> 23) & 0xFF) - 127;
 }

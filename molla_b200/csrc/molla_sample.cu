@@ -87,6 +87,18 @@ struct BatchArgs {
     unsigned long long *wlist;   // scratch: per CTA, 2 x 16 x R list entries
     long long *prof;             // optional [B x 16] clock64 stamps per row (testing aid)
     int knobs;                   // experiment switches (testing aid; 0 in production)
+    // decode-step form: which row of the logit block each batch row reads, which slot of the
+    // per-stream arrays (settings and state) it uses, the final-logit softcap, and the state
+    const int *rows;             // [B] or nullptr (row r reads logit row r)
+    const int *slot;             // [B] or nullptr (row r uses slot r)
+    float softcap;               // 0 = none
+    long long *ring;             // [slots x ring_cap] token windows, or nullptr (windows come from hist)
+    int ring_cap;
+    int *ring_head, *ring_filled;
+    const int *ring_len;         // [slots] repeat_last_n of every slot (0 = penalties off)
+    unsigned long long *drawn_rw;  // [slots] draw counters, advanced by one per pick
+    const long long *stop_token;   // [slots] or nullptr
+    unsigned char *stopped;        // [B] or nullptr: the pick was the slot's stop token
     int *topk_out; int topk_cap; // optional [B x cap] ids of the sorted head after top-k (testing aid)
     // vocab-sharded form: this GPU holds columns [col0, col0 + V) of a vocabulary of Vg
     int mode;                    // 0 whole pipeline; 1, 2, 3 the stages around the two all-gathers
@@ -158,6 +170,7 @@ struct Ctx {
     const float *src;     // this row in global memory
     bool aligned;
     bool last_read;       // the pass being streamed is the last one over this row: L2 need not keep it
+    float softcap;        // final-logit softcap applied to every logit as it is read (0 = none)
     unsigned int status;
     // this warp's region and pipeline
     int rbeg, rlen, npieces;
@@ -299,6 +312,11 @@ __device__ __forceinline__ void load_chunk(const Ctx &c, const float *slot, int 
     const unsigned int pm = (l0 < n) ? (patch_mask(c, g0) & ((1u << LT) - 1u)) : 0u;
 #pragma unroll
     for (int j = 0; j < LT; j++) x[j] = (l0 + j < n) ? slot[l0 + j] : -INFINITY;
+    if (c.softcap > 0.0f) {
+#pragma unroll
+        for (int j = 0; j < LT; j++)
+            if (l0 + j < n) x[j] = softcap_pinned(x[j], c.softcap);
+    }
     if (pm) {
 #pragma unroll
         for (int j = 0; j < LT; j++)
@@ -1311,15 +1329,16 @@ __global__ void shard_merge_kernel(int B, int Vg, int world, int rank, const flo
 // Rows differ in cost by an order of magnitude (a greedy row is one pass, a hot row keeps
 // most of its vocabulary). Handing out the dearest first keeps the last CTAs from running
 // long: this small kernel sorts the rows by a cost estimate.
-__global__ void __launch_bounds__(NT, 1) order_rows_kernel(const float *temperature, const int *top_k, int B, int *order) {
+__global__ void __launch_bounds__(NT, 1) order_rows_kernel(const float *temperature, const int *top_k, const int *slot, int B, int *order) {
     __shared__ unsigned long long keys[ORDER_CAP];
     int n2 = 2;
     while (n2 < B) n2 <<= 1;
     for (int i = threadIdx.x; i < n2; i += NT) {
         float cost = -1.0f;
         if (i < B) {
-            const float T = temperature ? temperature[i] : 0.0f;
-            const int k = top_k ? top_k[i] : 0;
+            const int q = slot ? slot[i] : i;
+            const float T = temperature ? temperature[q] : 0.0f;
+            const int k = top_k ? top_k[q] : 0;
             cost = (T > 0.0f && k != 1) ? T + ((k == 0 || k >= HEAD_NEED) ? 0.25f : 0.0f) : 0.0f;
         }
         keys[i] = ((unsigned long long)fkey(cost) << 32) | (unsigned long long)(0xFFFFu - (unsigned int)(i & 0xFFFF));
@@ -1371,19 +1390,24 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         const int r = A->cur_row;
         if (r >= a.B) break;
         c.status = 0; c.last_read = false; c.nphase = 0; c.tmass = 0; c.tbuild = 0;
-        const float T = a.temperature ? a.temperature[r] : 0.0f;
-        const int k = a.top_k ? a.top_k[r] : 0;
-        const float P = a.top_p ? a.top_p[r] : 1.0f;
-        const float minp = a.min_p ? a.min_p[r] : 0.0f;
-        const float typ = a.typical_p ? a.typical_p[r] : 1.0f;
-        const float rp = a.repeat_penalty ? a.repeat_penalty[r] : 1.0f;
-        const float fp = a.frequency_penalty ? a.frequency_penalty[r] : 0.0f;
-        const float pp = a.presence_penalty ? a.presence_penalty[r] : 0.0f;
-        const bool won = a.window_on ? (a.window_on[r] != 0) : true;
-        const int h0 = (a.hist && a.hist_off) ? a.hist_off[r] : 0;
-        const int H = (a.hist && a.hist_off) ? (a.hist_off[r + 1] - h0) : 0;
-        const int b0 = (a.bias_ids && a.bias_off) ? a.bias_off[r] : 0;
-        const int nb = (a.bias_ids && a.bias_off) ? (a.bias_off[r + 1] - b0) : 0;
+        const int q = a.slot ? a.slot[r] : r;  // where this row's settings and state live
+        const float T = a.temperature ? a.temperature[q] : 0.0f;
+        const int k = a.top_k ? a.top_k[q] : 0;
+        const float P = a.top_p ? a.top_p[q] : 1.0f;
+        const float minp = a.min_p ? a.min_p[q] : 0.0f;
+        const float typ = a.typical_p ? a.typical_p[q] : 1.0f;
+        const float rp = a.repeat_penalty ? a.repeat_penalty[q] : 1.0f;
+        const float fp = a.frequency_penalty ? a.frequency_penalty[q] : 0.0f;
+        const float pp = a.presence_penalty ? a.presence_penalty[q] : 0.0f;
+        const int ring_n = a.ring ? min(max(a.ring_len[q], 0), a.ring_cap) : 0;
+        const bool won = a.ring ? (ring_n > 0) : (a.window_on ? (a.window_on[q] != 0) : true);
+        const int h0 = (a.hist && a.hist_off) ? a.hist_off[q] : 0;
+        // a window kept on the device fills from its first slot (sample.mojo:246-258): the first
+        // `filled` entries are the window, whatever the head is
+        const long long *histp = a.ring ? a.ring + (size_t)q * (size_t)a.ring_cap : (a.hist ? a.hist + h0 : nullptr);
+        const int H = a.ring ? min(max(a.ring_filled[q], 0), ring_n) : ((a.hist && a.hist_off) ? (a.hist_off[q + 1] - h0) : 0);
+        const int b0 = (a.bias_ids && a.bias_off) ? a.bias_off[q] : 0;
+        const int nb = (a.bias_ids && a.bias_off) ? (a.bias_off[q + 1] - b0) : 0;
         // the rules of SamplerConfig.check (sample.mojo:140-154); NaN fails every test
         const bool valid = (T >= 0.0f) && (k >= 0) && (P > 0.0f && P <= 1.0f) && (minp >= 0.0f && minp <= 1.0f) &&
                            (typ > 0.0f && typ <= 1.0f) && (rp > 0.0f) && H >= 0 && nb >= 0;
@@ -1405,7 +1429,8 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             }
             continue;
         }
-        c.src = a.logits + (long long)r * a.row_stride;
+        c.src = a.logits + (long long)(a.rows ? a.rows[r] : r) * a.row_stride;
+        c.softcap = a.softcap;
         c.aligned = ((reinterpret_cast<uintptr_t>(c.src) & 15u) == 0);
         STAMP(0);
 
@@ -1418,7 +1443,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             __syncthreads();
             for (int i = c.tid; i < npatch; i += NT) {
                 const bool is_bias = i < nb;
-                const long long t64 = (is_bias ? a.bias_ids[b0 + i] : a.hist[h0 + (i - nb)]) - a.col0;
+                const long long t64 = (is_bias ? a.bias_ids[b0 + i] : histp[i - nb]) - a.col0;
                 if (t64 < 0 || t64 >= a.V) continue;
                 const int tok = (int)t64;
                 int s = hslot(tok);
@@ -1433,8 +1458,9 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 const int tok = A->hkey[s];
                 if (tok < 0) continue;
                 float v = __ldg(c.src + tok);
-                for (int q = 0; q < nb; q++)  // duplicates add up, in the order they were given
-                    if (a.bias_ids[b0 + q] == (long long)tok + a.col0) v = __fadd_rn(v, a.bias_vals[b0 + q]);
+                if (c.softcap > 0.0f) v = softcap_pinned(v, c.softcap);
+                for (int bq = 0; bq < nb; bq++)  // duplicates add up, in the order they were given
+                    if (a.bias_ids[b0 + bq] == (long long)tok + a.col0) v = __fadd_rn(v, a.bias_vals[b0 + bq]);
                 const int n = A->hcnt[s];
                 if (n > 0) {
                     if (v > 0.0f) v = __fdiv_rn(v, rp);
@@ -1548,7 +1574,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             const float top = (T == 1.0f) ? xmax : __fdiv_rn(xmax, T);
             const bool topp_on = (P < 1.0f) && (n_lim > 1);
             const bool pure = !topp_on && n_lim == (long long)a.Vg;
-            const float u01 = draw01(a.seed ? a.seed[r] : 0ull, a.drawn ? a.drawn[r] : 0ull);
+            const float u01 = draw01(a.seed ? a.seed[q] : 0ull, a.drawn ? a.drawn[q] : 0ull);
             const bool filter_ok = fabsf(top) < 1.0e5f;
             long long need = n_lim + 1;
             if (need > HEAD_NEED) need = HEAD_NEED;
@@ -2023,6 +2049,18 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         if (c.tid == 0) {
             a.tokens[r] = token;
             a.row_status[r] = c.status;
+            if (a.ring && token >= 0) {  // `_took` (sample.mojo:361-363): observe, then one more draw used
+                if (ring_n > 0) {        // `observe` (:246-258)
+                    const int hd = a.ring_head[q];
+                    const int at = (hd >= 0 && hd < ring_n) ? hd : 0;
+                    a.ring[(size_t)q * (size_t)a.ring_cap + at] = (long long)token;
+                    a.ring_head[q] = (at + 1) % ring_n;
+                    const int f = a.ring_filled[q];
+                    a.ring_filled[q] = f < ring_n ? f + 1 : ring_n;
+                }
+                a.drawn_rw[q] += 1ull;
+                if (a.stopped) a.stopped[r] = (a.stop_token && a.stop_token[q] == (long long)token) ? 1 : 0;
+            }
             if (a.diag) { a.diag[4 * r] = dZ; a.diag[4 * r + 1] = dsum; a.diag[4 * r + 2] = dtarget; a.diag[4 * r + 3] = dp; }
         }
     }
@@ -2034,7 +2072,8 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
 // =============================================================================
 __global__ void __launch_bounds__(NT, 1) logprob_kernel(const float *logits, long long row_stride, int B, int V,
                                                         const int *tokens, int top_n, float *chosen_lp,
-                                                        int *top_ids, float *top_lps, float *full_out) {
+                                                        int *top_ids, float *top_lps, float *full_out,
+                                                        const int *rows, float softcap) {
     __shared__ float wsf[NWARP + 1];
     __shared__ double wsd[NWARP + 1];
     __shared__ unsigned long long cand[NT];
@@ -2042,10 +2081,11 @@ __global__ void __launch_bounds__(NT, 1) logprob_kernel(const float *logits, lon
     __shared__ float s_thr;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int r = blockIdx.x; r < B; r += gridDim.x) {
-        const float *z = logits + (long long)r * row_stride;
+        const float *z = logits + (long long)(rows ? rows[r] : r) * row_stride;
+        auto at = [&](int i) -> float { const float x = __ldg(z + i); return softcap > 0.0f ? softcap_pinned(x, softcap) : x; };
         // pass 1: maximum and each thread's own maximum
         float tm = -INFINITY;
-        for (int i = tid; i < V; i += NT) tm = fmaxf(tm, __ldg(z + i));
+        for (int i = tid; i < V; i += NT) tm = fmaxf(tm, at(i));
         float m = warp_max(tm);
         __syncthreads();
         if (lane == 0) wsf[warp] = m;
@@ -2074,7 +2114,7 @@ __global__ void __launch_bounds__(NT, 1) logprob_kernel(const float *logits, lon
         // pass 2: sum of exp(z - top) accumulated in fp64, candidates for the top-N
         double acc = 0.0;
         for (int i = tid; i < V; i += NT) {
-            float x = __ldg(z + i);
+            float x = at(i);
             acc += (double)expf_pinned(__fsub_rn(x, top));
             if (top_n > 0 && x >= thr) {
                 int pos = atomicAdd(&ncand, 1);
@@ -2095,11 +2135,11 @@ __global__ void __launch_bounds__(NT, 1) logprob_kernel(const float *logits, lon
         const float offset = (float)log(sum);
         if (chosen_lp && tokens && tid == 0) {
             int t = tokens[r];
-            chosen_lp[r] = (t >= 0 && t < V) ? __fsub_rn(__fsub_rn(__ldg(z + t), top), offset) : 0.0f;
+            chosen_lp[r] = (t >= 0 && t < V) ? __fsub_rn(__fsub_rn(at(t), top), offset) : 0.0f;
         }
         if (full_out) {
             float *o = full_out + (long long)r * V;
-            for (int i = tid; i < V; i += NT) o[i] = __fsub_rn(__fsub_rn(__ldg(z + i), top), offset);
+            for (int i = tid; i < V; i += NT) o[i] = __fsub_rn(__fsub_rn(at(i), top), offset);
         }
         if (top_n > 0) {
             __syncthreads();
@@ -2111,7 +2151,7 @@ __global__ void __launch_bounds__(NT, 1) logprob_kernel(const float *logits, lon
                 if (tid < n) {
                     int id = (int)(0xFFFFFFFFu - (unsigned int)(cand[tid] & 0xFFFFFFFFull));
                     top_ids[(long long)r * top_n + tid] = id;
-                    top_lps[(long long)r * top_n + tid] = __fsub_rn(__fsub_rn(__ldg(z + id), top), offset);
+                    top_lps[(long long)r * top_n + tid] = __fsub_rn(__fsub_rn(at(id), top), offset);
                 } else {
                     top_ids[(long long)r * top_n + tid] = -1;
                     top_lps[(long long)r * top_n + tid] = 0.0f;
@@ -2196,7 +2236,7 @@ int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, in
     a.order = nullptr;
     if (!a.penalised_only && a.B > grid && a.B <= ORDER_CAP && a.temperature) {
         int *order = (int *)((char *)d_workspace + 256);
-        order_rows_kernel<<<1, NT, 0, st>>>(a.temperature, a.top_k, a.B, order);
+        order_rows_kernel<<<1, NT, 0, st>>>(a.temperature, a.top_k, a.slot, a.B, order);
         a.order = order;
     }
     sample_rows_kernel<<<grid, NT, smem, st>>>(a);
@@ -2267,7 +2307,70 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         int grid = B < sms ? B : sms;
         logprob_kernel<<<grid, NT, 0, st>>>(d_logits, row_stride, B, V, d_tokens, top_n, d_chosen_logprob,
-                                            d_top_ids, d_top_logprobs, nullptr);
+                                            d_top_ids, d_top_logprobs, nullptr, nullptr, 0.0f);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
+    }
+    return MOLLA_OK;
+}
+
+int32_t molla_sample_decode_step(const float *d_logits, int64_t row_stride, int32_t n_logit_rows, int32_t V,
+                                 const int32_t *d_rows, const int32_t *d_slots, int32_t B, int32_t n_slots,
+                                 float final_softcap, const float *d_temperature, const int32_t *d_top_k,
+                                 const float *d_top_p, const float *d_min_p, const float *d_typical_p,
+                                 const float *d_repeat_penalty, const float *d_frequency_penalty,
+                                 const float *d_presence_penalty, const uint64_t *d_seed, uint64_t *d_drawn,
+                                 int64_t *d_ring, int32_t ring_cap, int32_t *d_ring_head, int32_t *d_ring_filled,
+                                 const int32_t *d_ring_len, const int64_t *d_stop_token, const int64_t *d_bias_ids,
+                                 const float *d_bias_vals, const int32_t *d_bias_off, int32_t top_n,
+                                 void *d_workspace, int64_t workspace_bytes, void *stream, int32_t *d_tokens,
+                                 uint8_t *d_stopped, float *d_chosen_logprob, int32_t *d_top_ids,
+                                 float *d_top_logprobs, uint32_t *d_row_status) {
+    g_err[0] = 0;
+    if (!d_logits || !d_tokens || !d_row_status) return fail(MOLLA_ERR_ARGUMENT, "logits, tokens and row status are required%s");
+    if (B < 0 || V <= 0 || row_stride < V || n_logit_rows < 0 || n_slots < 0) return fail(MOLLA_ERR_ARGUMENT, "bad block shape%s");
+    if (!d_rows && B > n_logit_rows) return fail(MOLLA_ERR_ARGUMENT, "more rows asked for than the block holds%s");
+    if (!d_slots && B > n_slots) return fail(MOLLA_ERR_ARGUMENT, "more rows than sampler slots%s");
+    if (!(final_softcap >= 0.0f)) return fail(MOLLA_ERR_ARGUMENT, "a softcap cannot be negative%s");
+    if (!d_drawn || !d_ring || !d_ring_head || !d_ring_filled || !d_ring_len || ring_cap <= 0)
+        return fail(MOLLA_ERR_ARGUMENT, "the sampler state (draw counters and windows) is required%s");
+    if (ring_cap > PATCH_MAX) return fail(MOLLA_ERR_ARGUMENT, "windows longer than 1024 tokens are not supported%s");
+    if (top_n < 0 || top_n > TOPN_MAX) return fail(MOLLA_ERR_ARGUMENT, "top_n out of range%s");
+    if (top_n > 0 && (!d_top_ids || !d_top_logprobs)) return fail(MOLLA_ERR_ARGUMENT, "top_n needs its output arrays%s");
+    if ((d_bias_ids == nullptr) != (d_bias_off == nullptr) || (d_bias_ids && !d_bias_vals))
+        return fail(MOLLA_ERR_ARGUMENT, "bias ids, values and offsets go together%s");
+    if (!d_workspace || workspace_bytes < molla_sample_workspace_bytes(B, V, top_n))
+        return fail(MOLLA_ERR_WORKSPACE, "workspace missing or too small%s");
+    if (B == 0) return MOLLA_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    BatchArgs a;
+    memset(&a, 0, sizeof(a));
+    a.logits = d_logits; a.row_stride = row_stride; a.B = B; a.V = V;
+    a.rows = d_rows; a.slot = d_slots; a.softcap = final_softcap;
+    a.temperature = d_temperature; a.top_k = d_top_k; a.top_p = d_top_p; a.min_p = d_min_p;
+    a.typical_p = d_typical_p; a.repeat_penalty = d_repeat_penalty;
+    a.frequency_penalty = d_frequency_penalty; a.presence_penalty = d_presence_penalty;
+    a.seed = (const unsigned long long *)d_seed; a.drawn = (const unsigned long long *)d_drawn;
+    a.drawn_rw = (unsigned long long *)d_drawn;
+    a.ring = (long long *)d_ring; a.ring_cap = ring_cap; a.ring_head = d_ring_head; a.ring_filled = d_ring_filled;
+    a.ring_len = d_ring_len; a.stop_token = (const long long *)d_stop_token; a.stopped = d_stopped;
+    a.bias_ids = (const long long *)d_bias_ids; a.bias_vals = d_bias_vals; a.bias_off = d_bias_off;
+    a.tokens = d_tokens; a.row_status = d_row_status;
+    a.prof = g_prof;
+    a.knobs = g_knobs;
+    if (d_stopped) {
+        cudaError_t e0 = cudaMemsetAsync(d_stopped, 0, (size_t)B, st);
+        if (e0 != cudaSuccess) return fail(MOLLA_ERR_CUDA, "clearing the stop flags failed: %s", cudaGetErrorString(e0));
+    }
+    int rc = launch_rows(a, d_workspace, st);
+    if (rc != MOLLA_OK) return rc;
+    if (d_chosen_logprob || top_n > 0) {
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        int grid = B < sms ? B : sms;
+        logprob_kernel<<<grid, NT, 0, st>>>(d_logits, row_stride, B, V, d_tokens, top_n, d_chosen_logprob,
+                                            d_top_ids, d_top_logprobs, nullptr, d_rows, final_softcap);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
     }
@@ -2335,7 +2438,7 @@ int32_t molla_sample_batch_noalloc(const float *d_logits, int64_t row_stride, in
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         int grid = B < sms ? B : sms;
         logprob_kernel<<<grid, NT, 0, st>>>(d_logits, row_stride, B, V, d_tokens, top_n, d_chosen_logprob,
-                                            d_top_ids, d_top_logprobs, nullptr);
+                                            d_top_ids, d_top_logprobs, nullptr, nullptr, 0.0f);
         e = cudaGetLastError();
         if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
     }
@@ -2584,7 +2687,7 @@ int32_t molla_sample_logprobs(const float *d_logits, int64_t row_stride, int32_t
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     int grid = B < sms ? B : sms;
     logprob_kernel<<<grid, NT, 0, (cudaStream_t)stream>>>(d_logits, row_stride, B, V, nullptr, 0, nullptr, nullptr,
-                                                          nullptr, d_out);
+                                                          nullptr, d_out, nullptr, 0.0f);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
     return MOLLA_OK;

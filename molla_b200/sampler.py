@@ -401,3 +401,110 @@ def pick_rows(logits: torch.Tensor, samplers: Sequence[Sampler], rows: Iterable[
             raise capi.MollaSampleError(capi.ERR_DEVICE, f"row status {st:#x}")
         s._took(t)
     return toks
+
+
+class DeviceSamplers:
+    """The samplers of `n_slots` live sequences kept on the device: settings, recent-token
+    windows and draw counters (`Sampler`'s fields, sample.mojo:157-212), so that a decode step
+    samples, records the token and advances the counter without a host round trip
+    (`molla_sample_decode_step`). A sequence takes a slot with `assign` and keeps it until
+    another `assign` gives the slot away."""
+
+    def __init__(self, n_slots: int, vocab: int, ring_cap: int = 64, device="cuda:0"):
+        if n_slots <= 0 or vocab <= 0 or ring_cap <= 0:
+            raise ValueError("slots, vocabulary and window capacity have to be positive")
+        self.n_slots, self.vocab, self.ring_cap = int(n_slots), int(vocab), int(ring_cap)
+        self.device = dev = torch.device(device)
+        z = lambda dt, *shape: torch.zeros(shape, dtype=dt, device=dev)
+        S = self.n_slots
+        self.temperature = z(torch.float32, S)
+        self.top_k = z(torch.int32, S)
+        self.top_p = torch.ones(S, dtype=torch.float32, device=dev)
+        self.min_p = z(torch.float32, S)
+        self.typical_p = torch.ones(S, dtype=torch.float32, device=dev)
+        self.repeat_penalty = torch.ones(S, dtype=torch.float32, device=dev)
+        self.frequency_penalty = z(torch.float32, S)
+        self.presence_penalty = z(torch.float32, S)
+        self.seed = z(torch.int64, S)          # uint64 bit patterns
+        self.drawn = z(torch.int64, S)
+        self.ring = torch.full((S, self.ring_cap), -1, dtype=torch.int64, device=dev)
+        self.ring_head = z(torch.int32, S)
+        self.ring_filled = z(torch.int32, S)
+        self.ring_len = z(torch.int32, S)
+        self.stop_token = torch.full((S,), -1, dtype=torch.int64, device=dev)
+        self._bias: list[list[tuple[int, float]]] = [[] for _ in range(S)]
+        self._bias_dev = None
+        self._ws: Workspace | None = None
+
+    def assign(self, slot: int, config: SamplerConfig, stop_token: int = -1,
+               bias: Sequence[tuple[int, float]] = ()) -> None:
+        """A new sequence in `slot`: its settings, an empty window, counter zero
+        (`Sampler.__init__`, sample.mojo:194-212)."""
+        config.check()
+        if not 0 <= slot < self.n_slots:
+            raise ValueError("no such slot")
+        if config.repeat_last_n > self.ring_cap:
+            raise ValueError("the window is longer than the capacity these samplers were built with")
+        for t, _ in bias:
+            if t < 0 or t >= self.vocab:
+                raise ValueError(f"a logit bias names token {t} and the vocabulary is {self.vocab} wide")
+        s = int(config.seed) & (2**64 - 1)
+        vals = dict(temperature=config.temperature, top_k=config.top_k, top_p=config.top_p, min_p=config.min_p,
+                    typical_p=config.typical_p, repeat_penalty=config.repeat_penalty,
+                    frequency_penalty=config.frequency_penalty, presence_penalty=config.presence_penalty,
+                    seed=s - 2**64 if s >= 2**63 else s, drawn=0, ring_head=0, ring_filled=0,
+                    ring_len=config.repeat_last_n,
+                    stop_token=int(stop_token))
+        for k, v in vals.items():
+            getattr(self, k)[slot] = v
+        self.ring[slot].fill_(-1)
+        self._bias[slot] = [(int(t), float(v)) for t, v in bias]
+        self._bias_dev = None
+
+    def _bias_arrays(self):
+        if self._bias_dev is None:
+            ids, vals, off = [], [], [0]
+            for lst in self._bias:
+                ids += [t for t, _ in lst]
+                vals += [v for _, v in lst]
+                off.append(len(ids))
+            if ids:
+                dev = self.device
+                self._bias_dev = (torch.tensor(ids, dtype=torch.int64, device=dev),
+                                  torch.tensor(vals, dtype=torch.float32, device=dev),
+                                  torch.tensor(off, dtype=torch.int32, device=dev))
+            else:
+                self._bias_dev = (None, None, None)
+        return self._bias_dev
+
+    def step(self, logits: torch.Tensor, rows: torch.Tensor | None, slots: torch.Tensor | None,
+             final_softcap: float = 0.0, top_n: int = 0, want_logprob: bool = False) -> dict:
+        """One decode step: batch row r samples logit row rows[r] with the sampler in slots[r]
+        (int32 device tensors; None = r). Returns device tensors; asynchronous on the current stream."""
+        if not logits.is_cuda or logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+            raise ValueError("logits must be a 2-D fp32 CUDA tensor with contiguous rows")
+        n_rows, V = logits.shape
+        if V != self.vocab:
+            raise ValueError(f"the samplers were built for a vocabulary of {self.vocab} and got {V} logits")
+        B = int(rows.numel()) if rows is not None else (int(slots.numel()) if slots is not None else n_rows)
+        dev = self.device
+        if self._ws is None or self._ws.bytes < capi.lib().molla_sample_workspace_bytes(B, V, top_n):
+            self._ws = Workspace(max(B, 1), V, top_n, dev)
+        tokens = torch.empty(B, dtype=torch.int32, device=dev)
+        status = torch.empty(B, dtype=torch.int32, device=dev)
+        stopped = torch.empty(B, dtype=torch.uint8, device=dev)
+        chosen = torch.empty(B, dtype=torch.float32, device=dev) if want_logprob else None
+        top_ids = torch.empty((B, top_n), dtype=torch.int32, device=dev) if top_n else None
+        top_lps = torch.empty((B, top_n), dtype=torch.float32, device=dev) if top_n else None
+        b_ids, b_vals, b_off = self._bias_arrays()
+        rc = capi.lib().molla_sample_decode_step(
+            _ptr(logits), logits.stride(0), n_rows, V, _ptr(rows), _ptr(slots), B, self.n_slots, float(final_softcap),
+            _ptr(self.temperature), _ptr(self.top_k), _ptr(self.top_p), _ptr(self.min_p), _ptr(self.typical_p),
+            _ptr(self.repeat_penalty), _ptr(self.frequency_penalty), _ptr(self.presence_penalty),
+            _ptr(self.seed), _ptr(self.drawn), _ptr(self.ring), self.ring_cap, _ptr(self.ring_head),
+            _ptr(self.ring_filled), _ptr(self.ring_len), _ptr(self.stop_token), _ptr(b_ids), _ptr(b_vals), _ptr(b_off),
+            top_n, _ptr(self._ws.buf), self._ws.bytes, _stream_ptr(dev), _ptr(tokens), _ptr(stopped), _ptr(chosen),
+            _ptr(top_ids), _ptr(top_lps), _ptr(status))
+        capi.check(rc)
+        return dict(tokens=tokens, stopped=stopped, row_status=status, chosen_logprob=chosen, top_ids=top_ids,
+                    top_logprobs=top_lps)

@@ -135,6 +135,19 @@ float molla_oracle_logf(float x) {
     return fmaf(dk, LN2_HI, fmaf(dk, LN2_LO, lm));
 }
 
+/* The final-logit softcap of Gemma-style models as the reference's device kernel computes it
+ * (src/molla/nn/gpu_ops.mojo:302-317: x = cap * _tanh(x / cap); _tanh :607-623 through one
+ * exponential of a non-positive argument), on the pinned exponential. */
+void molla_oracle_softcap(const float *x, int64_t n, float cap, float *out) {
+    for (int64_t i = 0; i < n; i++) {
+        float t = x[i] / cap;
+        float v = t >= 0 ? t : -t;
+        float e = molla_oracle_expf(-2.0f * v);
+        float r = (1.0f - e) / (1.0f + e);
+        out[i] = cap * (t >= 0 ? r : -r);
+    }
+}
+
 static inline float log_sel(float x, int mode) {
     return mode == 1 ? logf(x) : molla_oracle_logf(x);
 }

@@ -50,6 +50,8 @@ def lib():
         L.molla_oracle_expf.argtypes = [C.c_float]
         L.molla_oracle_logf_array.restype = None
         L.molla_oracle_logf_array.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
+        L.molla_oracle_softcap.restype = None
+        L.molla_oracle_softcap.argtypes = [C.c_void_p, C.c_int64, C.c_float, C.c_void_p]
         L.molla_oracle_argmax.restype = C.c_int64
         L.molla_oracle_argmax.argtypes = [C.c_void_p, C.c_int64, C.c_int64]
         L.molla_oracle_logprobs.restype = None
@@ -83,6 +85,14 @@ def logf(x) -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=np.float32).ravel()
     out = np.empty_like(x)
     lib().molla_oracle_logf_array(x.ctypes.data_as(C.c_void_p), x.size, out.ctypes.data_as(C.c_void_p))
+    return out
+
+
+def softcap(x, cap: float) -> np.ndarray:
+    """cap * tanh(x / cap) as the reference's device kernel evaluates it, same shape as x."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    lib().molla_oracle_softcap(x.ctypes.data_as(C.c_void_p), x.size, C.c_float(cap), out.ctypes.data_as(C.c_void_p))
     return out
 
 
