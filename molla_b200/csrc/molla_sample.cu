@@ -176,7 +176,7 @@ struct Ctx {
     int rbeg, rlen, npieces;
     unsigned int parbits;
     int nphase;           // histogram phases run by the descending walks of this row (profiling aid)
-    long long tmass, tbuild;  // cycles thread 0 spent in the exact sum's serial walk / waiting for its tables (profiling aid)
+    long long t_stage, t_build;  // cycles of the exact sum spent staging list blocks / building their tables (profiling aid)
 };
 
 #define STAMP(i) do { if (a.prof && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
@@ -634,7 +634,7 @@ __device__ void p1_block(Ctx &c, V vals, int n, int base, bool locate, float tar
     if ((L & 1) == 0) L += 1;
     const long long tq0 = clock64();
     p1_build(c, vals, n, L, (double)A->walk_s);
-    c.tbuild += clock64() - tq0;
+    c.t_build += clock64() - tq0;
     if (c.tid == 0) {
         Walker w; w.s = A->walk_s; w.found = 0; w.at = -1; w.slow = A->walk_slow;
         p1_walk(c, vals, n, L, locate, target, w);
@@ -678,7 +678,7 @@ __device__ void p1_run(Ctx &c, const LView &lv, unsigned int *vals, bool locate,
             lv.for_range(c.tid, o, o + n, [&](int v, unsigned long long k) { vals[v - o] = (unsigned int)(k >> 32); });
         }
         __syncthreads();
-        c.tmass += clock64() - tq0;
+        c.t_stage += clock64() - tq0;
         if (locate && A->walk_found) break;
         p1_block(c, ValBits{vals}, n, b * VBLK, locate, target);
     }
@@ -1389,7 +1389,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         __syncthreads();
         const int r = A->cur_row;
         if (r >= a.B) break;
-        c.status = 0; c.last_read = false; c.nphase = 0; c.tmass = 0; c.tbuild = 0;
+        c.status = 0; c.last_read = false; c.nphase = 0; c.t_stage = 0; c.t_build = 0;
         const int q = a.slot ? a.slot[r] : r;  // where this row's settings and state live
         const float T = a.temperature ? a.temperature[q] : 0.0f;
         const int k = a.top_k ? a.top_k[q] : 0;
@@ -2045,7 +2045,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             }
         }
         STAMP(9);
-        if (a.prof && c.tid == 0) { a.prof[(long long)r * 16 + 8] = c.nphase; a.prof[(long long)r * 16 + 14] = c.tmass; a.prof[(long long)r * 16 + 15] = c.tbuild; }
+        if (a.prof && c.tid == 0) { a.prof[(long long)r * 16 + 8] = c.nphase; a.prof[(long long)r * 16 + 14] = c.t_stage; a.prof[(long long)r * 16 + 15] = c.t_build; }
         if (c.tid == 0) {
             a.tokens[r] = token;
             a.row_status[r] = c.status;
