@@ -70,6 +70,7 @@ constexpr int ORDER_CAP = 4096;      // rows whose order is sorted by cost insid
 // otherwise use generic loads, stores and atomics on shared memory).
 #define IN_SHARED(ptr) __builtin_assume(__isShared(ptr))
 
+struct HelpSlot;
 struct BatchArgs {
     const float *logits; long long row_stride; int B, V;
     const float *temperature; const int *top_k; const float *top_p; const float *min_p;
@@ -87,6 +88,10 @@ struct BatchArgs {
     unsigned long long *wlist;   // scratch: per CTA, 2 x 16 x R list entries
     long long *prof;             // optional [B x 16] clock64 stamps per row (testing aid)
     int knobs;                   // experiment switches (testing aid; 0 in production)
+    // thread blocks that ran out of rows help the ones still converting a long list (HelpSlot)
+    struct HelpSlot *help;       // [grid] one per thread block, or nullptr
+    unsigned int *help_tables;   // [grid x HELP_TABLE_WORDS]
+    int *rows_done;              // rows finished so far (zeroed before the launch)
     // decode-step form: which row of the logit block each batch row reads, which slot of the
     // per-stream arrays (settings and state) it uses, the final-logit softcap, and the state
     const int *rows;             // [B] or nullptr (row r reads logit row r)
@@ -377,7 +382,7 @@ struct LView {
         for (int q = 1; q < NWARP; q++) w += (v >= woff[q]) ? 1 : 0;
         return seg + (size_t)w * stride + (size_t)(v - woff[w]);
     }
-    __device__ __forceinline__ unsigned long long at(int v) const { return *slot(v); }
+    __device__ __forceinline__ unsigned long long at(int v) const { return flat ? *slot(v) : __ldcg(slot(v)); }
     // f(index in the whole list, key) over the entries [v0, v1): the whole block on one segment
     // after the other, 16-byte loads (two entries), eight in flight per thread
     template <class F>
@@ -401,7 +406,7 @@ struct LView {
                 ulonglong2 k[8];
 #pragma unroll
                 for (int q = 0; q < 8; q++)
-                    k[q] = (i + q * NT < p1) ? (flat ? b2[i + q * NT] : ldg_keep(b2 + i + q * NT, keep)) : make_ulonglong2(0ull, 0ull);
+                    k[q] = (i + q * NT < p1) ? (flat ? b2[i + q * NT] : __ldcg(b2 + i + q * NT)) : make_ulonglong2(0ull, 0ull);
 #pragma unroll
                 for (int q = 0; q < 8; q++)
                     if (i + q * NT < p1) { f(o + 2 * (i + q * NT), k[q].x); f(o + 2 * (i + q * NT) + 1, k[q].y); }
@@ -425,7 +430,7 @@ struct LView {
         for (; i + 7 * step < mp; i += 8 * step) {
             ulonglong2 k[8];
 #pragma unroll
-            for (int q = 0; q < 8; q++) k[q] = flat ? b2[i + q * step] : ldg_keep(b2 + i + q * step, keep);
+            for (int q = 0; q < 8; q++) k[q] = flat ? b2[i + q * step] : __ldcg(b2 + i + q * step);
 #pragma unroll
             for (int q = 0; q < 8; q++) {
                 const int e = 2 * (i + q * step);
@@ -433,7 +438,7 @@ struct LView {
             }
         }
         for (; i < mp; i += step) {
-            const ulonglong2 k = flat ? b2[i] : ldg_keep(b2 + i, keep);
+            const ulonglong2 k = flat ? b2[i] : __ldcg(b2 + i);
             f(o + 2 * i, k.x, b + 2 * i); f(o + 2 * i + 1, k.y, b + 2 * i + 1);
         }
         if ((m & 1) && t == 0) f(o + m - 1, b[m - 1], b + m - 1);
@@ -1198,6 +1203,175 @@ __device__ bool descend_masses(Ctx &c, const LView &lv, const MassTable &mt, Mas
 }
 
 // =============================================================================
+// Help with long lists. The step is as long as its dearest row, and the dearest rows are the
+// ones whose list is most of the vocabulary; they are handed out first, so when they reach
+// the pass that turns their list into probabilities and bin masses, most other thread blocks
+// have run out of rows. Those blocks then take segments of that pass: the owner publishes
+// what the pass needs in its HelpSlot, owner and helpers claim segments with an atomic
+// counter, a helper converts a segment in place (global memory, L1 bypassed on both sides),
+// collects the segment's bin masses in its own shared memory and adds them into the owner's
+// table in global memory. The owner never depends on a helper turning up: it claims segments
+// itself until none are left and then waits, with a bound, for the ones still in other hands.
+// =============================================================================
+constexpr int HELP_TABLE_WORDS = MASS_SETS * MASS_SET_WORDS + NBINS;  // the sets, then the bin counts
+constexpr int HELP_MIN_LIST = 24576;                                  // shorter lists are not worth publishing
+struct __align__(256) HelpSlot {
+    int open;            // 1 while segments can be claimed
+    int claim;           // next segment to hand out
+    int done;            // segments finished
+    int nunits;
+    float Z;
+    unsigned int tau_bits;
+    int mark_head;
+    int j0;
+    unsigned int tau0;
+    int count[NWARP];    // entries in each segment
+};
+
+// One segment of a long list: exponentials to probabilities in place, and every entry's
+// contribution into `mt` (this block's shared memory). All threads; 16-byte accesses that
+// bypass L1 (the segment may have been written, or will be read, by another SM).
+__device__ __forceinline__ void convert_segment(Ctx &c, unsigned long long *ks, int m, float Z, unsigned int tau_bits,
+                                                bool mark_head, const MassTable &mt) {
+    auto one = [&](unsigned long long kk) -> unsigned long long {
+        unsigned int pb = __float_as_uint(__fdiv_rn(key_val(kk), Z));
+        if (mark_head && (unsigned int)(kk >> 32) >= tau_bits) pb = 0xFFFFFFFFu;  // the head took it in pass B
+        masses_add(mt, pb);
+        return ((unsigned long long)pb << 32) | (kk & 0xFFFFFFFFull);
+    };
+    ulonglong2 *k2 = reinterpret_cast<ulonglong2 *>(ks);
+    const int mp = m >> 1;
+    for (int i = c.tid; i < mp; i += 8 * NT) {
+        ulonglong2 k[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) k[q] = (i + q * NT < mp) ? __ldcg(k2 + i + q * NT) : make_ulonglong2(0ull, 0ull);
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+            if (i + q * NT < mp) { k[q].x = one(k[q].x); k[q].y = one(k[q].y); __stcg(k2 + i + q * NT, k[q]); }
+    }
+    if ((m & 1) && c.tid == 0) __stcg(ks + m - 1, one(__ldcg(ks + m - 1)));
+}
+
+// The owner's side: publish, work, wait, merge. Returns false if a helper did not report back
+// within the bound (the row is then failed; its list may be half converted).
+__device__ bool helped_convert(Ctx &c, const BatchArgs &a, unsigned long long *wl_seg, float Z, unsigned int tau_bits,
+                               bool mark_head, const MassTable &mt) {
+    Aux *A = c.A;
+    IN_SHARED(A);
+    HelpSlot *hs = a.help + blockIdx.x;
+    unsigned int *gt = a.help_tables + (size_t)blockIdx.x * HELP_TABLE_WORDS;
+    __syncthreads();
+    for (int i = c.tid; i < HELP_TABLE_WORDS; i += NT) __stcg(gt + i, 0u);
+    if (c.tid < NWARP) hs->count[c.tid] = A->woff[c.tid + 1] - A->woff[c.tid];
+    if (c.tid == 0) {
+        hs->Z = Z; hs->tau_bits = tau_bits; hs->mark_head = mark_head ? 1 : 0; hs->j0 = mt.j0; hs->tau0 = mt.tau0;
+        hs->nunits = NWARP; hs->done = 0;
+    }
+    __threadfence();
+    __syncthreads();
+    if (c.tid == 0) { atomicExch(&hs->claim, 0); __threadfence(); atomicExch(&hs->open, 1); }
+    for (;;) {
+        __syncthreads();
+        if (c.tid == 0) A->evt_thread = atomicAdd(&hs->claim, 1);
+        __syncthreads();
+        const int u = A->evt_thread;
+        if (u >= NWARP) break;
+        convert_segment(c, wl_seg + (size_t)u * (size_t)a.R, A->woff[u + 1] - A->woff[u], Z, tau_bits, mark_head, mt);
+        __threadfence();
+        __syncthreads();
+        if (c.tid == 0) atomicAdd(&hs->done, 1);
+    }
+    if (c.tid == 0) {
+        int ok = 0;
+        for (int spin = 0; spin < (1 << 22); spin++) {
+            if (atomicAdd(&hs->done, 0) >= NWARP) { ok = 1; break; }
+            __nanosleep(200);
+        }
+        atomicExch(&hs->open, 0);
+        A->evt_thread = ok;
+    }
+    __syncthreads();
+    const bool ok = A->evt_thread != 0;
+    __threadfence();
+    // what the helpers found: sums add, care bits and nothing else are or-ed
+    for (int i = c.tid; i < HELP_TABLE_WORDS; i += NT) {
+        const unsigned int v = __ldcg(gt + i);
+        if (!v) continue;
+        if (i >= MASS_SETS * MASS_SET_WORDS) { mt.cnt[i - MASS_SETS * MASS_SET_WORDS] += v; continue; }
+        const int k = i / MASS_SET_WORDS, j = i - k * MASS_SET_WORDS;
+        unsigned int *set = mt.sets + k * MASS_SET_WORDS;
+        if (j >= 2 * NBINS) set[j] |= v; else set[j] += v;
+    }
+    __syncthreads();
+    return ok;
+}
+
+// A block with no rows left: look for a published pass and take segments of it, until every
+// row of the launch is done.
+__device__ void help_others(Ctx &c, const BatchArgs &a) {
+    Aux *A = c.A;
+    IN_SHARED(A);
+    const int nslots = (int)gridDim.x;
+    MassTable mt;
+    mt.cnt = reinterpret_cast<unsigned int *>(A->hval);
+    mt.sets = reinterpret_cast<unsigned int *>(c.stage);
+    mt.j0 = 0; mt.tau0 = 0u; mt.Cm0 = mt.half0 = mt.big0 = 0.0f;
+    if (c.tid == 0) A->ncand = ((int)blockIdx.x + 1) % nslots;  // the slot the scan starts from (shared by the block)
+    for (int poll = 0; poll < (1 << 20); poll++) {
+        __syncthreads();
+        if (c.tid == 0) { A->evt_thread = 0x7fffffff; A->specbin = (*(volatile int *)a.rows_done >= a.B) ? 1 : 0; }
+        __syncthreads();
+        if (A->specbin) return;
+        const int next = A->ncand;
+        // every thread looks at one slot; the nearest open one after the slot served last is tried
+        for (int sidx = c.tid; sidx < nslots; sidx += NT) {
+            if (sidx == (int)blockIdx.x) continue;
+            const volatile HelpSlot *hs = a.help + sidx;
+            if (hs->open == 1 && hs->claim < NWARP) atomicMin(&A->evt_thread, (sidx - next + nslots) % nslots);
+        }
+        __syncthreads();
+        const int pick = A->evt_thread;
+        __syncthreads();
+        if (c.tid == 0) {
+            int found = -1, unit = 0;
+            if (pick != 0x7fffffff) {
+                const int sidx = (pick + next) % nslots;
+                unit = atomicAdd(&a.help[sidx].claim, 1);
+                if (unit < NWARP) { found = sidx; A->ncand = sidx; }
+            } else {
+                __nanosleep(500);
+            }
+            A->evt_thread = found; A->specbin = unit;
+        }
+        __syncthreads();
+        const int sidx = A->evt_thread, u = A->specbin;
+        if (sidx < 0) continue;
+        HelpSlot *hs = a.help + sidx;
+        __threadfence();
+        const float Z = __ldcg(&hs->Z);
+        const unsigned int tau_bits = __ldcg(&hs->tau_bits);
+        const bool mark_head = __ldcg(&hs->mark_head) != 0;
+        const int m = __ldcg(&hs->count[u]);
+        masses_begin(c, mt, __ldcg(&hs->j0), __ldcg(&hs->tau0));
+        unsigned long long *seg = a.wlist + (size_t)sidx * 2 * NWARP * (size_t)a.R + (size_t)u * (size_t)a.R;
+        convert_segment(c, seg, m, Z, tau_bits, mark_head, mt);
+        __syncthreads();
+        unsigned int *gt = a.help_tables + (size_t)sidx * HELP_TABLE_WORDS;
+        for (int i = c.tid; i < HELP_TABLE_WORDS; i += NT) {
+            unsigned int v;
+            if (i >= MASS_SETS * MASS_SET_WORDS) v = mt.cnt[i - MASS_SETS * MASS_SET_WORDS];
+            else v = mt.sets[i];
+            if (!v) continue;
+            const int j = i % MASS_SET_WORDS;
+            if (i < MASS_SETS * MASS_SET_WORDS && j >= 2 * NBINS) atomicOr(gt + i, v); else atomicAdd(gt + i, v);
+        }
+        __threadfence();
+        __syncthreads();
+        if (c.tid == 0) atomicAdd(&hs->done, 1);
+    }
+}
+
+// =============================================================================
 // Typical-p (sample.mojo:525-567) on a kept set that lies inside the sorted head: m
 // probabilities pc[0..m), descending, ids in hidx. Entropy H = -sum p log p, added up
 // in that order in fp32; distance |-log p - H|; stable order by distance; the smallest
@@ -1379,9 +1553,11 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
     const int nwords = (a.V + 31) >> 5;
     const uint64_t keep_policy = (a.knobs & 4) ? l2_normal_policy() : l2_keep_policy();
 
+    bool had_row = false;
     for (;;) {
         __syncthreads();
         if (c.tid == 0) {
+            if (had_row && a.rows_done) { __threadfence(); atomicAdd(a.rows_done, 1); }
             int t = atomicAdd(a.row_counter, 1);
             if (a.order && t < a.B) t = a.order[t];
             A->cur_row = t;
@@ -1389,6 +1565,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         __syncthreads();
         const int r = A->cur_row;
         if (r >= a.B) break;
+        had_row = true;
         c.status = 0; c.last_read = false; c.nphase = 0; c.t_stage = 0; c.t_build = 0;
         const int q = a.slot ? a.slot[r] : r;  // where this row's settings and state live
         const float T = a.temperature ? a.temperature[q] : 0.0f;
@@ -1433,6 +1610,11 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         c.softcap = a.softcap;
         c.aligned = ((reinterpret_cast<uintptr_t>(c.src) & 15u) == 0);
         STAMP(0);
+        if (a.prof && c.tid == 0) {  // when and where the row ran, on the clock all SMs share
+            unsigned long long gt;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+            a.prof[(long long)r * 16 + 10] = (long long)gt; a.prof[(long long)r * 16 + 12] = blockIdx.x;
+        }
 
         // ---- 1. logit bias and penalties (sample.mojo:381-417) touch at most a window's worth of
         // tokens: their new values go into a hash, a bitmap over the vocabulary marks them.
@@ -1690,7 +1872,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 lb += A->u.s.pmax[c.warp][p];
                 tqc += clock64() - tq0;
             }
-            if (a.prof && c.tid == 32 * 5) { a.prof[(long long)r * 16 + 10] = tqa; a.prof[(long long)r * 16 + 11] = tqb; a.prof[(long long)r * 16 + 12] = tqc; a.prof[(long long)r * 16 + 13] = base; }
+            if (a.prof && c.tid == 32 * 5) a.prof[(long long)r * 16 + 13] = base;
             if (c.lane == 0) A->wcnt[c.warp] = base;
             } else if (c.tid < NWARP) {
                 // stage 3: the segments are the shards' lists, already in vocabulary order
@@ -1964,6 +2146,11 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         mt.sets = reinterpret_cast<unsigned int *>(c.stage);  // idle while the list is a global view
                         const bool use_mt = (a.mode == 0) && !lv.flat && !list_is_p && head_s > 0.0f;
                         if (use_mt) { masses_begin(c, mt, fexpo(head_s), tau_head); mass_on = true; }
+                        if (use_mt && a.help && nl >= HELP_MIN_LIST && !(a.knobs & 8)) {
+                            // a long list: blocks that have run out of rows take segments of this pass
+                            if (!helped_convert(c, a, wl_seg, Z, tau_bits, mark_head, mt)) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
+                            list_is_p = true;
+                        }
                         if (!list_is_p) { convert_list(false); list_is_p = true; }
                         mass_on = false;
                         STAMP(7);
@@ -2045,6 +2232,11 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             }
         }
         STAMP(9);
+        if (a.prof && c.tid == 0) {
+            unsigned long long gt;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+            a.prof[(long long)r * 16 + 11] = (long long)gt;
+        }
         if (a.prof && c.tid == 0) { a.prof[(long long)r * 16 + 8] = c.nphase; a.prof[(long long)r * 16 + 14] = c.t_stage; a.prof[(long long)r * 16 + 15] = c.t_build; }
         if (c.tid == 0) {
             a.tokens[r] = token;
@@ -2064,6 +2256,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             if (a.diag) { a.diag[4 * r] = dZ; a.diag[4 * r + 1] = dsum; a.diag[4 * r + 2] = dtarget; a.diag[4 * r + 3] = dp; }
         }
     }
+    if (a.help && !(a.knobs & 8)) help_others(c, a);  // no rows left: lend a hand to the blocks still on a long list
 }
 
 // =============================================================================
@@ -2208,12 +2401,15 @@ int region_floats(int V) { return (((V + NWARP - 1) / NWARP) + 3) & ~3; }
 // scratch layout: [row counter, 256 bytes][per CTA: 16 per-warp list segments + one contiguous
 // copy, each entry an (exp bits, token id) pair]
 constexpr size_t WS_HEADER = 256 + (size_t)ORDER_CAP * 4;
+// ... and behind the lists, for the ordinary entry points, one HelpSlot and one bin-mass table
+// per CTA
+size_t help_bytes(size_t ctas) { return ctas * (sizeof(HelpSlot) + (size_t)HELP_TABLE_WORDS * 4); }
 size_t batch_workspace_bytes(int B, int V, int sms) {
     const size_t ctas = (size_t)(B < sms ? B : sms);
-    return WS_HEADER + ctas * 2 * (size_t)NWARP * (size_t)region_floats(V) * 8;
+    return WS_HEADER + ctas * 2 * (size_t)NWARP * (size_t)region_floats(V) * 8 + help_bytes(ctas);
 }
 
-int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, int max_ctas = 0x7fffffff) {
+int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, int max_ctas = 0x7fffffff, bool with_help = false) {
     BatchArgs a = args_in;
     const int sms = sm_count();
     if (sms <= 0) return fail(MOLLA_ERR_CUDA, "cannot query the device%s");
@@ -2233,6 +2429,16 @@ int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, in
     if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "workspace clear failed: %s", cudaGetErrorString(e));
     int grid = a.B < sms ? a.B : sms;
     if (grid > max_ctas) grid = max_ctas;
+    a.rows_done = (int *)d_workspace + 2;
+    a.help = nullptr; a.help_tables = nullptr;
+    if (with_help && a.mode == 0 && grid > 1) {
+        const size_t ctas = (size_t)(a.B < sms ? a.B : sms);
+        char *hb = (char *)d_workspace + WS_HEADER + ctas * 2 * (size_t)NWARP * (size_t)a.R * 8;
+        a.help = (HelpSlot *)hb;
+        a.help_tables = (unsigned int *)(hb + ctas * sizeof(HelpSlot));
+        e = cudaMemsetAsync(hb, 0, ctas * sizeof(HelpSlot), st);
+        if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "workspace clear failed: %s", cudaGetErrorString(e));
+    }
     a.order = nullptr;
     if (!a.penalised_only && a.B > grid && a.B <= ORDER_CAP && a.temperature) {
         int *order = (int *)((char *)d_workspace + 256);
@@ -2299,7 +2505,7 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
     a.prof = g_prof;
     a.knobs = g_knobs;
     a.topk_out = g_topk; a.topk_cap = g_topk_cap;
-    int rc = launch_rows(a, d_workspace, st);
+    int rc = launch_rows(a, d_workspace, st, 0x7fffffff, true);
     if (rc != MOLLA_OK) return rc;
     if (d_chosen_logprob || top_n > 0) {
         int dev = 0, sms = 148;
@@ -2362,7 +2568,7 @@ int32_t molla_sample_decode_step(const float *d_logits, int64_t row_stride, int3
         cudaError_t e0 = cudaMemsetAsync(d_stopped, 0, (size_t)B, st);
         if (e0 != cudaSuccess) return fail(MOLLA_ERR_CUDA, "clearing the stop flags failed: %s", cudaGetErrorString(e0));
     }
-    int rc = launch_rows(a, d_workspace, st);
+    int rc = launch_rows(a, d_workspace, st, 0x7fffffff, true);
     if (rc != MOLLA_OK) return rc;
     if (d_chosen_logprob || top_n > 0) {
         int dev = 0, sms = 148;
