@@ -1123,10 +1123,260 @@ __device__ __forceinline__ void masses_add(const MassTable &mt, unsigned int pb)
     }
 }
 
+// =============================================================================
+// Help with long lists. The step is as long as its dearest row, and the dearest rows are the
+// ones whose list is most of the vocabulary; they are handed out first, so when they reach
+// the pass that turns their list into probabilities and bin masses, most other thread blocks
+// have run out of rows. Those blocks then take segments of that pass: the owner publishes
+// what the pass needs in its HelpSlot, owner and helpers claim segments with an atomic
+// counter, a helper converts a segment in place (global memory, L1 bypassed on both sides),
+// collects the segment's bin masses in its own shared memory and adds them into the owner's
+// table in global memory. The owner never depends on a helper turning up: it claims segments
+// itself until none are left and then waits, with a bound, for the ones still in other hands.
+// =============================================================================
+constexpr int HELP_MASS_WORDS = MASS_SETS * MASS_SET_WORDS + NBINS;    // the sets, then the bin counts
+constexpr int HELP_TABLE_WORDS = HELP_MASS_WORDS + 2 * NC;             // ... then a candidate buffer of NC keys
+constexpr int HELP_MIN_LIST = 24576;                                  // shorter lists are not worth publishing
+struct __align__(256) HelpSlot {
+    int open;            // 1 while segments can be claimed
+    int claim;           // next segment to hand out
+    int done;            // segments finished
+    int nunits;
+    float Z;
+    unsigned int tau_bits;
+    int mark_head;
+    int j0;
+    unsigned int tau0;
+    int count[NWARP];    // entries in each segment
+    int kind;            // 0: turn a segment into probabilities and bin masses; 1: collect one bin's entries
+    int bin;             // kind 1: the bin
+    int found;           // kind 1: entries the helpers have put into the owner's global candidate buffer
+};
+
+// One segment of a long list: exponentials to probabilities in place, and every entry's
+// contribution into `mt` (this block's shared memory). All threads; 16-byte accesses that
+// bypass L1 (the segment may have been written, or will be read, by another SM).
+__device__ __forceinline__ void convert_segment(Ctx &c, unsigned long long *ks, int m, float Z, unsigned int tau_bits,
+                                                bool mark_head, const MassTable &mt) {
+    auto one = [&](unsigned long long kk) -> unsigned long long {
+        unsigned int pb = __float_as_uint(__fdiv_rn(key_val(kk), Z));
+        if (mark_head && (unsigned int)(kk >> 32) >= tau_bits) pb = 0xFFFFFFFFu;  // the head took it in pass B
+        masses_add(mt, pb);
+        return ((unsigned long long)pb << 32) | (kk & 0xFFFFFFFFull);
+    };
+    ulonglong2 *k2 = reinterpret_cast<ulonglong2 *>(ks);
+    const int mp = m >> 1;
+    for (int i = c.tid; i < mp; i += 8 * NT) {
+        ulonglong2 k[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) k[q] = (i + q * NT < mp) ? __ldcg(k2 + i + q * NT) : make_ulonglong2(0ull, 0ull);
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+            if (i + q * NT < mp) { k[q].x = one(k[q].x); k[q].y = one(k[q].y); __stcg(k2 + i + q * NT, k[q]); }
+    }
+    if ((m & 1) && c.tid == 0) __stcg(ks + m - 1, one(__ldcg(ks + m - 1)));
+}
+
+// The owner's side: publish, work, wait, merge. Returns false if a helper did not report back
+// within the bound (the row is then failed; its list may be half converted).
+__device__ bool helped_convert(Ctx &c, const BatchArgs &a, unsigned long long *wl_seg, float Z, unsigned int tau_bits,
+                               bool mark_head, const MassTable &mt) {
+    Aux *A = c.A;
+    IN_SHARED(A);
+    HelpSlot *hs = a.help + blockIdx.x;
+    unsigned int *gt = a.help_tables + (size_t)blockIdx.x * HELP_TABLE_WORDS;
+    __syncthreads();
+    for (int i = c.tid; i < HELP_MASS_WORDS; i += NT) __stcg(gt + i, 0u);
+    if (c.tid < NWARP) hs->count[c.tid] = A->woff[c.tid + 1] - A->woff[c.tid];
+    if (c.tid == 0) {
+        hs->Z = Z; hs->tau_bits = tau_bits; hs->mark_head = mark_head ? 1 : 0; hs->j0 = mt.j0; hs->tau0 = mt.tau0;
+        hs->nunits = NWARP; hs->done = 0; hs->kind = 0;
+    }
+    __threadfence();
+    __syncthreads();
+    if (c.tid == 0) { atomicExch(&hs->claim, 0); __threadfence(); atomicExch(&hs->open, 1); }
+    for (;;) {
+        __syncthreads();
+        if (c.tid == 0) A->evt_thread = atomicAdd(&hs->claim, 1);
+        __syncthreads();
+        const int u = A->evt_thread;
+        if (u >= NWARP) break;
+        convert_segment(c, wl_seg + (size_t)u * (size_t)a.R, A->woff[u + 1] - A->woff[u], Z, tau_bits, mark_head, mt);
+        __threadfence();
+        __syncthreads();
+        if (c.tid == 0) atomicAdd(&hs->done, 1);
+    }
+    if (c.tid == 0) {
+        int ok = 0;
+        for (int spin = 0; spin < (1 << 22); spin++) {
+            if (atomicAdd(&hs->done, 0) >= NWARP) { ok = 1; break; }
+            __nanosleep(200);
+        }
+        atomicExch(&hs->open, 0);
+        A->evt_thread = ok;
+    }
+    __syncthreads();
+    const bool ok = A->evt_thread != 0;
+    __threadfence();
+    // what the helpers found: sums add, care bits and nothing else are or-ed
+    for (int i = c.tid; i < HELP_MASS_WORDS; i += NT) {
+        const unsigned int v = __ldcg(gt + i);
+        if (!v) continue;
+        if (i >= MASS_SETS * MASS_SET_WORDS) { mt.cnt[i - MASS_SETS * MASS_SET_WORDS] += v; continue; }
+        const int k = i / MASS_SET_WORDS, j = i - k * MASS_SET_WORDS;
+        unsigned int *set = mt.sets + k * MASS_SET_WORDS;
+        if (j >= 2 * NBINS) set[j] |= v; else set[j] += v;
+    }
+    __syncthreads();
+    return ok;
+}
+
+// The entries of one segment that lie in value bin `hb` (below tau0), handed to `sink`. All threads.
+template <class S>
+__device__ __forceinline__ void gather_segment(Ctx &c, const unsigned long long *ks, int m, unsigned int tau0, int hb, S sink) {
+    const ulonglong2 *k2 = reinterpret_cast<const ulonglong2 *>(ks);
+    const int mp = m >> 1;
+    auto one = [&](unsigned long long kk) {
+        const unsigned int pb = (unsigned int)(kk >> 32);
+        if (pb < tau0 && bk_bin(pb) == hb) sink(kk);
+    };
+    for (int i = c.tid; i < mp; i += 8 * NT) {
+        ulonglong2 k[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) k[q] = (i + q * NT < mp) ? __ldcg(k2 + i + q * NT) : make_ulonglong2(~0ull, ~0ull);
+#pragma unroll
+        for (int q = 0; q < 8; q++) { one(k[q].x); one(k[q].y); }
+    }
+    if ((m & 1) && c.tid == 0) one(__ldcg(ks + m - 1));
+}
+
+// The owner's side of a helped gather: the bin's entries end up in A->cand[0 .. A->ncand).
+__device__ bool helped_gather(Ctx &c, const BatchArgs &a, const unsigned long long *wl_seg, unsigned int tau0, int hb) {
+    Aux *A = c.A;
+    IN_SHARED(A);
+    HelpSlot *hs = a.help + blockIdx.x;
+    unsigned long long *gc = reinterpret_cast<unsigned long long *>(a.help_tables + (size_t)blockIdx.x * HELP_TABLE_WORDS + HELP_MASS_WORDS);
+    __syncthreads();
+    if (c.tid < NWARP) hs->count[c.tid] = A->woff[c.tid + 1] - A->woff[c.tid];
+    if (c.tid == 0) { hs->tau0 = tau0; hs->bin = hb; hs->kind = 1; hs->found = 0; hs->nunits = NWARP; hs->done = 0; A->ncand = 0; }
+    __threadfence();
+    __syncthreads();
+    if (c.tid == 0) { atomicExch(&hs->claim, 0); __threadfence(); atomicExch(&hs->open, 1); }
+    for (;;) {
+        __syncthreads();
+        if (c.tid == 0) A->evt_thread = atomicAdd(&hs->claim, 1);
+        __syncthreads();
+        const int u = A->evt_thread;
+        if (u >= NWARP) break;
+        gather_segment(c, wl_seg + (size_t)u * (size_t)a.R, A->woff[u + 1] - A->woff[u], tau0, hb, [&](unsigned long long kk) {
+            const int pos = satom_add(&A->ncand, 1);
+            if (pos < NC) A->cand[pos] = kk;
+        });
+        __syncthreads();
+        if (c.tid == 0) atomicAdd(&hs->done, 1);
+    }
+    if (c.tid == 0) {
+        int ok = 0;
+        for (int spin = 0; spin < (1 << 22); spin++) {
+            if (atomicAdd(&hs->done, 0) >= NWARP) { ok = 1; break; }
+            __nanosleep(100);
+        }
+        atomicExch(&hs->open, 0);
+        A->evt_thread = ok;
+    }
+    __syncthreads();
+    const bool ok = A->evt_thread != 0;
+    __threadfence();
+    const int ng = min(atomicAdd(&hs->found, 0), NC), n0 = A->ncand;
+    __syncthreads();
+    for (int i = c.tid; i < ng; i += NT)
+        if (n0 + i < NC) A->cand[n0 + i] = __ldcg(gc + i);
+    __syncthreads();
+    if (c.tid == 0) A->ncand = n0 + ng;
+    __syncthreads();
+    return ok;
+}
+
+// A block with no rows left: look for a published pass and take segments of it, until every
+// row of the launch is done.
+__device__ void help_others(Ctx &c, const BatchArgs &a) {
+    Aux *A = c.A;
+    IN_SHARED(A);
+    const int nslots = (int)gridDim.x;
+    MassTable mt;
+    mt.cnt = reinterpret_cast<unsigned int *>(A->hval);
+    mt.sets = reinterpret_cast<unsigned int *>(c.stage);
+    mt.j0 = 0; mt.tau0 = 0u; mt.Cm0 = mt.half0 = mt.big0 = 0.0f;
+    if (c.tid == 0) A->ncand = ((int)blockIdx.x + 1) % nslots;  // the slot the scan starts from (shared by the block)
+    for (int poll = 0; poll < (1 << 20); poll++) {
+        __syncthreads();
+        if (c.tid == 0) { A->evt_thread = 0x7fffffff; A->specbin = (*(volatile int *)a.rows_done >= a.B) ? 1 : 0; }
+        __syncthreads();
+        if (A->specbin) return;
+        const int next = A->ncand;
+        // every thread looks at one slot; the nearest open one after the slot served last is tried
+        for (int sidx = c.tid; sidx < nslots; sidx += NT) {
+            if (sidx == (int)blockIdx.x) continue;
+            const volatile HelpSlot *hs = a.help + sidx;
+            if (hs->open == 1 && hs->claim < NWARP) atomicMin(&A->evt_thread, (sidx - next + nslots) % nslots);
+        }
+        __syncthreads();
+        const int pick = A->evt_thread;
+        __syncthreads();
+        if (c.tid == 0) {
+            int found = -1, unit = 0;
+            if (pick != 0x7fffffff) {
+                const int sidx = (pick + next) % nslots;
+                unit = atomicAdd(&a.help[sidx].claim, 1);
+                if (unit < NWARP) { found = sidx; A->ncand = sidx; }
+            } else {
+                __nanosleep(500);
+            }
+            A->evt_thread = found; A->specbin = unit;
+        }
+        __syncthreads();
+        const int sidx = A->evt_thread, u = A->specbin;
+        if (sidx < 0) continue;
+        HelpSlot *hs = a.help + sidx;
+        __threadfence();
+        unsigned long long *seg = a.wlist + (size_t)sidx * 2 * NWARP * (size_t)a.R + (size_t)u * (size_t)a.R;
+        if (__ldcg(&hs->kind) == 1) {
+            unsigned long long *gc = reinterpret_cast<unsigned long long *>(a.help_tables + (size_t)sidx * HELP_TABLE_WORDS + HELP_MASS_WORDS);
+            gather_segment(c, seg, __ldcg(&hs->count[u]), __ldcg(&hs->tau0), __ldcg(&hs->bin), [&](unsigned long long kk) {
+                const int pos = atomicAdd(&hs->found, 1);
+                if (pos < NC) __stcg(gc + pos, kk);
+            });
+            __threadfence();
+            __syncthreads();
+            if (c.tid == 0) atomicAdd(&hs->done, 1);
+            continue;
+        }
+        const float Z = __ldcg(&hs->Z);
+        const unsigned int tau_bits = __ldcg(&hs->tau_bits);
+        const bool mark_head = __ldcg(&hs->mark_head) != 0;
+        const int m = __ldcg(&hs->count[u]);
+        masses_begin(c, mt, __ldcg(&hs->j0), __ldcg(&hs->tau0));
+        convert_segment(c, seg, m, Z, tau_bits, mark_head, mt);
+        __syncthreads();
+        unsigned int *gt = a.help_tables + (size_t)sidx * HELP_TABLE_WORDS;
+        for (int i = c.tid; i < HELP_MASS_WORDS; i += NT) {
+            unsigned int v;
+            if (i >= MASS_SETS * MASS_SET_WORDS) v = mt.cnt[i - MASS_SETS * MASS_SET_WORDS];
+            else v = mt.sets[i];
+            if (!v) continue;
+            const int j = i % MASS_SET_WORDS;
+            if (i < MASS_SETS * MASS_SET_WORDS && j >= 2 * NBINS) atomicOr(gt + i, v); else atomicAdd(gt + i, v);
+        }
+        __threadfence();
+        __syncthreads();
+        if (c.tid == 0) atomicAdd(&hs->done, 1);
+    }
+}
+
 // Returns false if it met something it leaves to the general walk (a running sum outside the
 // tables' binades, or a bin larger than the candidate buffer); `w` then holds the exact state
 // to continue from.
-__device__ bool descend_masses(Ctx &c, const LView &lv, const MassTable &mt, MassCk &ck, Walk &w, int &hi, float x_ge, float x_gt,
+__device__ bool descend_masses(Ctx &c, const BatchArgs &a, bool helped, const LView &lv, const MassTable &mt, MassCk &ck, Walk &w, int &hi, float x_ge, float x_gt,
                                long long nstop) {
     Aux *A = c.A;
     IN_SHARED(A);
@@ -1182,6 +1432,9 @@ __device__ bool descend_masses(Ctx &c, const LView &lv, const MassTable &mt, Mas
         if (c.tid == 0) A->ncand = 0;
         __syncthreads();
         const unsigned int tau0 = mt.tau0;
+        if (helped) {
+            if (!helped_gather(c, a, lv.seg, tau0, hb)) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
+        } else
         lv.for_each(c.tid, [&](int, unsigned long long key, unsigned long long *) {
             const unsigned int pb = (unsigned int)(key >> 32);
             if (pb < tau0 && bk_bin(pb) == hb) {
@@ -1200,175 +1453,6 @@ __device__ bool descend_masses(Ctx &c, const LView &lv, const MassTable &mt, Mas
         }
     }
     return false;
-}
-
-// =============================================================================
-// Help with long lists. The step is as long as its dearest row, and the dearest rows are the
-// ones whose list is most of the vocabulary; they are handed out first, so when they reach
-// the pass that turns their list into probabilities and bin masses, most other thread blocks
-// have run out of rows. Those blocks then take segments of that pass: the owner publishes
-// what the pass needs in its HelpSlot, owner and helpers claim segments with an atomic
-// counter, a helper converts a segment in place (global memory, L1 bypassed on both sides),
-// collects the segment's bin masses in its own shared memory and adds them into the owner's
-// table in global memory. The owner never depends on a helper turning up: it claims segments
-// itself until none are left and then waits, with a bound, for the ones still in other hands.
-// =============================================================================
-constexpr int HELP_TABLE_WORDS = MASS_SETS * MASS_SET_WORDS + NBINS;  // the sets, then the bin counts
-constexpr int HELP_MIN_LIST = 24576;                                  // shorter lists are not worth publishing
-struct __align__(256) HelpSlot {
-    int open;            // 1 while segments can be claimed
-    int claim;           // next segment to hand out
-    int done;            // segments finished
-    int nunits;
-    float Z;
-    unsigned int tau_bits;
-    int mark_head;
-    int j0;
-    unsigned int tau0;
-    int count[NWARP];    // entries in each segment
-};
-
-// One segment of a long list: exponentials to probabilities in place, and every entry's
-// contribution into `mt` (this block's shared memory). All threads; 16-byte accesses that
-// bypass L1 (the segment may have been written, or will be read, by another SM).
-__device__ __forceinline__ void convert_segment(Ctx &c, unsigned long long *ks, int m, float Z, unsigned int tau_bits,
-                                                bool mark_head, const MassTable &mt) {
-    auto one = [&](unsigned long long kk) -> unsigned long long {
-        unsigned int pb = __float_as_uint(__fdiv_rn(key_val(kk), Z));
-        if (mark_head && (unsigned int)(kk >> 32) >= tau_bits) pb = 0xFFFFFFFFu;  // the head took it in pass B
-        masses_add(mt, pb);
-        return ((unsigned long long)pb << 32) | (kk & 0xFFFFFFFFull);
-    };
-    ulonglong2 *k2 = reinterpret_cast<ulonglong2 *>(ks);
-    const int mp = m >> 1;
-    for (int i = c.tid; i < mp; i += 8 * NT) {
-        ulonglong2 k[8];
-#pragma unroll
-        for (int q = 0; q < 8; q++) k[q] = (i + q * NT < mp) ? __ldcg(k2 + i + q * NT) : make_ulonglong2(0ull, 0ull);
-#pragma unroll
-        for (int q = 0; q < 8; q++)
-            if (i + q * NT < mp) { k[q].x = one(k[q].x); k[q].y = one(k[q].y); __stcg(k2 + i + q * NT, k[q]); }
-    }
-    if ((m & 1) && c.tid == 0) __stcg(ks + m - 1, one(__ldcg(ks + m - 1)));
-}
-
-// The owner's side: publish, work, wait, merge. Returns false if a helper did not report back
-// within the bound (the row is then failed; its list may be half converted).
-__device__ bool helped_convert(Ctx &c, const BatchArgs &a, unsigned long long *wl_seg, float Z, unsigned int tau_bits,
-                               bool mark_head, const MassTable &mt) {
-    Aux *A = c.A;
-    IN_SHARED(A);
-    HelpSlot *hs = a.help + blockIdx.x;
-    unsigned int *gt = a.help_tables + (size_t)blockIdx.x * HELP_TABLE_WORDS;
-    __syncthreads();
-    for (int i = c.tid; i < HELP_TABLE_WORDS; i += NT) __stcg(gt + i, 0u);
-    if (c.tid < NWARP) hs->count[c.tid] = A->woff[c.tid + 1] - A->woff[c.tid];
-    if (c.tid == 0) {
-        hs->Z = Z; hs->tau_bits = tau_bits; hs->mark_head = mark_head ? 1 : 0; hs->j0 = mt.j0; hs->tau0 = mt.tau0;
-        hs->nunits = NWARP; hs->done = 0;
-    }
-    __threadfence();
-    __syncthreads();
-    if (c.tid == 0) { atomicExch(&hs->claim, 0); __threadfence(); atomicExch(&hs->open, 1); }
-    for (;;) {
-        __syncthreads();
-        if (c.tid == 0) A->evt_thread = atomicAdd(&hs->claim, 1);
-        __syncthreads();
-        const int u = A->evt_thread;
-        if (u >= NWARP) break;
-        convert_segment(c, wl_seg + (size_t)u * (size_t)a.R, A->woff[u + 1] - A->woff[u], Z, tau_bits, mark_head, mt);
-        __threadfence();
-        __syncthreads();
-        if (c.tid == 0) atomicAdd(&hs->done, 1);
-    }
-    if (c.tid == 0) {
-        int ok = 0;
-        for (int spin = 0; spin < (1 << 22); spin++) {
-            if (atomicAdd(&hs->done, 0) >= NWARP) { ok = 1; break; }
-            __nanosleep(200);
-        }
-        atomicExch(&hs->open, 0);
-        A->evt_thread = ok;
-    }
-    __syncthreads();
-    const bool ok = A->evt_thread != 0;
-    __threadfence();
-    // what the helpers found: sums add, care bits and nothing else are or-ed
-    for (int i = c.tid; i < HELP_TABLE_WORDS; i += NT) {
-        const unsigned int v = __ldcg(gt + i);
-        if (!v) continue;
-        if (i >= MASS_SETS * MASS_SET_WORDS) { mt.cnt[i - MASS_SETS * MASS_SET_WORDS] += v; continue; }
-        const int k = i / MASS_SET_WORDS, j = i - k * MASS_SET_WORDS;
-        unsigned int *set = mt.sets + k * MASS_SET_WORDS;
-        if (j >= 2 * NBINS) set[j] |= v; else set[j] += v;
-    }
-    __syncthreads();
-    return ok;
-}
-
-// A block with no rows left: look for a published pass and take segments of it, until every
-// row of the launch is done.
-__device__ void help_others(Ctx &c, const BatchArgs &a) {
-    Aux *A = c.A;
-    IN_SHARED(A);
-    const int nslots = (int)gridDim.x;
-    MassTable mt;
-    mt.cnt = reinterpret_cast<unsigned int *>(A->hval);
-    mt.sets = reinterpret_cast<unsigned int *>(c.stage);
-    mt.j0 = 0; mt.tau0 = 0u; mt.Cm0 = mt.half0 = mt.big0 = 0.0f;
-    if (c.tid == 0) A->ncand = ((int)blockIdx.x + 1) % nslots;  // the slot the scan starts from (shared by the block)
-    for (int poll = 0; poll < (1 << 20); poll++) {
-        __syncthreads();
-        if (c.tid == 0) { A->evt_thread = 0x7fffffff; A->specbin = (*(volatile int *)a.rows_done >= a.B) ? 1 : 0; }
-        __syncthreads();
-        if (A->specbin) return;
-        const int next = A->ncand;
-        // every thread looks at one slot; the nearest open one after the slot served last is tried
-        for (int sidx = c.tid; sidx < nslots; sidx += NT) {
-            if (sidx == (int)blockIdx.x) continue;
-            const volatile HelpSlot *hs = a.help + sidx;
-            if (hs->open == 1 && hs->claim < NWARP) atomicMin(&A->evt_thread, (sidx - next + nslots) % nslots);
-        }
-        __syncthreads();
-        const int pick = A->evt_thread;
-        __syncthreads();
-        if (c.tid == 0) {
-            int found = -1, unit = 0;
-            if (pick != 0x7fffffff) {
-                const int sidx = (pick + next) % nslots;
-                unit = atomicAdd(&a.help[sidx].claim, 1);
-                if (unit < NWARP) { found = sidx; A->ncand = sidx; }
-            } else {
-                __nanosleep(500);
-            }
-            A->evt_thread = found; A->specbin = unit;
-        }
-        __syncthreads();
-        const int sidx = A->evt_thread, u = A->specbin;
-        if (sidx < 0) continue;
-        HelpSlot *hs = a.help + sidx;
-        __threadfence();
-        const float Z = __ldcg(&hs->Z);
-        const unsigned int tau_bits = __ldcg(&hs->tau_bits);
-        const bool mark_head = __ldcg(&hs->mark_head) != 0;
-        const int m = __ldcg(&hs->count[u]);
-        masses_begin(c, mt, __ldcg(&hs->j0), __ldcg(&hs->tau0));
-        unsigned long long *seg = a.wlist + (size_t)sidx * 2 * NWARP * (size_t)a.R + (size_t)u * (size_t)a.R;
-        convert_segment(c, seg, m, Z, tau_bits, mark_head, mt);
-        __syncthreads();
-        unsigned int *gt = a.help_tables + (size_t)sidx * HELP_TABLE_WORDS;
-        for (int i = c.tid; i < HELP_TABLE_WORDS; i += NT) {
-            unsigned int v;
-            if (i >= MASS_SETS * MASS_SET_WORDS) v = mt.cnt[i - MASS_SETS * MASS_SET_WORDS];
-            else v = mt.sets[i];
-            if (!v) continue;
-            const int j = i % MASS_SET_WORDS;
-            if (i < MASS_SETS * MASS_SET_WORDS && j >= 2 * NBINS) atomicOr(gt + i, v); else atomicAdd(gt + i, v);
-        }
-        __threadfence();
-        __syncthreads();
-        if (c.tid == 0) atomicAdd(&hs->done, 1);
-    }
 }
 
 // =============================================================================
@@ -2146,7 +2230,8 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         mt.sets = reinterpret_cast<unsigned int *>(c.stage);  // idle while the list is a global view
                         const bool use_mt = (a.mode == 0) && !lv.flat && !list_is_p && head_s > 0.0f;
                         if (use_mt) { masses_begin(c, mt, fexpo(head_s), tau_head); mass_on = true; }
-                        if (use_mt && a.help && nl >= HELP_MIN_LIST && !(a.knobs & 8)) {
+                        const bool help_on = use_mt && a.help && nl >= HELP_MIN_LIST && !(a.knobs & 8);
+                        if (help_on) {
                             // a long list: blocks that have run out of rows take segments of this pass
                             if (!helped_convert(c, a, wl_seg, Z, tau_bits, mark_head, mt)) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
                             list_is_p = true;
@@ -2160,7 +2245,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         const bool limited = n_use < (long long)a.Vg;
                         {
                             int hi = NBINS;
-                            const bool done = use_mt && descend_masses(c, lv, mt, ck, cutw, hi, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_use : -1);
+                            const bool done = use_mt && descend_masses(c, a, help_on, lv, mt, ck, cutw, hi, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_use : -1);
                             if (!done) descend(c, lv, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_use : -1);
                         }
                         if (cutw.event != EV_DEGENERATE) {
@@ -2193,7 +2278,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                                     bool ddone = false;
                                     if (use_mt) {
                                         int hi = NBINS;
-                                        ddone = descend_masses(c, lv, mt, ck, dw, hi, 3.4e38f, target, -1);
+                                        ddone = descend_masses(c, a, help_on, lv, mt, ck, dw, hi, 3.4e38f, target, -1);
                                     }
                                     if (!ddone) descend(c, lv, dw, 3.4e38f, target, -1);
                                     if (dw.event == EV_DRAW) {
