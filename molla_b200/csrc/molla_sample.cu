@@ -181,6 +181,8 @@ struct Ctx {
     int rbeg, rlen, npieces;
     unsigned int parbits;
     int nphase;           // histogram phases run by the descending walks of this row (profiling aid)
+    int own_units, helped_passes;  // segments this block did itself in passes it shared / such passes (profiling aid)
+    long long t_help;     // cycles spent in the filtered passes shared with helpers (profiling aid)
     long long t_stage, t_build;  // cycles of the exact sum spent staging list blocks / building their tables (profiling aid)
 };
 
@@ -1194,6 +1196,7 @@ __device__ bool helped_convert(Ctx &c, const BatchArgs &a, unsigned long long *w
     }
     __threadfence();
     __syncthreads();
+    c.helped_passes++;
     if (c.tid == 0) { atomicExch(&hs->claim, 0); __threadfence(); atomicExch(&hs->open, 1); }
     for (;;) {
         __syncthreads();
@@ -1201,6 +1204,7 @@ __device__ bool helped_convert(Ctx &c, const BatchArgs &a, unsigned long long *w
         __syncthreads();
         const int u = A->evt_thread;
         if (u >= NWARP) break;
+        c.own_units++;
         convert_segment(c, wl_seg + (size_t)u * (size_t)a.R, A->woff[u + 1] - A->woff[u], Z, tau_bits, mark_head, mt);
         __threadfence();
         __syncthreads();
@@ -1261,6 +1265,7 @@ __device__ bool helped_gather(Ctx &c, const BatchArgs &a, const unsigned long lo
     if (c.tid == 0) { hs->tau0 = tau0; hs->bin = hb; hs->kind = 1; hs->found = 0; hs->nunits = NWARP; hs->done = 0; A->ncand = 0; }
     __threadfence();
     __syncthreads();
+    c.helped_passes++;
     if (c.tid == 0) { atomicExch(&hs->claim, 0); __threadfence(); atomicExch(&hs->open, 1); }
     for (;;) {
         __syncthreads();
@@ -1268,6 +1273,7 @@ __device__ bool helped_gather(Ctx &c, const BatchArgs &a, const unsigned long lo
         __syncthreads();
         const int u = A->evt_thread;
         if (u >= NWARP) break;
+        c.own_units++;
         gather_segment(c, wl_seg + (size_t)u * (size_t)a.R, A->woff[u + 1] - A->woff[u], tau0, hb, [&](unsigned long long kk) {
             const int pos = satom_add(&A->ncand, 1);
             if (pos < NC) A->cand[pos] = kk;
@@ -1330,7 +1336,7 @@ __device__ void help_others(Ctx &c, const BatchArgs &a) {
                 unit = atomicAdd(&a.help[sidx].claim, 1);
                 if (unit < NWARP) { found = sidx; A->ncand = sidx; }
             } else {
-                __nanosleep(500);
+                __nanosleep(100);
             }
             A->evt_thread = found; A->specbin = unit;
         }
@@ -1433,7 +1439,9 @@ __device__ bool descend_masses(Ctx &c, const BatchArgs &a, bool helped, const LV
         __syncthreads();
         const unsigned int tau0 = mt.tau0;
         if (helped) {
+            const long long tq0 = clock64();
             if (!helped_gather(c, a, lv.seg, tau0, hb)) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
+            c.t_help += clock64() - tq0;
         } else
         lv.for_each(c.tid, [&](int, unsigned long long key, unsigned long long *) {
             const unsigned int pb = (unsigned int)(key >> 32);
@@ -1650,7 +1658,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         const int r = A->cur_row;
         if (r >= a.B) break;
         had_row = true;
-        c.status = 0; c.last_read = false; c.nphase = 0; c.t_stage = 0; c.t_build = 0;
+        c.status = 0; c.last_read = false; c.nphase = 0; c.own_units = 0; c.helped_passes = 0; c.t_help = 0; c.t_stage = 0; c.t_build = 0;
         const int q = a.slot ? a.slot[r] : r;  // where this row's settings and state live
         const float T = a.temperature ? a.temperature[q] : 0.0f;
         const int k = a.top_k ? a.top_k[q] : 0;
@@ -1956,7 +1964,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 lb += A->u.s.pmax[c.warp][p];
                 tqc += clock64() - tq0;
             }
-            if (a.prof && c.tid == 32 * 5) a.prof[(long long)r * 16 + 13] = base;
+
             if (c.lane == 0) A->wcnt[c.warp] = base;
             } else if (c.tid < NWARP) {
                 // stage 3: the segments are the shards' lists, already in vocabulary order
@@ -2322,7 +2330,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
             a.prof[(long long)r * 16 + 11] = (long long)gt;
         }
-        if (a.prof && c.tid == 0) { a.prof[(long long)r * 16 + 8] = c.nphase; a.prof[(long long)r * 16 + 14] = c.t_stage; a.prof[(long long)r * 16 + 15] = c.t_build; }
+        if (a.prof && c.tid == 0) { a.prof[(long long)r * 16 + 13] = c.own_units * 100 + c.helped_passes; a.prof[(long long)r * 16 + 5] = c.t_help; a.prof[(long long)r * 16 + 8] = c.nphase; a.prof[(long long)r * 16 + 14] = c.t_stage; a.prof[(long long)r * 16 + 15] = c.t_build; }
         if (c.tid == 0) {
             a.tokens[r] = token;
             a.row_status[r] = c.status;
