@@ -2491,8 +2491,8 @@ size_t smem_bytes(int V) {
 
 int region_floats(int V) { return (((V + NWARP - 1) / NWARP) + 3) & ~3; }
 
-// scratch layout: [row counter, 256 bytes][per CTA: 16 per-warp list segments + one contiguous
-// copy, each entry an (exp bits, token id) pair]
+// scratch layout: [row counter and finished-rows counter, 256 bytes][row order][per CTA: 16 per-warp
+// list segments + one contiguous copy, each entry an (exp bits, token id) pair]
 constexpr size_t WS_HEADER = 256 + (size_t)ORDER_CAP * 4;
 // ... and behind the lists, for the ordinary entry points, one HelpSlot and one bin-mass table
 // per CTA
