@@ -208,9 +208,13 @@ __device__ __forceinline__ void block_argmax(Ctx &c, float &v, int &i) {
 // bitonic sort, descending, of n2 (power of two) keys in shared memory
 __device__ void bitonic_desc(unsigned long long *k, int n2, int tid) {
     IN_SHARED(k);
+    // A warp's 32 consecutive pair indices cover 64 consecutive keys whenever the stride is at
+    // most 16, the same 64 for every such stride: those stages only need the warp to agree.
+    bool local = false;  // the previous stage was such a stage
     for (int size = 2; size <= n2; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            __syncthreads();
+            if (local && stride <= 16) __syncwarp(); else __syncthreads();
+            local = stride <= 16 && !(size == 2);
             for (int i = tid; i < (n2 >> 1); i += NT) {
                 int pos = ((i / stride) * stride * 2) + (i % stride);
                 int par = pos + stride;
