@@ -290,6 +290,25 @@ def test_typical_p_against_the_oracle(dev, lib, oracle):
     assert np.all(got["row_status"] & np.uint32(capi.ROW_UNSUPPORTED)) and np.all(got["tokens"] == -1)
 
 
+def test_long_lists_shared_with_idle_blocks(dev, lib, oracle):
+    """Rows whose list is most of the vocabulary next to rows that finish at once: the blocks of the
+    latter take segments of the former's list passes. Results must not depend on who did what."""
+    B = 48
+    w = W.config3(seed=41, B=B, V=151936, H=32)
+    hot = np.arange(B) % 2 == 0
+    w["temperature"][hot] = np.float32(1.25) + np.float32(0.01) * np.arange(hot.sum(), dtype=np.float32)
+    w["top_k"][hot] = 0
+    w["top_p"][hot] = np.float32([0.8, 0.95, 0.99, 0.999] * (hot.sum() // 4))
+    w["temperature"][~hot] = 0.0     # greedy: done after one pass, then helping
+    r = compare(w, dev, oracle, "shared list passes", max_exception_frac=0.2)
+    assert r["rows"] == B
+    # the same rows twice in a row give the same answers (who helps whom differs from run to run)
+    a = run_gpu(w, dev)
+    b = run_gpu(w, dev)
+    assert np.array_equal(a["tokens"], b["tokens"]) and np.array_equal(a["row_status"], b["row_status"])
+    assert np.array_equal(a["diag"].view(np.uint32), b["diag"].view(np.uint32))
+
+
 # ---- the benchmark configurations -------------------------------------------------------------
 
 def test_config1(dev, lib, oracle):
