@@ -6,7 +6,8 @@
 // than the L2 holds, so HBM sees each logit once. In both passes every warp runs its
 // own pipeline: it owns a contiguous sixteenth of the row, fetches it piece by piece
 // with bulk asynchronous copies (TMA without a tensor map) into its own shared-memory
-// slots behind its own mbarriers, and never waits for another warp.
+// slots behind its own mbarriers, and never waits for another warp. Thread blocks that
+// run out of rows lend themselves to the blocks still working on a long list (HelpSlot).
 //
 // The reference (src/molla/engine/sample.mojo) defines its result through
 // *sequential* fp32 sums: the softmax denominator is accumulated in vocabulary
