@@ -272,7 +272,8 @@ def run_ours(args):
                 "value": world * B * e2e_steps / (e2e_ms / 1e3), "unit": "tokens/s",
                 "h2d_bytes_per_step": hb.h2d_bytes, "d2h_bytes_per_step": hb.d2h_bytes,
                 "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps},
-            "gpu_launches": args.steps,
+            # per step: sample_rows_kernel, and order_rows_kernel when there are more rows than thread blocks
+            "gpu_launches": args.steps * (2 if B > torch.cuda.get_device_properties(dev).multi_processor_count else 1),
             "clocks": clk,
         }
         if cpu is not None:
