@@ -190,7 +190,8 @@ struct Ctx {
 #define STAMP(i) do { if (a.prof && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
 
 // ---- block collectives (NT threads) ----------------------------------------------
-__device__ __forceinline__ void block_argmax(Ctx &c, float &v, int &i) {
+template <class CX>
+__device__ __forceinline__ void block_argmax(CX &c, float &v, int &i) {
     warp_argmax(v, i);
     __syncthreads();
     if (c.lane == 0) { c.A->wsf[c.warp] = v; c.A->wsi[c.warp] = i; }
@@ -475,24 +476,28 @@ __device__ __forceinline__ void p1_sim(V lst, int i0, int i1, bool locate, float
     w.s = s;
 }
 
+// this thread's estimate of the sum of its own L entries
 template <class V>
-__device__ void p1_build(Ctx &c, V lst, int n, int L, double sbase) {
-    Aux *A = c.A;
+__device__ __forceinline__ float p1_csum(V lst, int n, int L, int tid) {
+    const int i0 = min(n, tid * L), i1 = min(n, (tid + 1) * L);
+    // only an estimate is needed here: four partial sums shorten the dependency chain
+    float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;
+    int i = i0;
+    for (; i + 4 <= i1; i += 4) {
+        c0 = __fadd_rn(c0, lst(i)); c1 = __fadd_rn(c1, lst(i + 1)); c2 = __fadd_rn(c2, lst(i + 2)); c3 = __fadd_rn(c3, lst(i + 3));
+    }
+    for (; i < i1; i++) c0 = __fadd_rn(c0, lst(i));
+    return __fadd_rn(__fadd_rn(c0, c1), __fadd_rn(c2, c3));
+}
+
+// The tables for the walk, given every thread's estimate `csum` and the estimated sum `sst` of
+// everything before its entries.
+template <class CX, class V>
+__device__ void p1_tables(CX &c, V lst, int n, int L, float csum, double sst) {
+    auto *A = c.A;
     IN_SHARED(A);
     const float EPS = 1.0f / 4096.0f;
     const int i0 = min(n, c.tid * L), i1 = min(n, (c.tid + 1) * L);
-    float csum = 0.0f;
-    {   // only an estimate is needed here: four partial sums shorten the dependency chain
-        float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;
-        int i = i0;
-        for (; i + 4 <= i1; i += 4) {
-            c0 = __fadd_rn(c0, lst(i)); c1 = __fadd_rn(c1, lst(i + 1)); c2 = __fadd_rn(c2, lst(i + 2)); c3 = __fadd_rn(c3, lst(i + 3));
-        }
-        for (; i < i1; i++) c0 = __fadd_rn(c0, lst(i));
-        csum = __fadd_rn(__fadd_rn(c0, c1), __fadd_rn(c2, c3));
-    }
-    double tot;
-    const double sst = sbase + block_excl_scan<double>((double)csum, A->wsd, &tot);
     short ja = SUS;
     unsigned char dual = 0;
     float da = 0.0f, db = 0.0f;
@@ -547,10 +552,20 @@ __device__ void p1_build(Ctx &c, V lst, int n, int L, double sbase) {
     __syncthreads();
 }
 
+template <class CX, class V>
+__device__ void p1_build(CX &c, V lst, int n, int L, double sbase) {
+    auto *A = c.A;
+    IN_SHARED(A);
+    const float csum = p1_csum(lst, n, L, c.tid);
+    double tot;
+    const double sst = sbase + block_excl_scan<double>((double)csum, A->wsd, &tot);
+    p1_tables(c, lst, n, L, csum, sst);
+}
+
 // thread 0 only; continues from the state in `w`
-template <class V>
-__device__ void p1_walk(Ctx &c, V lst, int n, int L, bool locate, float target, Walker &w) {
-    Aux *A = c.A;
+template <class CX, class V>
+__device__ void p1_walk(CX &c, V lst, int n, int L, bool locate, float target, Walker &w) {
+    auto *A = c.A;
     IN_SHARED(A);
     const int nseg = A->nseg;
     const double *PA = A->u.p1.pa, *PB = A->u.p1.pb;
@@ -716,16 +731,19 @@ struct BinQuery {
     const unsigned int *hq, *hqh, *hc;  // per bin: integer mass (low MASS_SPLIT bits summed, the rest summed) and count
 };
 
-__device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
-    Aux *A = c.A;
+// `bin_load(b, q, n)` gives bin b's integer mass and count (one thread block's tables, or the
+// sum over the tables of a cluster's thread blocks).
+template <class CX, class LD>
+__device__ void find_event_bin_with(CX &c, const BinQuery &qy, LD bin_load) {
+    auto *A = c.A;
     IN_SHARED(A);
     unsigned long long q[BPT], n[BPT], sq = 0, sn = 0;
 #pragma unroll
     for (int i = 0; i < BPT; i++) {
         const int b = NBINS - 1 - BPT * c.tid - i;
         const bool live = b < qy.bin_hi;
-        q[i] = live ? ((unsigned long long)qy.hq[b] + ((unsigned long long)qy.hqh[b] << MASS_SPLIT)) : 0ull;
-        n[i] = live ? qy.hc[b] : 0u;
+        q[i] = 0ull; n[i] = 0ull;
+        if (live) bin_load(b, q[i], n[i]);
         sq += q[i]; sn += n[i];
     }
     unsigned long long tq, tc;
@@ -751,9 +769,18 @@ __device__ void find_event_bin(Ctx &c, const BinQuery &qy) {
     __syncthreads();
 }
 
+template <class CX>
+__device__ void find_event_bin(CX &c, const BinQuery &qy) {
+    find_event_bin_with(c, qy, [&](int b, unsigned long long &q, unsigned long long &n) {
+        q = (unsigned long long)qy.hq[b] + ((unsigned long long)qy.hqh[b] << MASS_SPLIT);
+        n = qy.hc[b];
+    });
+}
+
 // Sort the candidate list (descending probability, ascending token id).
-__device__ void sort_cands(Ctx &c, int n) {
-    Aux *A = c.A;
+template <class CX>
+__device__ void sort_cands(CX &c, int n) {
+    auto *A = c.A;
     IN_SHARED(A);
     int n2 = 2;
     while (n2 < n) n2 <<= 1;
@@ -771,9 +798,10 @@ __device__ void sort_cands(Ctx &c, int n) {
 // candidate that takes the sum across a power of two is added by itself and the scan resumes
 // behind it; a rounding tie or a candidate >= sum/4 sends the rest to one thread.
 // Results: A->b_event, b_s, b_pos, and for an event b_idx (token), b_p, b_aux (tie).
-__device__ void walk_sorted(Ctx &c, int nb, float s0, long long pos0, float x_ge, float x_gt, bool counting,
+template <class CX>
+__device__ void walk_sorted(CX &c, int nb, float s0, long long pos0, float x_ge, float x_gt, bool counting,
                             long long nstop) {
-    Aux *A = c.A;
+    auto *A = c.A;
     IN_SHARED(A);
     constexpr int EPT = NC / NT;
     __syncthreads();
@@ -1476,8 +1504,9 @@ __device__ bool descend_masses(Ctx &c, const BatchArgs &a, bool helped, const LV
 // that prefix in that order. The sums run on one thread (m is at most the head's 1024).
 // Results: A->b_idx (token), b_p, b_sum, b_target, b_aux (tie bits).
 // =============================================================================
-__device__ void typical_head(Ctx &c, int m, float typ, float u01) {
-    Aux *A = c.A;
+template <class CX>
+__device__ void typical_head(CX &c, int m, float typ, float u01) {
+    auto *A = c.A;
     IN_SHARED(A);
     float *lg = reinterpret_cast<float *>(A->cand);             // log p
     float *tt = lg + HEADC;                                     // p * log p
