@@ -1,0 +1,959 @@
+// The row kernel of the ordinary entry points: one logit row per thread-block cluster.
+//
+// A row of up to 8 x 38400 logits is split into contiguous column ranges, one per thread block
+// of the cluster, and every block keeps its range in shared memory from the moment the bulk
+// copies (TMA without a tensor map, never multicast) land until the row's token is known. HBM
+// sees every logit once and no pass after the first touches global memory: bias and penalties
+// are written into the resident range, the maximum is taken from it, the exponentials replace
+// the logits in place (what cannot matter to any sum becomes zero, which adds nothing to a
+// sequential fp32 sum), and the exact softmax denominator, the sorted head and the walks past
+// it all read shared memory. The range's position is the token id, so nothing carries indices.
+//
+// What the blocks of a cluster have to tell each other (the range maxima, a lower bound of the
+// running sum before each range, the threads' maxima for the head threshold, the estimated
+// range sums, the exact running sum handed from range to range, the head's candidates, the
+// bin tables of a walk) goes through distributed shared memory between cluster barriers. All
+// blocks of a cluster take the same branches: every decision is made from values all of them
+// hold.
+//
+// This file is included by molla_sample.cu inside its unnamed namespace and uses the device
+// functions defined there (the exact sum, the bin search, the sorted walk, typical-p).
+#pragma once
+
+constexpr int CL_MAX_G = 8;                  // thread blocks per cluster at most (the portable limit)
+constexpr int CL_LMAX = 75;                  // logits per thread at most (odd: conflict-free strides)
+constexpr int CL_CAPF = NT * CL_LMAX;        // logits per thread block at most: 38400 (150 KB)
+constexpr int XT = HEAD_NEED;                // thread maxima every block shows the others
+constexpr int CL_PIECE = 4096;               // floats per bulk copy
+
+#define CSTAMP(i) do { if (a.prof && leader && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
+
+struct __align__(16) AuxC {
+    union {
+        struct {
+            double pa[NT + 1];
+            double pb[NT + 1];
+            float csum[NT];
+            short ja[NT];
+            unsigned char dual[NT];
+            unsigned short seg[NT];
+        } p1;
+        struct {
+            unsigned int hq[NBINS];
+            unsigned int hqh[NBINS];
+            unsigned int hc[NBINS];
+        } h;
+    } u;
+    unsigned long long cand[NC];   // first the hash of the patched tokens, then the head / a bin's candidates
+    float pc[NC];
+    float pre[HEADC];
+    unsigned int hidx[HEADC];
+    double wsd[2 * (NWARP + 1)];
+    unsigned long long wsu[NWARP + 1];
+    float wsf[NWARP + 1];
+    int wsi[NWARP + 1];
+    int nseg, ncand, evt_thread, specbin, hit_bin;
+    unsigned long long hit_qbefore, hit_cbefore, tot_q, tot_c;
+    float walk_s; int walk_found, walk_idx, walk_slow;
+    float b_s; unsigned int b_tau; int b_event; int b_idx; float b_p; long long b_pos; int b_aux;
+    float b_sum; float b_target;
+    uint64_t mbar;
+    float thr[NT];                       // per thread range: the threshold of the second pass
+    unsigned short ppos[NWARP][128];     // per warp: positions of the kept elements of a 128-element block
+    // what the blocks of the cluster write into each other (slot = the writer's rank)
+    float x1_max[CL_MAX_G]; int x1_idx[CL_MAX_G]; int x1_eq[CL_MAX_G]; unsigned int x1_status[CL_MAX_G];
+    float x2_total[CL_MAX_G]; float x2_top[CL_MAX_G][XT];
+    double x3_tot[CL_MAX_G]; int x3_n[CL_MAX_G];
+    int x4_n[CL_MAX_G]; unsigned long long x5_key[CL_MAX_G];
+    float ch_s; int ch_found, ch_at, ch_slow;   // the exact sum on its way from range to range
+    int r_kind; int r_idx; float r_s; long long r_pos; unsigned int r_status;  // the leader's word after the head
+};
+
+struct CtxC {
+    int tid, lane, warp;
+    AuxC *A;
+    unsigned int status;
+};
+
+struct ClWalk {
+    float s; long long pos; unsigned int tau;
+    int event; int idx; float p; int tie;
+};
+
+struct ClGeo {          // where this thread block stands
+    int G, rank, c0, nloc, L;
+};
+
+// The exact sequential fp32 sum of the cluster's row (values `bits`, zero = absent), in vocabulary
+// order: every block builds the tables of its range from an estimate of the sum before it, then
+// the exact running sum travels from range to range. With `locate`, stops at the first entry
+// whose running sum exceeds `target`; its token id is returned in `at`.
+struct ClSum { float s; int found; int at; int slow; };
+
+__device__ ClSum cluster_exact_sum(cg::cluster_group &cl, CtxC &c, const ClGeo &g, const unsigned int *bits,
+                                   bool locate, float target, long long *stamps = nullptr) {
+    AuxC *A = c.A;
+    IN_SHARED(A);
+    IN_SHARED(bits);
+    ValBits vals{bits};
+    __syncthreads();
+    const float csum = p1_csum(vals, g.nloc, g.L, c.tid);
+    double tot;
+    const double ex = block_excl_scan<double>((double)csum, A->wsd, &tot);
+    if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x3_tot[g.rank] = tot;
+    cl.sync();
+    double sbase = 0.0;
+    for (int h = 0; h < g.rank; h++) sbase += A->x3_tot[h];
+    if (stamps && c.tid == 0) stamps[0] = clock64();
+    p1_tables(c, vals, g.nloc, g.L, csum, sbase + ex);
+    if (stamps && c.tid == 0) stamps[1] = clock64();
+    for (int q = 0; q < g.G; q++) {
+        if (g.rank == q && c.tid == 0) {
+            Walker w;
+            if (q == 0) { w.s = 0.0f; w.found = 0; w.at = -1; w.slow = 0; }
+            else { w.s = A->ch_s; w.found = A->ch_found; w.at = A->ch_at; w.slow = A->ch_slow; }
+            if (!(locate && w.found)) {
+                p1_walk(c, vals, g.nloc, g.L, locate, target, w);
+                if (w.found) w.at += g.c0;
+            }
+            if (q + 1 < g.G) {
+                AuxC *nx = cl.map_shared_rank(A, q + 1);
+                nx->ch_s = w.s; nx->ch_found = w.found; nx->ch_at = w.at; nx->ch_slow = w.slow;
+            } else {
+                for (int o = 0; o < g.G; o++) {
+                    AuxC *ox = cl.map_shared_rank(A, o);
+                    ox->ch_s = w.s; ox->ch_found = w.found; ox->ch_at = w.at; ox->ch_slow = w.slow;
+                }
+            }
+        }
+        cl.sync();
+    }
+    ClSum out;
+    out.s = A->ch_s; out.found = A->ch_found; out.at = A->ch_at; out.slow = A->ch_slow;
+    return out;
+}
+
+// Token id of the (nth+1)-th entry, in vocabulary order, whose bits equal `eb` (eb below tau).
+__device__ int cluster_nth_equal(cg::cluster_group &cl, CtxC &c, const ClGeo &g, const unsigned int *bits,
+                                 unsigned int eb, int nth) {
+    AuxC *A = c.A;
+    IN_SHARED(A);
+    IN_SHARED(bits);
+    const int i0 = min(g.nloc, c.tid * g.L), i1 = min(g.nloc, (c.tid + 1) * g.L);
+    int cnt = 0;
+    for (int i = i0; i < i1; i++) cnt += (bits[i] == eb) ? 1 : 0;
+    int tot;
+    const int ex = block_excl_scan<int>(cnt, A->wsi, &tot);
+    if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x4_n[g.rank] = tot;
+    if (c.tid == 0) A->r_idx = -1;
+    cl.sync();
+    int base = 0;
+    for (int h = 0; h < g.rank; h++) base += A->x4_n[h];
+    if (nth >= base + ex && nth < base + ex + cnt) {
+        int seen = base + ex;
+        for (int i = i0; i < i1; i++) {
+            if (bits[i] == eb) {
+                if (seen == nth) {
+                    for (int o = 0; o < g.G; o++) cl.map_shared_rank(A, o)->r_idx = g.c0 + i;
+                    break;
+                }
+                seen++;
+            }
+        }
+    }
+    cl.sync();
+    return A->r_idx;
+}
+
+// The descending walk past the sorted head (sample.mojo:492-506 and :580-590) over the cluster's
+// row of probabilities. State as in `descend`: exact running sum, elements consumed, and tau:
+// everything with probability bits >= tau is consumed. Every phase histograms what remains by
+// value bin (each block its range; the tables are added up across the cluster as they are
+// read), consumes whole bins up to the first one holding an event, gathers that bin into the
+// leader's candidate buffer, and the leader sorts it and adds it element by element.
+__device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, const unsigned int *bits,
+                                ClWalk &w, float x_ge, float x_gt, long long nstop) {
+    AuxC *A = c.A;
+    IN_SHARED(A);
+    IN_SHARED(bits);
+    AuxC *lead = cl.map_shared_rank(A, 0);
+    const bool counting = nstop >= 0;
+    int lvl = 1;
+    unsigned int lo = 0u;
+    int shift = BIN_SHIFT;
+    for (int phase = 0; phase < 8192; phase++) {
+        cl.sync();  // nobody still reads the tables or the leader's results of the phase before
+        for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0u; A->u.h.hqh[i] = 0u; A->u.h.hc[i] = 0u; }
+        if (c.tid == 0) { A->specbin = -1; A->ncand = 0; }
+        __syncthreads();
+        const bool have_s = w.s > 0.0f;
+        const int j = have_s ? fexpo(w.s) : 0;
+        const bool binade_ok = have_s && j >= -100 && j <= 100;
+        const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1);
+        const float inv_u = fpow2(23 - j);
+        for (int i = c.tid; i < g.nloc; i += NT) {
+            const unsigned int eb = bits[i];
+            if (eb == 0u || eb >= w.tau || eb < lo) continue;
+            const int bin = (int)((eb - lo) >> shift);
+            if (!binade_ok) { sred_add(&A->u.h.hc[bin], 1u); continue; }
+            const float p = __uint_as_float(eb);
+            const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
+            const float rr = __fsub_rn(p, q);
+            if (fabsf(rr) == halfu || p >= bigthr) {
+                sred_max(&A->specbin, bin);
+                if (counting) sred_add(&A->u.h.hc[bin], 1u);
+                continue;
+            }
+            const unsigned int qu = __float2uint_rn(__fmul_rn(q, inv_u));
+            if (qu) {
+                sred_add(&A->u.h.hq[bin], qu & MASS_LO_MASK);
+                if (qu >> MASS_SPLIT) sred_add(&A->u.h.hqh[bin], qu >> MASS_SPLIT);
+            }
+            if (counting) sred_add(&A->u.h.hc[bin], 1u);
+        }
+        cl.sync();
+        int specbin = -1;
+        for (int o = 0; o < g.G; o++) specbin = max(specbin, cl.map_shared_rank(A, o)->specbin);
+        BinQuery qy;
+        qy.specbin = specbin; qy.bin_hi = NBINS; qy.spec_bits = nullptr;
+        qy.hq = nullptr; qy.hqh = nullptr; qy.hc = nullptr;
+        qy.pos0 = (unsigned long long)w.pos;
+        qy.nstop = counting ? (unsigned long long)nstop : ~0ull;
+        qy.m0 = 0; qy.xq = ~0ull;
+        if (binade_ok) {
+            qy.m0 = (unsigned long long)((double)w.s * (double)inv_u);
+            unsigned long long xq = 1ull << 24;  // leaving the binade
+            if (x_ge < 3.0e38f) {
+                double t = ceil((double)x_ge * (double)inv_u);
+                if (t < (double)xq) xq = (t <= 0.0) ? 0ull : (unsigned long long)t;
+            }
+            if (x_gt < 3.0e38f) {
+                double t = floor((double)x_gt * (double)inv_u) + 1.0;
+                if (t < (double)xq) xq = (t <= 0.0) ? 0ull : (unsigned long long)t;
+            }
+            qy.xq = xq;
+        } else {
+            qy.pos0 = 0; qy.nstop = 1;  // nothing consumed yet: take the highest non-empty bin
+        }
+        find_event_bin_with(c, qy, [&](int b, unsigned long long &q, unsigned long long &n) {
+            unsigned long long ql = 0, qh = 0, nn = 0;
+            for (int o = 0; o < g.G; o++) {
+                const AuxC *ox = cl.map_shared_rank(A, o);
+                ql += ox->u.h.hq[b]; qh += ox->u.h.hqh[b]; nn += ox->u.h.hc[b];
+            }
+            q = ql + (qh << MASS_SPLIT); n = nn;
+        });
+        const int hb = A->hit_bin;
+        if (hb < 0) {
+            // nothing left in this range triggers an event: consume it whole
+            if (binade_ok) w.s = (float)((double)(qy.m0 + A->tot_q) * (double)fpow2(j - 23));
+            w.pos += (long long)A->tot_c;
+            if (lvl == 1) { w.tau = 0; w.event = EV_EXHAUSTED; cl.sync(); return; }
+            w.tau = lo; lvl = 1; lo = 0u; shift = BIN_SHIFT;  // back to the coarse bins below this range
+            continue;
+        }
+        const unsigned long long qb = A->hit_qbefore, cb = A->hit_cbefore;
+        const unsigned int blo = lo + ((unsigned int)hb << shift);
+        const unsigned long long bhi64 = (unsigned long long)lo + ((unsigned long long)(hb + 1) << shift);
+        const unsigned int bhi = bhi64 > 0xFFFFFFFFull ? 0xFFFFFFFFu : (unsigned int)bhi64;
+        // the bin's entries go to the leader (everybody has read the leader's counter of the phase
+        // before by now: it was cleared ahead of the barrier above)
+        for (int i = c.tid; i < g.nloc; i += NT) {
+            const unsigned int eb = bits[i];
+            if (eb != 0u && eb < w.tau && eb >= blo && eb < bhi) {
+                const int pos = atomicAdd(&lead->ncand, 1);
+                if (pos < NC) lead->cand[pos] = make_key(eb, g.c0 + i);
+            }
+        }
+        cl.sync();
+        const int nb = lead->ncand;
+        // what lies above the bin is consumed without an event either way
+        const float s_bin = binade_ok ? (float)((double)(qy.m0 + qb) * (double)fpow2(j - 23)) : w.s;
+        const long long pos_bin = w.pos + ((counting || !binade_ok) ? (long long)cb : 0);
+        if (nb > NC && lvl < 3) {
+            w.s = s_bin; w.pos = pos_bin;
+            w.tau = bhi < w.tau ? bhi : w.tau;
+            lo = blo; shift = (lvl == 1) ? 8 : 0; lvl++;
+            c.status |= MOLLA_ROW_SLOW_PATH;
+            continue;
+        }
+        if (nb > NC) {
+            // one value, more copies than the buffer holds: add them one at a time (the leader's
+            // thread 0), then find which copy, in token order, the event fell on
+            c.status |= MOLLA_ROW_SLOW_PATH;
+            const float pv = __uint_as_float(blo);
+            if (g.rank == 0 && c.tid == 0) {
+                float s = s_bin;
+                long long pos = pos_bin;
+                int ev = EV_NONE, at = -1;
+                for (int i = 0; i < nb; i++) {
+                    s = __fadd_rn(s, pv);
+                    pos++;
+                    if (s >= x_ge) ev = EV_CUT;
+                    else if (x_gt < s) ev = EV_DRAW;
+                    else if (counting && pos >= nstop) ev = EV_LIMIT;
+                    if (ev != EV_NONE) { at = i; break; }
+                }
+                A->b_event = ev; A->b_s = s; A->b_pos = pos; A->b_aux = at;
+            }
+            cl.sync();
+            const int ev = lead->b_event, at = lead->b_aux;
+            w.s = lead->b_s; w.pos = lead->b_pos;
+            if (ev != EV_NONE) {
+                const int id = cluster_nth_equal(cl, c, g, bits, blo, at);
+                w.event = ev; w.idx = id; w.p = pv; w.tie = 1;
+                return;
+            }
+            w.tau = blo;
+            continue;
+        }
+        if (g.rank == 0) {
+            sort_cands(c, nb);
+            walk_sorted(c, nb, s_bin, pos_bin, x_ge, x_gt, counting, nstop);
+        }
+        cl.sync();
+        w.s = lead->b_s; w.pos = lead->b_pos; w.tau = blo;
+        const int ev = lead->b_event;
+        if (ev != EV_NONE) {
+            w.event = ev; w.idx = lead->b_idx; w.p = lead->b_p; w.tie = lead->b_aux;
+            cl.sync();  // the leader's results are read before anyone moves on
+            return;
+        }
+        if (phase > 8) c.status |= MOLLA_ROW_SLOW_PATH;
+    }
+    w.event = EV_DEGENERATE;
+    c.status |= MOLLA_ROW_DEGENERATE;
+}
+
+__global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid_constant__ BatchArgs a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    cg::cluster_group cl = cg::this_cluster();
+    CtxC c;
+    c.tid = threadIdx.x; c.lane = c.tid & 31; c.warp = c.tid >> 5; c.status = 0;
+    float *rowbuf = reinterpret_cast<float *>(smem_raw);
+    unsigned int *rowbits = reinterpret_cast<unsigned int *>(smem_raw);
+    AuxC *A = reinterpret_cast<AuxC *>(smem_raw + (size_t)CL_CAPF * 4);
+    c.A = A;
+    IN_SHARED(A);
+    IN_SHARED(rowbuf);
+    IN_SHARED(rowbits);
+    ClGeo g;
+    g.G = a.G; g.rank = (int)cl.block_rank(); g.L = a.L;
+    g.c0 = g.rank * a.Vc;
+    g.nloc = max(0, min(a.Vc, a.V - g.c0));
+    const int row_i = (int)blockIdx.x / g.G;
+    const int r = a.order ? a.order[row_i] : row_i;
+    const bool leader = g.rank == 0;
+    AuxC *lead = cl.map_shared_rank(A, 0);
+
+    // ---- settings (the same in every block of the cluster)
+    const int q = a.slot ? a.slot[r] : r;
+    const long long lrow = a.rows ? (long long)a.rows[r] : (long long)r;
+    const bool idx_ok = (!a.slot || (q >= 0 && (a.n_slots <= 0 || q < a.n_slots))) &&
+                        (!a.rows || (lrow >= 0 && (a.n_logit_rows <= 0 || lrow < a.n_logit_rows)));
+    if (!idx_ok) {  // a stale row or slot index: nothing of that row or slot is touched
+        if (leader && c.tid == 0) { a.tokens[r] = -1; a.row_status[r] = MOLLA_ROW_INVALID_CONFIG; }
+        return;
+    }
+    const float T = a.temperature ? a.temperature[q] : 0.0f;
+    const int k = a.top_k ? a.top_k[q] : 0;
+    const float P = a.top_p ? a.top_p[q] : 1.0f;
+    const float minp = a.min_p ? a.min_p[q] : 0.0f;
+    const float typ = a.typical_p ? a.typical_p[q] : 1.0f;
+    const float rp = a.repeat_penalty ? a.repeat_penalty[q] : 1.0f;
+    const float fp = a.frequency_penalty ? a.frequency_penalty[q] : 0.0f;
+    const float pp = a.presence_penalty ? a.presence_penalty[q] : 0.0f;
+    const int ring_n = a.ring ? min(max(a.ring_len[q], 0), a.ring_cap) : 0;
+    const bool won = a.ring ? (ring_n > 0) : (a.window_on ? (a.window_on[q] != 0) : true);
+    const int h0 = (a.hist && a.hist_off) ? a.hist_off[q] : 0;
+    const long long *histp = a.ring ? a.ring + (size_t)q * (size_t)a.ring_cap : (a.hist ? a.hist + h0 : nullptr);
+    const int H = a.ring ? min(max(a.ring_filled[q], 0), ring_n) : ((a.hist && a.hist_off) ? (a.hist_off[q + 1] - h0) : 0);
+    const int b0 = (a.bias_ids && a.bias_off) ? a.bias_off[q] : 0;
+    const int nb = (a.bias_ids && a.bias_off) ? (a.bias_off[q + 1] - b0) : 0;
+    // the rules of SamplerConfig.check (sample.mojo:140-154); NaN fails every test
+    const bool valid = (T >= 0.0f) && (k >= 0) && (P > 0.0f && P <= 1.0f) && (minp >= 0.0f && minp <= 1.0f) &&
+                       (typ > 0.0f && typ <= 1.0f) && (rp > 0.0f) && H >= 0 && nb >= 0;
+    const bool greedy = !(T > 0.0f);
+    const bool penalizing = won && H > 0 && (rp != 1.0f || fp != 0.0f || pp != 0.0f);
+    const int npatch = (penalizing ? H : 0) + nb;
+    if (!valid) c.status |= MOLLA_ROW_INVALID_CONFIG;
+    // typical-p is done on rows an earlier filter sorted and cut to a set inside the sorted head
+    else if (!greedy && typ < 1.0f && !((k > 0 && k < a.V) || P < 1.0f)) c.status |= MOLLA_ROW_UNSUPPORTED;
+    if (npatch > PATCH_MAX) c.status |= MOLLA_ROW_UNSUPPORTED;
+
+    float dZ = 0.0f, dsum = 0.0f, dtarget = 0.0f, dp = 0.0f;
+    int token = -1;
+    // the end of every row: the leader's thread 0 writes the answer and does `_took`
+    auto finish = [&]() {
+        if (!(leader && c.tid == 0)) return;
+        if (a.prof) {
+            unsigned long long gt;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+            a.prof[(long long)r * 16 + 11] = (long long)gt; a.prof[(long long)r * 16 + 9] = clock64();
+        }
+        if (c.status & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG | MOLLA_ROW_UNSUPPORTED)) token = -1;
+        a.tokens[r] = token;
+        a.row_status[r] = c.status;
+        if (a.ring && token >= 0) {  // `_took` (sample.mojo:361-363): observe, then one more draw used
+            if (ring_n > 0) {        // `observe` (:246-258)
+                const int hd = a.ring_head[q];
+                const int at = (hd >= 0 && hd < ring_n) ? hd : 0;
+                a.ring[(size_t)q * (size_t)a.ring_cap + at] = (long long)token;
+                a.ring_head[q] = (at + 1) % ring_n;
+                const int f = a.ring_filled[q];
+                a.ring_filled[q] = f < ring_n ? f + 1 : ring_n;
+            }
+            a.drawn_rw[q] += 1ull;
+            if (a.stopped) a.stopped[r] = (a.stop_token && a.stop_token[q] == (long long)token) ? 1 : 0;
+        }
+        if (a.diag) { a.diag[4 * r] = dZ; a.diag[4 * r + 1] = dsum; a.diag[4 * r + 2] = dtarget; a.diag[4 * r + 3] = dp; }
+    };
+    if (c.status) { finish(); return; }
+
+    CSTAMP(0);
+    if (a.prof && leader && c.tid == 0) {
+        unsigned long long gt;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+        a.prof[(long long)r * 16 + 10] = (long long)gt; a.prof[(long long)r * 16 + 12] = blockIdx.x;
+    }
+    // ---- 1. this block's range of the row, HBM -> shared memory
+    const float *src = a.logits + lrow * a.row_stride + g.c0;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
+    const int nbulk = aligned ? (g.nloc & ~3) : 0;
+    if (c.tid == 0) {
+        mbar_init(&A->mbar, 1);
+        fence_proxy_async();
+        if (nbulk > 0) {
+            mbar_expect_tx(&A->mbar, (uint32_t)nbulk * 4u);
+            for (int o = 0; o < nbulk; o += CL_PIECE)
+                bulk_g2s_last_use(rowbuf + o, src + o, (uint32_t)min(CL_PIECE, nbulk - o) * 4u, &A->mbar);
+        }
+    }
+    // meanwhile: the tokens a bias or a penalty touches (sample.mojo:381-417), those of this range.
+    // A small hash (keys and window counts) in the space the candidates use later.
+    int *hkey = reinterpret_cast<int *>(A->cand);
+    int *hcnt = hkey + HSLOTS;
+    if (npatch > 0) {
+        for (int i = c.tid; i < HSLOTS; i += NT) { hkey[i] = -1; hcnt[i] = 0; }
+        __syncthreads();
+        for (int i = c.tid; i < npatch; i += NT) {
+            const bool is_bias = i < nb;
+            const long long t64 = (is_bias ? a.bias_ids[b0 + i] : histp[i - nb]) - (long long)g.c0;
+            if (t64 < 0 || t64 >= g.nloc) continue;
+            const int tok = (int)t64;
+            int s = hslot(tok);
+            for (int probe = 0; probe < HSLOTS; probe++) {
+                const int old = atomicCAS(&hkey[s], -1, tok);
+                if (old == -1 || old == tok) { if (!is_bias) atomicAdd(&hcnt[s], 1); break; }
+                s = (s + 1) & (HSLOTS - 1);
+            }
+        }
+    }
+    // what the bulk copies do not bring: the ragged end, or all of a row that is not 16-byte aligned
+    for (int i = nbulk + c.tid; i < g.nloc; i += NT) rowbuf[i] = __ldg(src + i);
+    for (int i = g.nloc + c.tid; i < NT * g.L; i += NT) rowbuf[i] = -INFINITY;
+    __syncthreads();  // the barrier is initialised before anyone waits on it
+    if (nbulk > 0) {
+        bool done = false;
+        for (int spin = 0; spin < (1 << 22); spin++) {
+            if (mbar_try_wait(&A->mbar, 0u)) { done = true; break; }
+        }
+        if (!done) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
+    }
+    if (__syncthreads_or((c.status & MOLLA_ROW_LOAD_TIMEOUT) ? 1 : 0)) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
+    CSTAMP(1);
+    if (a.softcap > 0.0f) {
+        for (int i = c.tid; i < g.nloc; i += NT) rowbuf[i] = softcap_pinned(rowbuf[i], a.softcap);
+        __syncthreads();
+    }
+    if (npatch > 0) {
+        for (int s = c.tid; s < HSLOTS; s += NT) {
+            const int tok = hkey[s];
+            if (tok < 0) continue;
+            float v = rowbuf[tok];
+            for (int bq = 0; bq < nb; bq++)  // duplicates add up, in the order they were given
+                if (a.bias_ids[b0 + bq] == (long long)tok + g.c0) v = __fadd_rn(v, a.bias_vals[b0 + bq]);
+            const int n = hcnt[s];
+            if (n > 0) {
+                if (v > 0.0f) v = __fdiv_rn(v, rp);
+                else v = __fmul_rn(v, rp);
+                v = __fsub_rn(v, __fmul_rn((float)n, fp));
+                v = __fsub_rn(v, pp);
+            }
+            rowbuf[tok] = v;
+        }
+        __syncthreads();
+    }
+
+    CSTAMP(2);
+    // ---- 2. the maximum and its first index (kernel.mojo:571-585, sample.mojo:342-346)
+    const int i0 = c.tid * g.L;
+    float tmax = -INFINITY;
+    {
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+        int j = 0;
+        for (; j + 4 <= g.L; j += 4) {
+            m0 = fmaxf(m0, rowbuf[i0 + j]); m1 = fmaxf(m1, rowbuf[i0 + j + 1]);
+            m2 = fmaxf(m2, rowbuf[i0 + j + 2]); m3 = fmaxf(m3, rowbuf[i0 + j + 3]);
+        }
+        for (; j < g.L; j++) m0 = fmaxf(m0, rowbuf[i0 + j]);
+        tmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+    }
+    float cmax;
+    {
+        const float wm = warp_max(tmax);
+        if (c.lane == 0) A->wsf[c.warp] = wm;
+        __syncthreads();
+        cmax = A->wsf[0];
+        for (int w = 1; w < NWARP; w++) cmax = fmaxf(cmax, A->wsf[w]);
+        __syncthreads();
+    }
+    int tfirst = 0x7fffffff, teq = 0;
+    if (tmax == cmax) {
+        for (int j = 0; j < g.L; j++)
+            if (i0 + j < g.nloc && rowbuf[i0 + j] == cmax) { if (tfirst == 0x7fffffff) tfirst = g.c0 + i0 + j; teq++; }
+    }
+    {
+        int f = tfirst, e = teq;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) { f = min(f, __shfl_xor_sync(0xffffffffu, f, o)); e += __shfl_xor_sync(0xffffffffu, e, o); }
+        if (c.lane == 0) { A->wsi[c.warp] = f; A->wsu[c.warp] = (unsigned long long)e; }
+        __syncthreads();
+        if (c.tid < g.G) {
+            int cf = 0x7fffffff, ce = 0;
+            for (int w = 0; w < NWARP; w++) { cf = min(cf, A->wsi[w]); ce += (int)A->wsu[w]; }
+            AuxC *ox = cl.map_shared_rank(A, c.tid);
+            ox->x1_max[g.rank] = cmax; ox->x1_idx[g.rank] = cf; ox->x1_eq[g.rank] = ce; ox->x1_status[g.rank] = c.status;
+        }
+    }
+    CSTAMP(13);
+    cl.sync();
+    float xmax = -INFINITY;
+    int imax = 0x7fffffff, eqs = 0;
+    for (int o = 0; o < g.G; o++) {
+        c.status |= A->x1_status[o];
+        const float m = A->x1_max[o];
+        if (m > xmax) { xmax = m; imax = A->x1_idx[o]; eqs = A->x1_eq[o]; }
+        else if (m == xmax) { imax = min(imax, A->x1_idx[o]); eqs += A->x1_eq[o]; }
+    }
+    if (imax == 0x7fffffff) imax = 0;
+    if (c.status & MOLLA_ROW_LOAD_TIMEOUT) { finish(); return; }
+
+    CSTAMP(3);
+    const long long n_lim = (k > 0 && k < a.V) ? (long long)k : (long long)a.V;
+    if (greedy) { token = imax; finish(); return; }
+    if (n_lim == 1) {
+        // top-k of one: the sort's first element is a maximum (sample.mojo:485-490)
+        if (eqs > 1) c.status |= MOLLA_ROW_TOPK_TIE;
+        token = imax; finish(); return;
+    }
+
+    const float top = (T == 1.0f) ? xmax : __fdiv_rn(xmax, T);
+    const bool topp_on = (P < 1.0f) && (n_lim > 1);
+    const bool pure = !topp_on && n_lim == (long long)a.V;
+    const float u01 = draw01(a.seed ? a.seed[q] : 0ull, a.drawn ? a.drawn[q] : 0ull);
+    const bool filter_ok = fabsf(top) < 1.0e5f;
+    long long need = n_lim + 1;
+    if (need > HEAD_NEED) need = HEAD_NEED;
+    if (need > a.V) need = a.V;
+    const bool p3row = !pure && (n_lim + 1 > HEAD_NEED);
+
+    // ---- 3. a lower bound of the running sum before every thread's range (each range adds at
+    // least the exponential of its own maximum), and the head's threshold: the need-th largest of
+    // all threads' maxima bounds the need-th largest element from below.
+    float et = 0.0f;
+    if (i0 < g.nloc && tmax > -INFINITY) {
+        const float v = (T == 1.0f) ? tmax : __fdiv_rn(tmax, T);
+        et = expf_pinned(__fsub_rn(v, top));
+    }
+    float etot;
+    const float eex = block_excl_scan<float>(et, A->wsf, &etot);
+    if (!pure) {
+        __syncthreads();
+        A->cand[c.tid] = ((unsigned long long)fkey(tmax) << 32) | (unsigned long long)c.tid;
+        bitonic_desc(A->cand, NT, c.tid);
+        if (c.tid < XT) {
+            const float v = fkey_inv((unsigned int)(A->cand[c.tid] >> 32));
+            for (int o = 0; o < g.G; o++) cl.map_shared_rank(A, o)->x2_top[g.rank][c.tid] = v;
+        }
+    }
+    if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x2_total[g.rank] = etot;
+    if (c.tid == 0) { A->ncand = 0; A->b_tau = 0xff800000u; }  // no candidates yet; threshold -inf until found
+    cl.sync();
+    float lbbase = 0.0f;
+    for (int h = 0; h < g.rank; h++) lbbase += A->x2_total[h];
+    float tau_x = INFINITY;
+    unsigned int tau_bits = 1u;
+    if (!pure) {
+        // the need-th largest of the G sorted lists: the value v with (#greater) < need <= (#greater or equal)
+        for (int t = c.tid; t < g.G * XT; t += NT) {
+            const float v = A->x2_top[t / XT][t % XT];
+            int gt = 0, ge = 0;
+            for (int o = 0; o < g.G; o++) {
+                const float *lst = A->x2_top[o];
+                int lo_ = 0, hi_ = XT;          // first index with lst[i] <= v
+                while (lo_ < hi_) { const int mid = (lo_ + hi_) >> 1; if (lst[mid] <= v) hi_ = mid; else lo_ = mid + 1; }
+                gt += lo_;
+                hi_ = XT;                        // first index with lst[i] < v
+                while (lo_ < hi_) { const int mid = (lo_ + hi_) >> 1; if (lst[mid] < v) hi_ = mid; else lo_ = mid + 1; }
+                ge += lo_;
+            }
+            if ((long long)gt < need && need <= (long long)ge) A->b_tau = __float_as_uint(v);
+        }
+        __syncthreads();
+        tau_x = __uint_as_float(A->b_tau);
+        const float tv = (T == 1.0f) ? tau_x : __fdiv_rn(tau_x, T);
+        const unsigned int tb_ = __float_as_uint(expf_pinned(__fsub_rn(tv, top)));
+        tau_bits = tb_ > 1u ? tb_ : 1u;
+    }
+    {
+        // what is below half an ulp of the bound is dropped; below top - 105 the exponential is
+        // exactly zero whatever came before
+        const float lb = lbbase + eex;
+        const float thr_rel = (filter_ok && lb > 0.0f) ? T * (top + logf(0.9f * lb) - REL_MARGIN) : -INFINITY;
+        const float thr_zero = filter_ok ? T * (top - 105.0f) : -INFINITY;
+        A->thr[c.tid] = fminf(fmaxf(thr_rel, thr_zero), tau_x);
+    }
+    __syncthreads();
+
+    CSTAMP(4);
+    // ---- 4. the second pass, in place: the exponential (temperature and softmax numerator,
+    // sample.mojo:419-434) of what can matter, zero for the rest. Every warp runs through its
+    // threads' ranges 128 elements at a time; where few are kept they are evaluated densely.
+    {
+        const int wbase = c.warp * 32 * g.L;           // first element of the warp's region
+        const int wlen = 32 * g.L;
+        float4 *row4 = reinterpret_cast<float4 *>(rowbuf + wbase);
+        unsigned short *pp_ = A->ppos[c.warp];
+        auto value = [&](float xx) -> float {
+            const float v = (T == 1.0f) ? xx : __fdiv_rn(xx, T);
+            return expf_pinned(__fsub_rn(v, top));
+        };
+        auto take = [&](unsigned int ebits, int i_block) {  // the head's candidates are picked up on the way
+            if (!pure && ebits >= tau_bits) {
+                const int pos = satom_add(&A->ncand, 1);
+                if (pos < HEADC) A->cand[pos] = make_key(ebits, g.c0 + i_block);
+            }
+        };
+        for (int e0 = 0; e0 < wlen; e0 += 128) {
+            const float thr = A->thr[c.warp * 32 + e0 / g.L];
+            const int e = e0 + 4 * c.lane;
+            const bool in = e < wlen;                  // wlen is a multiple of 4
+            float4 x = in ? row4[e >> 2] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            const bool k0 = in && x.x >= thr, k1 = in && x.y >= thr, k2 = in && x.z >= thr, k3 = in && x.w >= thr;
+            const int cnt = (int)k0 + (int)k1 + (int)k2 + (int)k3;
+            const int incl = warp_incl_scan(cnt, c.lane);
+            const int total = __shfl_sync(0xffffffffu, incl, 31);
+            if (total > 64) {
+                float4 y;
+                y.x = k0 ? value(x.x) : 0.0f; y.y = k1 ? value(x.y) : 0.0f;
+                y.z = k2 ? value(x.z) : 0.0f; y.w = k3 ? value(x.w) : 0.0f;
+                if (in) row4[e >> 2] = y;
+                if (k0) take(__float_as_uint(y.x), wbase + e);
+                if (k1) take(__float_as_uint(y.y), wbase + e + 1);
+                if (k2) take(__float_as_uint(y.z), wbase + e + 2);
+                if (k3) take(__float_as_uint(y.w), wbase + e + 3);
+            } else {
+                int off = incl - cnt;
+                if (k0) pp_[off++] = (unsigned short)(e);
+                if (k1) pp_[off++] = (unsigned short)(e + 1);
+                if (k2) pp_[off++] = (unsigned short)(e + 2);
+                if (k3) pp_[off++] = (unsigned short)(e + 3);
+                if (in) row4[e >> 2] = make_float4(k0 ? x.x : 0.0f, k1 ? x.y : 0.0f, k2 ? x.z : 0.0f, k3 ? x.w : 0.0f);
+                __syncwarp();
+                for (int i = c.lane; i < total; i += 32) {
+                    const int pos = (int)pp_[i];
+                    const float ev = value(rowbuf[wbase + pos]);
+                    rowbuf[wbase + pos] = ev;
+                    take(__float_as_uint(ev), wbase + pos);
+                }
+                __syncwarp();
+            }
+        }
+    }
+    __syncthreads();
+    CSTAMP(5);
+    // how many candidates for the head every block holds
+    if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x3_n[g.rank] = A->ncand;
+
+    // ---- 5. the softmax denominator, exactly as the sequential loop rounds it
+    const ClSum zs = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f, (a.prof && leader) ? a.prof + (long long)r * 16 + 14 : nullptr);
+    const float Z = zs.s;
+    if (zs.slow) c.status |= MOLLA_ROW_SLOW_PATH;
+    dZ = Z;
+
+    CSTAMP(6);
+    const unsigned int tau_p = __float_as_uint(__fdiv_rn(__uint_as_float(tau_bits), Z));
+    const unsigned int tau_pb = tau_p > 1u ? tau_p : 1u;
+    (void)tau_pb;
+
+    // min-p (sample.mojo:508-523): see the note at the same place in sample_rows_kernel
+    long long n_use = n_lim;
+    const bool typ_on = typ < 1.0f;
+    unsigned int minp_pbits = 0u;
+    if (minp > 0.0f) {
+        const float p_top = __fdiv_rn(expf_pinned(__fsub_rn(top, top)), Z);
+        const float floor_p = __fmul_rn(p_top, minp);
+        minp_pbits = __float_as_uint(floor_p);
+        if (!(floor_p >= 2.2e-8f)) {
+            c.status |= MOLLA_ROW_UNSUPPORTED;
+        } else if (!pure) {
+            unsigned int lo_b = 0u, hi_b = 0x3F800000u;
+            for (int it = 0; it < 32 && lo_b < hi_b; it++) {
+                const unsigned int mid = lo_b + ((hi_b - lo_b) >> 1);
+                if (__fdiv_rn(__uint_as_float(mid), Z) >= floor_p) hi_b = mid; else lo_b = mid + 1u;
+            }
+            const unsigned int e_floor = hi_b;
+            int cnt_ge = 0;
+            for (int i = c.tid; i < g.nloc; i += NT) cnt_ge += (rowbits[i] >= e_floor && rowbits[i] != 0u) ? 1 : 0;
+            int n_ge_loc;
+            (void)block_excl_scan<int>(cnt_ge, A->wsi, &n_ge_loc);
+            if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x4_n[g.rank] = n_ge_loc;
+            cl.sync();
+            long long n_ge = 0;
+            for (int o = 0; o < g.G; o++) n_ge += A->x4_n[o];
+            if (n_ge < 1) n_ge = 1;  // never empties
+            if (n_ge < n_use) n_use = n_ge;
+        }
+    }
+    if (c.status & MOLLA_ROW_UNSUPPORTED) { finish(); return; }
+
+    if (pure) {
+        // ---- 6a. nothing sorted: the draw walks the vocabulary in order (sample.mojo:365-369,
+        // 580-594): probabilities p = e / Z (:437-438), what min-p drops becomes zero
+        for (int i = c.tid; i < g.nloc; i += NT) {
+            const unsigned int eb = rowbits[i];
+            if (eb == 0u) continue;
+            unsigned int pb = __float_as_uint(__fdiv_rn(__uint_as_float(eb), Z));
+            if (pb < minp_pbits) pb = 0u;
+            rowbits[i] = pb;
+        }
+        const ClSum s1 = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f);
+        const float sum = s1.s;
+        const float target = __fmul_rn(u01, sum);
+        const ClSum s2 = cluster_exact_sum(cl, c, g, rowbits, true, target);
+        if (s1.slow || s2.slow) c.status |= MOLLA_ROW_SLOW_PATH;
+        dsum = sum; dtarget = target;
+        if (s2.found) token = s2.at;
+        else {
+            // the walk fell off the end: the reference returns the last token of the vocabulary,
+            // whether or not it could matter to any sum ... or the last one min-p left
+            token = a.V - 1;
+            if (minp_pbits) {
+                int last = -1;
+                for (int i = c.tid; i < g.nloc; i += NT)
+                    if (rowbits[i] >= minp_pbits && rowbits[i] != 0u) last = max(last, g.c0 + i);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
+                __syncthreads();
+                if (c.lane == 0) A->wsi[c.warp] = last;
+                __syncthreads();
+                if (c.tid < g.G) {
+                    int m = -1;
+                    for (int w = 0; w < NWARP; w++) m = max(m, A->wsi[w]);
+                    cl.map_shared_rank(A, c.tid)->x4_n[g.rank] = m;
+                }
+                cl.sync();
+                last = -1;
+                for (int o = 0; o < g.G; o++) last = max(last, A->x4_n[o]);
+                token = last >= 0 ? last : imax;
+            }
+        }
+        finish();
+        return;
+    }
+
+    CSTAMP(7);
+    // ---- 6b. sorted order. The head's candidates go to the leader as probabilities.
+    int nc_tot = 0, cbase = 0;
+    bool head_overflow = false;
+    for (int o = 0; o < g.G; o++) {
+        const int n = A->x3_n[o];
+        if (o < g.rank) cbase += n;
+        nc_tot += n;
+        if (n > HEADC) head_overflow = true;
+    }
+    if (nc_tot > HEADC) head_overflow = true;
+    if (!head_overflow) {
+        const int mine = A->x3_n[g.rank];
+        for (int i = c.tid; i < mine; i += NT) {
+            const unsigned long long kk = A->cand[i];
+            const unsigned long long nk = ((unsigned long long)__float_as_uint(__fdiv_rn(key_val(kk), Z)) << 32) | (kk & 0xFFFFFFFFull);
+            if (leader) A->cand[i] = nk; else lead->cand[cbase + i] = nk;
+        }
+    }
+    cl.sync();
+    int nc = head_overflow ? 0 : nc_tot;
+    unsigned int tau_head = 0xFFFFFFFFu;
+    if (head_overflow) c.status |= MOLLA_ROW_SLOW_PATH;  // no head: the descending walk takes everything from the top
+    if (leader) {
+        sort_cands(c, nc);
+        for (int i = c.tid; i < nc; i += NT) {
+            const float p = A->pc[i];
+            const bool eq = (i > 0 && A->pc[i - 1] == p) || (i + 1 < nc && A->pc[i + 1] == p);
+            A->hidx[i] = (unsigned int)key_idx(A->cand[i]) | (eq ? 0x80000000u : 0u);
+        }
+        __syncthreads();
+        if (a.topk_out) {
+            for (int i = c.tid; i < a.topk_cap; i += NT)
+                a.topk_out[(long long)r * a.topk_cap + i] =
+                    (i < nc && (long long)i < n_use) ? (int)(A->hidx[i] & 0x7fffffffu) : -1;
+        }
+        if (c.tid == 0) {
+            float s = 0.0f;
+            long long pos = 0;
+            int cut = -1, tie = 0;
+            for (int i = 0; i < nc; i++) {
+                if (pos >= n_use) break;
+                s = __fadd_rn(s, A->pc[i]);
+                A->pre[i] = s;
+                pos++;
+                if (topp_on && s >= P) {
+                    cut = i + 1;
+                    if (i + 1 < nc && (long long)(i + 1) < n_use && A->pc[i + 1] == A->pc[i]) tie |= MOLLA_ROW_TOPP_TIE;
+                    break;
+                }
+                if (pos >= n_use) { cut = i + 1; break; }
+            }
+            if (cut < 0 && !p3row && !head_overflow) cut = nc;  // everything that can matter is in the head
+            if (n_use < (long long)a.V && (long long)nc > n_use && A->pc[n_use] == A->pc[n_use - 1])
+                tie |= MOLLA_ROW_TOPK_TIE;
+            A->b_s = s; A->b_pos = pos; A->b_event = EV_NONE; A->b_idx = -1; A->b_p = 0.0f;
+            if (typ_on) {
+                A->ncand = cut;  // the typical-p filter takes over from here
+            } else if (cut > 0) {
+                const float sum = A->pre[cut - 1];
+                const float target = __fmul_rn(u01, sum);
+                int at = cut - 1;
+                for (int i = 0; i < cut; i++)
+                    if (target < A->pre[i]) { at = i; break; }
+                A->b_event = EV_DRAW; A->b_idx = (int)(A->hidx[at] & 0x7fffffffu); A->b_p = A->pc[at];
+                if ((at > 0 && A->pc[at - 1] == A->pc[at]) || (at + 1 < cut && A->pc[at + 1] == A->pc[at]))
+                    tie |= MOLLA_ROW_CHOSEN_TIE;
+                A->b_sum = sum; A->b_target = target;
+            }
+            A->b_aux = tie;
+        }
+        __syncthreads();
+        c.status |= (unsigned int)A->b_aux;
+        const float head_s = A->b_s;
+        const long long head_pos = A->b_pos;
+        int kind = 1;  // 0: the row is finished; 1: past the head
+        if (typ_on) {
+            const int m = A->ncand;
+            if (m <= 0) {
+                c.status |= MOLLA_ROW_UNSUPPORTED;  // what the earlier filters left reaches past the head
+            } else {
+                typical_head(c, m, typ, u01);
+                token = A->b_idx; dp = A->b_p; dsum = A->b_sum; dtarget = A->b_target;
+                c.status |= (unsigned int)A->b_aux;
+            }
+            kind = 0;
+        } else if (A->b_event == EV_DRAW) {
+            token = A->b_idx; dp = A->b_p; dsum = A->b_sum; dtarget = A->b_target;
+            kind = 0;
+        }
+        __syncthreads();
+        if (c.tid < g.G) {
+            AuxC *ox = cl.map_shared_rank(A, c.tid);
+            ox->r_kind = kind; ox->r_s = head_s; ox->r_pos = head_pos; ox->r_status = c.status;
+        }
+    }
+    cl.sync();
+    if (A->r_kind == 0) { finish(); return; }
+    c.status |= A->r_status;
+    const float head_s = A->r_s;
+    const long long head_pos = A->r_pos;
+
+    CSTAMP(8);
+    // ---- 7. past the head: the cut walk, then the draw walk, over the probabilities
+    // (sample.mojo:437-438); what the head took is consumed
+    for (int i = c.tid; i < g.nloc; i += NT) {
+        const unsigned int eb = rowbits[i];
+        if (eb == 0u) continue;
+        unsigned int pb = __float_as_uint(__fdiv_rn(__uint_as_float(eb), Z));
+        if (!head_overflow && eb >= tau_bits) pb = 0u;
+        rowbits[i] = pb;
+    }
+    __syncthreads();
+    ClWalk cutw;
+    cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
+    cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
+    const bool limited = n_use < (long long)a.V;
+    descend_cluster(cl, c, g, rowbits, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_use : -1);
+    if (cutw.event != EV_DEGENERATE) {
+        if (cutw.event == EV_CUT && cutw.tie) c.status |= MOLLA_ROW_TOPP_TIE;
+        if (cutw.event == EV_LIMIT && cutw.tie) c.status |= MOLLA_ROW_TOPK_TIE;
+        const float sum = cutw.s;
+        const float target = __fmul_rn(u01, sum);
+        dsum = sum; dtarget = target;
+        cl.sync();
+        if (leader && c.tid == 0) {  // is the drawn element in the head?
+            int at = -1;
+            for (int i = 0; i < nc; i++)
+                if (target < A->pre[i]) { at = i; break; }
+            int ev = EV_NONE, idx = -1, aux = 0;
+            float pv = 0.0f;
+            if (at >= 0) {
+                ev = EV_DRAW; idx = (int)(A->hidx[at] & 0x7fffffffu);
+                pv = __fsub_rn(A->pre[at], at > 0 ? A->pre[at - 1] : 0.0f);
+                aux = (A->hidx[at] & 0x80000000u) ? MOLLA_ROW_CHOSEN_TIE : 0;
+            }
+            for (int o = 0; o < g.G; o++) {
+                AuxC *ox = cl.map_shared_rank(A, o);
+                ox->r_kind = ev; ox->r_idx = idx; ox->r_s = pv; ox->r_status = (unsigned int)aux;
+            }
+        }
+        cl.sync();
+        if (A->r_kind == EV_DRAW) {
+            token = A->r_idx; dp = A->r_s; c.status |= A->r_status;
+        } else {
+            bool resolved = false;
+            if (target < sum) {
+                ClWalk dw;
+                dw.s = head_s; dw.pos = head_pos; dw.tau = tau_head;
+                dw.event = EV_NONE; dw.idx = -1; dw.p = 0; dw.tie = 0;
+                descend_cluster(cl, c, g, rowbits, dw, 3.4e38f, target, -1);
+                if (dw.event == EV_DRAW) {
+                    token = dw.idx; dp = dw.p; resolved = true;
+                    if (dw.tie) c.status |= MOLLA_ROW_CHOSEN_TIE;
+                } else if (dw.event == EV_DEGENERATE) {
+                    resolved = true;
+                }
+            }
+            if (!resolved) {
+                // the walk falls off the end: the last kept candidate (sample.mojo:591-594)
+                if (cutw.event == EV_CUT || cutw.event == EV_LIMIT) {
+                    token = cutw.idx; dp = cutw.p;
+                } else {
+                    // everything listed was kept: its smallest value, highest id last
+                    unsigned long long best = ~0ull;
+                    for (int i = c.tid; i < g.nloc; i += NT) {
+                        const unsigned int pb = rowbits[i];
+                        if (pb == 0u) continue;
+                        const unsigned long long kk = make_key(pb, g.c0 + i);
+                        best = kk < best ? kk : best;
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        unsigned long long ob = __shfl_xor_sync(0xffffffffu, best, o);
+                        best = ob < best ? ob : best;
+                    }
+                    __syncthreads();
+                    if (c.lane == 0) A->wsu[c.warp] = best;
+                    __syncthreads();
+                    if (c.tid < g.G) {
+                        unsigned long long m = A->wsu[0];
+                        for (int w = 1; w < NWARP; w++) m = A->wsu[w] < m ? A->wsu[w] : m;
+                        cl.map_shared_rank(A, c.tid)->x5_key[g.rank] = m;
+                    }
+                    cl.sync();
+                    best = ~0ull;
+                    for (int o = 0; o < g.G; o++) best = A->x5_key[o] < best ? A->x5_key[o] : best;
+                    token = (best != ~0ull) ? key_idx(best) : imax;
+                }
+            }
+        }
+    }
+    finish();
+}

@@ -34,16 +34,19 @@
 // (:440-483) leaves equal probabilities in; rows where that order could matter
 // are marked in the row status (MOLLA_ROW_*_TIE) and equal probabilities are
 // ordered by token id.
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "../../include/molla_sample.h"
 #include "molla_device.cuh"
 
 using namespace molla;
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -107,6 +110,9 @@ struct BatchArgs {
     unsigned char *stopped;        // [B] or nullptr: the pick was the slot's stop token
     int *topk_out; int topk_cap; // optional [B x cap] ids of the sorted head after top-k (testing aid)
     // vocab-sharded form: this GPU holds columns [col0, col0 + V) of a vocabulary of Vg
+    int n_logit_rows, n_slots;   // bounds of rows[] and slot[] values (0 = not given)
+    // one row per thread-block cluster: blocks per cluster, logits per block, logits per thread
+    int G, Vc, L;
     int mode;                    // 0 whole pipeline; 1, 2, 3 the stages around the two all-gathers
     int col0, Vg;
     float *sa_out;               // stage 1 out: [B x SA_WORDS] summary of the slice
@@ -2386,6 +2392,8 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
     if (a.help && !(a.knobs & 8)) help_others(c, a);  // no rows left: lend a hand to the blocks still on a long list
 }
 
+#include "molla_rows_cluster.cuh"
+
 // =============================================================================
 // Logprobs of the raw logits (sample.mojo:268-293): one CTA per row, the row is
 // read twice (second read is an L2 hit for blocks that fit).
@@ -2578,6 +2586,77 @@ int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, in
     return MOLLA_OK;
 }
 
+// ---- one row per cluster -------------------------------------------------------------
+// How a vocabulary of V logits is laid over a cluster: blocks per cluster (0 = too wide, the
+// streaming kernel takes the call), logits per block (a multiple of four: bulk copies start on
+// 16-byte boundaries) and logits per thread (odd: conflict-free shared-memory strides).
+struct ClusterShape { int G, Vc, L; };
+
+ClusterShape cluster_shape(int V) {
+    for (int G = 1; G <= CL_MAX_G; G *= 2) {
+        const int Vc = ((((V + G - 1) / G) + 3) / 4) * 4;
+        int L = (Vc + NT - 1) / NT;
+        if ((L & 1) == 0) L += 1;
+        if (L <= CL_LMAX) return ClusterShape{G, Vc, L};
+    }
+    return ClusterShape{0, 0, 0};
+}
+
+constexpr size_t CL_SMEM = (size_t)CL_CAPF * 4 + ((sizeof(AuxC) + 15) / 16) * 16;
+
+// Whether this device can hold a cluster of G of the kernel's blocks (asked once per device and size).
+bool cluster_fits(int G) {
+    static int known[NOALLOC_MAX_DEVICES][CL_MAX_G + 1] = {};  // 0 unknown, 1 yes, -1 no
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return false;
+    if (known[dev][G]) return known[dev][G] > 0;
+    bool ok = cudaFuncSetAttribute(sample_rows_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CL_SMEM) == cudaSuccess;
+    if (ok) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)G); cfg.blockDim = dim3(NT); cfg.dynamicSmemBytes = CL_SMEM;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = (unsigned)G; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        int n = 0;
+        ok = cudaOccupancyMaxActiveClusters(&n, sample_rows_cluster_kernel, &cfg) == cudaSuccess && n > 0;
+    }
+    if (!ok) (void)cudaGetLastError();
+    known[dev][G] = ok ? 1 : -1;
+    return ok;
+}
+
+// The ordinary entry points' launch: the cluster kernel when the vocabulary fits a cluster, else
+// the streaming kernel with its lists in the workspace.
+int launch_sampling(const BatchArgs &args_in, void *d_workspace, cudaStream_t st) {
+    const ClusterShape cs = cluster_shape(args_in.V);
+    static const bool cluster_on = [] { const char *e = getenv("MOLLA_SAMPLE_CLUSTER"); return e && e[0] == '1'; }();
+    if (!cluster_on || cs.G == 0 || !cluster_fits(cs.G)) return launch_rows(args_in, d_workspace, st, 0x7fffffff, true);
+    BatchArgs a = args_in;
+    a.G = cs.G; a.Vc = cs.Vc; a.L = cs.L;
+    a.Vg = a.V; a.col0 = 0; a.mode = 0;
+    a.order = nullptr;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // clusters start in grid order: when not all rows can start at once, the dearest go first
+    if (a.B * cs.G > sms && a.B <= ORDER_CAP && a.temperature) {
+        int *order = (int *)((char *)d_workspace + 256);
+        order_rows_kernel<<<1, NT, 0, st>>>(a.temperature, a.top_k, a.slot, a.B, order);
+        a.order = order;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)a.B * (unsigned)cs.G); cfg.blockDim = dim3(NT);
+    cfg.dynamicSmemBytes = CL_SMEM; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)cs.G; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, sample_rows_cluster_kernel, a);
+    if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+    return MOLLA_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -2632,7 +2711,7 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
     a.prof = g_prof;
     a.knobs = g_knobs;
     a.topk_out = g_topk; a.topk_cap = g_topk_cap;
-    int rc = launch_rows(a, d_workspace, st, 0x7fffffff, true);
+    int rc = launch_sampling(a, d_workspace, st);
     if (rc != MOLLA_OK) return rc;
     if (d_chosen_logprob || top_n > 0) {
         int dev = 0, sms = 148;
@@ -2689,13 +2768,14 @@ int32_t molla_sample_decode_step(const float *d_logits, int64_t row_stride, int3
     a.ring_len = d_ring_len; a.stop_token = (const long long *)d_stop_token; a.stopped = d_stopped;
     a.bias_ids = (const long long *)d_bias_ids; a.bias_vals = d_bias_vals; a.bias_off = d_bias_off;
     a.tokens = d_tokens; a.row_status = d_row_status;
+    a.n_logit_rows = n_logit_rows; a.n_slots = n_slots;
     a.prof = g_prof;
     a.knobs = g_knobs;
     if (d_stopped) {
         cudaError_t e0 = cudaMemsetAsync(d_stopped, 0, (size_t)B, st);
         if (e0 != cudaSuccess) return fail(MOLLA_ERR_CUDA, "clearing the stop flags failed: %s", cudaGetErrorString(e0));
     }
-    int rc = launch_rows(a, d_workspace, st, 0x7fffffff, true);
+    int rc = launch_sampling(a, d_workspace, st);
     if (rc != MOLLA_OK) return rc;
     if (d_chosen_logprob || top_n > 0) {
         int dev = 0, sms = 148;
