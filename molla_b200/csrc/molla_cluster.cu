@@ -16,9 +16,20 @@
 // blocks of a cluster take the same branches: every decision is made from values all of them
 // hold.
 //
-// This file is included by molla_sample.cu inside its unnamed namespace and uses the device
-// functions defined there (the exact sum, the bin search, the sorted walk, typical-p).
-#pragma once
+// The device functions this kernel shares with the streaming kernel (the exact sum, the bin
+// search, the sorted walk, typical-p) come from molla_exact.cuh.
+#include <cooperative_groups.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "molla_exact.cuh"
+#include "molla_cluster.h"
+
+namespace cg = cooperative_groups;
+
+namespace {
 
 constexpr int CL_MAX_G = 8;                  // thread blocks per cluster at most (the portable limit)
 constexpr int CL_LMAX = 75;                  // logits per thread at most (odd: conflict-free strides)
@@ -273,7 +284,7 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         if (nb > NC && lvl < 3) {
             w.s = s_bin; w.pos = pos_bin;
             w.tau = bhi < w.tau ? bhi : w.tau;
-            lo = blo; shift = (lvl == 1) ? 8 : 0; lvl++;
+            lo = blo; shift = (lvl == 1) ? BIN_SHIFT2 : 0; lvl++;
             c.status |= MOLLA_ROW_SLOW_PATH;
             continue;
         }
@@ -956,4 +967,100 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         }
     }
     finish();
+}
+
+// Rows by decreasing cost estimate (a greedy row is one pass over its logits, a warm row with a
+// wide nucleus keeps most of its vocabulary): clusters start in grid order, and the dearest rows
+// should not be the last to start. One thread per row counts the rows that come before it.
+__global__ void __launch_bounds__(1024, 1) order_rows_rank_kernel(const float *temperature, const int *top_k, const int *slot, int B, int *order) {
+    __shared__ float cost[ORDER_CAP];
+    for (int i = threadIdx.x; i < B; i += blockDim.x) {
+        const int q = slot ? slot[i] : i;
+        const float T = temperature ? temperature[q] : 0.0f;
+        const int k = top_k ? top_k[q] : 0;
+        cost[i] = (T > 0.0f && k != 1) ? T + ((k == 0 || k >= HEAD_NEED) ? 0.25f : 0.0f) : 0.0f;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < B; i += blockDim.x) {
+        const float ci = cost[i];
+        int rank = 0;
+        for (int j = 0; j < B; j++) {
+            const float cj = cost[j];
+            rank += (cj > ci || (cj == ci && j < i)) ? 1 : 0;
+        }
+        order[rank] = i;
+    }
+}
+
+// How a vocabulary of V logits is laid over a cluster: blocks per cluster (0 = too wide), logits
+// per block (a multiple of four: bulk copies start on 16-byte boundaries) and logits per thread
+// (odd: conflict-free shared-memory strides).
+struct ClusterShape { int G, Vc, L; };
+
+ClusterShape cluster_shape(int V) {
+    for (int G = 1; G <= CL_MAX_G; G *= 2) {
+        const int Vc = ((((V + G - 1) / G) + 3) / 4) * 4;
+        int L = (Vc + NT - 1) / NT;
+        if ((L & 1) == 0) L += 1;
+        if (L <= CL_LMAX) return ClusterShape{G, Vc, L};
+    }
+    return ClusterShape{0, 0, 0};
+}
+
+constexpr size_t CL_SMEM = (size_t)CL_CAPF * 4 + ((sizeof(AuxC) + 15) / 16) * 16;
+constexpr int CL_MAX_DEVICES = 64;
+
+void cluster_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *at, unsigned int blocks, int G, cudaStream_t st) {
+    cfg = cudaLaunchConfig_t{};
+    cfg.gridDim = dim3(blocks); cfg.blockDim = dim3(NT);
+    cfg.dynamicSmemBytes = CL_SMEM; cfg.stream = st;
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)G; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+}
+
+// Whether this device can hold a cluster of G of the kernel's blocks (asked once per device and size).
+bool cluster_fits(int dev, int G) {
+    static int known[CL_MAX_DEVICES][CL_MAX_G + 1] = {};  // 0 unknown, 1 yes, -1 no
+    if (dev < 0 || dev >= CL_MAX_DEVICES) return false;
+    if (known[dev][G]) return known[dev][G] > 0;
+    bool ok = cudaFuncSetAttribute(sample_rows_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CL_SMEM) == cudaSuccess;
+    if (ok) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute at[1];
+        cluster_config(cfg, at, (unsigned)G, G, nullptr);
+        int n = 0;
+        ok = cudaOccupancyMaxActiveClusters(&n, sample_rows_cluster_kernel, &cfg) == cudaSuccess && n > 0;
+    }
+    if (!ok) (void)cudaGetLastError();
+    known[dev][G] = ok ? 1 : -1;
+    return ok;
+}
+
+}  // namespace
+
+int molla_cluster_launch(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, char *err, size_t errlen) {
+    const ClusterShape cs = cluster_shape(args_in.V);
+    int dev = 0, sms = 0;
+    if (cs.G == 0 || cudaGetDevice(&dev) != cudaSuccess || !cluster_fits(dev, cs.G)) return MOLLA_CLUSTER_DECLINED;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    BatchArgs a = args_in;
+    a.G = cs.G; a.Vc = cs.Vc; a.L = cs.L;
+    a.Vg = a.V; a.col0 = 0; a.mode = 0;
+    a.order = nullptr;
+    // clusters start in grid order: when not all rows can start at once, the dearest go first
+    if (a.B * cs.G > sms && a.B <= ORDER_CAP && a.temperature) {
+        int *order = (int *)((char *)d_workspace + 256);
+        order_rows_rank_kernel<<<1, 1024, 0, st>>>(a.temperature, a.top_k, a.slot, a.B, order);
+        a.order = order;
+    }
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute at[1];
+    cluster_config(cfg, at, (unsigned)a.B * (unsigned)cs.G, cs.G, st);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, sample_rows_cluster_kernel, a);
+    if (e != cudaSuccess) {
+        snprintf(err, errlen, "kernel launch failed: %s", cudaGetErrorString(e));
+        return MOLLA_ERR_CUDA;
+    }
+    return MOLLA_OK;
 }

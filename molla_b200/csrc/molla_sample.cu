@@ -34,7 +34,6 @@
 // (:440-483) leaves equal probabilities in; rows where that order could matter
 // are marked in the row status (MOLLA_ROW_*_TIE) and equal probabilities are
 // ordered by token id.
-#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
@@ -44,9 +43,10 @@
 
 #include "../../include/molla_sample.h"
 #include "molla_device.cuh"
+#include "molla_exact.cuh"
+#include "molla_cluster.h"
 
 using namespace molla;
-namespace cg = cooperative_groups;
 
 namespace {
 
@@ -54,72 +54,10 @@ constexpr int LT = 11;               // elements per lane per piece (odd: confli
 constexpr int PIECE = 32 * LT;       // 352 floats = 1408 bytes: what one warp fetches at a time
 constexpr int NSTAGE = 4;            // pieces in flight per warp
 constexpr int MAX_PIECES = 128;      // per warp: V <= 16 * 128 * 352 = 720896
-constexpr int NBINS = 2048;          // histogram bins over the top bits of exp(v - max) in [0, 1]
-constexpr int BIN_SHIFT = 19;        // sign + 8 exponent + 4 mantissa bits
-constexpr int BPT = NBINS / NT;      // bins per thread in the bin search
-constexpr int NC = 2048;             // candidate-list capacity (gathered bins)
-constexpr int HEADC = 1024;          // head-list capacity
-constexpr int HEAD_NEED = 128;       // the sorted head covers top-k + 1 up to this many
-constexpr int HSLOTS = 2048;         // hash slots for penalised / biased tokens
-constexpr int PATCH_MAX = 1024;      // window + bias entries per row
-constexpr short SUS = -32768;        // chunk that must be replayed sequentially
-constexpr int TOPN_MAX = 20;
-constexpr float REL_MARGIN = 17.6f;  // > 25 ln 2 = 17.33: this far below ln(running sum) nothing can matter
 constexpr int STAGE_FLOATS = NWARP * NSTAGE * PIECE;       // 22528 floats = 90112 bytes
 constexpr int SLIST_CAP = STAGE_FLOATS / 2;                 // list entries that fit the stage area
 constexpr int SA_WORDS = 3 + NWARP + HEAD_NEED + 1;  // max, argmax, ties, region maxima, top thread maxima
-constexpr int ORDER_CAP = 4096;      // rows whose order is sorted by cost inside the kernel
 
-// Tell the compiler which address space a pointer is in (functions it does not inline would
-// otherwise use generic loads, stores and atomics on shared memory).
-#define IN_SHARED(ptr) __builtin_assume(__isShared(ptr))
-
-struct HelpSlot;
-struct BatchArgs {
-    const float *logits; long long row_stride; int B, V;
-    const float *temperature; const int *top_k; const float *top_p; const float *min_p;
-    const float *typical_p; const float *repeat_penalty; const float *frequency_penalty;
-    const float *presence_penalty; const unsigned char *window_on;
-    const unsigned long long *seed; const unsigned long long *drawn;
-    const long long *hist; const int *hist_off;
-    const long long *bias_ids; const float *bias_vals; const int *bias_off;
-    int *tokens; unsigned int *row_status; float *diag;
-    float *penalised;  // optional dump [B x V]
-    int penalised_only;
-    int R;                       // floats per warp region (multiple of 4)
-    int *row_counter;            // scratch: next row to hand out (zeroed before the launch)
-    const int *order;            // scratch: rows by decreasing cost (NULL = as given)
-    unsigned long long *wlist;   // scratch: per CTA, 2 x 16 x R list entries
-    long long *prof;             // optional [B x 16] clock64 stamps per row (testing aid)
-    int knobs;                   // experiment switches (testing aid; 0 in production)
-    // thread blocks that ran out of rows help the ones still converting a long list (HelpSlot)
-    struct HelpSlot *help;       // [grid] one per thread block, or nullptr
-    unsigned int *help_tables;   // [grid x HELP_TABLE_WORDS]
-    int *rows_done;              // rows finished so far (zeroed before the launch)
-    // decode-step form: which row of the logit block each batch row reads, which slot of the
-    // per-stream arrays (settings and state) it uses, the final-logit softcap, and the state
-    const int *rows;             // [B] or nullptr (row r reads logit row r)
-    const int *slot;             // [B] or nullptr (row r uses slot r)
-    float softcap;               // 0 = none
-    long long *ring;             // [slots x ring_cap] token windows, or nullptr (windows come from hist)
-    int ring_cap;
-    int *ring_head, *ring_filled;
-    const int *ring_len;         // [slots] repeat_last_n of every slot (0 = penalties off)
-    unsigned long long *drawn_rw;  // [slots] draw counters, advanced by one per pick
-    const long long *stop_token;   // [slots] or nullptr
-    unsigned char *stopped;        // [B] or nullptr: the pick was the slot's stop token
-    int *topk_out; int topk_cap; // optional [B x cap] ids of the sorted head after top-k (testing aid)
-    // vocab-sharded form: this GPU holds columns [col0, col0 + V) of a vocabulary of Vg
-    int n_logit_rows, n_slots;   // bounds of rows[] and slot[] values (0 = not given)
-    // one row per thread-block cluster: blocks per cluster, logits per block, logits per thread
-    int G, Vc, L;
-    int mode;                    // 0 whole pipeline; 1, 2, 3 the stages around the two all-gathers
-    int col0, Vg;
-    float *sa_out;               // stage 1 out: [B x SA_WORDS] summary of the slice
-    const float *sb_in;          // stages 2, 3 in: [B x 4] global max, head threshold, sum bound before the slice, global argmax
-    unsigned long long *sb_list; int *sb_count; int list_cap;     // stage 2 out: the slice's list
-    const unsigned long long *sc_list; const int *sc_count; int world;  // stage 3 in: [world][B][cap], [world][B]
-};
 
 struct __align__(16) Aux {
     union {
@@ -170,7 +108,6 @@ struct __align__(16) Aux {
     float b_sum; float b_target;
 };
 
-enum { EV_NONE = 0, EV_CUT = 1, EV_DRAW = 2, EV_LIMIT = 3, EV_EXHAUSTED = 4, EV_DEGENERATE = 5 };
 
 struct Ctx {
     int tid, lane, warp;
@@ -195,62 +132,6 @@ struct Ctx {
 
 #define STAMP(i) do { if (a.prof && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
 
-// ---- block collectives (NT threads) ----------------------------------------------
-template <class CX>
-__device__ __forceinline__ void block_argmax(CX &c, float &v, int &i) {
-    warp_argmax(v, i);
-    __syncthreads();
-    if (c.lane == 0) { c.A->wsf[c.warp] = v; c.A->wsi[c.warp] = i; }
-    __syncthreads();
-    float bv = c.A->wsf[0];
-    int bi = c.A->wsi[0];
-#pragma unroll
-    for (int w = 1; w < NWARP; w++) {
-        float ov = c.A->wsf[w];
-        int oi = c.A->wsi[w];
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-    v = bv; i = bi;
-}
-
-// bitonic sort, descending, of n2 (power of two) keys in shared memory
-__device__ void bitonic_desc(unsigned long long *k, int n2, int tid) {
-    IN_SHARED(k);
-    // A warp's 32 consecutive pair indices cover 64 consecutive keys whenever the stride is at
-    // most 16, the same 64 for every such stride: those stages only need the warp to agree.
-    bool local = false;  // the previous stage was such a stage
-    for (int size = 2; size <= n2; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            if (local && stride <= 16) __syncwarp(); else __syncthreads();
-            local = stride <= 16 && !(size == 2);
-            for (int i = tid; i < (n2 >> 1); i += NT) {
-                int pos = ((i / stride) * stride * 2) + (i % stride);
-                int par = pos + stride;
-                bool desc = ((pos & size) == 0);
-                unsigned long long x = k[pos], y = k[par];
-                if ((x < y) == desc) { k[pos] = y; k[par] = x; }
-            }
-        }
-    }
-    __syncthreads();
-}
-
-__device__ __forceinline__ unsigned int fkey(float f) {  // order-preserving key of a float
-    unsigned int b = __float_as_uint(f);
-    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-}
-__device__ __forceinline__ float fkey_inv(unsigned int k) {
-    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
-}
-__device__ __forceinline__ int key_idx(unsigned long long k) {
-    return (int)(0xFFFFFFFFu - (unsigned int)(k & 0xFFFFFFFFull));
-}
-__device__ __forceinline__ float key_val(unsigned long long k) {
-    return __uint_as_float((unsigned int)(k >> 32));
-}
-__device__ __forceinline__ unsigned long long make_key(unsigned int ebits, int idx) {
-    return ((unsigned long long)ebits << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)idx);
-}
 
 // ---- the warp's own pipeline: piece p of its region lands in slot p % NSTAGE --------
 __device__ __forceinline__ float *wslot(const Ctx &c, int p) {
@@ -304,7 +185,6 @@ __device__ __forceinline__ const float *piece_acquire(Ctx &c, int p, int &n) {
 }
 
 // ---- patched tokens: bitmap over the vocabulary + a small hash of their values -----
-__device__ __forceinline__ int hslot(int tok) { return (int)(((unsigned int)tok * 2654435761u) >> 21); }
 
 __device__ __forceinline__ float patch_lookup(const Aux *A, int tok, float x) {
     int s = hslot(tok);
@@ -355,30 +235,6 @@ __device__ __forceinline__ void for_list(const unsigned long long *lst, int nl, 
     for (; i < nl; i += NT) f(i, lst[i]);
 }
 
-// =============================================================================
-// The exact sequential fp32 sum of the list's values, in list (= vocabulary) order.
-// =============================================================================
-// Every thread owns L consecutive entries. From approximate prefix sums each chunk
-// guesses the binade(s) the true running sum can be in when it reaches the chunk (a
-// margin of 2^-12 covers the rounding drift of the true sum) and adds up its terms'
-// integer contributions for that binade (`pa`) and, when the guess straddles a power
-// of two, for the next one (`pb`). Chunks holding a rounding tie, a term >= sum/4, or
-// a span of more than two binades are replayed term by term. Thread 0 then carries
-// the exact sum across the list from those tables (`p1_walk`), optionally stopping at
-// the first entry whose running sum exceeds a target.
-struct Walker {
-    float s; int found; int at; int slow;
-};
-
-// value accessors (shared memory): a list of (value bits << 32 | ~id) keys, or bare value bits
-struct ValKeys {
-    const unsigned long long *p;
-    __device__ __forceinline__ float operator()(int i) const { IN_SHARED(p); return __uint_as_float((unsigned int)(p[i] >> 32)); }
-};
-struct ValBits {
-    const unsigned int *p;
-    __device__ __forceinline__ float operator()(int i) const { IN_SHARED(p); return __uint_as_float(p[i]); }
-};
 
 // A row's list as the later phases see it: a copy in shared memory when it is small, else the
 // segments pass B wrote (one per warp, each in vocabulary order, `stride` entries apart).
@@ -459,197 +315,6 @@ struct LView {
     }
 };
 
-template <class V>
-__device__ __forceinline__ void p1_sim(V lst, int i0, int i1, bool locate, float target,
-                                       Walker &w) {
-    float s = w.s;
-    int i = i0;
-    for (; i + 8 <= i1; i += 8) {  // the loads do not depend on the running sum: fetch eight, then add
-        float v[8];
-#pragma unroll
-        for (int q = 0; q < 8; q++) v[q] = lst(i + q);
-#pragma unroll
-        for (int q = 0; q < 8; q++) {
-            s = __fadd_rn(s, v[q]);
-            if (locate && !w.found && target < s) { w.found = 1; w.at = i + q; }
-        }
-        if (locate && w.found) { w.s = s; return; }
-    }
-    for (; i < i1; i++) {
-        s = __fadd_rn(s, lst(i));
-        if (locate && target < s) { w.found = 1; w.at = i; break; }
-    }
-    w.s = s;
-}
-
-// this thread's estimate of the sum of its own L entries
-template <class V>
-__device__ __forceinline__ float p1_csum(V lst, int n, int L, int tid) {
-    const int i0 = min(n, tid * L), i1 = min(n, (tid + 1) * L);
-    // only an estimate is needed here: four partial sums shorten the dependency chain
-    float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;
-    int i = i0;
-    for (; i + 4 <= i1; i += 4) {
-        c0 = __fadd_rn(c0, lst(i)); c1 = __fadd_rn(c1, lst(i + 1)); c2 = __fadd_rn(c2, lst(i + 2)); c3 = __fadd_rn(c3, lst(i + 3));
-    }
-    for (; i < i1; i++) c0 = __fadd_rn(c0, lst(i));
-    return __fadd_rn(__fadd_rn(c0, c1), __fadd_rn(c2, c3));
-}
-
-// The tables for the walk, given every thread's estimate `csum` and the estimated sum `sst` of
-// everything before its entries.
-template <class CX, class V>
-__device__ void p1_tables(CX &c, V lst, int n, int L, float csum, double sst) {
-    auto *A = c.A;
-    IN_SHARED(A);
-    const float EPS = 1.0f / 4096.0f;
-    const int i0 = min(n, c.tid * L), i1 = min(n, (c.tid + 1) * L);
-    short ja = SUS;
-    unsigned char dual = 0;
-    float da = 0.0f, db = 0.0f;
-    const float lo = (float)(sst * (1.0 - (double)EPS));
-    const float hi = (float)((sst + (double)csum) * (1.0 + (double)EPS));
-    if (lo > 0.0f && i1 > i0) {
-        const int jl = fexpo(lo), j2 = fexpo(hi);
-        if (j2 <= jl + 1 && jl >= -100 && j2 <= 100) {
-            bool bad = false;
-            const bool two = (j2 == jl + 1);
-            const float C1 = __fmul_rn(1.5f, fpow2(jl)), h1 = fpow2(jl - 24), b1 = fpow2(jl - 1);
-            const float C2 = __fmul_rn(1.5f, fpow2(jl + 1)), h2 = fpow2(jl - 23);
-            // the terms are multiples of the binade's unit and their sum stays below 2^24 units, so
-            // these additions are exact in any order: two accumulators each
-            float da1 = 0.0f, db1 = 0.0f;
-            auto term = [&](int i, float &xa, float &xb) {
-                const float v = lst(i);
-                const float q = __fsub_rn(__fadd_rn(v, C1), C1);
-                const float r = __fsub_rn(v, q);
-                bad |= (fabsf(r) == h1) | (v >= b1);
-                xa = __fadd_rn(xa, q);
-                const float q2 = __fsub_rn(__fadd_rn(v, C2), C2);
-                const float r2 = __fsub_rn(v, q2);
-                bad |= two & (fabsf(r2) == h2);
-                xb = __fadd_rn(xb, q2);
-            };
-            int i = i0;
-            for (; i + 2 <= i1; i += 2) { term(i, da, db); term(i + 1, da1, db1); }
-            if (i < i1) term(i, da, db);
-            da = __fadd_rn(da, da1); db = __fadd_rn(db, db1);
-            if (!bad) { ja = (short)jl; dual = two ? 1 : 0; }
-        }
-    }
-    if (ja == SUS) { da = 0.0f; db = 0.0f; dual = 0; }
-    A->u.p1.csum[c.tid] = (i1 > i0) ? csum : 0.0f;
-    A->u.p1.ja[c.tid] = ja;
-    A->u.p1.dual[c.tid] = dual;
-    double pa, pb, ta, tb;
-    block_excl_scan2((double)da, (double)(dual ? db : da), A->wsd, pa, pb, ta, tb);
-    A->u.p1.pa[c.tid] = pa;
-    A->u.p1.pb[c.tid] = pb;
-    if (c.tid == NT - 1) { A->u.p1.pa[NT] = ta; A->u.p1.pb[NT] = tb; }
-    __syncthreads();
-    // segment list: chunks where (binade guess, dual, replay) changes
-    const bool start = (c.tid == 0) || ja == SUS || A->u.p1.ja[c.tid - 1] != ja || A->u.p1.dual[c.tid - 1] != dual;
-    const unsigned int bal = __ballot_sync(0xffffffffu, start);
-    int wtot;
-    int wex = block_excl_scan<int>(c.lane == 0 ? __popc(bal) : 0, A->wsi, &wtot);
-    wex = __shfl_sync(0xffffffffu, wex, 0);
-    if (start) A->u.p1.seg[wex + __popc(bal & ((1u << c.lane) - 1u))] = (unsigned short)c.tid;
-    if (c.tid == 0) A->nseg = wtot;
-    __syncthreads();
-}
-
-template <class CX, class V>
-__device__ void p1_build(CX &c, V lst, int n, int L, double sbase) {
-    auto *A = c.A;
-    IN_SHARED(A);
-    const float csum = p1_csum(lst, n, L, c.tid);
-    double tot;
-    const double sst = sbase + block_excl_scan<double>((double)csum, A->wsd, &tot);
-    p1_tables(c, lst, n, L, csum, sst);
-}
-
-// thread 0 only; continues from the state in `w`
-template <class CX, class V>
-__device__ void p1_walk(CX &c, V lst, int n, int L, bool locate, float target, Walker &w) {
-    auto *A = c.A;
-    IN_SHARED(A);
-    const int nseg = A->nseg;
-    const double *PA = A->u.p1.pa, *PB = A->u.p1.pb;
-    for (int si = 0; si < nseg && !(locate && w.found); si++) {
-        const int t0 = A->u.p1.seg[si];
-        const int t1 = (si + 1 < nseg) ? (int)A->u.p1.seg[si + 1] : NT;
-        const int j = A->u.p1.ja[t0];
-        const int e0 = min(n, t0 * L), e1 = min(n, t1 * L);
-        if (e1 <= e0) break;  // chunks past the end of the list are empty
-        if (j == SUS) {
-            if (A->u.p1.csum[t0] != 0.0f) p1_sim(lst, e0, e1, locate, target, w);
-            continue;
-        }
-        const bool dual = A->u.p1.dual[t0] != 0;
-        const double pa0 = PA[t0], pa1 = PA[t1], pb0 = PB[t0], pb1 = PB[t1];
-        if (pa1 == pa0 && pb1 == pb0) continue;  // every term rounds to nothing in either binade
-        bool ok = false;
-        if (w.s > 0.0f) {
-            const int js = fexpo(w.s);
-            const double sd = (double)w.s;
-            // step over chunks [ta, tb) with table P, valid while the sum stays below lim
-            auto bulk = [&](const double *P, int ta, int tb, double lim) -> bool {
-                double sn = (double)w.s + (P[tb] - P[ta]);
-                if (!(sn < lim)) return false;
-                if (locate && target < (float)sn) {
-                    int lo_ = ta, hi_ = tb - 1;  // first chunk whose end value exceeds the target
-                    while (lo_ < hi_) {
-                        int mid = (lo_ + hi_) >> 1;
-                        if (target < (float)((double)w.s + (P[mid + 1] - P[ta]))) hi_ = mid;
-                        else lo_ = mid + 1;
-                    }
-                    w.s = (float)((double)w.s + (P[lo_] - P[ta]));
-                    p1_sim(lst, min(n, lo_ * L), min(n, (lo_ + 1) * L), true, target, w);
-                    return true;
-                }
-                w.s = (float)sn;
-                return true;
-            };
-            if (!dual) {
-                if (js == j) ok = bulk(PA, t0, t1, ldexp(1.0, j + 1));
-            } else if (js == j + 1) {
-                ok = bulk(PB, t0, t1, ldexp(1.0, j + 2));
-            } else if (js == j) {
-                const double lim = ldexp(1.0, j + 1);
-                if (sd + (pa1 - pa0) < lim) {
-                    ok = bulk(PA, t0, t1, lim);
-                } else {
-                    // the running sum leaves binade j inside this segment: find the chunk
-                    int lo_ = t0, hi_ = t1 - 1;
-                    while (lo_ < hi_) {
-                        int mid = (lo_ + hi_) >> 1;
-                        if (sd + (PA[mid + 1] - pa0) >= lim) hi_ = mid;
-                        else lo_ = mid + 1;
-                    }
-                    const int ts = lo_;
-                    bool fine = true;
-                    if (ts > t0) fine = bulk(PA, t0, ts, lim);
-                    if (fine) {
-                        ok = true;
-                        if (!(locate && w.found)) {
-                            p1_sim(lst, min(n, ts * L), min(n, (ts + 1) * L), locate, target, w);
-                            if (!(locate && w.found) && ts + 1 < t1) {
-                                if (!(fexpo(w.s) == j + 1 && bulk(PB, ts + 1, t1, ldexp(1.0, j + 2)))) {
-                                    w.slow = 1;
-                                    p1_sim(lst, min(n, (ts + 1) * L), e1, locate, target, w);
-                                }
-                            }
-                        }
-                    }
-                }
-            }
-        }
-        if (!ok) {
-            w.slow = 1;
-            p1_sim(lst, e0, e1, locate, target, w);
-        }
-    }
-}
 
 // The whole list, exactly: in one go when it sits in shared memory, else in blocks of bare
 // values staged there (`vals`, VBLK entries) with the exact sum carried from block to block.
@@ -719,194 +384,6 @@ __device__ void p1_run(Ctx &c, const LView &lv, unsigned int *vals, bool locate,
     __syncthreads();
 }
 
-// =============================================================================
-// Histogram search: thread t owns bins NBINS-1-BPT*t-i (i < BPT), so a scan over the
-// threads runs through the bins in descending order.
-// =============================================================================
-// A bin's integer mass is kept as two sums, of the low MASS_SPLIT bits of each contribution and of
-// the rest: contributions are below 2^27 (32 elements of less than 2^22 units each) and a bin holds
-// fewer than 2^20 elements, so neither sum can wrap, and the additions need no return value.
-constexpr int MASS_SPLIT = 11;
-constexpr unsigned int MASS_LO_MASK = (1u << MASS_SPLIT) - 1u;
-struct BinQuery {
-    unsigned long long m0, xq;       // mass event: m0 + cum_q >= xq   (xq = ~0 disables)
-    unsigned long long pos0, nstop;  // count event: pos0 + cum_c >= nstop (nstop = ~0 disables)
-    int specbin;                     // stop at this bin (-1 disables)
-    int bin_hi;                      // only bins below this one count (NBINS = all)
-    const unsigned int *spec_bits;   // or: stop at any bin whose bit is set here (nullptr = use specbin)
-    const unsigned int *hq, *hqh, *hc;  // per bin: integer mass (low MASS_SPLIT bits summed, the rest summed) and count
-};
-
-// `bin_load(b, q, n)` gives bin b's integer mass and count (one thread block's tables, or the
-// sum over the tables of a cluster's thread blocks).
-template <class CX, class LD>
-__device__ void find_event_bin_with(CX &c, const BinQuery &qy, LD bin_load) {
-    auto *A = c.A;
-    IN_SHARED(A);
-    unsigned long long q[BPT], n[BPT], sq = 0, sn = 0;
-#pragma unroll
-    for (int i = 0; i < BPT; i++) {
-        const int b = NBINS - 1 - BPT * c.tid - i;
-        const bool live = b < qy.bin_hi;
-        q[i] = 0ull; n[i] = 0ull;
-        if (live) bin_load(b, q[i], n[i]);
-        sq += q[i]; sn += n[i];
-    }
-    unsigned long long tq, tc;
-    const unsigned long long eq = block_excl_scan<unsigned long long>(sq, A->wsu, &tq);
-    const unsigned long long ec = block_excl_scan<unsigned long long>(sn, A->wsu, &tc);
-    __syncthreads();
-    if (c.tid == 0) { A->evt_thread = 0x7fffffff; A->tot_q = tq; A->tot_c = tc; A->hit_bin = -1; }
-    __syncthreads();
-    int hit = -1;
-    unsigned long long cq = eq, cc = ec, hq_before = 0, hc_before = 0;
-#pragma unroll
-    for (int i = 0; i < BPT; i++) {
-        const int b = NBINS - 1 - BPT * c.tid - i;
-        const unsigned long long q1 = cq + q[i], c1 = cc + n[i];
-        const bool pr = (qy.xq != ~0ull && qy.m0 + q1 >= qy.xq) || (qy.nstop != ~0ull && qy.pos0 + c1 >= qy.nstop) ||
-                        (qy.spec_bits ? (b < qy.bin_hi && ((qy.spec_bits[b >> 5] >> (b & 31)) & 1u)) : (b <= qy.specbin));
-        if (pr && hit < 0) { hit = b; hq_before = cq; hc_before = cc; }
-        cq = q1; cc = c1;
-    }
-    if (hit >= 0) atomicMin(&A->evt_thread, c.tid);
-    __syncthreads();
-    if (A->evt_thread == c.tid) { A->hit_bin = hit; A->hit_qbefore = hq_before; A->hit_cbefore = hc_before; }
-    __syncthreads();
-}
-
-template <class CX>
-__device__ void find_event_bin(CX &c, const BinQuery &qy) {
-    find_event_bin_with(c, qy, [&](int b, unsigned long long &q, unsigned long long &n) {
-        q = (unsigned long long)qy.hq[b] + ((unsigned long long)qy.hqh[b] << MASS_SPLIT);
-        n = qy.hc[b];
-    });
-}
-
-// Sort the candidate list (descending probability, ascending token id).
-template <class CX>
-__device__ void sort_cands(CX &c, int n) {
-    auto *A = c.A;
-    IN_SHARED(A);
-    int n2 = 2;
-    while (n2 < n) n2 <<= 1;
-    __syncthreads();
-    for (int i = n + c.tid; i < n2; i += NT) A->cand[i] = 0ull;
-    bitonic_desc(A->cand, n2, c.tid);
-    for (int i = c.tid; i < n; i += NT) A->pc[i] = key_val(A->cand[i]);
-    __syncthreads();
-}
-
-// Adds the sorted candidates pc[0..nb) to the running sum `s0` in order, exactly as the
-// reference's loops do (sample.mojo:497-506, 585-590), and stops at the first event: the sum
-// reaching x_ge, exceeding x_gt, or the count reaching nstop. Where the sum stays in one
-// binade the additions are integers and the first event is found with a block scan; a
-// candidate that takes the sum across a power of two is added by itself and the scan resumes
-// behind it; a rounding tie or a candidate >= sum/4 sends the rest to one thread.
-// Results: A->b_event, b_s, b_pos, and for an event b_idx (token), b_p, b_aux (tie).
-template <class CX>
-__device__ void walk_sorted(CX &c, int nb, float s0, long long pos0, float x_ge, float x_gt, bool counting,
-                            long long nstop) {
-    auto *A = c.A;
-    IN_SHARED(A);
-    constexpr int EPT = NC / NT;
-    __syncthreads();
-    if (c.tid == 0) { A->b_s = s0; A->b_event = EV_NONE; A->b_aux = -1; A->b_idx = 0; }
-    __syncthreads();
-    for (int round = 0; round < 256; round++) {
-        const int st = A->b_idx;      // candidates before st are consumed
-        const float s = A->b_s;
-        if (A->b_event != EV_NONE || st >= nb) break;
-        const bool have_s = s > 0.0f;
-        const int j = have_s ? fexpo(s) : 0;
-        const bool ok = have_s && j >= -100 && j <= 100;
-        const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1), inv_u = fpow2(23 - j);
-        unsigned int q[EPT];
-        bool special = !ok;
-#pragma unroll
-        for (int e = 0; e < EPT; e++) {
-            const int i = st + c.tid * EPT + e;
-            q[e] = 0u;
-            if (i < nb && ok) {
-                const float p = A->pc[i];
-                const float qf = __fsub_rn(__fadd_rn(p, Cm), Cm);
-                const float r = __fsub_rn(p, qf);
-                if (fabsf(r) == halfu || p >= bigthr) special = true;
-                q[e] = __float2uint_rn(__fmul_rn(qf, inv_u));
-            }
-        }
-        if (__syncthreads_or(special ? 1 : 0)) {
-            // one thread, one addition at a time, from st to the first event or the end
-            if (c.tid == 0) {
-                float acc = s;
-                long long pos = pos0 + st;
-                int ev = EV_NONE, at = -1;
-                for (int i = st; i < nb; i++) {
-                    acc = __fadd_rn(acc, A->pc[i]);
-                    pos++;
-                    if (acc >= x_ge) ev = EV_CUT;
-                    else if (x_gt < acc) ev = EV_DRAW;
-                    else if (counting && pos >= nstop) ev = EV_LIMIT;
-                    if (ev != EV_NONE) { at = i; break; }
-                }
-                A->b_s = acc; A->b_event = ev; A->b_aux = at; A->b_idx = nb;
-            }
-            __syncthreads();
-            break;
-        }
-        unsigned long long loc = 0;
-#pragma unroll
-        for (int e = 0; e < EPT; e++) loc += q[e];
-        unsigned long long tot;
-        const unsigned long long ex = block_excl_scan<unsigned long long>(loc, A->wsu, &tot);
-        const unsigned long long m0 = (unsigned long long)((double)s * (double)inv_u);
-        unsigned long long X = 1ull << 24;
-        if (x_ge < 3.0e38f) { double t = ceil((double)x_ge * (double)inv_u); if (t < (double)X) X = t <= 0.0 ? 0ull : (unsigned long long)t; }
-        if (x_gt < 3.0e38f) { double t = floor((double)x_gt * (double)inv_u) + 1.0; if (t < (double)X) X = t <= 0.0 ? 0ull : (unsigned long long)t; }
-        __syncthreads();
-        if (c.tid == 0) A->evt_thread = 0x7fffffff;
-        __syncthreads();
-        unsigned long long m = m0 + ex, mb_first = 0;
-        int first = -1;
-#pragma unroll
-        for (int e = 0; e < EPT; e++) {
-            const int i = st + c.tid * EPT + e;
-            const unsigned long long mb = m;
-            m += q[e];
-            if (i < nb && first < 0 && (m >= X || (counting && pos0 + i + 1 >= nstop))) { first = i; mb_first = mb; }
-        }
-        if (first >= 0) atomicMin(&A->evt_thread, first);
-        __syncthreads();
-        const int hit = A->evt_thread;
-        if (hit == 0x7fffffff) {
-            if (c.tid == 0) { A->b_s = (float)((double)(m0 + tot) * (double)fpow2(j - 23)); A->b_idx = nb; }
-            __syncthreads();
-            break;
-        }
-        if (first == hit) {
-            // the true addition at the candidate the integers point at decides what happened there
-            const float sb = (float)((double)mb_first * (double)fpow2(j - 23));
-            const float acc = __fadd_rn(sb, A->pc[hit]);
-            int ev = EV_NONE;
-            if (acc >= x_ge) ev = EV_CUT;
-            else if (x_gt < acc) ev = EV_DRAW;
-            else if (counting && pos0 + hit + 1 >= nstop) ev = EV_LIMIT;
-            A->b_s = acc; A->b_event = ev; A->b_aux = (ev != EV_NONE) ? hit : -1; A->b_idx = hit + 1;
-        }
-        __syncthreads();
-    }
-    if (c.tid == 0) {
-        const int at = A->b_aux;
-        const int consumed = (A->b_event != EV_NONE) ? at + 1 : nb;
-        A->b_pos = pos0 + consumed;
-        if (A->b_event != EV_NONE) {
-            const float p = A->pc[at];
-            A->b_idx = key_idx(A->cand[at]); A->b_p = p;
-            A->b_aux = ((at > 0 && A->pc[at - 1] == p) || (at + 1 < nb && A->pc[at + 1] == p)) ? 1 : 0;
-        }
-    }
-    __syncthreads();
-}
 
 // =============================================================================
 // The descending walk past the sorted head (sample.mojo:492-506 and :580-590 on rows
@@ -1044,7 +521,7 @@ __device__ void descend(Ctx &c, const LView &lv, Walk &w, float x_ge, float x_gt
         if (nb > NC && lvl < 3) {
             w.s = s_bin; w.pos = pos_bin;
             w.tau = bhi < w.tau ? bhi : w.tau;
-            lo = blo; shift = (lvl == 1) ? 8 : 0; lvl++;
+            lo = blo; shift = (lvl == 1) ? BIN_SHIFT2 : 0; lvl++;
             c.status |= MOLLA_ROW_SLOW_PATH;
             continue;
         }
@@ -1224,7 +701,7 @@ __device__ bool helped_convert(Ctx &c, const BatchArgs &a, unsigned long long *w
                                bool mark_head, const MassTable &mt) {
     Aux *A = c.A;
     IN_SHARED(A);
-    HelpSlot *hs = a.help + blockIdx.x;
+    HelpSlot *hs = static_cast<HelpSlot *>(a.help) + blockIdx.x;
     unsigned int *gt = a.help_tables + (size_t)blockIdx.x * HELP_TABLE_WORDS;
     __syncthreads();
     for (int i = c.tid; i < HELP_MASS_WORDS; i += NT) __stcg(gt + i, 0u);
@@ -1297,7 +774,7 @@ __device__ __forceinline__ void gather_segment(Ctx &c, const unsigned long long 
 __device__ bool helped_gather(Ctx &c, const BatchArgs &a, const unsigned long long *wl_seg, unsigned int tau0, int hb) {
     Aux *A = c.A;
     IN_SHARED(A);
-    HelpSlot *hs = a.help + blockIdx.x;
+    HelpSlot *hs = static_cast<HelpSlot *>(a.help) + blockIdx.x;
     unsigned long long *gc = reinterpret_cast<unsigned long long *>(a.help_tables + (size_t)blockIdx.x * HELP_TABLE_WORDS + HELP_MASS_WORDS);
     __syncthreads();
     if (c.tid < NWARP) hs->count[c.tid] = A->woff[c.tid + 1] - A->woff[c.tid];
@@ -1362,7 +839,7 @@ __device__ void help_others(Ctx &c, const BatchArgs &a) {
         // every thread looks at one slot; the nearest open one after the slot served last is tried
         for (int sidx = c.tid; sidx < nslots; sidx += NT) {
             if (sidx == (int)blockIdx.x) continue;
-            const volatile HelpSlot *hs = a.help + sidx;
+            const volatile HelpSlot *hs = static_cast<HelpSlot *>(a.help) + sidx;
             if (hs->open == 1 && hs->claim < NWARP) atomicMin(&A->evt_thread, (sidx - next + nslots) % nslots);
         }
         __syncthreads();
@@ -1372,7 +849,7 @@ __device__ void help_others(Ctx &c, const BatchArgs &a) {
             int found = -1, unit = 0;
             if (pick != 0x7fffffff) {
                 const int sidx = (pick + next) % nslots;
-                unit = atomicAdd(&a.help[sidx].claim, 1);
+                unit = atomicAdd(&static_cast<HelpSlot *>(a.help)[sidx].claim, 1);
                 if (unit < NWARP) { found = sidx; A->ncand = sidx; }
             } else {
                 __nanosleep(100);
@@ -1382,7 +859,7 @@ __device__ void help_others(Ctx &c, const BatchArgs &a) {
         __syncthreads();
         const int sidx = A->evt_thread, u = A->specbin;
         if (sidx < 0) continue;
-        HelpSlot *hs = a.help + sidx;
+        HelpSlot *hs = static_cast<HelpSlot *>(a.help) + sidx;
         __threadfence();
         unsigned long long *seg = a.wlist + (size_t)sidx * 2 * NWARP * (size_t)a.R + (size_t)u * (size_t)a.R;
         if (__ldcg(&hs->kind) == 1) {
@@ -1502,83 +979,6 @@ __device__ bool descend_masses(Ctx &c, const BatchArgs &a, bool helped, const LV
     return false;
 }
 
-// =============================================================================
-// Typical-p (sample.mojo:525-567) on a kept set that lies inside the sorted head: m
-// probabilities pc[0..m), descending, ids in hidx. Entropy H = -sum p log p, added up
-// in that order in fp32; distance |-log p - H|; stable order by distance; the smallest
-// prefix whose probabilities add up to typ; then the draw of sample.mojo:569-594 over
-// that prefix in that order. The sums run on one thread (m is at most the head's 1024).
-// Results: A->b_idx (token), b_p, b_sum, b_target, b_aux (tie bits).
-// =============================================================================
-template <class CX>
-__device__ void typical_head(CX &c, int m, float typ, float u01) {
-    auto *A = c.A;
-    IN_SHARED(A);
-    float *lg = reinterpret_cast<float *>(A->cand);             // log p
-    float *tt = lg + HEADC;                                     // p * log p
-    unsigned long long *keys = reinterpret_cast<unsigned long long *>(&A->u);  // HEADC sort keys
-    __syncthreads();
-    for (int i = c.tid; i < m; i += NT) {
-        const float p = A->pc[i];
-        const float l = (p > 0.0f) ? logf_pinned(p) : 0.0f;
-        lg[i] = l;
-        tt[i] = __fmul_rn(p, l);
-    }
-    __syncthreads();
-    if (c.tid == 0) {
-        float ent = 0.0f;
-        for (int i = 0; i < m; i++)
-            if (A->pc[i] > 0.0f) ent = __fsub_rn(ent, tt[i]);
-        A->b_s = ent;
-    }
-    __syncthreads();
-    const float ent = A->b_s;
-    int n2 = 2;
-    while (n2 < m) n2 <<= 1;
-    for (int i = c.tid; i < n2; i += NT) {
-        unsigned long long key = 0ull;
-        if (i < m) {
-            const float sur = (A->pc[i] > 0.0f) ? -lg[i] : 0.0f;
-            const float d = fabsf(__fsub_rn(sur, ent));
-            // descending keys = ascending distance, and among equal distances ascending position (stable)
-            key = ((unsigned long long)(~__float_as_uint(d)) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)i);
-        }
-        keys[i] = key;
-    }
-    bitonic_desc(keys, n2, c.tid);
-    if (c.tid == 0) {
-        float s = 0.0f;
-        int kept = m;
-        for (int j = 0; j < m; j++) {
-            const int i = (int)(0xFFFFFFFFu - (unsigned int)(keys[j] & 0xFFFFFFFFull));
-            s = __fadd_rn(s, A->pc[i]);
-            A->pre[j] = s;
-            if (s >= typ) { kept = j + 1; break; }
-        }
-        const float sum = A->pre[kept - 1];
-        int at = kept - 1;
-        float target = 0.0f;
-        if (sum <= 0.0f) at = 0;  // sample.mojo:583-584
-        else {
-            target = __fmul_rn(u01, sum);
-            for (int j = 0; j < kept; j++)
-                if (target < A->pre[j]) { at = j; break; }
-        }
-        const int i_at = (int)(0xFFFFFFFFu - (unsigned int)(keys[at] & 0xFFFFFFFFull));
-        int tie = 0;
-        if (A->hidx[i_at] & 0x80000000u) tie |= MOLLA_ROW_CHOSEN_TIE;
-        // the last one kept and the first one dropped equally probable: which of them the
-        // reference keeps depends on the order its sort left them in
-        if (kept < m) {
-            const int i_last = (int)(0xFFFFFFFFu - (unsigned int)(keys[kept - 1] & 0xFFFFFFFFull));
-            const int i_next = (int)(0xFFFFFFFFu - (unsigned int)(keys[kept] & 0xFFFFFFFFull));
-            if (A->pc[i_last] == A->pc[i_next]) tie |= MOLLA_ROW_TOPP_TIE;
-        }
-        A->b_idx = (int)(A->hidx[i_at] & 0x7fffffffu); A->b_p = A->pc[i_at];
-        A->b_sum = sum; A->b_target = target; A->b_aux = tie;
-    }
-    __syncthreads();
-}
 
 // Between the two all-gathers of the vocab-sharded form: one thread per row folds the shards'
 // stage-1 summaries into what stage 2 needs (the global maximum, the head threshold, a bound on
@@ -2392,8 +1792,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
     if (a.help && !(a.knobs & 8)) help_others(c, a);  // no rows left: lend a hand to the blocks still on a long list
 }
 
-#include "molla_rows_cluster.cuh"
-
 // =============================================================================
 // Logprobs of the raw logits (sample.mojo:268-293): one CTA per row, the row is
 // read twice (second read is an L2 hit for blocks that fit).
@@ -2569,7 +1967,7 @@ int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, in
     if (with_help && a.mode == 0 && grid > 1) {
         const size_t ctas = (size_t)(a.B < sms ? a.B : sms);
         char *hb = (char *)d_workspace + WS_HEADER + ctas * 2 * (size_t)NWARP * (size_t)a.R * 8;
-        a.help = (HelpSlot *)hb;
+        a.help = hb;
         a.help_tables = (unsigned int *)(hb + ctas * sizeof(HelpSlot));
         e = cudaMemsetAsync(hb, 0, ctas * sizeof(HelpSlot), st);
         if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "workspace clear failed: %s", cudaGetErrorString(e));
@@ -2586,75 +1984,15 @@ int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, in
     return MOLLA_OK;
 }
 
-// ---- one row per cluster -------------------------------------------------------------
-// How a vocabulary of V logits is laid over a cluster: blocks per cluster (0 = too wide, the
-// streaming kernel takes the call), logits per block (a multiple of four: bulk copies start on
-// 16-byte boundaries) and logits per thread (odd: conflict-free shared-memory strides).
-struct ClusterShape { int G, Vc, L; };
-
-ClusterShape cluster_shape(int V) {
-    for (int G = 1; G <= CL_MAX_G; G *= 2) {
-        const int Vc = ((((V + G - 1) / G) + 3) / 4) * 4;
-        int L = (Vc + NT - 1) / NT;
-        if ((L & 1) == 0) L += 1;
-        if (L <= CL_LMAX) return ClusterShape{G, Vc, L};
-    }
-    return ClusterShape{0, 0, 0};
-}
-
-constexpr size_t CL_SMEM = (size_t)CL_CAPF * 4 + ((sizeof(AuxC) + 15) / 16) * 16;
-
-// Whether this device can hold a cluster of G of the kernel's blocks (asked once per device and size).
-bool cluster_fits(int G) {
-    static int known[NOALLOC_MAX_DEVICES][CL_MAX_G + 1] = {};  // 0 unknown, 1 yes, -1 no
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return false;
-    if (known[dev][G]) return known[dev][G] > 0;
-    bool ok = cudaFuncSetAttribute(sample_rows_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CL_SMEM) == cudaSuccess;
-    if (ok) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)G); cfg.blockDim = dim3(NT); cfg.dynamicSmemBytes = CL_SMEM;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeClusterDimension;
-        at[0].val.clusterDim.x = (unsigned)G; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-        cfg.attrs = at; cfg.numAttrs = 1;
-        int n = 0;
-        ok = cudaOccupancyMaxActiveClusters(&n, sample_rows_cluster_kernel, &cfg) == cudaSuccess && n > 0;
-    }
-    if (!ok) (void)cudaGetLastError();
-    known[dev][G] = ok ? 1 : -1;
-    return ok;
-}
-
 // The ordinary entry points' launch: the cluster kernel when the vocabulary fits a cluster, else
 // the streaming kernel with its lists in the workspace.
 int launch_sampling(const BatchArgs &args_in, void *d_workspace, cudaStream_t st) {
-    const ClusterShape cs = cluster_shape(args_in.V);
     static const bool cluster_on = [] { const char *e = getenv("MOLLA_SAMPLE_CLUSTER"); return e && e[0] == '1'; }();
-    if (!cluster_on || cs.G == 0 || !cluster_fits(cs.G)) return launch_rows(args_in, d_workspace, st, 0x7fffffff, true);
-    BatchArgs a = args_in;
-    a.G = cs.G; a.Vc = cs.Vc; a.L = cs.L;
-    a.Vg = a.V; a.col0 = 0; a.mode = 0;
-    a.order = nullptr;
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    // clusters start in grid order: when not all rows can start at once, the dearest go first
-    if (a.B * cs.G > sms && a.B <= ORDER_CAP && a.temperature) {
-        int *order = (int *)((char *)d_workspace + 256);
-        order_rows_kernel<<<1, NT, 0, st>>>(a.temperature, a.top_k, a.slot, a.B, order);
-        a.order = order;
+    if (cluster_on) {
+        const int rc = molla_cluster_launch(args_in, d_workspace, st, g_err, sizeof(g_err));
+        if (rc != MOLLA_CLUSTER_DECLINED) return rc;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)a.B * (unsigned)cs.G); cfg.blockDim = dim3(NT);
-    cfg.dynamicSmemBytes = CL_SMEM; cfg.stream = st;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = (unsigned)cs.G; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, sample_rows_cluster_kernel, a);
-    if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
-    return MOLLA_OK;
+    return launch_rows(args_in, d_workspace, st, 0x7fffffff, true);
 }
 
 }  // namespace

@@ -58,7 +58,10 @@ def test_noalloc_matches_the_ordinary_entry_point_twice(dev, lib):
         torch.cuda.synchronize()
         tok, st, ch, ids, lps = noalloc(logits, p, top_n)
         assert np.array_equal(tok, ref["tokens"].cpu().numpy())
-        assert np.array_equal(st, ref["row_status"].cpu().numpy())
+        # the status words agree except for the informational bit that says a sequential fallback
+        # ran (the two entry points do not run the same kernel)
+        info = np.int32(capi.ROW_SLOW_PATH)
+        assert np.array_equal(st & ~info, ref["row_status"].cpu().numpy() & ~info)
         assert np.array_equal(ch, ref["chosen_logprob"].cpu().numpy())
         assert np.array_equal(ids, ref["top_ids"].cpu().numpy())
         assert np.array_equal(lps, ref["top_logprobs"].cpu().numpy())
