@@ -22,6 +22,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stddef.h>
 #include <stdio.h>
 
 #include "molla_exact.cuh"
@@ -34,10 +35,15 @@ namespace {
 constexpr int CL_MAX_G = 8;                  // thread blocks per cluster at most (the portable limit)
 constexpr int CL_LMAX = 75;                  // logits per thread at most (odd: conflict-free strides)
 constexpr int CL_CAPF = NT * CL_LMAX;        // logits per thread block at most: 38400 (150 KB)
-constexpr int XT = HEAD_NEED;                // thread maxima every block shows the others
 constexpr int CL_PIECE = 4096;               // floats per bulk copy
+constexpr int TIE_CAP = 64;                   // rounding ties a walk resolves by parity; more send it the slow way
+constexpr int TBINS = NT;                    // bins of the threads' maxima by distance below the row's maximum
+constexpr float TRES = (float)(NT / 32);     // bins per unit of logit: the bins cover 32 units
+// positions listed for the balanced evaluation of the second pass: they use the space of the bin
+// tables, the candidates and their values (all idle then)
+constexpr int PLIST_CAP = (3 * NBINS * 4 + NC * 8 + NC * 4) / 2;
 
-#define CSTAMP(i) do { if (a.prof && leader && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
+#define CSTAMP(i) do { if (a.prof && leader && c.tid == 0) a.prof[(long long)r * 32 + (i)] = clock64(); } while (0)
 
 struct __align__(16) AuxC {
     union {
@@ -69,14 +75,16 @@ struct __align__(16) AuxC {
     float b_s; unsigned int b_tau; int b_event; int b_idx; float b_p; long long b_pos; int b_aux;
     float b_sum; float b_target;
     uint64_t mbar;
-    float thr[NT];                       // per thread range: the threshold of the second pass
-    unsigned short ppos[NWARP][128];     // per warp: positions of the kept elements of a 128-element block
+    unsigned int thist[TBINS];           // the threads' maxima by distance below the block's maximum
     // what the blocks of the cluster write into each other (slot = the writer's rank)
     float x1_max[CL_MAX_G]; int x1_idx[CL_MAX_G]; int x1_eq[CL_MAX_G]; unsigned int x1_status[CL_MAX_G];
-    float x2_total[CL_MAX_G]; float x2_top[CL_MAX_G][XT];
+    float x2_total[CL_MAX_G];
     double x3_tot[CL_MAX_G]; int x3_n[CL_MAX_G];
     int x4_n[CL_MAX_G]; unsigned long long x5_key[CL_MAX_G];
     float ch_s; int ch_found, ch_at, ch_slow;   // the exact sum on its way from range to range
+    // elements of a walk that would round on a tie: their keys, bins, the mass before them
+    int ntie[2]; unsigned long long tkey[TIE_CAP]; int tbin[TIE_CAP]; unsigned long long tpq[TIE_CAP], tpqm[TIE_CAP], tabove[TIE_CAP], tc[TIE_CAP];
+    unsigned int tbits[NBINS / 32];
     int r_kind; int r_idx; float r_s; long long r_pos; unsigned int r_status;  // the leader's word after the head
 };
 
@@ -102,7 +110,7 @@ struct ClGeo {          // where this thread block stands
 struct ClSum { float s; int found; int at; int slow; };
 
 __device__ ClSum cluster_exact_sum(cg::cluster_group &cl, CtxC &c, const ClGeo &g, const unsigned int *bits,
-                                   bool locate, float target, long long *stamps = nullptr) {
+                                   bool locate, float target, long long *stamps = nullptr, long long *stamps2 = nullptr) {
     AuxC *A = c.A;
     IN_SHARED(A);
     IN_SHARED(bits);
@@ -124,8 +132,10 @@ __device__ ClSum cluster_exact_sum(cg::cluster_group &cl, CtxC &c, const ClGeo &
             if (q == 0) { w.s = 0.0f; w.found = 0; w.at = -1; w.slow = 0; }
             else { w.s = A->ch_s; w.found = A->ch_found; w.at = A->ch_at; w.slow = A->ch_slow; }
             if (!(locate && w.found)) {
+                const long long tw0 = clock64();
                 p1_walk(c, vals, g.nloc, g.L, locate, target, w);
                 if (w.found) w.at += g.c0;
+                if (stamps2) { stamps2[q] = clock64() - tw0; stamps2[4 + q] = w.nsim * 100000ll + w.nel; stamps2[8 + q] = A->nseg; }
             }
             if (q + 1 < g.G) {
                 AuxC *nx = cl.map_shared_rank(A, q + 1);
@@ -182,8 +192,14 @@ __device__ int cluster_nth_equal(cg::cluster_group &cl, CtxC &c, const ClGeo &g,
 // value bin (each block its range; the tables are added up across the cluster as they are
 // read), consumes whole bins up to the first one holding an event, gathers that bin into the
 // leader's candidate buffer, and the leader sorts it and adds it element by element.
+//
+// An element whose addition would be a rounding tie (its value is an odd multiple of half the
+// running sum's unit) rounds up or down with the parity of the sum before it. Such elements do
+// not stop a phase: they are listed, a second pass adds up what precedes each of them inside
+// its own bin, and one thread then resolves them from the top down, each from the exact integer
+// sum before it; their contributions go into their bins' masses before the event is searched.
 __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, const unsigned int *bits,
-                                ClWalk &w, float x_ge, float x_gt, long long nstop) {
+                                ClWalk &w, float x_ge, float x_gt, long long nstop, long long *dbg = nullptr) {
     AuxC *A = c.A;
     IN_SHARED(A);
     IN_SHARED(bits);
@@ -192,16 +208,22 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
     int lvl = 1;
     unsigned int lo = 0u;
     int shift = BIN_SHIFT;
+    bool tie_mode = true;
+    if (c.tid == 0) { A->ntie[0] = 0; A->ntie[1] = 0; }
     for (int phase = 0; phase < 8192; phase++) {
         cl.sync();  // nobody still reads the tables or the leader's results of the phase before
+        long long tp0 = clock64();
+#define DT(k) do { if (dbg && c.tid == 0) { const long long t_ = clock64(); dbg[k] += t_ - tp0; tp0 = t_; } } while (0)
         for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0u; A->u.h.hqh[i] = 0u; A->u.h.hc[i] = 0u; }
-        if (c.tid == 0) { A->specbin = -1; A->ncand = 0; }
+        for (int i = c.tid; i < NBINS / 32; i += NT) A->tbits[i] = 0u;
+        if (c.tid == 0) { A->specbin = -1; A->ncand = 0; A->ntie[(phase + 1) & 1] = 0; }  // the other blocks add to this phase's counter already
         __syncthreads();
         const bool have_s = w.s > 0.0f;
         const int j = have_s ? fexpo(w.s) : 0;
         const bool binade_ok = have_s && j >= -100 && j <= 100;
         const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1);
         const float inv_u = fpow2(23 - j);
+        const bool ties_listed = tie_mode && lvl == 1 && binade_ok;
         for (int i = c.tid; i < g.nloc; i += NT) {
             const unsigned int eb = bits[i];
             if (eb == 0u || eb >= w.tau || eb < lo) continue;
@@ -210,8 +232,15 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
             const float p = __uint_as_float(eb);
             const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
             const float rr = __fsub_rn(p, q);
-            if (fabsf(rr) == halfu || p >= bigthr) {
+            const bool tie = fabsf(rr) == halfu, big = p >= bigthr;
+            if (big || (tie && !ties_listed)) {
                 sred_max(&A->specbin, bin);
+                if (counting) sred_add(&A->u.h.hc[bin], 1u);
+                continue;
+            }
+            if (tie) {
+                const int pos = atomicAdd(&lead->ntie[phase & 1], 1);
+                if (pos < TIE_CAP) { lead->tkey[pos] = make_key(eb, g.c0 + i); lead->tbin[pos] = bin; }
                 if (counting) sred_add(&A->u.h.hc[bin], 1u);
                 continue;
             }
@@ -223,6 +252,35 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
             if (counting) sred_add(&A->u.h.hc[bin], 1u);
         }
         cl.sync();
+        const int ntie = ties_listed ? lead->ntie[phase & 1] : 0;
+        DT(3);
+        if (dbg && c.tid == 0) { dbg[0] += 1; dbg[1] += ntie; }
+        if (ntie > TIE_CAP) { tie_mode = false; c.status |= MOLLA_ROW_SLOW_PATH; continue; }  // too many: they stop phases instead
+        if (ntie > 0) {
+            // what precedes each listed element inside its own bin (descending value, then ascending id)
+            if (c.tid < ntie) {
+                const int b = lead->tbin[c.tid];
+                A->tkey[c.tid] = lead->tkey[c.tid]; A->tbin[c.tid] = b; A->tpq[c.tid] = 0ull;
+                sred_or(&A->tbits[b >> 5], 1u << (b & 31));
+            }
+            __syncthreads();
+            for (int i = c.tid; i < g.nloc; i += NT) {
+                const unsigned int eb = bits[i];
+                if (eb == 0u || eb >= w.tau || eb < lo) continue;
+                const int bin = (int)((eb - lo) >> shift);
+                if (!((A->tbits[bin >> 5] >> (bin & 31)) & 1u)) continue;
+                const float p = __uint_as_float(eb);
+                const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
+                const float rr = __fsub_rn(p, q);
+                if (fabsf(rr) == halfu || p >= bigthr) continue;
+                const unsigned long long qu = (unsigned long long)__float2uint_rn(__fmul_rn(q, inv_u));
+                const unsigned long long key = make_key(eb, g.c0 + i);
+                for (int t = 0; t < ntie; t++)
+                    if (A->tbin[t] == bin && key > A->tkey[t] && qu) atomicAdd(&A->tpq[t], qu);
+            }
+            cl.sync();
+        }
+        DT(4);
         int specbin = -1;
         for (int o = 0; o < g.G; o++) specbin = max(specbin, cl.map_shared_rank(A, o)->specbin);
         BinQuery qy;
@@ -246,14 +304,63 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         } else {
             qy.pos0 = 0; qy.nstop = 1;  // nothing consumed yet: take the highest non-empty bin
         }
-        find_event_bin_with(c, qy, [&](int b, unsigned long long &q, unsigned long long &n) {
-            unsigned long long ql = 0, qh = 0, nn = 0;
-            for (int o = 0; o < g.G; o++) {
-                const AuxC *ox = cl.map_shared_rank(A, o);
-                ql += ox->u.h.hq[b]; qh += ox->u.h.hqh[b]; nn += ox->u.h.hc[b];
-            }
-            q = ql + (qh << MASS_SPLIT); n = nn;
-        });
+        find_event_bin_adj(c, qy,
+            [&](int b, unsigned long long &q, unsigned long long &n) {
+                unsigned long long ql = 0, qh = 0, nn = 0;
+                for (int o = 0; o < g.G; o++) {
+                    const AuxC *ox = cl.map_shared_rank(A, o);
+                    ql += ox->u.h.hq[b]; qh += ox->u.h.hqh[b]; nn += ox->u.h.hc[b];
+                }
+                q = ql + (qh << MASS_SPLIT); n = nn;
+            },
+            [&](unsigned long long (&q)[BPT], unsigned long long eq) -> bool {
+                if (ntie == 0) return false;
+                // the mass before each listed element: the bins above its own (the thread that owns
+                // the bin knows), what precedes it inside the bin (added up over the blocks)
+                unsigned long long run = eq;
+#pragma unroll
+                for (int i = 0; i < BPT; i++) {
+                    const int b = NBINS - 1 - BPT * c.tid - i;
+                    for (int t = 0; t < ntie; t++)
+                        if (A->tbin[t] == b) A->tabove[t] = run;
+                    run += q[i];
+                }
+                if (c.tid < ntie) {
+                    unsigned long long s_ = 0;
+                    for (int o = 0; o < g.G; o++) s_ += cl.map_shared_rank(A, o)->tpq[c.tid];
+                    A->tpqm[c.tid] = s_; A->tc[c.tid] = 0ull;
+                }
+                __syncthreads();
+                if (c.tid == 0) {
+                    // from the top down (ties above an earlier event never matter: the walk stops there)
+                    unsigned long long done = 0ull, carried = 0ull;  // bit t: resolved; contributions so far
+                    for (int round = 0; round < ntie; round++) {
+                        int best = -1;
+                        for (int t = 0; t < ntie; t++)
+                            if (!((done >> t) & 1ull) && (best < 0 || A->tkey[t] > A->tkey[best])) best = t;
+                        done |= 1ull << best;
+                        const float p = key_val(A->tkey[best]);
+                        const float qf = __fsub_rn(__fadd_rn(p, Cm), Cm);
+                        unsigned long long k = (unsigned long long)__float2uint_rn(__fmul_rn(qf, inv_u));
+                        if (qf > p) k -= 1ull;  // the multiple of the unit below p
+                        const unsigned long long mb = qy.m0 + A->tabove[best] + A->tpqm[best] + carried;
+                        if (qy.xq != ~0ull && mb >= qy.xq) break;  // an event before this element: what lies below does not matter
+                        const unsigned long long ct = k + ((mb + k) & 1ull);
+                        A->tc[best] = ct;
+                        carried += ct;
+                        if (qy.xq != ~0ull && mb + ct >= qy.xq) break;
+                    }
+                }
+                __syncthreads();
+#pragma unroll
+                for (int i = 0; i < BPT; i++) {
+                    const int b = NBINS - 1 - BPT * c.tid - i;
+                    for (int t = 0; t < ntie; t++)
+                        if (A->tbin[t] == b) q[i] += A->tc[t];
+                }
+                return true;
+            });
+        DT(5);
         const int hb = A->hit_bin;
         if (hb < 0) {
             // nothing left in this range triggers an event: consume it whole
@@ -267,17 +374,27 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         const unsigned int blo = lo + ((unsigned int)hb << shift);
         const unsigned long long bhi64 = (unsigned long long)lo + ((unsigned long long)(hb + 1) << shift);
         const unsigned int bhi = bhi64 > 0xFFFFFFFFull ? 0xFFFFFFFFu : (unsigned int)bhi64;
-        // the bin's entries go to the leader (everybody has read the leader's counter of the phase
-        // before by now: it was cleared ahead of the barrier above)
+        // the bin's entries: every block collects its own, then they move to the leader in one piece
+        // (a counter in another block's memory is far too slow to hand out slots one by one)
         for (int i = c.tid; i < g.nloc; i += NT) {
             const unsigned int eb = bits[i];
             if (eb != 0u && eb < w.tau && eb >= blo && eb < bhi) {
-                const int pos = atomicAdd(&lead->ncand, 1);
-                if (pos < NC) lead->cand[pos] = make_key(eb, g.c0 + i);
+                const int pos = satom_add(&A->ncand, 1);
+                if (pos < NC) A->cand[pos] = make_key(eb, g.c0 + i);
             }
         }
+        __syncthreads();
+        if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x4_n[g.rank] = A->ncand;
         cl.sync();
-        const int nb = lead->ncand;
+        int nb = 0, cbase = 0;
+        for (int o = 0; o < g.G; o++) { if (o < g.rank) cbase += A->x4_n[o]; nb += A->x4_n[o]; }
+        if (nb <= NC && g.rank > 0) {
+            const int mine = A->x4_n[g.rank];
+            for (int i = c.tid; i < mine; i += NT) lead->cand[cbase + i] = A->cand[i];
+        }
+        cl.sync();
+        DT(6);
+        if (dbg && c.tid == 0) dbg[2] = nb;
         // what lies above the bin is consumed without an event either way
         const float s_bin = binade_ok ? (float)((double)(qy.m0 + qb) * (double)fpow2(j - 23)) : w.s;
         const long long pos_bin = w.pos + ((counting || !binade_ok) ? (long long)cb : 0);
@@ -323,6 +440,7 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
             walk_sorted(c, nb, s_bin, pos_bin, x_ge, x_gt, counting, nstop);
         }
         cl.sync();
+        DT(7);
         w.s = lead->b_s; w.pos = lead->b_pos; w.tau = blo;
         const int ev = lead->b_event;
         if (ev != EV_NONE) {
@@ -400,7 +518,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         if (a.prof) {
             unsigned long long gt;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-            a.prof[(long long)r * 16 + 11] = (long long)gt; a.prof[(long long)r * 16 + 9] = clock64();
+            a.prof[(long long)r * 32 + 11] = (long long)gt; a.prof[(long long)r * 32 + 9] = clock64();
         }
         if (c.status & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG | MOLLA_ROW_UNSUPPORTED)) token = -1;
         a.tokens[r] = token;
@@ -425,7 +543,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     if (a.prof && leader && c.tid == 0) {
         unsigned long long gt;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-        a.prof[(long long)r * 16 + 10] = (long long)gt; a.prof[(long long)r * 16 + 12] = blockIdx.x;
+        a.prof[(long long)r * 32 + 10] = (long long)gt; a.prof[(long long)r * 32 + 12] = blockIdx.x;
     }
     // ---- 1. this block's range of the row, HBM -> shared memory
     const float *src = a.logits + lrow * a.row_stride + g.c0;
@@ -498,45 +616,72 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
 
     CSTAMP(2);
     // ---- 2. the maximum and its first index (kernel.mojo:571-585, sample.mojo:342-346)
+    const long long n_lim = (k > 0 && k < a.V) ? (long long)k : (long long)a.V;
+    const bool sampled = !greedy && n_lim > 1;  // rows that need more than the maximum
+    const bool topp_on = (P < 1.0f) && (n_lim > 1);
+    const bool pure = !topp_on && n_lim == (long long)a.V;
     const int i0 = c.tid * g.L;
-    float tmax = -INFINITY;
+    float tmax;
+    int tj;
     {
+        // four interleaved runs over the thread's range, each keeping its first maximum
         float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+        int j0 = 0, j1 = 1, j2 = 2, j3 = 3;
         int j = 0;
         for (; j + 4 <= g.L; j += 4) {
-            m0 = fmaxf(m0, rowbuf[i0 + j]); m1 = fmaxf(m1, rowbuf[i0 + j + 1]);
-            m2 = fmaxf(m2, rowbuf[i0 + j + 2]); m3 = fmaxf(m3, rowbuf[i0 + j + 3]);
+            const float x0 = rowbuf[i0 + j], x1 = rowbuf[i0 + j + 1], x2 = rowbuf[i0 + j + 2], x3 = rowbuf[i0 + j + 3];
+            if (x0 > m0) { m0 = x0; j0 = j; }
+            if (x1 > m1) { m1 = x1; j1 = j + 1; }
+            if (x2 > m2) { m2 = x2; j2 = j + 2; }
+            if (x3 > m3) { m3 = x3; j3 = j + 3; }
         }
-        for (; j < g.L; j++) m0 = fmaxf(m0, rowbuf[i0 + j]);
-        tmax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        for (; j < g.L; j++) {
+            const float x0 = rowbuf[i0 + j];
+            if (x0 > m0) { m0 = x0; j0 = j; }
+        }
+        tmax = m0; tj = j0;
+        if (m1 > tmax || (m1 == tmax && j1 < tj)) { tmax = m1; tj = j1; }
+        if (m2 > tmax || (m2 == tmax && j2 < tj)) { tmax = m2; tj = j2; }
+        if (m3 > tmax || (m3 == tmax && j3 < tj)) { tmax = m3; tj = j3; }
     }
-    float cmax;
-    {
-        const float wm = warp_max(tmax);
-        if (c.lane == 0) A->wsf[c.warp] = wm;
-        __syncthreads();
-        cmax = A->wsf[0];
-        for (int w = 1; w < NWARP; w++) cmax = fmaxf(cmax, A->wsf[w]);
-        __syncthreads();
+    float cmax = tmax;
+    int cidx = g.c0 + i0 + tj;
+    block_argmax(c, cmax, cidx);
+    int ceq = 0;
+    if (!greedy && n_lim == 1) {
+        // only a top-k of one asks how many share the maximum (the sort's first element is one of them)
+        int e = 0;
+        for (int j = 0; j < g.L; j++) e += (i0 + j < g.nloc && rowbuf[i0 + j] == cmax) ? 1 : 0;
+        (void)block_excl_scan<int>(e, A->wsi, &ceq);
     }
-    int tfirst = 0x7fffffff, teq = 0;
-    if (tmax == cmax) {
-        for (int j = 0; j < g.L; j++)
-            if (i0 + j < g.nloc && rowbuf[i0 + j] == cmax) { if (tfirst == 0x7fffffff) tfirst = g.c0 + i0 + j; teq++; }
-    }
-    {
-        int f = tfirst, e = teq;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) { f = min(f, __shfl_xor_sync(0xffffffffu, f, o)); e += __shfl_xor_sync(0xffffffffu, e, o); }
-        if (c.lane == 0) { A->wsi[c.warp] = f; A->wsu[c.warp] = (unsigned long long)e; }
-        __syncthreads();
-        if (c.tid < g.G) {
-            int cf = 0x7fffffff, ce = 0;
-            for (int w = 0; w < NWARP; w++) { cf = min(cf, A->wsi[w]); ce += (int)A->wsu[w]; }
-            AuxC *ox = cl.map_shared_rank(A, c.tid);
-            ox->x1_max[g.rank] = cmax; ox->x1_idx[g.rank] = cf; ox->x1_eq[g.rank] = ce; ox->x1_status[g.rank] = c.status;
+    // A lower bound of the running sum before every thread's range: each range adds at least the
+    // exponential of its own maximum. Relative to this block's maximum for now; the others' are
+    // not known yet.
+    float et = 0.0f, eex = 0.0f, etot = 0.0f;
+    if (sampled) {
+        if (i0 < g.nloc && tmax > -INFINITY) {
+            const float d = __fsub_rn(tmax, cmax);
+            et = expf_pinned((T == 1.0f) ? d : __fdiv_rn(d, T));
+        }
+        eex = block_excl_scan<float>(et, A->wsf, &etot);
+        if (!pure) {
+            // the head's threshold comes from the threads' maxima: how many lie how far below the maximum
+            A->thist[c.tid] = 0u;
+            __syncthreads();
+            if (i0 < g.nloc) {
+                const float dd = __fmul_rn(__fsub_rn(cmax, tmax), TRES);
+                const int b = (dd >= 0.0f && dd < (float)(TBINS - 1)) ? (int)dd : TBINS - 1;
+                sred_add(&A->thist[b], 1u);
+            }
         }
     }
+    __syncthreads();
+    if (c.tid < g.G) {
+        AuxC *ox = cl.map_shared_rank(A, c.tid);
+        ox->x1_max[g.rank] = cmax; ox->x1_idx[g.rank] = cidx; ox->x1_eq[g.rank] = ceq; ox->x1_status[g.rank] = c.status;
+        ox->x2_total[g.rank] = etot;
+    }
+    if (c.tid == 0) { A->ncand = 0; A->evt_thread = 0x7fffffff; }
     CSTAMP(13);
     cl.sync();
     float xmax = -INFINITY;
@@ -551,7 +696,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     if (c.status & MOLLA_ROW_LOAD_TIMEOUT) { finish(); return; }
 
     CSTAMP(3);
-    const long long n_lim = (k > 0 && k < a.V) ? (long long)k : (long long)a.V;
     if (greedy) { token = imax; finish(); return; }
     if (n_lim == 1) {
         // top-k of one: the sort's first element is a maximum (sample.mojo:485-490)
@@ -560,8 +704,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     }
 
     const float top = (T == 1.0f) ? xmax : __fdiv_rn(xmax, T);
-    const bool topp_on = (P < 1.0f) && (n_lim > 1);
-    const bool pure = !topp_on && n_lim == (long long)a.V;
     const float u01 = draw01(a.seed ? a.seed[q] : 0ull, a.drawn ? a.drawn[q] : 0ull);
     const bool filter_ok = fabsf(top) < 1.0e5f;
     long long need = n_lim + 1;
@@ -569,118 +711,138 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     if (need > a.V) need = a.V;
     const bool p3row = !pure && (n_lim + 1 > HEAD_NEED);
 
-    // ---- 3. a lower bound of the running sum before every thread's range (each range adds at
-    // least the exponential of its own maximum), and the head's threshold: the need-th largest of
-    // all threads' maxima bounds the need-th largest element from below.
-    float et = 0.0f;
-    if (i0 < g.nloc && tmax > -INFINITY) {
-        const float v = (T == 1.0f) ? tmax : __fdiv_rn(tmax, T);
-        et = expf_pinned(__fsub_rn(v, top));
-    }
-    float etot;
-    const float eex = block_excl_scan<float>(et, A->wsf, &etot);
-    if (!pure) {
-        __syncthreads();
-        A->cand[c.tid] = ((unsigned long long)fkey(tmax) << 32) | (unsigned long long)c.tid;
-        bitonic_desc(A->cand, NT, c.tid);
-        if (c.tid < XT) {
-            const float v = fkey_inv((unsigned int)(A->cand[c.tid] >> 32));
-            for (int o = 0; o < g.G; o++) cl.map_shared_rank(A, o)->x2_top[g.rank][c.tid] = v;
+    // ---- 3. the bound relative to the row's maximum, and the head's threshold: a value that at
+    // least `need` of the threads' maxima reach bounds the need-th largest element from below.
+    float lb;
+    {
+        float lbbase = 0.0f, mine = 0.0f;
+        for (int o = 0; o <= g.rank; o++) {
+            const float d = __fsub_rn(A->x1_max[o], xmax);
+            const float f = (A->x1_max[o] > -INFINITY) ? expf_pinned((T == 1.0f) ? d : __fdiv_rn(d, T)) : 0.0f;
+            if (o < g.rank) lbbase += A->x2_total[o] * f; else mine = f;
         }
+        lb = lbbase + eex * mine;
     }
-    if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x2_total[g.rank] = etot;
-    if (c.tid == 0) { A->ncand = 0; A->b_tau = 0xff800000u; }  // no candidates yet; threshold -inf until found
-    cl.sync();
-    float lbbase = 0.0f;
-    for (int h = 0; h < g.rank; h++) lbbase += A->x2_total[h];
     float tau_x = INFINITY;
     unsigned int tau_bits = 1u;
     if (!pure) {
-        // the need-th largest of the G sorted lists: the value v with (#greater) < need <= (#greater or equal)
-        for (int t = c.tid; t < g.G * XT; t += NT) {
-            const float v = A->x2_top[t / XT][t % XT];
-            int gt = 0, ge = 0;
-            for (int o = 0; o < g.G; o++) {
-                const float *lst = A->x2_top[o];
-                int lo_ = 0, hi_ = XT;          // first index with lst[i] <= v
-                while (lo_ < hi_) { const int mid = (lo_ + hi_) >> 1; if (lst[mid] <= v) hi_ = mid; else lo_ = mid + 1; }
-                gt += lo_;
-                hi_ = XT;                        // first index with lst[i] < v
-                while (lo_ < hi_) { const int mid = (lo_ + hi_) >> 1; if (lst[mid] < v) hi_ = mid; else lo_ = mid + 1; }
-                ge += lo_;
-            }
-            if ((long long)gt < need && need <= (long long)ge) A->b_tau = __float_as_uint(v);
+        // thread t adds up, over the blocks, the counts of bin t of distance below the row's maximum
+        // (a block's own bins are shifted by its maximum's distance, rounded up)
+        int cnt = 0;
+        for (int o = 0; o < g.G; o++) {
+            const float dd = __fmul_rn(__fsub_rn(xmax, A->x1_max[o]), TRES);
+            if (!(dd >= 0.0f && dd < (float)TBINS)) continue;
+            const int lb_ = c.tid - (int)ceilf(dd);
+            if (lb_ >= 0 && lb_ < TBINS - 1) cnt += (int)cl.map_shared_rank(A, o)->thist[lb_];
         }
+        int tot;
+        const int ex = block_excl_scan<int>(cnt, A->wsi, &tot);
+        if ((long long)ex < need && (long long)(ex + cnt) >= need) A->evt_thread = c.tid;
         __syncthreads();
-        tau_x = __uint_as_float(A->b_tau);
+        const int gb = A->evt_thread;
+        tau_x = (gb < TBINS - 1 && fabsf(xmax) < 65536.0f) ? __fsub_rn(xmax, __fmul_rn((float)(gb + 2), 1.0f / TRES)) : -INFINITY;
         const float tv = (T == 1.0f) ? tau_x : __fdiv_rn(tau_x, T);
         const unsigned int tb_ = __float_as_uint(expf_pinned(__fsub_rn(tv, top)));
         tau_bits = tb_ > 1u ? tb_ : 1u;
     }
+    // what is below half an ulp of the bound is dropped; below top - 105 the exponential is
+    // exactly zero whatever came before
+    float mythr;
     {
-        // what is below half an ulp of the bound is dropped; below top - 105 the exponential is
-        // exactly zero whatever came before
-        const float lb = lbbase + eex;
         const float thr_rel = (filter_ok && lb > 0.0f) ? T * (top + logf(0.9f * lb) - REL_MARGIN) : -INFINITY;
         const float thr_zero = filter_ok ? T * (top - 105.0f) : -INFINITY;
-        A->thr[c.tid] = fminf(fmaxf(thr_rel, thr_zero), tau_x);
+        mythr = fminf(fmaxf(thr_rel, thr_zero), tau_x);
     }
-    __syncthreads();
 
     CSTAMP(4);
     // ---- 4. the second pass, in place: the exponential (temperature and softmax numerator,
-    // sample.mojo:419-434) of what can matter, zero for the rest. Every warp runs through its
-    // threads' ranges 128 elements at a time; where few are kept they are evaluated densely.
+    // sample.mojo:419-434) of what can matter, zero for the rest. Where a row's sum is still small
+    // (its first columns) nearly everything matters, later almost nothing: the threads list the
+    // positions they keep and the whole block evaluates the list, so that no warp is left alone
+    // with the dense stretch. What does not fit the list is evaluated by its owner.
     {
-        const int wbase = c.warp * 32 * g.L;           // first element of the warp's region
-        const int wlen = 32 * g.L;
-        float4 *row4 = reinterpret_cast<float4 *>(rowbuf + wbase);
-        unsigned short *pp_ = A->ppos[c.warp];
+        static_assert(offsetof(AuxC, cand) == sizeof(A->u) && offsetof(AuxC, pc) == offsetof(AuxC, cand) + sizeof(A->cand) &&
+                      offsetof(AuxC, pre) == offsetof(AuxC, pc) + sizeof(A->pc) && offsetof(AuxC, hidx) == offsetof(AuxC, pre) + sizeof(A->pre),
+                      "the list and the head's candidates rely on this layout");
+        unsigned short *plist = reinterpret_cast<unsigned short *>(&A->u);
+        unsigned long long *hcand = reinterpret_cast<unsigned long long *>(A->pre);  // HEADC keys over pre + hidx
         auto value = [&](float xx) -> float {
             const float v = (T == 1.0f) ? xx : __fdiv_rn(xx, T);
-            return expf_pinned(__fsub_rn(v, top));
+            return expf_pinned_nonpos(__fsub_rn(v, top));  // no logit of the row exceeds its maximum
         };
         auto take = [&](unsigned int ebits, int i_block) {  // the head's candidates are picked up on the way
             if (!pure && ebits >= tau_bits) {
                 const int pos = satom_add(&A->ncand, 1);
-                if (pos < HEADC) A->cand[pos] = make_key(ebits, g.c0 + i_block);
+                if (pos < HEADC) hcand[pos] = make_key(ebits, g.c0 + i_block);
             }
         };
-        for (int e0 = 0; e0 < wlen; e0 += 128) {
-            const float thr = A->thr[c.warp * 32 + e0 / g.L];
-            const int e = e0 + 4 * c.lane;
-            const bool in = e < wlen;                  // wlen is a multiple of 4
-            float4 x = in ? row4[e >> 2] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-            const bool k0 = in && x.x >= thr, k1 = in && x.y >= thr, k2 = in && x.z >= thr, k3 = in && x.w >= thr;
-            const int cnt = (int)k0 + (int)k1 + (int)k2 + (int)k3;
-            const int incl = warp_incl_scan(cnt, c.lane);
-            const int total = __shfl_sync(0xffffffffu, incl, 31);
-            if (total > 64) {
-                float4 y;
-                y.x = k0 ? value(x.x) : 0.0f; y.y = k1 ? value(x.y) : 0.0f;
-                y.z = k2 ? value(x.z) : 0.0f; y.w = k3 ? value(x.w) : 0.0f;
-                if (in) row4[e >> 2] = y;
-                if (k0) take(__float_as_uint(y.x), wbase + e);
-                if (k1) take(__float_as_uint(y.y), wbase + e + 1);
-                if (k2) take(__float_as_uint(y.z), wbase + e + 2);
-                if (k3) take(__float_as_uint(y.w), wbase + e + 3);
-            } else {
-                int off = incl - cnt;
-                if (k0) pp_[off++] = (unsigned short)(e);
-                if (k1) pp_[off++] = (unsigned short)(e + 1);
-                if (k2) pp_[off++] = (unsigned short)(e + 2);
-                if (k3) pp_[off++] = (unsigned short)(e + 3);
-                if (in) row4[e >> 2] = make_float4(k0 ? x.x : 0.0f, k1 ? x.y : 0.0f, k2 ? x.z : 0.0f, k3 ? x.w : 0.0f);
-                __syncwarp();
-                for (int i = c.lane; i < total; i += 32) {
-                    const int pos = (int)pp_[i];
-                    const float ev = value(rowbuf[wbase + pos]);
-                    rowbuf[wbase + pos] = ev;
-                    take(__float_as_uint(ev), wbase + pos);
+        // which of this thread's elements are kept (bit j = element j; the rest becomes zero at once)
+        unsigned long long m0 = 0ull;
+        unsigned int m1 = 0u;
+        {
+            const int n0 = min(g.L, 64);
+            int j = 0;
+            for (; j + 4 <= n0; j += 4) {
+                float x[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) x[u] = rowbuf[i0 + j + u];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    if (x[u] >= mythr) m0 |= 1ull << (j + u); else rowbuf[i0 + j + u] = 0.0f;
                 }
-                __syncwarp();
+            }
+            for (; j < n0; j++) {
+                if (rowbuf[i0 + j] >= mythr) m0 |= 1ull << j; else rowbuf[i0 + j] = 0.0f;
+            }
+            for (j = 64; j < g.L; j++) {
+                if (rowbuf[i0 + j] >= mythr) m1 |= 1u << (j - 64); else rowbuf[i0 + j] = 0.0f;
             }
         }
+        const int cnt = __popcll(m0) + __popc(m1);
+        int tot;
+        const int base = block_excl_scan<int>(cnt, A->wsi, &tot);
+        CSTAMP(16);
+        if (a.prof && leader && c.tid == 0) a.prof[(long long)r * 32 + 19] = tot;
+        int o = base;  // the list offset of this thread's next kept element
+        for (int lo_ = 0; lo_ < tot; lo_ += PLIST_CAP) {
+            // this thread's kept positions that fall into [lo_, lo_ + PLIST_CAP) of the block's list
+            while (m0 && o < lo_ + PLIST_CAP) {
+                const int b = __ffsll((long long)m0) - 1;
+                m0 &= m0 - 1ull;
+                plist[o - lo_] = (unsigned short)(i0 + b);
+                o++;
+            }
+            while (!m0 && m1 && o < lo_ + PLIST_CAP) {
+                const int b = __ffs((int)m1) - 1;
+                m1 &= m1 - 1u;
+                plist[o - lo_] = (unsigned short)(i0 + 64 + b);
+                o++;
+            }
+            __syncthreads();
+            const int nl = min(tot - lo_, PLIST_CAP);
+            for (int i = c.tid; i < nl; i += 4 * NT) {
+                int pos[4];
+                float y[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) pos[u] = (i + u * NT < nl) ? (int)plist[i + u * NT] : -1;
+#pragma unroll
+                for (int u = 0; u < 4; u++) y[u] = (pos[u] >= 0) ? value(rowbuf[pos[u]]) : 0.0f;
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    if (pos[u] >= 0) { rowbuf[pos[u]] = y[u]; take(__float_as_uint(y[u]), pos[u]); }
+            }
+            __syncthreads();
+            if (lo_ == 0) CSTAMP(17);
+        }
+        // the head's candidates to where the head looks for them
+        const int nh = min(A->ncand, HEADC);
+        unsigned long long mine[(HEADC + NT - 1) / NT];
+#pragma unroll
+        for (int u = 0; u < (HEADC + NT - 1) / NT; u++) mine[u] = (c.tid + u * NT < nh) ? hcand[c.tid + u * NT] : 0ull;
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < (HEADC + NT - 1) / NT; u++)
+            if (c.tid + u * NT < nh) A->cand[c.tid + u * NT] = mine[u];
     }
     __syncthreads();
     CSTAMP(5);
@@ -688,7 +850,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x3_n[g.rank] = A->ncand;
 
     // ---- 5. the softmax denominator, exactly as the sequential loop rounds it
-    const ClSum zs = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f, (a.prof && leader) ? a.prof + (long long)r * 16 + 14 : nullptr);
+    const ClSum zs = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f, (a.prof && leader) ? a.prof + (long long)r * 32 + 14 : nullptr, a.prof ? a.prof + (long long)r * 32 + 20 : nullptr);
     const float Z = zs.s;
     if (zs.slow) c.status |= MOLLA_ROW_SLOW_PATH;
     dZ = Z;
@@ -891,7 +1053,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
     cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
     const bool limited = n_use < (long long)a.V;
-    descend_cluster(cl, c, g, rowbits, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_use : -1);
+    descend_cluster(cl, c, g, rowbits, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_use : -1, (a.prof && leader) ? a.prof + (long long)r * 32 + 20 : nullptr);
     if (cutw.event != EV_DEGENERATE) {
         if (cutw.event == EV_CUT && cutw.tie) c.status |= MOLLA_ROW_TOPP_TIE;
         if (cutw.event == EV_LIMIT && cutw.tie) c.status |= MOLLA_ROW_TOPK_TIE;
@@ -924,7 +1086,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
                 ClWalk dw;
                 dw.s = head_s; dw.pos = head_pos; dw.tau = tau_head;
                 dw.event = EV_NONE; dw.idx = -1; dw.p = 0; dw.tie = 0;
-                descend_cluster(cl, c, g, rowbits, dw, 3.4e38f, target, -1);
+                descend_cluster(cl, c, g, rowbits, dw, 3.4e38f, target, -1, nullptr);
                 if (dw.event == EV_DRAW) {
                     token = dw.idx; dp = dw.p; resolved = true;
                     if (dw.tie) c.status |= MOLLA_ROW_CHOSEN_TIE;

@@ -58,6 +58,34 @@ __device__ __forceinline__ float expf_pinned(float x) {
     return scale2(p, n);
 }
 
+// The same exponential for arguments that cannot be positive (a scaled logit minus the row's
+// maximum), without a branch: identical bits to expf_pinned for every x <= 0, NaN included.
+// The scaling by 2^n goes through 2^(n+64) * 2^-64 for every n: the first factor never
+// rounds, the second rounds once where the result is subnormal, as scale2 does.
+__device__ __forceinline__ float expf_pinned_nonpos(float x) {
+    const float LOG2E = 1.442695040888963f;
+    const float LN2_HI = 0.693145751953125f;
+    const float LN2_LO = 1.428606765330187e-06f;
+    const float MAGIC = 12582912.0f;
+    const float xc = fmaxf(x, -128.0f);  // below -104 the answer is zero anyway; keeps n in range
+    float t = __fmaf_rn(xc, LOG2E, MAGIC);
+    float nf = __fsub_rn(t, MAGIC);
+    float r = __fmaf_rn(nf, -LN2_HI, xc);
+    r = __fmaf_rn(nf, -LN2_LO, r);
+    float p = 1.0f / 5040.0f;
+    p = __fmaf_rn(p, r, 1.0f / 720.0f);
+    p = __fmaf_rn(p, r, 1.0f / 120.0f);
+    p = __fmaf_rn(p, r, 1.0f / 24.0f);
+    p = __fmaf_rn(p, r, 1.0f / 6.0f);
+    p = __fmaf_rn(p, r, 0.5f);
+    p = __fmaf_rn(p, r, 1.0f);
+    p = __fmaf_rn(p, r, 1.0f);
+    const int n = (int)nf;
+    const float a = __int_as_float((n + 64 + 127) << 23);
+    const float res = __fmul_rn(__fmul_rn(p, a), __int_as_float((-64 + 127) << 23));
+    return (x < -104.0f) ? 0.0f : ((x != x) ? x : res);
+}
+
 // The typical-p filter's logarithm: the same operations in the same order as the CPU oracle's
 // molla_oracle_logf, each rounded once, so the bits agree. Within 2 ulp of the true logarithm.
 __device__ __forceinline__ float logf_pinned(float x) {

@@ -128,6 +128,25 @@ __device__ void bitonic_desc(unsigned long long *k, int n2, int tid) {
     __syncthreads();
 }
 
+// The same sort by one warp (the others wait at the caller's barrier): a short list costs far
+// less in warp barriers than in block barriers.
+__device__ void bitonic_desc_warp(unsigned long long *k, int n2, int lane) {
+    IN_SHARED(k);
+    for (int size = 2; size <= n2; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncwarp();
+            for (int i = lane; i < (n2 >> 1); i += 32) {
+                int pos = ((i / stride) * stride * 2) + (i % stride);
+                int par = pos + stride;
+                bool desc = ((pos & size) == 0);
+                unsigned long long x = k[pos], y = k[par];
+                if ((x < y) == desc) { k[pos] = y; k[par] = x; }
+            }
+        }
+    }
+    __syncwarp();
+}
+
 __device__ __forceinline__ unsigned int fkey(float f) {  // order-preserving key of a float
     unsigned int b = __float_as_uint(f);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
@@ -160,6 +179,7 @@ __device__ __forceinline__ int hslot(int tok) { return (int)(((unsigned int)tok 
 // the first entry whose running sum exceeds a target.
 struct Walker {
     float s; int found; int at; int slow;
+    int nsim = 0, nel = 0;  // replays and entries replayed (diagnostics)
 };
 
 // value accessors (shared memory): a list of (value bits << 32 | ~id) keys, or bare value bits
@@ -172,27 +192,46 @@ struct ValBits {
     __device__ __forceinline__ float operator()(int i) const { IN_SHARED(p); return __uint_as_float(p[i]); }
 };
 
-template <class V>
-__device__ __forceinline__ void p1_sim(V lst, int i0, int i1, bool locate, float target,
-                                       Walker &w) {
+template <bool LOCATE, class V>
+__device__ __forceinline__ void p1_sim_t(V lst, int i0, int i1, float target, Walker &w) {
     float s = w.s;
     int i = i0;
-    for (; i + 8 <= i1; i += 8) {  // the loads do not depend on the running sum: fetch eight, then add
-        float v[8];
+    // the loads do not depend on the running sum: the next eight are fetched while these are added
+    float v[8];
+    if (i + 8 <= i1) {
 #pragma unroll
         for (int q = 0; q < 8; q++) v[q] = lst(i + q);
+    }
+    for (; i + 8 <= i1; i += 8) {
+        float nv[8];
+        const bool more = i + 16 <= i1;
+        if (more) {
+#pragma unroll
+            for (int q = 0; q < 8; q++) nv[q] = lst(i + 8 + q);
+        }
 #pragma unroll
         for (int q = 0; q < 8; q++) {
             s = __fadd_rn(s, v[q]);
-            if (locate && !w.found && target < s) { w.found = 1; w.at = i + q; }
+            if (LOCATE && !w.found && target < s) { w.found = 1; w.at = i + q; }
         }
-        if (locate && w.found) { w.s = s; return; }
+        if (LOCATE && w.found) { w.s = s; return; }
+        if (more) {
+#pragma unroll
+            for (int q = 0; q < 8; q++) v[q] = nv[q];
+        }
     }
     for (; i < i1; i++) {
         s = __fadd_rn(s, lst(i));
-        if (locate && target < s) { w.found = 1; w.at = i; break; }
+        if (LOCATE && target < s) { w.found = 1; w.at = i; break; }
     }
     w.s = s;
+}
+
+template <class V>
+__device__ __forceinline__ void p1_sim(V lst, int i0, int i1, bool locate, float target, Walker &w) {
+    w.nsim++; w.nel += i1 - i0;
+    if (locate) p1_sim_t<true>(lst, i0, i1, target, w);
+    else p1_sim_t<false>(lst, i0, i1, target, w);
 }
 
 // this thread's estimate of the sum of its own L entries
@@ -243,10 +282,24 @@ __device__ void p1_tables(CX &c, V lst, int n, int L, float csum, double sst) {
                 bad |= two & (fabsf(r2) == h2);
                 xb = __fadd_rn(xb, q2);
             };
+            auto term1 = [&](int i, float &xa) {  // the guess lies inside one binade
+                const float v = lst(i);
+                const float q = __fsub_rn(__fadd_rn(v, C1), C1);
+                const float r = __fsub_rn(v, q);
+                bad |= (fabsf(r) == h1) | (v >= b1);
+                xa = __fadd_rn(xa, q);
+            };
             int i = i0;
-            for (; i + 2 <= i1; i += 2) { term(i, da, db); term(i + 1, da1, db1); }
-            if (i < i1) term(i, da, db);
-            da = __fadd_rn(da, da1); db = __fadd_rn(db, db1);
+            if (two) {
+                for (; i + 2 <= i1; i += 2) { term(i, da, db); term(i + 1, da1, db1); }
+                if (i < i1) term(i, da, db);
+                da = __fadd_rn(da, da1); db = __fadd_rn(db, db1);
+            } else {
+                float da2 = 0.0f, da3 = 0.0f;
+                for (; i + 4 <= i1; i += 4) { term1(i, da); term1(i + 1, da1); term1(i + 2, da2); term1(i + 3, da3); }
+                for (; i < i1; i++) term1(i, da);
+                da = __fadd_rn(__fadd_rn(da, da1), __fadd_rn(da2, da3));
+            }
             if (!bad) { ja = (short)jl; dual = two ? 1 : 0; }
         }
     }
@@ -260,8 +313,29 @@ __device__ void p1_tables(CX &c, V lst, int n, int L, float csum, double sst) {
     A->u.p1.pb[c.tid] = pb;
     if (c.tid == NT - 1) { A->u.p1.pa[NT] = ta; A->u.p1.pb[NT] = tb; }
     __syncthreads();
-    // segment list: chunks where (binade guess, dual, replay) changes
-    const bool start = (c.tid == 0) || ja == SUS || A->u.p1.ja[c.tid - 1] != ja || A->u.p1.dual[c.tid - 1] != dual;
+    // Segment list: chunks where (binade guess, dual, replay) changes. A chunk of zeros adds
+    // nothing in any binade: it joins the segment before it whatever its own guess was, so a
+    // sparse row has few segments. `prev` is the last chunk before this one that is not empty.
+    const bool nonempty = (i1 > i0) && csum != 0.0f;
+    int prev = -1;
+    {
+        const unsigned int ne = __ballot_sync(0xffffffffu, nonempty);
+        if (c.lane == 0) A->wsi[c.warp] = ne ? (c.warp * 32 + 31 - __clz((int)ne)) : -1;  // (block_excl_scan2 is done with wsd, not wsi)
+        __syncthreads();
+        const unsigned int below = ne & ((1u << c.lane) - 1u);
+        if (below) prev = c.warp * 32 + 31 - __clz((int)below);
+        else
+            for (int w = c.warp - 1; w >= 0 && prev < 0; w--) prev = A->wsi[w];
+        __syncthreads();
+    }
+    bool start = (c.tid == 0);
+    if (nonempty && !start) {
+        start = ja == SUS || prev < 0;
+        if (!start) {
+            const short pj = A->u.p1.ja[prev];
+            start = pj == SUS || pj != ja || A->u.p1.dual[prev] != dual;
+        }
+    }
     const unsigned int bal = __ballot_sync(0xffffffffu, start);
     int wtot;
     int wex = block_excl_scan<int>(c.lane == 0 ? __popc(bal) : 0, A->wsi, &wtot);
@@ -281,6 +355,10 @@ __device__ void p1_build(CX &c, V lst, int n, int L, double sbase) {
     p1_tables(c, lst, n, L, csum, sst);
 }
 
+__device__ __forceinline__ double dpow2(int j) {  // 2^j as a double, -1022 <= j <= 1023
+    return __longlong_as_double((long long)(j + 1023) << 52);
+}
+
 // thread 0 only; continues from the state in `w`
 template <class CX, class V>
 __device__ void p1_walk(CX &c, V lst, int n, int L, bool locate, float target, Walker &w) {
@@ -295,7 +373,8 @@ __device__ void p1_walk(CX &c, V lst, int n, int L, bool locate, float target, W
         const int e0 = min(n, t0 * L), e1 = min(n, t1 * L);
         if (e1 <= e0) break;  // chunks past the end of the list are empty
         if (j == SUS) {
-            if (A->u.p1.csum[t0] != 0.0f) p1_sim(lst, e0, e1, locate, target, w);
+            // (the chunks behind t0 in this segment hold zeros only)
+            if (A->u.p1.csum[t0] != 0.0f) p1_sim(lst, e0, min(e1, min(n, (t0 + 1) * L)), locate, target, w);
             continue;
         }
         const bool dual = A->u.p1.dual[t0] != 0;
@@ -324,11 +403,11 @@ __device__ void p1_walk(CX &c, V lst, int n, int L, bool locate, float target, W
                 return true;
             };
             if (!dual) {
-                if (js == j) ok = bulk(PA, t0, t1, ldexp(1.0, j + 1));
+                if (js == j) ok = bulk(PA, t0, t1, dpow2(j + 1));
             } else if (js == j + 1) {
-                ok = bulk(PB, t0, t1, ldexp(1.0, j + 2));
+                ok = bulk(PB, t0, t1, dpow2(j + 2));
             } else if (js == j) {
-                const double lim = ldexp(1.0, j + 1);
+                const double lim = dpow2(j + 1);
                 if (sd + (pa1 - pa0) < lim) {
                     ok = bulk(PA, t0, t1, lim);
                 } else {
@@ -347,7 +426,7 @@ __device__ void p1_walk(CX &c, V lst, int n, int L, bool locate, float target, W
                         if (!(locate && w.found)) {
                             p1_sim(lst, min(n, ts * L), min(n, (ts + 1) * L), locate, target, w);
                             if (!(locate && w.found) && ts + 1 < t1) {
-                                if (!(fexpo(w.s) == j + 1 && bulk(PB, ts + 1, t1, ldexp(1.0, j + 2)))) {
+                                if (!(fexpo(w.s) == j + 1 && bulk(PB, ts + 1, t1, dpow2(j + 2)))) {
                                     w.slow = 1;
                                     p1_sim(lst, min(n, (ts + 1) * L), e1, locate, target, w);
                                 }
@@ -384,8 +463,10 @@ struct BinQuery {
 
 // `bin_load(b, q, n)` gives bin b's integer mass and count (one thread block's tables, or the
 // sum over the tables of a cluster's thread blocks).
-template <class CX, class LD>
-__device__ void find_event_bin_with(CX &c, const BinQuery &qy, LD bin_load) {
+// `adjust(q, eq)` may change the masses of the thread's bins once their sum before the bins (eq)
+// is known; it returns whether it did (the same answer in every thread).
+template <class CX, class LD, class ADJ>
+__device__ void find_event_bin_adj(CX &c, const BinQuery &qy, LD bin_load, ADJ adjust) {
     auto *A = c.A;
     IN_SHARED(A);
     unsigned long long q[BPT], n[BPT], sq = 0, sn = 0;
@@ -398,7 +479,13 @@ __device__ void find_event_bin_with(CX &c, const BinQuery &qy, LD bin_load) {
         sq += q[i]; sn += n[i];
     }
     unsigned long long tq, tc;
-    const unsigned long long eq = block_excl_scan<unsigned long long>(sq, A->wsu, &tq);
+    unsigned long long eq = block_excl_scan<unsigned long long>(sq, A->wsu, &tq);
+    if (adjust(q, eq)) {
+        sq = 0;
+#pragma unroll
+        for (int i = 0; i < BPT; i++) sq += q[i];
+        eq = block_excl_scan<unsigned long long>(sq, A->wsu, &tq);
+    }
     const unsigned long long ec = block_excl_scan<unsigned long long>(sn, A->wsu, &tc);
     __syncthreads();
     if (c.tid == 0) { A->evt_thread = 0x7fffffff; A->tot_q = tq; A->tot_c = tc; A->hit_bin = -1; }
@@ -420,6 +507,11 @@ __device__ void find_event_bin_with(CX &c, const BinQuery &qy, LD bin_load) {
     __syncthreads();
 }
 
+template <class CX, class LD>
+__device__ void find_event_bin_with(CX &c, const BinQuery &qy, LD bin_load) {
+    find_event_bin_adj(c, qy, bin_load, [](unsigned long long (&)[BPT], unsigned long long) { return false; });
+}
+
 template <class CX>
 __device__ void find_event_bin(CX &c, const BinQuery &qy) {
     find_event_bin_with(c, qy, [&](int b, unsigned long long &q, unsigned long long &n) {
@@ -437,7 +529,13 @@ __device__ void sort_cands(CX &c, int n) {
     while (n2 < n) n2 <<= 1;
     __syncthreads();
     for (int i = n + c.tid; i < n2; i += NT) A->cand[i] = 0ull;
-    bitonic_desc(A->cand, n2, c.tid);
+    if (n2 <= 256) {
+        __syncthreads();
+        if (c.warp == 0) bitonic_desc_warp(A->cand, n2, c.lane);
+        __syncthreads();
+    } else {
+        bitonic_desc(A->cand, n2, c.tid);
+    }
     for (int i = c.tid; i < n; i += NT) A->pc[i] = key_val(A->cand[i]);
     __syncthreads();
 }

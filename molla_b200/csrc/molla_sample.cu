@@ -1890,7 +1890,7 @@ __global__ void __launch_bounds__(NT, 1) logprob_kernel(const float *logits, lon
 
 __global__ void expf_kernel(const float *x, long long n, float *out) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = expf_pinned(x[i]);
+    if (i < n) out[i] = (x[i] <= 0.0f) ? expf_pinned_nonpos(x[i]) : expf_pinned(x[i]);  // both forms are in use
 }
 
 __global__ void logf_kernel(const float *x, long long n, float *out) {
