@@ -4,6 +4,8 @@
 // the block's scratch in shared memory (the member names used below). The sizes NBINS and NC
 // can be set per translation unit before this file is included.
 #pragma once
+#include <type_traits>
+
 #include "molla_device.cuh"
 #include "../../include/molla_sample.h"
 
@@ -196,29 +198,16 @@ template <bool LOCATE, class V>
 __device__ __forceinline__ void p1_sim_t(V lst, int i0, int i1, float target, Walker &w) {
     float s = w.s;
     int i = i0;
-    // the loads do not depend on the running sum: the next eight are fetched while these are added
-    float v[8];
-    if (i + 8 <= i1) {
+    for (; i + 8 <= i1; i += 8) {  // the loads do not depend on the running sum: fetch eight, then add
+        float v[8];
 #pragma unroll
         for (int q = 0; q < 8; q++) v[q] = lst(i + q);
-    }
-    for (; i + 8 <= i1; i += 8) {
-        float nv[8];
-        const bool more = i + 16 <= i1;
-        if (more) {
-#pragma unroll
-            for (int q = 0; q < 8; q++) nv[q] = lst(i + 8 + q);
-        }
 #pragma unroll
         for (int q = 0; q < 8; q++) {
             s = __fadd_rn(s, v[q]);
             if (LOCATE && !w.found && target < s) { w.found = 1; w.at = i + q; }
         }
         if (LOCATE && w.found) { w.s = s; return; }
-        if (more) {
-#pragma unroll
-            for (int q = 0; q < 8; q++) v[q] = nv[q];
-        }
     }
     for (; i < i1; i++) {
         s = __fadd_rn(s, lst(i));
@@ -463,6 +452,7 @@ struct BinQuery {
 
 // `bin_load(b, q, n)` gives bin b's integer mass and count (one thread block's tables, or the
 // sum over the tables of a cluster's thread blocks).
+struct NoAdjust {};
 // `adjust(q, eq)` may change the masses of the thread's bins once their sum before the bins (eq)
 // is known; it returns whether it did (the same answer in every thread).
 template <class CX, class LD, class ADJ>
@@ -480,7 +470,7 @@ __device__ void find_event_bin_adj(CX &c, const BinQuery &qy, LD bin_load, ADJ a
     }
     unsigned long long tq, tc;
     unsigned long long eq = block_excl_scan<unsigned long long>(sq, A->wsu, &tq);
-    if (adjust(q, eq)) {
+    if constexpr (!std::is_same<ADJ, NoAdjust>::value) if (adjust(q, eq)) {
         sq = 0;
 #pragma unroll
         for (int i = 0; i < BPT; i++) sq += q[i];
@@ -509,7 +499,7 @@ __device__ void find_event_bin_adj(CX &c, const BinQuery &qy, LD bin_load, ADJ a
 
 template <class CX, class LD>
 __device__ void find_event_bin_with(CX &c, const BinQuery &qy, LD bin_load) {
-    find_event_bin_adj(c, qy, bin_load, [](unsigned long long (&)[BPT], unsigned long long) { return false; });
+    find_event_bin_adj(c, qy, bin_load, NoAdjust{});
 }
 
 template <class CX>

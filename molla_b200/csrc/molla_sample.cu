@@ -38,7 +38,6 @@
 #include <math.h>
 #include <stdint.h>
 #include <stdio.h>
-#include <stdlib.h>
 #include <string.h>
 
 #include "../../include/molla_sample.h"
@@ -1987,11 +1986,8 @@ int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, in
 // The ordinary entry points' launch: the cluster kernel when the vocabulary fits a cluster, else
 // the streaming kernel with its lists in the workspace.
 int launch_sampling(const BatchArgs &args_in, void *d_workspace, cudaStream_t st) {
-    static const bool cluster_on = [] { const char *e = getenv("MOLLA_SAMPLE_CLUSTER"); return e && e[0] == '1'; }();
-    if (cluster_on) {
-        const int rc = molla_cluster_launch(args_in, d_workspace, st, g_err, sizeof(g_err));
-        if (rc != MOLLA_CLUSTER_DECLINED) return rc;
-    }
+    const int rc = molla_cluster_launch(args_in, d_workspace, st, g_err, sizeof(g_err));
+    if (rc != MOLLA_CLUSTER_DECLINED) return rc;
     return launch_rows(args_in, d_workspace, st, 0x7fffffff, true);
 }
 
