@@ -83,7 +83,9 @@ struct __align__(16) AuxC {
     int x4_n[CL_MAX_G]; unsigned long long x5_key[CL_MAX_G];
     float ch_s; int ch_found, ch_at, ch_slow;   // the exact sum on its way from range to range
     // elements of a walk that would round on a tie: their keys, bins, the mass before them
-    int ntie[2]; unsigned long long tkey[TIE_CAP]; int tbin[TIE_CAP]; unsigned long long tpq[TIE_CAP], tpqm[TIE_CAP], tabove[TIE_CAP], tc[TIE_CAP];
+    long long rx[8];          // words fetched from the leader for the whole block
+    int ngath, ngath_over;   // a bin's entries collected by this block; blocks whose own buffer overflowed (leader's)
+    int ntie[2]; unsigned long long tkey[TIE_CAP]; int tbin[TIE_CAP]; unsigned int tpq_lo[TIE_CAP], tpq_hi[TIE_CAP]; unsigned long long tpqm[TIE_CAP], tabove[TIE_CAP], tc[TIE_CAP];
     unsigned int tbits[NBINS / 32];
     int r_kind; int r_idx; float r_s; long long r_pos; unsigned int r_status;  // the leader's word after the head
 };
@@ -186,6 +188,15 @@ __device__ int cluster_nth_equal(cg::cluster_group &cl, CtxC &c, const ClGeo &g,
     return A->r_idx;
 }
 
+// A few words of the leader's memory for the whole block: threads 0..n-1 fetch one each into
+// `A->rx` (a load from another block's memory by every thread would queue up there).
+template <class F>
+__device__ __forceinline__ void fetch_from_leader(CtxC &c, int n, F word) {
+    __syncthreads();
+    if (c.tid < n) c.A->rx[c.tid] = word(c.tid);
+    __syncthreads();
+}
+
 // The descending walk past the sorted head (sample.mojo:492-506 and :580-590) over the cluster's
 // row of probabilities. State as in `descend`: exact running sum, elements consumed, and tau:
 // everything with probability bits >= tau is consumed. Every phase histograms what remains by
@@ -204,6 +215,7 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
     IN_SHARED(A);
     IN_SHARED(bits);
     AuxC *lead = cl.map_shared_rank(A, 0);
+    const bool leader = g.rank == 0;
     const bool counting = nstop >= 0;
     int lvl = 1;
     unsigned int lo = 0u;
@@ -216,7 +228,7 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
 #define DT(k) do { if (dbg && c.tid == 0) { const long long t_ = clock64(); dbg[k] += t_ - tp0; tp0 = t_; } } while (0)
         for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0u; A->u.h.hqh[i] = 0u; A->u.h.hc[i] = 0u; }
         for (int i = c.tid; i < NBINS / 32; i += NT) A->tbits[i] = 0u;
-        if (c.tid == 0) { A->specbin = -1; A->ncand = 0; A->ntie[(phase + 1) & 1] = 0; }  // the other blocks add to this phase's counter already
+        if (c.tid == 0) { A->specbin = -1; A->ncand = 0; A->ngath = 0; A->ngath_over = 0; A->ntie[(phase + 1) & 1] = 0; }  // the other blocks add to this phase's counter already
         __syncthreads();
         const bool have_s = w.s > 0.0f;
         const int j = have_s ? fexpo(w.s) : 0;
@@ -224,68 +236,88 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1);
         const float inv_u = fpow2(23 - j);
         const bool ties_listed = tie_mode && lvl == 1 && binade_ok;
-        for (int i = c.tid; i < g.nloc; i += NT) {
-            const unsigned int eb = bits[i];
-            if (eb == 0u || eb >= w.tau || eb < lo) continue;
-            const int bin = (int)((eb - lo) >> shift);
-            if (!binade_ok) { sred_add(&A->u.h.hc[bin], 1u); continue; }
-            const float p = __uint_as_float(eb);
-            const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
-            const float rr = __fsub_rn(p, q);
-            const bool tie = fabsf(rr) == halfu, big = p >= bigthr;
-            if (big || (tie && !ties_listed)) {
-                sred_max(&A->specbin, bin);
+        // every thread's elements four at a time (independent loads and arithmetic)
+        const int ntie_slot = phase & 1;
+        for (int i4 = c.tid; i4 < g.nloc; i4 += 4 * NT) {
+            unsigned int ebs[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) ebs[u] = (i4 + u * NT < g.nloc) ? bits[i4 + u * NT] : 0u;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const unsigned int eb = ebs[u];
+                if (eb == 0u || eb >= w.tau || eb < lo) continue;
+                const int i = i4 + u * NT;
+                const int bin = (int)((eb - lo) >> shift);
+                if (!binade_ok) { sred_add(&A->u.h.hc[bin], 1u); continue; }
+                const float p = __uint_as_float(eb);
+                const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
+                const float rr = __fsub_rn(p, q);
+                const bool tie = fabsf(rr) == halfu, big = p >= bigthr;
+                if (big || (tie && !ties_listed)) {
+                    sred_max(&A->specbin, bin);
+                    if (counting) sred_add(&A->u.h.hc[bin], 1u);
+                    continue;
+                }
+                if (tie) {
+                    const int pos = atomicAdd(&lead->ntie[ntie_slot], 1);
+                    if (pos < TIE_CAP) { lead->tkey[pos] = make_key(eb, g.c0 + i); lead->tbin[pos] = bin; }
+                    if (counting) sred_add(&A->u.h.hc[bin], 1u);
+                    continue;
+                }
+                const unsigned int qu = __float2uint_rn(__fmul_rn(q, inv_u));
+                if (qu) {
+                    sred_add(&A->u.h.hq[bin], qu & MASS_LO_MASK);
+                    if (qu >> MASS_SPLIT) sred_add(&A->u.h.hqh[bin], qu >> MASS_SPLIT);
+                }
                 if (counting) sred_add(&A->u.h.hc[bin], 1u);
-                continue;
             }
-            if (tie) {
-                const int pos = atomicAdd(&lead->ntie[phase & 1], 1);
-                if (pos < TIE_CAP) { lead->tkey[pos] = make_key(eb, g.c0 + i); lead->tbin[pos] = bin; }
-                if (counting) sred_add(&A->u.h.hc[bin], 1u);
-                continue;
-            }
-            const unsigned int qu = __float2uint_rn(__fmul_rn(q, inv_u));
-            if (qu) {
-                sred_add(&A->u.h.hq[bin], qu & MASS_LO_MASK);
-                if (qu >> MASS_SPLIT) sred_add(&A->u.h.hqh[bin], qu >> MASS_SPLIT);
-            }
-            if (counting) sred_add(&A->u.h.hc[bin], 1u);
         }
         cl.sync();
-        const int ntie = ties_listed ? lead->ntie[phase & 1] : 0;
-        DT(3);
+        fetch_from_leader(c, 1, [&](int) { return (long long)lead->ntie[ntie_slot]; });
+        const int ntie = ties_listed ? (int)A->rx[0] : 0;
         if (dbg && c.tid == 0) { dbg[0] += 1; dbg[1] += ntie; }
+        DT(3);
         if (ntie > TIE_CAP) { tie_mode = false; c.status |= MOLLA_ROW_SLOW_PATH; continue; }  // too many: they stop phases instead
         if (ntie > 0) {
             // what precedes each listed element inside its own bin (descending value, then ascending id)
             if (c.tid < ntie) {
                 const int b = lead->tbin[c.tid];
-                A->tkey[c.tid] = lead->tkey[c.tid]; A->tbin[c.tid] = b; A->tpq[c.tid] = 0ull;
+                A->tkey[c.tid] = lead->tkey[c.tid]; A->tbin[c.tid] = b; A->tpq_lo[c.tid] = 0u; A->tpq_hi[c.tid] = 0u;
                 sred_or(&A->tbits[b >> 5], 1u << (b & 31));
             }
             __syncthreads();
-            for (int i = c.tid; i < g.nloc; i += NT) {
-                const unsigned int eb = bits[i];
-                if (eb == 0u || eb >= w.tau || eb < lo) continue;
-                const int bin = (int)((eb - lo) >> shift);
-                if (!((A->tbits[bin >> 5] >> (bin & 31)) & 1u)) continue;
-                const float p = __uint_as_float(eb);
-                const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
-                const float rr = __fsub_rn(p, q);
-                if (fabsf(rr) == halfu || p >= bigthr) continue;
-                const unsigned long long qu = (unsigned long long)__float2uint_rn(__fmul_rn(q, inv_u));
-                const unsigned long long key = make_key(eb, g.c0 + i);
-                for (int t = 0; t < ntie; t++)
-                    if (A->tbin[t] == bin && key > A->tkey[t] && qu) atomicAdd(&A->tpq[t], qu);
+            for (int i4 = c.tid; i4 < g.nloc; i4 += 4 * NT) {
+                unsigned int ebs[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) ebs[u] = (i4 + u * NT < g.nloc) ? bits[i4 + u * NT] : 0u;
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const unsigned int eb = ebs[u];
+                    if (eb == 0u || eb >= w.tau || eb < lo) continue;
+                    const int bin = (int)((eb - lo) >> shift);
+                    if (!((A->tbits[bin >> 5] >> (bin & 31)) & 1u)) continue;
+                    const float p = __uint_as_float(eb);
+                    const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
+                    const float rr = __fsub_rn(p, q);
+                    if (fabsf(rr) == halfu || p >= bigthr) continue;
+                    const unsigned int qu = __float2uint_rn(__fmul_rn(q, inv_u));
+                    const unsigned long long key = make_key(eb, g.c0 + i4 + u * NT);
+                    for (int t = 0; t < ntie; t++)
+                        if (A->tbin[t] == bin && key > A->tkey[t] && qu) {  // two halves, as in the bin tables
+                            sred_add(&A->tpq_lo[t], qu & MASS_LO_MASK);
+                            if (qu >> MASS_SPLIT) sred_add(&A->tpq_hi[t], qu >> MASS_SPLIT);
+                        }
+                }
             }
             cl.sync();
         }
         DT(4);
-        int specbin = -1;
-        for (int o = 0; o < g.G; o++) specbin = max(specbin, cl.map_shared_rank(A, o)->specbin);
+        // The leader adds the other blocks' tables to its own (whole rows of bins at a time, so that
+        // the loads from the other blocks' memory are few and wide), searches the event bin and
+        // tells everybody.
         BinQuery qy;
-        qy.specbin = specbin; qy.bin_hi = NBINS; qy.spec_bits = nullptr;
-        qy.hq = nullptr; qy.hqh = nullptr; qy.hc = nullptr;
+        qy.bin_hi = NBINS; qy.spec_bits = nullptr;
+        qy.hq = A->u.h.hq; qy.hqh = A->u.h.hqh; qy.hc = A->u.h.hc;
         qy.pos0 = (unsigned long long)w.pos;
         qy.nstop = counting ? (unsigned long long)nstop : ~0ull;
         qy.m0 = 0; qy.xq = ~0ull;
@@ -304,62 +336,88 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         } else {
             qy.pos0 = 0; qy.nstop = 1;  // nothing consumed yet: take the highest non-empty bin
         }
-        find_event_bin_adj(c, qy,
-            [&](int b, unsigned long long &q, unsigned long long &n) {
-                unsigned long long ql = 0, qh = 0, nn = 0;
-                for (int o = 0; o < g.G; o++) {
-                    const AuxC *ox = cl.map_shared_rank(A, o);
-                    ql += ox->u.h.hq[b]; qh += ox->u.h.hqh[b]; nn += ox->u.h.hc[b];
-                }
-                q = ql + (qh << MASS_SPLIT); n = nn;
-            },
-            [&](unsigned long long (&q)[BPT], unsigned long long eq) -> bool {
-                if (ntie == 0) return false;
-                // the mass before each listed element: the bins above its own (the thread that owns
-                // the bin knows), what precedes it inside the bin (added up over the blocks)
-                unsigned long long run = eq;
-#pragma unroll
-                for (int i = 0; i < BPT; i++) {
-                    const int b = NBINS - 1 - BPT * c.tid - i;
-                    for (int t = 0; t < ntie; t++)
-                        if (A->tbin[t] == b) A->tabove[t] = run;
-                    run += q[i];
+        if (leader) {
+            {
+                uint4 *mine = reinterpret_cast<uint4 *>(&A->u.h);
+                constexpr int NV = 3 * NBINS / 4;  // the three tables, four bins at a time
+                for (int v0 = c.tid; v0 < NV; v0 += NT) {
+                    uint4 acc = mine[v0];
+                    for (int o = 1; o < g.G; o++) {
+                        const uint4 x = reinterpret_cast<const uint4 *>(&cl.map_shared_rank(A, o)->u.h)[v0];
+                        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+                    }
+                    mine[v0] = acc;
                 }
                 if (c.tid < ntie) {
-                    unsigned long long s_ = 0;
-                    for (int o = 0; o < g.G; o++) s_ += cl.map_shared_rank(A, o)->tpq[c.tid];
+                    unsigned long long s_ = 0ull;
+                    for (int o = 0; o < g.G; o++) {
+                        const AuxC *ox = cl.map_shared_rank(A, o);
+                        s_ += (unsigned long long)ox->tpq_lo[c.tid] + ((unsigned long long)ox->tpq_hi[c.tid] << MASS_SPLIT);
+                    }
                     A->tpqm[c.tid] = s_; A->tc[c.tid] = 0ull;
                 }
-                __syncthreads();
                 if (c.tid == 0) {
-                    // from the top down (ties above an earlier event never matter: the walk stops there)
-                    unsigned long long done = 0ull, carried = 0ull;  // bit t: resolved; contributions so far
-                    for (int round = 0; round < ntie; round++) {
-                        int best = -1;
-                        for (int t = 0; t < ntie; t++)
-                            if (!((done >> t) & 1ull) && (best < 0 || A->tkey[t] > A->tkey[best])) best = t;
-                        done |= 1ull << best;
-                        const float p = key_val(A->tkey[best]);
-                        const float qf = __fsub_rn(__fadd_rn(p, Cm), Cm);
-                        unsigned long long k = (unsigned long long)__float2uint_rn(__fmul_rn(qf, inv_u));
-                        if (qf > p) k -= 1ull;  // the multiple of the unit below p
-                        const unsigned long long mb = qy.m0 + A->tabove[best] + A->tpqm[best] + carried;
-                        if (qy.xq != ~0ull && mb >= qy.xq) break;  // an event before this element: what lies below does not matter
-                        const unsigned long long ct = k + ((mb + k) & 1ull);
-                        A->tc[best] = ct;
-                        carried += ct;
-                        if (qy.xq != ~0ull && mb + ct >= qy.xq) break;
-                    }
+                    int sb = A->specbin;
+                    for (int o = 1; o < g.G; o++) sb = max(sb, cl.map_shared_rank(A, o)->specbin);
+                    A->specbin = sb;
                 }
                 __syncthreads();
+            }
+            qy.specbin = A->specbin;
+            find_event_bin_adj(c, qy,
+                [&](int b, unsigned long long &q, unsigned long long &n) {
+                    q = (unsigned long long)qy.hq[b] + ((unsigned long long)qy.hqh[b] << MASS_SPLIT);
+                    n = qy.hc[b];
+                },
+                [&](unsigned long long (&q)[BPT], unsigned long long eq) -> bool {
+                    if (ntie == 0) return false;
+                    // the mass before each listed element: the bins above its own (the thread that
+                    // owns the bin knows), what precedes it inside the bin (added up over the blocks)
+                    unsigned long long run = eq;
 #pragma unroll
-                for (int i = 0; i < BPT; i++) {
-                    const int b = NBINS - 1 - BPT * c.tid - i;
-                    for (int t = 0; t < ntie; t++)
-                        if (A->tbin[t] == b) q[i] += A->tc[t];
-                }
-                return true;
-            });
+                    for (int i = 0; i < BPT; i++) {
+                        const int b = NBINS - 1 - BPT * c.tid - i;
+                        for (int t = 0; t < ntie; t++)
+                            if (A->tbin[t] == b) A->tabove[t] = run;
+                        run += q[i];
+                    }
+                    __syncthreads();
+                    if (c.tid == 0) {
+                        // from the top down (what lies below an event never matters: the walk stops there)
+                        unsigned long long done = 0ull, carried = 0ull;
+                        for (int round = 0; round < ntie; round++) {
+                            int best = -1;
+                            for (int t = 0; t < ntie; t++)
+                                if (!((done >> t) & 1ull) && (best < 0 || A->tkey[t] > A->tkey[best])) best = t;
+                            done |= 1ull << best;
+                            const float p = key_val(A->tkey[best]);
+                            const float qf = __fsub_rn(__fadd_rn(p, Cm), Cm);
+                            unsigned long long k = (unsigned long long)__float2uint_rn(__fmul_rn(qf, inv_u));
+                            if (qf > p) k -= 1ull;  // the multiple of the unit below p
+                            const unsigned long long mb = qy.m0 + A->tabove[best] + A->tpqm[best] + carried;
+                            if (qy.xq != ~0ull && mb >= qy.xq) break;
+                            const unsigned long long ct = k + ((mb + k) & 1ull);
+                            A->tc[best] = ct;
+                            carried += ct;
+                            if (qy.xq != ~0ull && mb + ct >= qy.xq) break;
+                        }
+                    }
+                    __syncthreads();
+#pragma unroll
+                    for (int i = 0; i < BPT; i++) {
+                        const int b = NBINS - 1 - BPT * c.tid - i;
+                        for (int t = 0; t < ntie; t++)
+                            if (A->tbin[t] == b) q[i] += A->tc[t];
+                    }
+                    return true;
+                });
+            if (c.tid < g.G && c.tid > 0) {
+                AuxC *ox = cl.map_shared_rank(A, c.tid);
+                ox->hit_bin = A->hit_bin; ox->hit_qbefore = A->hit_qbefore; ox->hit_cbefore = A->hit_cbefore;
+                ox->tot_q = A->tot_q; ox->tot_c = A->tot_c;
+            }
+        }
+        cl.sync();
         DT(5);
         const int hb = A->hit_bin;
         if (hb < 0) {
@@ -374,38 +432,50 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         const unsigned int blo = lo + ((unsigned int)hb << shift);
         const unsigned long long bhi64 = (unsigned long long)lo + ((unsigned long long)(hb + 1) << shift);
         const unsigned int bhi = bhi64 > 0xFFFFFFFFull ? 0xFFFFFFFFu : (unsigned int)bhi64;
-        // the bin's entries: every block collects its own, then they move to the leader in one piece
-        // (a counter in another block's memory is far too slow to hand out slots one by one)
-        for (int i = c.tid; i < g.nloc; i += NT) {
-            const unsigned int eb = bits[i];
-            if (eb != 0u && eb < w.tau && eb >= blo && eb < bhi) {
-                const int pos = satom_add(&A->ncand, 1);
-                if (pos < NC) A->cand[pos] = make_key(eb, g.c0 + i);
+        // The bin's entries: every block collects its own (in the space of the candidates' values),
+        // reserves room at the leader with one addition to the leader's counter and copies them over.
+        unsigned long long *mybuf = reinterpret_cast<unsigned long long *>(A->pc);
+        constexpr int MYCAP = NC / 2;
+        for (int i4 = c.tid; i4 < g.nloc; i4 += 4 * NT) {
+            unsigned int ebs[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) ebs[u] = (i4 + u * NT < g.nloc) ? bits[i4 + u * NT] : 0u;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const unsigned int eb = ebs[u];
+                if (eb != 0u && eb < w.tau && eb >= blo && eb < bhi) {
+                    const int pos = satom_add(&A->ngath, 1);
+                    if (pos < MYCAP) mybuf[pos] = make_key(eb, g.c0 + i4 + u * NT);
+                }
             }
         }
         __syncthreads();
-        if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x4_n[g.rank] = A->ncand;
-        cl.sync();
-        int nb = 0, cbase = 0;
-        for (int o = 0; o < g.G; o++) { if (o < g.rank) cbase += A->x4_n[o]; nb += A->x4_n[o]; }
-        if (nb <= NC && g.rank > 0) {
-            const int mine = A->x4_n[g.rank];
-            for (int i = c.tid; i < mine; i += NT) lead->cand[cbase + i] = A->cand[i];
+        const int mine = A->ngath;
+        if (c.tid == 0) {
+            A->specbin = atomicAdd(&lead->ncand, mine);
+            if (mine > MYCAP) atomicAdd(&lead->ngath_over, 1);  // more than this block could hold: the bin is split further
         }
+        __syncthreads();
+        const int cbase = A->specbin;
+        if (mine <= MYCAP && cbase + mine <= NC)
+            for (int i = c.tid; i < mine; i += NT) lead->cand[cbase + i] = mybuf[i];
         cl.sync();
+        fetch_from_leader(c, 2, [&](int i) { return (long long)(i == 0 ? lead->ncand : lead->ngath_over); });
+        const int nb = (int)A->rx[0];
+        const bool crowded = nb > NC || A->rx[1] > 0;
         DT(6);
         if (dbg && c.tid == 0) dbg[2] = nb;
         // what lies above the bin is consumed without an event either way
         const float s_bin = binade_ok ? (float)((double)(qy.m0 + qb) * (double)fpow2(j - 23)) : w.s;
         const long long pos_bin = w.pos + ((counting || !binade_ok) ? (long long)cb : 0);
-        if (nb > NC && lvl < 3) {
+        if (crowded && lvl < 3) {
             w.s = s_bin; w.pos = pos_bin;
             w.tau = bhi < w.tau ? bhi : w.tau;
             lo = blo; shift = (lvl == 1) ? BIN_SHIFT2 : 0; lvl++;
             c.status |= MOLLA_ROW_SLOW_PATH;
             continue;
         }
-        if (nb > NC) {
+        if (crowded) {
             // one value, more copies than the buffer holds: add them one at a time (the leader's
             // thread 0), then find which copy, in token order, the event fell on
             c.status |= MOLLA_ROW_SLOW_PATH;
@@ -425,8 +495,11 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
                 A->b_event = ev; A->b_s = s; A->b_pos = pos; A->b_aux = at;
             }
             cl.sync();
-            const int ev = lead->b_event, at = lead->b_aux;
-            w.s = lead->b_s; w.pos = lead->b_pos;
+            fetch_from_leader(c, 4, [&](int i) {
+                return i == 0 ? (long long)lead->b_event : i == 1 ? (long long)lead->b_aux
+                     : i == 2 ? (long long)__float_as_int(lead->b_s) : lead->b_pos; });
+            const int ev = (int)A->rx[0], at = (int)A->rx[1];
+            w.s = __int_as_float((int)A->rx[2]); w.pos = A->rx[3];
             if (ev != EV_NONE) {
                 const int id = cluster_nth_equal(cl, c, g, bits, blo, at);
                 w.event = ev; w.idx = id; w.p = pv; w.tie = 1;
@@ -441,10 +514,14 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         }
         cl.sync();
         DT(7);
-        w.s = lead->b_s; w.pos = lead->b_pos; w.tau = blo;
-        const int ev = lead->b_event;
+        fetch_from_leader(c, 6, [&](int i) {
+            return i == 0 ? (long long)lead->b_event : i == 1 ? (long long)lead->b_aux
+                 : i == 2 ? (long long)__float_as_int(lead->b_s) : i == 3 ? lead->b_pos
+                 : i == 4 ? (long long)lead->b_idx : (long long)__float_as_int(lead->b_p); });
+        w.s = __int_as_float((int)A->rx[2]); w.pos = A->rx[3]; w.tau = blo;
+        const int ev = (int)A->rx[0];
         if (ev != EV_NONE) {
-            w.event = ev; w.idx = lead->b_idx; w.p = lead->b_p; w.tie = lead->b_aux;
+            w.event = ev; w.idx = (int)A->rx[4]; w.p = __int_as_float((int)A->rx[5]); w.tie = (int)A->rx[1];
             cl.sync();  // the leader's results are read before anyone moves on
             return;
         }
@@ -850,7 +927,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x3_n[g.rank] = A->ncand;
 
     // ---- 5. the softmax denominator, exactly as the sequential loop rounds it
-    const ClSum zs = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f, (a.prof && leader) ? a.prof + (long long)r * 32 + 14 : nullptr, a.prof ? a.prof + (long long)r * 32 + 20 : nullptr);
+    const ClSum zs = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f, (a.prof && leader) ? a.prof + (long long)r * 32 + 14 : nullptr, (a.prof && !p3row) ? a.prof + (long long)r * 32 + 20 : nullptr);
     const float Z = zs.s;
     if (zs.slow) c.status |= MOLLA_ROW_SLOW_PATH;
     dZ = Z;
