@@ -304,22 +304,6 @@ int32_t molla_sample_expf(const float *d_x, int64_t n, void *stream, float *d_ou
  * library at sample.mojo:541,550), element-wise on the device. For tests. */
 int32_t molla_sample_logf(const float *d_x, int64_t n, void *stream, float *d_out);
 
-/* Testing aid with no counterpart in the reference: experiment switches of the row kernel
- * (bit 1: no last-use hint on the second pass over a row; bit 2: no keep hint on list
- * traffic). 0, the default, is the production behaviour. */
-void molla_sample_debug_knobs(int32_t knobs);
-
-/* Testing aid with no counterpart in the reference: when given a device buffer of
- * B x 16 int64, later molla_sample_batch calls from any thread record clock64() stamps
- * at the phase boundaries of each row (NULL switches it off again). */
-void molla_sample_debug_profile(void *d_stamps);
-
-/* Testing aid with no counterpart in the reference: when given a device buffer of
- * B x cap int32, later molla_sample_batch calls write, for every row sampled with
- * 1 < top_k < 128, the ids that survive top-k (`_top_k`, sample.mojo:485-490) in
- * descending probability, padded with -1 (NULL switches it off again). */
-void molla_sample_debug_topk(void *d_ids, int32_t cap);
-
 /* cudaStreamSynchronize on `stream`, returning a status; then, if
  * `d_row_status` is given, nothing else is implied: rows report for themselves. */
 int32_t molla_sample_sync(void *stream);

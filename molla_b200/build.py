@@ -9,8 +9,12 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = [os.path.join(_HERE, "csrc", "molla_sample.cu"), os.path.join(_HERE, "csrc", "molla_cluster.cu")]
 DEPS = SRC + [os.path.join(_HERE, "csrc", "molla_device.cuh"), os.path.join(_HERE, "csrc", "molla_exact.cuh"),
               os.path.join(_HERE, "csrc", "molla_cluster.h"),
-              os.path.join(os.path.dirname(_HERE), "include", "molla_sample.h")]
+              os.path.join(os.path.dirname(_HERE), "include", "molla_sample.h"),
+              os.path.join(os.path.dirname(_HERE), "include", "molla_sample_testing.h")]
 OUT = os.path.join(_HERE, "lib", "libmolla_sample.so")
+# the same sources with -DMOLLA_SAMPLE_TESTING: profiling stamps, experiment switches and the
+# exports of include/molla_sample_testing.h, for the tests and for profiling sessions
+OUT_TESTING = os.path.join(_HERE, "lib", "libmolla_sample_testing.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -27,21 +31,25 @@ def nvcc() -> str:
     raise RuntimeError("nvcc not found: the CUDA library cannot be built")
 
 
-def stale() -> bool:
-    if not os.path.exists(OUT):
+def stale(out: str = OUT) -> bool:
+    if not os.path.exists(out):
         return True
-    t = os.path.getmtime(OUT)
+    t = os.path.getmtime(out)
     return any(os.path.getmtime(d) > t for d in DEPS if os.path.exists(d))
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
-    if not force and not stale():
-        return OUT
-    os.makedirs(os.path.dirname(OUT), exist_ok=True)
-    cmd = [nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", OUT] + SRC
+def build_library(force: bool = False, verbose: bool = False, testing: bool = False) -> str:
+    """Builds libmolla_sample.so (or, with `testing`, libmolla_sample_testing.so) if it is out of date."""
+    out = OUT_TESTING if testing else OUT
+    if not force and not stale(out):
+        return out
+    os.makedirs(os.path.dirname(out), exist_ok=True)
+    cmd = ([nvcc()] + NVCC_FLAGS + (["-DMOLLA_SAMPLE_TESTING"] if testing else [])
+           + (["-Xptxas", "-v"] if verbose else []) + ["-o", out] + SRC)
     subprocess.check_call(cmd)
-    return OUT
+    return out
 
 
 if __name__ == "__main__":
     print(build_library(force=True, verbose=True))
+    print(build_library(force=True, testing=True))

@@ -35,8 +35,10 @@ EXPORTS = (
     "molla_sample_workspace_bytes", "molla_sample_batch", "molla_sample_host_workspace_bytes",
     "molla_sample_batch_host", "molla_sample_batch_noalloc", "molla_sample_shard_summary_words",
     "molla_sample_shard_stage_a", "molla_sample_shard_merge", "molla_sample_shard_stage_b", "molla_sample_shard_stage_c", "molla_sample_penalised",
-    "molla_sample_decode_step", "molla_sample_logprobs", "molla_sample_expf", "molla_sample_logf", "molla_sample_debug_knobs", "molla_sample_sync", "molla_sample_debug_profile", "molla_sample_debug_topk",
+    "molla_sample_decode_step", "molla_sample_logprobs", "molla_sample_expf", "molla_sample_logf", "molla_sample_sync",
 )
+TESTING_EXPORTS = ("molla_sample_debug_knobs", "molla_sample_debug_profile", "molla_sample_debug_topk")
+TESTING_LIB_PATH = os.path.join(_HERE, "lib", "libmolla_sample_testing.so")
 
 
 class MollaSampleError(RuntimeError):
@@ -46,18 +48,42 @@ class MollaSampleError(RuntimeError):
 
 
 _lib = None
+_testing_lib = None
 
 
 def lib():
     """The loaded library. Raises if it is not there: nothing else can do its work."""
     global _lib
-    if _lib is not None:
-        return _lib
-    if not os.path.exists(LIB_PATH):
+    if _lib is None:
+        _lib = _load(LIB_PATH, testing=False)
+    return _lib
+
+
+class testing_library:
+    """`with capi.testing_library() as L:` routes every call of this package through
+    libmolla_sample_testing.so (the same kernels built with their profiling stamps and experiment
+    switches, see include/molla_sample_testing.h) and back to the production library afterwards."""
+
+    def __enter__(self):
+        global _lib, _testing_lib
+        if _testing_lib is None:
+            _testing_lib = _load(TESTING_LIB_PATH, testing=True)
+        self._saved = _lib
+        _lib = _testing_lib
+        return _testing_lib
+
+    def __exit__(self, *exc):
+        global _lib
+        _lib = self._saved
+        return False
+
+
+def _load(path, testing):
+    if not os.path.exists(path):
         raise RuntimeError(
-            f"{LIB_PATH} is missing: build it with `python -m molla_b200.build` "
+            f"{path} is missing: build it with `python -m molla_b200.build` "
             "(there is no CPU or PyTorch fallback for the sampling kernels)")
-    L = C.CDLL(LIB_PATH)
+    L = C.CDLL(path)
     vp, i32, i64, u64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_float
     L.molla_sample_abi_version.restype = i32
     L.molla_sample_abi_version.argtypes = []
@@ -96,15 +122,15 @@ def lib():
     L.molla_sample_expf.argtypes = [vp, i64, vp, vp]
     L.molla_sample_logf.restype = i32
     L.molla_sample_logf.argtypes = [vp, i64, vp, vp]
-    L.molla_sample_debug_knobs.restype = None
-    L.molla_sample_debug_knobs.argtypes = [i32]
-    L.molla_sample_debug_profile.restype = None
-    L.molla_sample_debug_profile.argtypes = [vp]
-    L.molla_sample_debug_topk.restype = None
-    L.molla_sample_debug_topk.argtypes = [vp, i32]
     L.molla_sample_sync.restype = i32
     L.molla_sample_sync.argtypes = [vp]
-    _lib = L
+    if testing:
+        L.molla_sample_debug_knobs.restype = None
+        L.molla_sample_debug_knobs.argtypes = [i32]
+        L.molla_sample_debug_profile.restype = None
+        L.molla_sample_debug_profile.argtypes = [vp]
+        L.molla_sample_debug_topk.restype = None
+        L.molla_sample_debug_topk.argtypes = [vp, i32]
     return L
 
 

@@ -43,7 +43,14 @@ constexpr float TRES = (float)(NT / 32);     // bins per unit of logit: the bins
 // tables, the candidates and their values (all idle then)
 constexpr int PLIST_CAP = (3 * NBINS * 4 + NC * 8 + NC * 4) / 2;
 
+// Profiling stamps exist in the testing build only (per row 32 slots of clock readings and counts).
+#ifdef MOLLA_SAMPLE_TESTING
 #define CSTAMP(i) do { if (a.prof && leader && c.tid == 0) a.prof[(long long)r * 32 + (i)] = clock64(); } while (0)
+#define CPROF_SLOTS(cond, first) ((a.prof && (cond)) ? a.prof + (long long)r * 32 + (first) : nullptr)
+#else
+#define CSTAMP(i) do { } while (0)
+#define CPROF_SLOTS(cond, first) nullptr
+#endif
 
 struct __align__(16) AuxC {
     union {
@@ -592,11 +599,13 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     // the end of every row: the leader's thread 0 writes the answer and does `_took`
     auto finish = [&]() {
         if (!(leader && c.tid == 0)) return;
+#ifdef MOLLA_SAMPLE_TESTING
         if (a.prof) {
             unsigned long long gt;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
             a.prof[(long long)r * 32 + 11] = (long long)gt; a.prof[(long long)r * 32 + 9] = clock64();
         }
+#endif
         if (c.status & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG | MOLLA_ROW_UNSUPPORTED)) token = -1;
         a.tokens[r] = token;
         a.row_status[r] = c.status;
@@ -617,11 +626,13 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     if (c.status) { finish(); return; }
 
     CSTAMP(0);
+#ifdef MOLLA_SAMPLE_TESTING
     if (a.prof && leader && c.tid == 0) {
         unsigned long long gt;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
         a.prof[(long long)r * 32 + 10] = (long long)gt; a.prof[(long long)r * 32 + 12] = blockIdx.x;
     }
+#endif
     // ---- 1. this block's range of the row, HBM -> shared memory
     const float *src = a.logits + lrow * a.row_stride + g.c0;
     const bool aligned = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0);
@@ -666,6 +677,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         }
         if (!done) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
     }
+    if (MOLLA_KNOB(a, 16) && c.warp == 3) c.status |= MOLLA_ROW_LOAD_TIMEOUT;  // testing build: one warp reports a wait that ran out
     if (__syncthreads_or((c.status & MOLLA_ROW_LOAD_TIMEOUT) ? 1 : 0)) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
     CSTAMP(1);
     if (a.softcap > 0.0f) {
@@ -879,7 +891,9 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         int tot;
         const int base = block_excl_scan<int>(cnt, A->wsi, &tot);
         CSTAMP(16);
+#ifdef MOLLA_SAMPLE_TESTING
         if (a.prof && leader && c.tid == 0) a.prof[(long long)r * 32 + 19] = tot;
+#endif
         int o = base;  // the list offset of this thread's next kept element
         for (int lo_ = 0; lo_ < tot; lo_ += PLIST_CAP) {
             // this thread's kept positions that fall into [lo_, lo_ + PLIST_CAP) of the block's list
@@ -927,7 +941,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x3_n[g.rank] = A->ncand;
 
     // ---- 5. the softmax denominator, exactly as the sequential loop rounds it
-    const ClSum zs = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f, (a.prof && leader) ? a.prof + (long long)r * 32 + 14 : nullptr, (a.prof && !p3row) ? a.prof + (long long)r * 32 + 20 : nullptr);
+    const ClSum zs = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f, CPROF_SLOTS(leader, 14), CPROF_SLOTS(!p3row, 20));
     const float Z = zs.s;
     if (zs.slow) c.status |= MOLLA_ROW_SLOW_PATH;
     dZ = Z;
@@ -1044,11 +1058,13 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
             A->hidx[i] = (unsigned int)key_idx(A->cand[i]) | (eq ? 0x80000000u : 0u);
         }
         __syncthreads();
+#ifdef MOLLA_SAMPLE_TESTING
         if (a.topk_out) {
             for (int i = c.tid; i < a.topk_cap; i += NT)
                 a.topk_out[(long long)r * a.topk_cap + i] =
                     (i < nc && (long long)i < n_use) ? (int)(A->hidx[i] & 0x7fffffffu) : -1;
         }
+#endif
         if (c.tid == 0) {
             float s = 0.0f;
             long long pos = 0;
@@ -1130,7 +1146,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
     cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
     const bool limited = n_use < (long long)a.V;
-    descend_cluster(cl, c, g, rowbits, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_use : -1, (a.prof && leader) ? a.prof + (long long)r * 32 + 20 : nullptr);
+    descend_cluster(cl, c, g, rowbits, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_use : -1, CPROF_SLOTS(leader, 20));
     if (cutw.event != EV_DEGENERATE) {
         if (cutw.event == EV_CUT && cutw.tie) c.status |= MOLLA_ROW_TOPP_TIE;
         if (cutw.event == EV_LIMIT && cutw.tie) c.status |= MOLLA_ROW_TOPK_TIE;

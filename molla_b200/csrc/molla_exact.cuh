@@ -27,8 +27,11 @@ struct BatchArgs {
     int *row_counter;            // scratch: next row to hand out (zeroed before the launch)
     const int *order;            // scratch: rows by decreasing cost (NULL = as given)
     unsigned long long *wlist;   // scratch: per CTA, 2 x 16 x R list entries
-    long long *prof;             // optional [B x 16] clock64 stamps per row (testing aid)
-    int knobs;                   // experiment switches (testing aid; 0 in production)
+#ifdef MOLLA_SAMPLE_TESTING
+    long long *prof;             // optional [B x 32] clock64 stamps per row
+    int knobs;                   // experiment switches (0 = production behaviour)
+    int *topk_out; int topk_cap; // optional [B x cap] ids of the sorted head after top-k
+#endif
     // thread blocks that ran out of rows help the ones still converting a long list (HelpSlot)
     void *help;                  // [grid] HelpSlot, one per thread block, or nullptr
     unsigned int *help_tables;   // [grid x HELP_TABLE_WORDS]
@@ -45,7 +48,6 @@ struct BatchArgs {
     unsigned long long *drawn_rw;  // [slots] draw counters, advanced by one per pick
     const long long *stop_token;   // [slots] or nullptr
     unsigned char *stopped;        // [B] or nullptr: the pick was the slot's stop token
-    int *topk_out; int topk_cap; // optional [B x cap] ids of the sorted head after top-k (testing aid)
     // vocab-sharded form: this GPU holds columns [col0, col0 + V) of a vocabulary of Vg
     int n_logit_rows, n_slots;   // bounds of rows[] and slot[] values (0 = not given)
     // one row per thread-block cluster: blocks per cluster, logits per block, logits per thread
@@ -82,6 +84,14 @@ constexpr float REL_MARGIN = 17.6f;  // > 25 ln 2 = 17.33: this far below ln(run
 constexpr int ORDER_CAP = 4096;      // rows whose order is sorted by cost
 static_assert(NBINS % NT == 0 && NC % NT == 0 && HEADC <= NC, "table sizes must be multiples of the block size");
 static_assert((1 << BIN_SHIFT2) <= NBINS, "the third level of the bin search looks at single values");
+
+// The testing build (-DMOLLA_SAMPLE_TESTING) carries experiment switches and profiling stamps;
+// the production build has neither.
+#ifdef MOLLA_SAMPLE_TESTING
+#define MOLLA_KNOB(a, bit) (((a).knobs & (bit)) != 0)
+#else
+#define MOLLA_KNOB(a, bit) false
+#endif
 
 // Tell the compiler which address space a pointer is in (functions it does not inline would
 // otherwise use generic loads, stores and atomics on shared memory).

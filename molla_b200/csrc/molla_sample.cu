@@ -41,6 +41,9 @@
 #include <string.h>
 
 #include "../../include/molla_sample.h"
+#ifdef MOLLA_SAMPLE_TESTING
+#include "../../include/molla_sample_testing.h"
+#endif
 #include "molla_device.cuh"
 #include "molla_exact.cuh"
 #include "molla_cluster.h"
@@ -123,13 +126,8 @@ struct Ctx {
     // this warp's region and pipeline
     int rbeg, rlen, npieces;
     unsigned int parbits;
-    int nphase;           // histogram phases run by the descending walks of this row (profiling aid)
-    int own_units, helped_passes;  // segments this block did itself in passes it shared / such passes (profiling aid)
-    long long t_help;     // cycles spent in the filtered passes shared with helpers (profiling aid)
-    long long t_stage, t_build;  // cycles of the exact sum spent staging list blocks / building their tables (profiling aid)
 };
 
-#define STAMP(i) do { if (a.prof && c.tid == 0) a.prof[(long long)r * 16 + (i)] = clock64(); } while (0)
 
 
 // ---- the warp's own pipeline: piece p of its region lands in slot p % NSTAGE --------
@@ -329,9 +327,7 @@ __device__ void p1_block(Ctx &c, V vals, int n, int base, bool locate, float tar
     IN_SHARED(A);
     int L = (n + NT - 1) / NT;
     if ((L & 1) == 0) L += 1;
-    const long long tq0 = clock64();
     p1_build(c, vals, n, L, (double)A->walk_s);
-    c.t_build += clock64() - tq0;
     if (c.tid == 0) {
         Walker w; w.s = A->walk_s; w.found = 0; w.at = -1; w.slow = A->walk_slow;
         p1_walk(c, vals, n, L, locate, target, w);
@@ -369,13 +365,11 @@ __device__ void p1_run(Ctx &c, const LView &lv, unsigned int *vals, bool locate,
         const int n = min(VBLK, lv.n - b * VBLK);
         __syncthreads();
         if (!locate && c.tid == 0 && b < MAX_VBLK) A->blk_s[b] = A->walk_s;
-        const long long tq0 = clock64();
         {
             const int o = b * VBLK;
             lv.for_range(c.tid, o, o + n, [&](int v, unsigned long long k) { vals[v - o] = (unsigned int)(k >> 32); });
         }
         __syncthreads();
-        c.t_stage += clock64() - tq0;
         if (locate && A->walk_found) break;
         p1_block(c, ValBits{vals}, n, b * VBLK, locate, target);
     }
@@ -439,7 +433,6 @@ __device__ void descend(Ctx &c, const LView &lv, Walk &w, float x_ge, float x_gt
     unsigned int lo = 0u;
     int shift = BIN_SHIFT;
     for (int phase = 0; phase < 8192; phase++) {
-        c.nphase++;
         __syncthreads();
         for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0u; A->u.h.hqh[i] = 0u; A->u.h.hc[i] = 0u; }
         if (c.tid == 0) { A->specbin = -1; A->ncand = 0; }
@@ -711,7 +704,6 @@ __device__ bool helped_convert(Ctx &c, const BatchArgs &a, unsigned long long *w
     }
     __threadfence();
     __syncthreads();
-    c.helped_passes++;
     if (c.tid == 0) { atomicExch(&hs->claim, 0); __threadfence(); atomicExch(&hs->open, 1); }
     for (;;) {
         __syncthreads();
@@ -719,7 +711,6 @@ __device__ bool helped_convert(Ctx &c, const BatchArgs &a, unsigned long long *w
         __syncthreads();
         const int u = A->evt_thread;
         if (u >= NWARP) break;
-        c.own_units++;
         convert_segment(c, wl_seg + (size_t)u * (size_t)a.R, A->woff[u + 1] - A->woff[u], Z, tau_bits, mark_head, mt);
         __threadfence();
         __syncthreads();
@@ -780,7 +771,6 @@ __device__ bool helped_gather(Ctx &c, const BatchArgs &a, const unsigned long lo
     if (c.tid == 0) { hs->tau0 = tau0; hs->bin = hb; hs->kind = 1; hs->found = 0; hs->nunits = NWARP; hs->done = 0; A->ncand = 0; }
     __threadfence();
     __syncthreads();
-    c.helped_passes++;
     if (c.tid == 0) { atomicExch(&hs->claim, 0); __threadfence(); atomicExch(&hs->open, 1); }
     for (;;) {
         __syncthreads();
@@ -788,7 +778,6 @@ __device__ bool helped_gather(Ctx &c, const BatchArgs &a, const unsigned long lo
         __syncthreads();
         const int u = A->evt_thread;
         if (u >= NWARP) break;
-        c.own_units++;
         gather_segment(c, wl_seg + (size_t)u * (size_t)a.R, A->woff[u + 1] - A->woff[u], tau0, hb, [&](unsigned long long kk) {
             const int pos = satom_add(&A->ncand, 1);
             if (pos < NC) A->cand[pos] = kk;
@@ -903,7 +892,6 @@ __device__ bool descend_masses(Ctx &c, const BatchArgs &a, bool helped, const LV
     IN_SHARED(A);
     const bool counting = nstop >= 0;
     for (int phase = 0; phase < 8192; phase++) {
-        c.nphase++;
         if (hi <= 0) { w.tau = 0; w.event = EV_EXHAUSTED; return true; }
         if (!(w.s > 0.0f)) return false;
         const int j = fexpo(w.s);
@@ -954,9 +942,7 @@ __device__ bool descend_masses(Ctx &c, const BatchArgs &a, bool helped, const LV
         __syncthreads();
         const unsigned int tau0 = mt.tau0;
         if (helped) {
-            const long long tq0 = clock64();
             if (!helped_gather(c, a, lv.seg, tau0, hb)) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
-            c.t_help += clock64() - tq0;
         } else
         lv.for_each(c.tid, [&](int, unsigned long long key, unsigned long long *) {
             const unsigned int pb = (unsigned int)(key >> 32);
@@ -1082,7 +1068,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
     unsigned long long *wl_flat = wl_seg + (size_t)NWARP * (size_t)a.R;                   // contiguous copy
     unsigned long long *slist = reinterpret_cast<unsigned long long *>(c.stage);           // list in shared memory
     const int nwords = (a.V + 31) >> 5;
-    const uint64_t keep_policy = (a.knobs & 4) ? l2_normal_policy() : l2_keep_policy();
+    const uint64_t keep_policy = MOLLA_KNOB(a, 4) ? l2_normal_policy() : l2_keep_policy();
 
     bool had_row = false;
     for (;;) {
@@ -1097,8 +1083,17 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         const int r = A->cur_row;
         if (r >= a.B) break;
         had_row = true;
-        c.status = 0; c.last_read = false; c.nphase = 0; c.own_units = 0; c.helped_passes = 0; c.t_help = 0; c.t_stage = 0; c.t_build = 0;
+        c.status = 0; c.last_read = false;
         const int q = a.slot ? a.slot[r] : r;  // where this row's settings and state live
+        {   // a stale row or slot index: nothing of that row or slot is touched
+            const long long lrow = a.rows ? (long long)a.rows[r] : (long long)r;
+            const bool idx_ok = (!a.slot || (q >= 0 && (a.n_slots <= 0 || q < a.n_slots))) &&
+                                (!a.rows || (lrow >= 0 && (a.n_logit_rows <= 0 || lrow < a.n_logit_rows)));
+            if (!idx_ok) {
+                if (c.tid == 0 && !a.penalised_only && a.tokens) { a.tokens[r] = -1; a.row_status[r] = MOLLA_ROW_INVALID_CONFIG; }
+                continue;
+            }
+        }
         const float T = a.temperature ? a.temperature[q] : 0.0f;
         const int k = a.top_k ? a.top_k[q] : 0;
         const float P = a.top_p ? a.top_p[q] : 1.0f;
@@ -1140,12 +1135,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         c.src = a.logits + (long long)(a.rows ? a.rows[r] : r) * a.row_stride;
         c.softcap = a.softcap;
         c.aligned = ((reinterpret_cast<uintptr_t>(c.src) & 15u) == 0);
-        STAMP(0);
-        if (a.prof && c.tid == 0) {  // when and where the row ran, on the clock all SMs share
-            unsigned long long gt;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-            a.prof[(long long)r * 16 + 10] = (long long)gt; a.prof[(long long)r * 16 + 12] = blockIdx.x;
-        }
 
         // ---- 1. logit bias and penalties (sample.mojo:381-417) touch at most a window's worth of
         // tokens: their new values go into a hash, a bitmap over the vocabulary marks them.
@@ -1187,7 +1176,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             __syncthreads();
             c.patching = true;
         }
-        STAMP(1);
 
         if (a.penalised) {
             float *dst = a.penalised + (long long)r * a.V;
@@ -1252,7 +1240,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         int imax = tidx;
         if (a.mode != 3) block_argmax(c, xmax, imax);
         if (imax == 0x7fffffff) imax = 0;
-        STAMP(2);
         if (a.mode == 1) {
             // stage 1 of the sharded form: what the other shards need to know about this slice
             int tot;
@@ -1345,14 +1332,11 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             for (int w = 0; w < c.warp; w++) lb += A->u.s.rmax[w];
             int base = 0;
             unsigned long long *myseg = wl_seg + (size_t)c.warp * (size_t)a.R;
-            long long tqa = 0, tqb = 0, tqc = 0, tq0;
-            c.last_read = !(a.knobs & 2);
+            c.last_read = !MOLLA_KNOB(a, 2);
             pieces_begin(c);
             for (int p = 0; p < c.npieces; p++) {
                 int n;
-                tq0 = clock64();
                 float *slot = const_cast<float *>(piece_acquire(c, p, n));
-                tqa += clock64() - tq0; tq0 = clock64();
                 const int g0 = c.rbeg + p * PIECE + c.lane * LT;
                 float x[LT];
                 load_chunk(c, slot, n, g0, x);
@@ -1376,7 +1360,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                     }
                 }
                 __syncwarp();
-                tqb += clock64() - tq0; tq0 = clock64();
                 {
                     const int gbase = a.col0 + c.rbeg + p * PIECE;
                     auto value = [&](int i) -> float {
@@ -1401,7 +1384,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 }
                 base += total;
                 lb += A->u.s.pmax[c.warp][p];
-                tqc += clock64() - tq0;
             }
 
             if (c.lane == 0) A->wcnt[c.warp] = base;
@@ -1460,7 +1442,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 __syncthreads();
                 lv.flat = nullptr; lv.seg = wl_flat; lv.stride = 0;
             }
-            STAMP(3);
 
             // ---- 4. the softmax denominator, exactly as the sequential loop rounds it
             if (c.tid == 0) A->walk_slow = 0;
@@ -1469,7 +1450,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             const float Z = A->walk_s;
             if (A->walk_slow) c.status |= MOLLA_ROW_SLOW_PATH;
             dZ = Z;
-            STAMP(4);
 
             // probabilities p = e / Z (sample.mojo:437-438). The head's candidates came out of pass B
             // and are converted on their own; the list itself is converted (once, in place) only for
@@ -1551,17 +1531,14 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 __syncthreads();
             }
 
-            STAMP(5);
             if (pure) {
                 // ---- 5a. nothing sorted: the draw walks the vocabulary in order (sample.mojo:365-369,
                 // 580-594): the same exact-sum machinery on the list of probabilities
                 __syncthreads();
                 p1_run(c, lv, vstage, false, 0.0f);
-                STAMP(6);
                 const float sum = A->walk_s;
                 const float target = __fmul_rn(u01, sum);
                 p1_run(c, lv, vstage, true, target);
-                STAMP(7);
                 if (c.tid == 0) {
                     A->b_sum = sum; A->b_target = target;
                     A->b_event = A->walk_found;
@@ -1611,11 +1588,13 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         A->hidx[i] = (unsigned int)key_idx(A->cand[i]) | (eq ? 0x80000000u : 0u);
                     }
                     __syncthreads();
+#ifdef MOLLA_SAMPLE_TESTING
                     if (a.topk_out) {
                         for (int i = c.tid; i < a.topk_cap; i += NT)
                             a.topk_out[(long long)r * a.topk_cap + i] =
                                 (i < nc && (long long)i < n_use) ? (int)(A->hidx[i] & 0x7fffffffu) : -1;
                     }
+#endif
                     if (c.tid == 0) {
                         float s = 0.0f;
                         long long pos = 0;
@@ -1668,7 +1647,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         token = A->b_idx; dp = A->b_p; dsum = A->b_sum; dtarget = A->b_target;
                     } else {
                         // ---- 6. past the head: the cut walk, then the draw walk
-                        STAMP(6);
                         // long lists (global memory) are first sorted into their value bins
                         // long lists (global memory): per-bin integer masses come out of the conversion pass
                         MassCk ck;
@@ -1677,7 +1655,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         mt.sets = reinterpret_cast<unsigned int *>(c.stage);  // idle while the list is a global view
                         const bool use_mt = (a.mode == 0) && !lv.flat && !list_is_p && head_s > 0.0f;
                         if (use_mt) { masses_begin(c, mt, fexpo(head_s), tau_head); mass_on = true; }
-                        const bool help_on = use_mt && a.help && nl >= HELP_MIN_LIST && !(a.knobs & 8);
+                        const bool help_on = use_mt && a.help && nl >= HELP_MIN_LIST && !MOLLA_KNOB(a, 8);
                         if (help_on) {
                             // a long list: blocks that have run out of rows take segments of this pass
                             if (!helped_convert(c, a, wl_seg, Z, tau_bits, mark_head, mt)) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
@@ -1685,7 +1663,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                         }
                         if (!list_is_p) { convert_list(false); list_is_p = true; }
                         mass_on = false;
-                        STAMP(7);
                         __syncthreads();
                         Walk cutw; cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
                         cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
@@ -1763,13 +1740,10 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
                 }
             }
         }
-        STAMP(9);
-        if (a.prof && c.tid == 0) {
-            unsigned long long gt;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-            a.prof[(long long)r * 16 + 11] = (long long)gt;
-        }
-        if (a.prof && c.tid == 0) { a.prof[(long long)r * 16 + 13] = c.own_units * 100 + c.helped_passes; a.prof[(long long)r * 16 + 5] = c.t_help; a.prof[(long long)r * 16 + 8] = c.nphase; a.prof[(long long)r * 16 + 14] = c.t_stage; a.prof[(long long)r * 16 + 15] = c.t_build; }
+        // a bounded wait that ran out in any warp fails the row; a failed row keeps its sampler state
+        if (MOLLA_KNOB(a, 16) && c.warp == 3) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
+        if (__syncthreads_or((c.status & MOLLA_ROW_LOAD_TIMEOUT) ? 1 : 0)) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
+        if (c.status & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG | MOLLA_ROW_UNSUPPORTED | MOLLA_ROW_SHARD_OVERFLOW)) token = -1;
         if (c.tid == 0) {
             a.tokens[r] = token;
             a.row_status[r] = c.status;
@@ -1788,7 +1762,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
             if (a.diag) { a.diag[4 * r] = dZ; a.diag[4 * r + 1] = dsum; a.diag[4 * r + 2] = dtarget; a.diag[4 * r + 3] = dp; }
         }
     }
-    if (a.help && !(a.knobs & 8)) help_others(c, a);  // no rows left: lend a hand to the blocks still on a long list
+    if (a.help && !MOLLA_KNOB(a, 8)) help_others(c, a);  // no rows left: lend a hand to the blocks still on a long list
 }
 
 // =============================================================================
@@ -1798,39 +1772,51 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
 __global__ void __launch_bounds__(NT, 1) logprob_kernel(const float *logits, long long row_stride, int B, int V,
                                                         const int *tokens, int top_n, float *chosen_lp,
                                                         int *top_ids, float *top_lps, float *full_out,
-                                                        const int *rows, float softcap) {
+                                                        const int *rows, int n_logit_rows, float softcap) {
     __shared__ float wsf[NWARP + 1];
+    __shared__ int wsi[NWARP + 1];
     __shared__ double wsd[NWARP + 1];
     __shared__ unsigned long long cand[NT];
     __shared__ int ncand;
     __shared__ float s_thr;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int r = blockIdx.x; r < B; r += gridDim.x) {
-        const float *z = logits + (long long)(rows ? rows[r] : r) * row_stride;
-        auto at = [&](int i) -> float { const float x = __ldg(z + i); return softcap > 0.0f ? softcap_pinned(x, softcap) : x; };
+        const long long lrow = rows ? (long long)rows[r] : (long long)r;
+        if (rows && (lrow < 0 || (n_logit_rows > 0 && lrow >= n_logit_rows))) {
+            // a stale row index: nothing is read; the row's sampling call has reported it
+            if (chosen_lp && tid == 0) chosen_lp[r] = 0.0f;
+            for (int i = tid; i < top_n; i += NT) { top_ids[(long long)r * top_n + i] = -1; top_lps[(long long)r * top_n + i] = 0.0f; }
+            continue;
+        }
+        const float *z = logits + lrow * row_stride;
+        auto cap1 = [&](float x) -> float { return softcap > 0.0f ? softcap_pinned(x, softcap) : x; };
+        auto at = [&](int i) -> float { return cap1(__ldg(z + i)); };
+        // rows that start on a 16-byte boundary are read four logits at a time
+        const bool vec = ((reinterpret_cast<uintptr_t>(z) & 15u) == 0);
+        const int n4 = vec ? (V >> 2) : 0;
+        const float4 *z4 = reinterpret_cast<const float4 *>(z);
         // pass 1: maximum and each thread's own maximum
         float tm = -INFINITY;
-        for (int i = tid; i < V; i += NT) tm = fmaxf(tm, at(i));
+        for (int i = tid; i < n4; i += NT) {
+            const float4 x = __ldg(z4 + i);
+            tm = fmaxf(fmaxf(tm, fmaxf(cap1(x.x), cap1(x.y))), fmaxf(cap1(x.z), cap1(x.w)));
+        }
+        for (int i = 4 * n4 + tid; i < V; i += NT) tm = fmaxf(tm, at(i));
         float m = warp_max(tm);
         __syncthreads();
         if (lane == 0) wsf[warp] = m;
         __syncthreads();
         float top = wsf[0];
         for (int w = 1; w < NWARP; w++) top = fmaxf(top, wsf[w]);
-        // threshold for the top-N: the N-th largest of the per-thread maxima
+        // threshold for the top-N: the N-th largest of the per-thread maxima (at least N logits reach it)
         float thr = -INFINITY;
         if (top_n > 0) {
-            // order-preserving key of a float
-            unsigned int b = __float_as_uint(tm);
-            unsigned int key = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
             __syncthreads();
-            cand[tid] = ((unsigned long long)key << 32) | (unsigned long long)tid;
+            cand[tid] = ((unsigned long long)fkey(tm) << 32) | (unsigned long long)tid;
             bitonic_desc(cand, NT, tid);
             if (tid == 0) {
-                int nth = min(top_n, V) - 1;
-                unsigned int kk = (unsigned int)(cand[nth] >> 32);
-                unsigned int bb = (kk & 0x80000000u) ? (kk & 0x7fffffffu) : ~kk;
-                s_thr = __uint_as_float(bb);
+                const int nth = min(min(top_n, V), NT) - 1;
+                s_thr = fkey_inv((unsigned int)(cand[nth] >> 32));
                 ncand = 0;
             }
             __syncthreads();
@@ -1838,18 +1824,18 @@ __global__ void __launch_bounds__(NT, 1) logprob_kernel(const float *logits, lon
         }
         // pass 2: sum of exp(z - top) accumulated in fp64, candidates for the top-N
         double acc = 0.0;
-        for (int i = tid; i < V; i += NT) {
-            float x = at(i);
+        auto one = [&](float x, int i) {
             acc += (double)expf_pinned(__fsub_rn(x, top));
             if (top_n > 0 && x >= thr) {
-                int pos = atomicAdd(&ncand, 1);
-                if (pos < NT) {
-                    unsigned int b = __float_as_uint(x);
-                    unsigned int key = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-                    cand[pos] = ((unsigned long long)key << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)i);
-                }
+                const int pos = atomicAdd(&ncand, 1);
+                if (pos < NT) cand[pos] = ((unsigned long long)fkey(x) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)i);
             }
+        };
+        for (int i = tid; i < n4; i += NT) {
+            const float4 x = __ldg(z4 + i);
+            one(cap1(x.x), 4 * i); one(cap1(x.y), 4 * i + 1); one(cap1(x.z), 4 * i + 2); one(cap1(x.w), 4 * i + 3);
         }
+        for (int i = 4 * n4 + tid; i < V; i += NT) one(at(i), i);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
         __syncthreads();
@@ -1868,18 +1854,49 @@ __global__ void __launch_bounds__(NT, 1) logprob_kernel(const float *logits, lon
         }
         if (top_n > 0) {
             __syncthreads();
-            int n = min(ncand, NT);
-            for (int i = n + tid; i < NT; i += NT) cand[i] = 0ull;
-            __syncthreads();
-            bitonic_desc(cand, NT, tid);
-            if (tid < top_n) {
-                if (tid < n) {
-                    int id = (int)(0xFFFFFFFFu - (unsigned int)(cand[tid] & 0xFFFFFFFFull));
-                    top_ids[(long long)r * top_n + tid] = id;
-                    top_lps[(long long)r * top_n + tid] = __fsub_rn(__fsub_rn(at(id), top), offset);
-                } else {
-                    top_ids[(long long)r * top_n + tid] = -1;
-                    top_lps[(long long)r * top_n + tid] = 0.0f;
+            const int n = ncand;
+            if (n <= NT) {
+                for (int i = n + tid; i < NT; i += NT) cand[i] = 0ull;
+                __syncthreads();
+                bitonic_desc(cand, NT, tid);
+                if (tid < top_n) {
+                    if (tid < n) {
+                        int id = (int)(0xFFFFFFFFu - (unsigned int)(cand[tid] & 0xFFFFFFFFull));
+                        top_ids[(long long)r * top_n + tid] = id;
+                        top_lps[(long long)r * top_n + tid] = __fsub_rn(__fsub_rn(at(id), top), offset);
+                    } else {
+                        top_ids[(long long)r * top_n + tid] = -1;
+                        top_lps[(long long)r * top_n + tid] = 0.0f;
+                    }
+                }
+            } else {
+                // More logits at or above the threshold than the buffer holds (a flat or heavily
+                // quantised row): the N largest one after the other, each the first in the order
+                // (value descending, index ascending) behind the one before it. A pass per pick.
+                float lastv = INFINITY;
+                int lasti = -1;
+                for (int k = 0; k < top_n; k++) {
+                    float bv = -INFINITY;
+                    int bi = 0x7fffffff;
+                    for (int i = tid; i < V; i += NT) {
+                        const float x = at(i);
+                        const bool behind = x < lastv || (x == lastv && i > lasti);
+                        if (behind && (x > bv || (x == bv && i < bi))) { bv = x; bi = i; }
+                    }
+                    warp_argmax(bv, bi);
+                    __syncthreads();
+                    if (lane == 0) { wsf[warp] = bv; wsi[warp] = bi; }
+                    __syncthreads();
+                    bv = wsf[0]; bi = wsi[0];
+                    for (int w = 1; w < NWARP; w++)
+                        if (wsf[w] > bv || (wsf[w] == bv && wsi[w] < bi)) { bv = wsf[w]; bi = wsi[w]; }
+                    const bool found = bi != 0x7fffffff;
+                    if (tid == 0) {
+                        top_ids[(long long)r * top_n + k] = found ? bi : -1;
+                        top_lps[(long long)r * top_n + k] = found ? __fsub_rn(__fsub_rn(bv, top), offset) : 0.0f;
+                    }
+                    lastv = bv; lasti = bi;
+                    if (!found) lastv = -INFINITY;
                 }
             }
         }
@@ -1907,10 +1924,15 @@ thread_local char g_err[512] = "";
 static __device__ __align__(256) unsigned char g_noalloc_scratch[MOLLA_NOALLOC_SCRATCH_BYTES];
 constexpr int NOALLOC_MAX_DEVICES = 64;
 void *g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};  // device address of the array, per device ordinal
+#ifdef MOLLA_SAMPLE_TESTING
 long long *g_prof = nullptr;
 int g_knobs = 0;
 int *g_topk = nullptr;
 int g_topk_cap = 0;
+#define MOLLA_SET_TESTING_ARGS(a) do { (a).prof = g_prof; (a).knobs = g_knobs; (a).topk_out = g_topk; (a).topk_cap = g_topk_cap; } while (0)
+#else
+#define MOLLA_SET_TESTING_ARGS(a) do { } while (0)
+#endif
 
 int fail(int code, const char *fmt, const char *detail = "") {
     snprintf(g_err, sizeof(g_err), fmt, detail);
@@ -2042,9 +2064,7 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
     a.bias_ids = (const long long *)d_bias_ids; a.bias_vals = d_bias_vals; a.bias_off = d_bias_off;
     a.tokens = d_tokens; a.row_status = d_row_status; a.diag = d_diag;
     a.penalised = nullptr; a.penalised_only = 0;
-    a.prof = g_prof;
-    a.knobs = g_knobs;
-    a.topk_out = g_topk; a.topk_cap = g_topk_cap;
+    MOLLA_SET_TESTING_ARGS(a);
     int rc = launch_sampling(a, d_workspace, st);
     if (rc != MOLLA_OK) return rc;
     if (d_chosen_logprob || top_n > 0) {
@@ -2053,7 +2073,7 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         int grid = B < sms ? B : sms;
         logprob_kernel<<<grid, NT, 0, st>>>(d_logits, row_stride, B, V, d_tokens, top_n, d_chosen_logprob,
-                                            d_top_ids, d_top_logprobs, nullptr, nullptr, 0.0f);
+                                            d_top_ids, d_top_logprobs, nullptr, nullptr, 0, 0.0f);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
     }
@@ -2103,8 +2123,7 @@ int32_t molla_sample_decode_step(const float *d_logits, int64_t row_stride, int3
     a.bias_ids = (const long long *)d_bias_ids; a.bias_vals = d_bias_vals; a.bias_off = d_bias_off;
     a.tokens = d_tokens; a.row_status = d_row_status;
     a.n_logit_rows = n_logit_rows; a.n_slots = n_slots;
-    a.prof = g_prof;
-    a.knobs = g_knobs;
+    MOLLA_SET_TESTING_ARGS(a);
     if (d_stopped) {
         cudaError_t e0 = cudaMemsetAsync(d_stopped, 0, (size_t)B, st);
         if (e0 != cudaSuccess) return fail(MOLLA_ERR_CUDA, "clearing the stop flags failed: %s", cudaGetErrorString(e0));
@@ -2117,7 +2136,7 @@ int32_t molla_sample_decode_step(const float *d_logits, int64_t row_stride, int3
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         int grid = B < sms ? B : sms;
         logprob_kernel<<<grid, NT, 0, st>>>(d_logits, row_stride, B, V, d_tokens, top_n, d_chosen_logprob,
-                                            d_top_ids, d_top_logprobs, nullptr, d_rows, final_softcap);
+                                            d_top_ids, d_top_logprobs, nullptr, d_rows, n_logit_rows, final_softcap);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
     }
@@ -2185,7 +2204,7 @@ int32_t molla_sample_batch_noalloc(const float *d_logits, int64_t row_stride, in
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         int grid = B < sms ? B : sms;
         logprob_kernel<<<grid, NT, 0, st>>>(d_logits, row_stride, B, V, d_tokens, top_n, d_chosen_logprob,
-                                            d_top_ids, d_top_logprobs, nullptr, nullptr, 0.0f);
+                                            d_top_ids, d_top_logprobs, nullptr, nullptr, 0, 0.0f);
         e = cudaGetLastError();
         if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
     }
@@ -2356,6 +2375,14 @@ int32_t molla_sample_batch_host(const float *h_logits, int64_t row_stride, int32
         if (typical_p && !(typical_p[r] > 0 && typical_p[r] <= 1)) return fail(MOLLA_ERR_CONFIG, "a typical-p has to be above zero and at most one%s");
         if (repeat_penalty && !(repeat_penalty[r] > 0)) return fail(MOLLA_ERR_CONFIG, "a repetition penalty of zero or less erases a logit%s");
     }
+    // the ragged windows and bias lists: offsets that start at zero and never go back
+    for (int pass = 0; pass < 2; pass++) {
+        const int32_t *off = pass ? bias_off : hist_off;
+        if (!off) continue;
+        if (off[0] != 0) return fail(MOLLA_ERR_ARGUMENT, "an offset array has to start at zero%s");
+        for (int r = 0; r < B; r++)
+            if (off[r + 1] < off[r]) return fail(MOLLA_ERR_ARGUMENT, "an offset array has to be non-decreasing%s");
+    }
     const long long n_hist = hist_off ? hist_off[B] : 0, n_bias = bias_off ? bias_off[B] : 0;
     for (long long j = 0; j < n_bias; j++)
         if (bias_ids[j] < 0 || bias_ids[j] >= V) return fail(MOLLA_ERR_CONFIG, "a logit bias names a token outside the vocabulary%s");
@@ -2396,9 +2423,13 @@ int32_t molla_sample_batch_host(const float *h_logits, int64_t row_stride, int32
     }
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "device to host copy failed: %s", cudaGetErrorString(e));
-    for (int r = 0; r < B; r++)
-        if (h_row_status[r] & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG))
+    // a row the library did not answer (token -1) fails the call, as `pick` would have raised
+    for (int r = 0; r < B; r++) {
+        if (h_row_status[r] & MOLLA_ROW_UNSUPPORTED)
+            return fail(MOLLA_ERR_DEVICE, "a row asked for a filter combination the library does not do yet (MOLLA_ROW_UNSUPPORTED)%s");
+        if (h_row_status[r] & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG | MOLLA_ROW_SHARD_OVERFLOW))
             return fail(MOLLA_ERR_DEVICE, "a row reported an error in its status word%s");
+    }
     return MOLLA_OK;
 }
 
@@ -2434,7 +2465,7 @@ int32_t molla_sample_logprobs(const float *d_logits, int64_t row_stride, int32_t
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     int grid = B < sms ? B : sms;
     logprob_kernel<<<grid, NT, 0, (cudaStream_t)stream>>>(d_logits, row_stride, B, V, nullptr, 0, nullptr, nullptr,
-                                                          nullptr, d_out, nullptr, 0.0f);
+                                                          nullptr, d_out, nullptr, 0, 0.0f);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
     return MOLLA_OK;
@@ -2462,10 +2493,11 @@ int32_t molla_sample_logf(const float *d_x, int64_t n, void *stream, float *d_ou
     return MOLLA_OK;
 }
 
+#ifdef MOLLA_SAMPLE_TESTING
 void molla_sample_debug_profile(void *d_stamps) { g_prof = (long long *)d_stamps; }
 void molla_sample_debug_knobs(int32_t k) { g_knobs = k; }
-
 void molla_sample_debug_topk(void *d_ids, int32_t cap) { g_topk = (int *)d_ids; g_topk_cap = d_ids ? cap : 0; }
+#endif
 
 int32_t molla_sample_sync(void *stream) {
     cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);

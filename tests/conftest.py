@@ -30,6 +30,7 @@ def lib():
     """The CUDA library, built in-tree if it is missing (nvcc cross-compiles without a GPU)."""
     from molla_b200 import build, capi
     build.build_library()
+    build.build_library(testing=True)
     return capi.lib()
 
 

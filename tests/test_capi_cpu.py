@@ -9,8 +9,8 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_functions():
-    text = open(os.path.join(ROOT, "include", "molla_sample.h")).read()
+def declared_functions(header="molla_sample.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(molla_sample_\w+)\s*\(", text)))
 
@@ -23,6 +23,18 @@ def test_every_declared_symbol_is_exported(lib):
         assert hasattr(lib, n), f"{n} is declared in the header but not exported"
     assert set(capi.EXPORTS) <= set(names)
     assert lib.molla_sample_abi_version() == 1
+
+
+def test_testing_aids_live_in_the_testing_library_only(lib):
+    from molla_b200 import capi
+    names = declared_functions("molla_sample_testing.h")
+    assert set(names) == set(capi.TESTING_EXPORTS)
+    for n in names:
+        assert not hasattr(lib, n), f"{n} is a testing aid and must not be in the production library"
+    with capi.testing_library() as T:
+        for n in names + list(capi.EXPORTS):
+            assert hasattr(T, n), n
+    assert capi.lib() is lib
 
 
 def test_draw_is_the_reference_generator(lib, golden):
@@ -76,3 +88,11 @@ def test_host_entry_validates_settings_like_the_reference(lib):
     assert call([0.0, 0.0], top_p=[1.5, 1.0])[0] == capi.ERR_CONFIG
     assert call([0.0, 0.0], rp=[1.0, 0.0])[0] == capi.ERR_CONFIG
     assert call([0.0, 0.0], bias=V)[0] == capi.ERR_CONFIG  # a bias outside the vocabulary
+    # ragged lists: offsets that go backwards are refused before anything is sized by them
+    t = np.zeros(B, np.float32)
+    hist = np.zeros(4, np.int64)
+    bad = np.array([0, 3, 1], np.int32)
+    rc = lib.molla_sample_batch_host(
+        p(logits), V, B, V, p(t), null, null, null, null, null, null, null, null, null, null, p(hist), p(bad),
+        null, null, null, 0, null, 0, null, p(tok), null, null, null, p(st))
+    assert rc == capi.ERR_ARGUMENT and "non-decreasing" in capi.last_error()

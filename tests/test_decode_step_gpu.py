@@ -108,3 +108,61 @@ def test_bad_arguments_are_refused_before_any_launch(dev, lib):
         ds.step(torch.zeros((2, 99), device=dev), None, None)
     with pytest.raises(capi.MollaSampleError):
         ds.step(torch.zeros((2, 100), device=dev), None, None, final_softcap=-1.0)
+
+
+def test_stale_row_and_slot_indices_touch_nothing(dev, lib):
+    """`pick` refuses a row outside the block (sample.mojo:316-322). The device form reports such a
+    row (and a slot outside the samplers) in its status word and reads and writes nothing of it.
+    The tensors here are larger than the sizes declared to the call, so that a missing check would
+    land in owned memory rather than fault."""
+    V, declared_rows, declared_slots = 1000, 4, 3
+    ds = S.DeviceSamplers(8, V, ring_cap=8, device=dev)          # 8 slots allocated, 3 declared
+    for slot in range(8):
+        ds.assign(slot, S.SamplerConfig(temperature=0.8, top_k=10, seed=slot, repeat_last_n=8))
+    ds.n_slots = declared_slots
+    block = torch.randn((8, V), device=dev)                      # 8 rows allocated, 4 declared
+    rows = torch.tensor([0, 5, 2, -1, 3], dtype=torch.int32, device=dev)
+    slots = torch.tensor([0, 1, 6, 2, 2], dtype=torch.int32, device=dev)
+    before = {k: getattr(ds, k).clone() for k in ("drawn", "ring", "ring_head", "ring_filled")}
+    got = ds.step(block[:declared_rows], rows, slots, want_logprob=True, top_n=3)
+    torch.cuda.synchronize()
+    st = got["row_status"].cpu().numpy().astype(np.uint32)
+    tok = got["tokens"].cpu().numpy()
+    for i in (1, 2, 3):   # row 5 of 4, slot 6 of 3, row -1
+        assert st[i] & capi.ROW_INVALID_CONFIG and tok[i] == -1, (i, st[i], tok[i])
+    assert st[0] == 0 and tok[0] >= 0 and (st[4] & capi.ROW_ERROR_BITS) == 0 and tok[4] >= 0
+    drawn = ds.drawn.cpu().numpy()
+    assert drawn[0] == 1 and drawn[2] == 1 and drawn[1] == 0 and drawn[6] == 0
+    for k in ("ring", "ring_head", "ring_filled"):
+        assert torch.equal(getattr(ds, k)[[1, 6]], before[k][[1, 6]]), k
+    assert np.all(got["top_ids"].cpu().numpy()[[1, 3]] == -1)
+
+
+def test_a_wait_that_ran_out_fails_the_row_and_keeps_its_state(dev, lib):
+    """The bounded wait on a row's load reports in one warp only. The testing build can pretend
+    that it ran out (nothing is withheld, nothing is left waiting): every such row must come back
+    with MOLLA_ROW_LOAD_TIMEOUT and token -1, and the sampler in its slot must be as it was."""
+    V = 20000
+    ds = S.DeviceSamplers(4, V, ring_cap=8, device=dev)
+    for slot in range(4):
+        ds.assign(slot, S.SamplerConfig(temperature=0.0 if slot == 0 else 0.9, top_k=[0, 1, 20, 0][slot],
+                                        top_p=0.9, seed=slot, repeat_last_n=8))
+    block = torch.randn((4, V), device=dev)
+    before = {k: getattr(ds, k).clone() for k in ("drawn", "ring", "ring_head", "ring_filled")}
+    with capi.testing_library() as T:
+        T.molla_sample_debug_knobs(16)
+        try:
+            got = ds.step(block, None, None)
+            torch.cuda.synchronize()
+        finally:
+            T.molla_sample_debug_knobs(0)
+    st = got["row_status"].cpu().numpy().astype(np.uint32)
+    assert np.all(st & capi.ROW_LOAD_TIMEOUT), st
+    assert np.all(got["tokens"].cpu().numpy() == -1)
+    for k, v in before.items():
+        assert torch.equal(getattr(ds, k), v), k
+    # and the same samplers work on the next call
+    got = ds.step(block, None, None)
+    torch.cuda.synchronize()
+    assert not np.any(got["row_status"].cpu().numpy().astype(np.uint32) & capi.ROW_ERROR_BITS)
+    assert np.all(ds.drawn.cpu().numpy() == 1)

@@ -54,7 +54,7 @@ def check(w, world, dev, oracle, **kw):
 
 
 def test_config5_eight_shards(dev, lib, oracle):
-    w = W.config5(B=64)
+    w = W.config5()  # all 128 rows of the configuration
     counts = check(w, 8, dev, oracle, check_all_ranks=True)
     assert counts.max() <= 18992 and counts.min() >= 0
 
