@@ -304,6 +304,41 @@ int32_t molla_sample_expf(const float *d_x, int64_t n, void *stream, float *d_ou
  * library at sample.mojo:541,550), element-wise on the device. For tests. */
 int32_t molla_sample_logf(const float *d_x, int64_t n, void *stream, float *d_out);
 
+/* ---- the vocab-sharded step as one call that owns its collectives ----------------------------
+ * No counterpart in the reference (tensor parallelism is on its roadmap, docs/roadmap.md:72-80);
+ * the call shape follows how the reference binds C (src/molla/tls/openssl.mojo:53-139): opaque
+ * handles as pointers, no callbacks. NCCL is loaded at run time (libnccl.so.2, or the path in
+ * MOLLA_LIBNCCL); a host without an NCCL binding creates its communicator through the three
+ * functions below: rank 0 asks for an id, hands the 128 bytes to the other ranks by any means it
+ * has, and every rank creates its communicator from them with its GPU current. */
+int32_t molla_sample_nccl_unique_id(uint8_t *out128);
+int32_t molla_sample_nccl_comm_create(const uint8_t *id128, int32_t rank, int32_t world, void **comm_out);
+int32_t molla_sample_nccl_comm_destroy(void *comm);
+const char *molla_sample_sharded_last_error(void);
+
+/* Device bytes molla_sample_sharded_step needs for B rows of V_local of V_global columns over
+ * `world` shards when a shard's list may hold list_cap entries per row (V_local never overflows). */
+int64_t molla_sample_sharded_workspace_bytes(int32_t B, int32_t V_local, int32_t V_global, int32_t world, int32_t list_cap);
+
+/* One sampling step on this rank's columns [col0, col0 + V_local) of every row: stage a, an
+ * all-gather of the slices' summaries, the merge, stage b, an all-gather of the list lengths
+ * and then of only as many list entries per row as the longest list anywhere holds, stage c.
+ * All on `stream`; the call waits once in the middle (for the list lengths). Every rank ends
+ * with the same tokens, equal to the unsharded call's. Arguments as molla_sample_batch's
+ * (per-row arrays replicated on every rank; window and bias ids are global token ids).
+ * `wire_bytes` (host, optional): [0] bytes this rank put into the all-gathers, [1] bytes it
+ * received, [2] list entries per row that travelled. */
+int32_t molla_sample_sharded_step(void *comm, int32_t rank, int32_t world, const float *d_logits, int64_t row_stride,
+                                  int32_t B, int32_t V_local, int32_t col0, int32_t V_global,
+                                  const float *d_temperature, const int32_t *d_top_k, const float *d_top_p,
+                                  const float *d_min_p, const float *d_typical_p, const float *d_repeat_penalty,
+                                  const float *d_frequency_penalty, const float *d_presence_penalty,
+                                  const uint8_t *d_window_on, const int64_t *d_hist, const int32_t *d_hist_off,
+                                  const int64_t *d_bias_ids, const float *d_bias_vals, const int32_t *d_bias_off,
+                                  const uint64_t *d_seed, const uint64_t *d_drawn, int32_t list_cap,
+                                  void *d_workspace, int64_t workspace_bytes, void *stream, int32_t *d_tokens,
+                                  uint32_t *d_row_status, float *d_diag, int64_t *wire_bytes);
+
 /* cudaStreamSynchronize on `stream`, returning a status; then, if
  * `d_row_status` is given, nothing else is implied: rows report for themselves. */
 int32_t molla_sample_sync(void *stream);

@@ -6,7 +6,8 @@ import shutil
 import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-SRC = [os.path.join(_HERE, "csrc", "molla_sample.cu"), os.path.join(_HERE, "csrc", "molla_cluster.cu")]
+SRC = [os.path.join(_HERE, "csrc", "molla_sample.cu"), os.path.join(_HERE, "csrc", "molla_cluster.cu"),
+       os.path.join(_HERE, "csrc", "molla_sharded.cu")]
 DEPS = SRC + [os.path.join(_HERE, "csrc", "molla_device.cuh"), os.path.join(_HERE, "csrc", "molla_exact.cuh"),
               os.path.join(_HERE, "csrc", "molla_cluster.h"),
               os.path.join(os.path.dirname(_HERE), "include", "molla_sample.h"),
@@ -20,7 +21,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     # every fp32 operation of the reference is rounded on its own: no implicit fused multiply-add
     "-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false",
-    "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared", "-t", "2",
+    "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared", "-ldl", "-t", "3",
 ]
 
 

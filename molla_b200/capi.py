@@ -36,6 +36,8 @@ EXPORTS = (
     "molla_sample_batch_host", "molla_sample_batch_noalloc", "molla_sample_shard_summary_words",
     "molla_sample_shard_stage_a", "molla_sample_shard_merge", "molla_sample_shard_stage_b", "molla_sample_shard_stage_c", "molla_sample_penalised",
     "molla_sample_decode_step", "molla_sample_logprobs", "molla_sample_expf", "molla_sample_logf", "molla_sample_sync",
+    "molla_sample_nccl_unique_id", "molla_sample_nccl_comm_create", "molla_sample_nccl_comm_destroy",
+    "molla_sample_sharded_last_error", "molla_sample_sharded_workspace_bytes", "molla_sample_sharded_step",
 )
 TESTING_EXPORTS = ("molla_sample_debug_knobs", "molla_sample_debug_profile", "molla_sample_debug_topk")
 TESTING_LIB_PATH = os.path.join(_HERE, "lib", "libmolla_sample_testing.so")
@@ -124,6 +126,19 @@ def _load(path, testing):
     L.molla_sample_logf.argtypes = [vp, i64, vp, vp]
     L.molla_sample_sync.restype = i32
     L.molla_sample_sync.argtypes = [vp]
+    L.molla_sample_nccl_unique_id.restype = i32
+    L.molla_sample_nccl_unique_id.argtypes = [vp]
+    L.molla_sample_nccl_comm_create.restype = i32
+    L.molla_sample_nccl_comm_create.argtypes = [vp, i32, i32, C.POINTER(vp)]
+    L.molla_sample_nccl_comm_destroy.restype = i32
+    L.molla_sample_nccl_comm_destroy.argtypes = [vp]
+    L.molla_sample_sharded_last_error.restype = C.c_char_p
+    L.molla_sample_sharded_last_error.argtypes = []
+    L.molla_sample_sharded_workspace_bytes.restype = i64
+    L.molla_sample_sharded_workspace_bytes.argtypes = [i32, i32, i32, i32, i32]
+    L.molla_sample_sharded_step.restype = i32
+    L.molla_sample_sharded_step.argtypes = ([vp, i32, i32, vp, i64, i32, i32, i32, i32] + [vp] * 16
+                                            + [i32, vp, i64, vp, vp, vp, vp, vp])
     if testing:
         L.molla_sample_debug_knobs.restype = None
         L.molla_sample_debug_knobs.argtypes = [i32]

@@ -112,3 +112,81 @@ def sample_vocab_sharded(shard: VocabShard, logits: torch.Tensor, p: dict, all_g
     shard.merge(gathered, p)
     lst, cnt = shard.stage_b(logits, p)
     return shard.stage_c(all_gather(lst), all_gather(cnt), p, diag)
+
+
+def overflowed(counts: torch.Tensor, cap: int) -> torch.Tensor:
+    """Rows whose list outgrew the exchange buffer on some shard: [world, B] gathered counts ->
+    [B] bool. Every rank holds the same counts after the all-gather, so every rank comes to the
+    same verdict about every row without talking again (stage c marks exactly these rows with
+    MOLLA_ROW_SHARD_OVERFLOW and answers -1 for them)."""
+    return ((counts < 0) | (counts > cap)).any(dim=0)
+
+
+class NcclShardedSampler:
+    """The vocab-sharded step through `molla_sample_sharded_step`: one C call per step that
+    enqueues the stages and owns the all-gathers (NCCL, loaded by the library itself). The
+    communicator is the library's own: rank 0 asks the library for an id, `share(id_bytes)` hands
+    it to the other ranks (any broadcast of 128 bytes will do), every rank creates its
+    communicator with its GPU current."""
+
+    def __init__(self, B: int, V_local: int, col0: int, V_global: int, rank: int, world: int, device, share,
+                 list_cap: int | None = None):
+        self.B, self.Vl, self.col0, self.Vg, self.rank, self.world = B, V_local, col0, V_global, rank, world
+        self.dev = torch.device(device)
+        self.cap = V_local if list_cap is None else int(list_cap)
+        L = capi.lib()
+        ident = (C.c_uint8 * 128)()
+        if rank == 0:
+            self._check(L.molla_sample_nccl_unique_id(C.cast(ident, C.c_void_p)))
+        ident = (C.c_uint8 * 128).from_buffer_copy(share(bytes(ident)))
+        comm = C.c_void_p()
+        with torch.cuda.device(self.dev):
+            self._check(L.molla_sample_nccl_comm_create(C.cast(ident, C.c_void_p), rank, world, C.byref(comm)))
+        self.comm = comm
+        n = L.molla_sample_sharded_workspace_bytes(B, V_local, V_global, world, self.cap)
+        if n < 0:
+            self._check(int(n))
+        self.ws = torch.empty(max(int(n), 256), dtype=torch.uint8, device=self.dev)
+        self.tokens = torch.full((B,), -1, dtype=torch.int32, device=self.dev)
+        self.status = torch.zeros(B, dtype=torch.int32, device=self.dev)
+        self.wire = (C.c_int64 * 3)()
+
+    @staticmethod
+    def _check(rc: int) -> None:
+        if rc != capi.OK:
+            text = (capi.lib().molla_sample_sharded_last_error() or b"").decode("utf-8", "replace") or capi.last_error()
+            raise capi.MollaSampleError(rc, text)
+
+    def step(self, logits: torch.Tensor, p: dict, diag: torch.Tensor | None = None):
+        g = p.get
+        rc = capi.lib().molla_sample_sharded_step(
+            self.comm, self.rank, self.world, _ptr(logits), logits.stride(0), self.B, self.Vl, self.col0, self.Vg,
+            _ptr(g("temperature")), _ptr(g("top_k")), _ptr(g("top_p")), _ptr(g("min_p")), _ptr(g("typical_p")),
+            _ptr(g("repeat_penalty")), _ptr(g("frequency_penalty")), _ptr(g("presence_penalty")), _ptr(g("window_on")),
+            _ptr(g("hist")), _ptr(g("hist_off")), _ptr(g("bias_ids")), _ptr(g("bias_vals")), _ptr(g("bias_off")),
+            _ptr(g("seed")), _ptr(g("drawn")), self.cap, _ptr(self.ws), self.ws.numel(), _stream_ptr(self.dev),
+            _ptr(self.tokens), _ptr(self.status), _ptr(diag), C.cast(self.wire, C.c_void_p))
+        self._check(rc)
+        return self.tokens, self.status
+
+    @property
+    def wire_bytes(self) -> dict:
+        return {"sent_per_rank": int(self.wire[0]), "received_per_rank": int(self.wire[1]),
+                "list_entries_per_row": int(self.wire[2])}
+
+    def close(self) -> None:
+        if self.comm:
+            capi.lib().molla_sample_nccl_comm_destroy(self.comm)
+            self.comm = None
+
+
+def share_over_torch_distributed(group=None):
+    """A `share` callable for NcclShardedSampler: rank 0's bytes to everybody over torch.distributed."""
+    import torch.distributed as dist
+
+    def share(blob: bytes) -> bytes:
+        box = [blob]
+        dist.broadcast_object_list(box, src=0, group=group)
+        return box[0]
+
+    return share
