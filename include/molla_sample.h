@@ -58,6 +58,7 @@ extern "C" {
 #define MOLLA_ROW_SLOW_PATH 0x040u      /* informational: a sequential fallback ran for this row */
 #define MOLLA_ROW_DEGENERATE 0x080u     /* more equal values than the candidate buffer holds; token = -1 */
 #define MOLLA_ROW_SHARD_OVERFLOW 0x100u /* vocab-sharded form: a shard's list outgrew the exchange buffer */
+#define MOLLA_ROW_EMPTY 0x200u          /* the grammar mask left no candidate; token = -1 (the reference raises, sample.mojo:578-579) */
 
 /* Replaces nothing in the reference; lets a binding check what it loaded. */
 int32_t molla_sample_abi_version(void);
@@ -303,6 +304,26 @@ int32_t molla_sample_expf(const float *d_x, int64_t n, void *stream, float *d_ou
 /* log(x) exactly as the typical-p filter evaluates it (`log` of the Mojo standard
  * library at sample.mojo:541,550), element-wise on the device. For tests. */
 int32_t molla_sample_logf(const float *d_x, int64_t n, void *stream, float *d_out);
+
+/* molla_sample_batch with a grammar mask: `_mask` (sample.mojo:371-379) is the place where a
+ * grammar drops the tokens it forbids, ahead of every other filter; the reference ships it
+ * empty. Row r may only choose among the tokens t whose bit is set in
+ * d_mask[r * mask_stride_words + t / 32] (bit t % 32); dropped tokens are no candidates at all:
+ * they take no bias, no penalty, and no place in the softmax or the top-k count. A row whose
+ * mask allows nothing comes back with MOLLA_ROW_EMPTY and token -1. d_mask = NULL is
+ * molla_sample_batch. Logprobs stay those of the unmasked logits (sample.mojo:268-293 reads the
+ * raw block). Vocabularies of more than 307200 logits are refused with MOLLA_ERR_VOCAB. */
+int32_t molla_sample_batch_masked(const uint32_t *d_mask, int64_t mask_stride_words,
+                                  const float *d_logits, int64_t row_stride, int32_t B, int32_t V,
+                                  const float *d_temperature, const int32_t *d_top_k, const float *d_top_p,
+                                  const float *d_min_p, const float *d_typical_p, const float *d_repeat_penalty,
+                                  const float *d_frequency_penalty, const float *d_presence_penalty,
+                                  const uint8_t *d_window_on, const uint64_t *d_seed, const uint64_t *d_drawn,
+                                  const int64_t *d_hist, const int32_t *d_hist_off, const int64_t *d_bias_ids,
+                                  const float *d_bias_vals, const int32_t *d_bias_off, int32_t top_n,
+                                  void *d_workspace, int64_t workspace_bytes, void *stream, int32_t *d_tokens,
+                                  float *d_chosen_logprob, int32_t *d_top_ids, float *d_top_logprobs,
+                                  uint32_t *d_row_status, float *d_diag);
 
 /* ---- the vocab-sharded step as one call that owns its collectives ----------------------------
  * No counterpart in the reference (tensor parallelism is on its roadmap, docs/roadmap.md:72-80);

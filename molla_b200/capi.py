@@ -27,12 +27,13 @@ ROW_LOAD_TIMEOUT = 0x020
 ROW_SLOW_PATH = 0x040
 ROW_DEGENERATE = 0x080
 ROW_SHARD_OVERFLOW = 0x100
+ROW_EMPTY = 0x200
 ROW_TIE_BITS = ROW_TOPK_TIE | ROW_TOPP_TIE | ROW_CHOSEN_TIE
-ROW_ERROR_BITS = ROW_INVALID_CONFIG | ROW_UNSUPPORTED | ROW_LOAD_TIMEOUT | ROW_DEGENERATE | ROW_SHARD_OVERFLOW
+ROW_ERROR_BITS = ROW_INVALID_CONFIG | ROW_UNSUPPORTED | ROW_LOAD_TIMEOUT | ROW_DEGENERATE | ROW_SHARD_OVERFLOW | ROW_EMPTY
 
 EXPORTS = (
     "molla_sample_abi_version", "molla_sample_last_error", "molla_sample_draw",
-    "molla_sample_workspace_bytes", "molla_sample_batch", "molla_sample_host_workspace_bytes",
+    "molla_sample_workspace_bytes", "molla_sample_batch", "molla_sample_batch_masked", "molla_sample_host_workspace_bytes",
     "molla_sample_batch_host", "molla_sample_batch_noalloc", "molla_sample_shard_summary_words",
     "molla_sample_shard_stage_a", "molla_sample_shard_merge", "molla_sample_shard_stage_b", "molla_sample_shard_stage_c", "molla_sample_penalised",
     "molla_sample_decode_step", "molla_sample_logprobs", "molla_sample_expf", "molla_sample_logf", "molla_sample_sync",
@@ -97,6 +98,8 @@ def _load(path, testing):
     L.molla_sample_workspace_bytes.argtypes = [i32, i32, i32]
     L.molla_sample_batch.restype = i32
     L.molla_sample_batch.argtypes = [vp, i64, i32, i32] + [vp] * 16 + [i32, vp, i64, vp] + [vp] * 6
+    L.molla_sample_batch_masked.restype = i32
+    L.molla_sample_batch_masked.argtypes = [vp, i64] + L.molla_sample_batch.argtypes
     L.molla_sample_decode_step.restype = i32
     L.molla_sample_decode_step.argtypes = ([vp, i64, i32, i32, vp, vp, i32, i32, f32] + [vp] * 8 + [vp, vp, vp, i32, vp, vp, vp, vp]
                                            + [vp, vp, vp, i32, vp, i64, vp] + [vp] * 6)

@@ -606,7 +606,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
             a.prof[(long long)r * 32 + 11] = (long long)gt; a.prof[(long long)r * 32 + 9] = clock64();
         }
 #endif
-        if (c.status & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG | MOLLA_ROW_UNSUPPORTED)) token = -1;
+        if (c.status & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG | MOLLA_ROW_UNSUPPORTED | MOLLA_ROW_EMPTY)) token = -1;
         a.tokens[r] = token;
         a.row_status[r] = c.status;
         if (a.ring && token >= 0) {  // `_took` (sample.mojo:361-363): observe, then one more draw used
@@ -682,6 +682,17 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     CSTAMP(1);
     if (a.softcap > 0.0f) {
         for (int i = c.tid; i < g.nloc; i += NT) rowbuf[i] = softcap_pinned(rowbuf[i], a.softcap);
+        __syncthreads();
+    }
+    if (a.mask) {
+        // `_mask` (sample.mojo:371-379): what the grammar forbids is no candidate at all. A logit of
+        // -inf is exactly that here: it wins no maximum, takes no bias or penalty that could bring it
+        // back, its exponential is zero, and zeros are absent from every sum, count and walk.
+        const unsigned int *mrow = a.mask + (long long)r * a.mask_stride;
+        for (int i = c.tid; i < g.nloc; i += NT) {
+            const int t = g.c0 + i;
+            if (!((__ldg(mrow + (t >> 5)) >> (t & 31)) & 1u)) rowbuf[i] = -INFINITY;
+        }
         __syncthreads();
     }
     if (npatch > 0) {
@@ -783,6 +794,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     }
     if (imax == 0x7fffffff) imax = 0;
     if (c.status & MOLLA_ROW_LOAD_TIMEOUT) { finish(); return; }
+    if (a.mask && !(xmax > -INFINITY)) { c.status |= MOLLA_ROW_EMPTY; finish(); return; }  // every candidate was filtered out
 
     CSTAMP(3);
     if (greedy) { token = imax; finish(); return; }

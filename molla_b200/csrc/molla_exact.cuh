@@ -50,6 +50,7 @@ struct BatchArgs {
     unsigned char *stopped;        // [B] or nullptr: the pick was the slot's stop token
     // vocab-sharded form: this GPU holds columns [col0, col0 + V) of a vocabulary of Vg
     int n_logit_rows, n_slots;   // bounds of rows[] and slot[] values (0 = not given)
+    const unsigned int *mask; long long mask_stride;  // grammar mask: bit t of row r's words = token t allowed (nullptr = all)
     // one row per thread-block cluster: blocks per cluster, logits per block, logits per thread
     int G, Vc, L;
     int mode;                    // 0 whole pipeline; 1, 2, 3 the stages around the two all-gathers

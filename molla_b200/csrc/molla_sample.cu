@@ -1743,7 +1743,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_kernel(const __grid_constan
         // a bounded wait that ran out in any warp fails the row; a failed row keeps its sampler state
         if (MOLLA_KNOB(a, 16) && c.warp == 3) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
         if (__syncthreads_or((c.status & MOLLA_ROW_LOAD_TIMEOUT) ? 1 : 0)) c.status |= MOLLA_ROW_LOAD_TIMEOUT;
-        if (c.status & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG | MOLLA_ROW_UNSUPPORTED | MOLLA_ROW_SHARD_OVERFLOW)) token = -1;
+        if (c.status & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG | MOLLA_ROW_UNSUPPORTED | MOLLA_ROW_SHARD_OVERFLOW | MOLLA_ROW_EMPTY)) token = -1;
         if (c.tid == 0) {
             a.tokens[r] = token;
             a.row_status[r] = c.status;
@@ -2010,6 +2010,7 @@ int launch_rows(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, in
 int launch_sampling(const BatchArgs &args_in, void *d_workspace, cudaStream_t st) {
     const int rc = molla_cluster_launch(args_in, d_workspace, st, g_err, sizeof(g_err));
     if (rc != MOLLA_CLUSTER_DECLINED) return rc;
+    if (args_in.mask) return fail(MOLLA_ERR_VOCAB, "a grammar mask is only done for vocabularies a thread-block cluster can hold%s");
     return launch_rows(args_in, d_workspace, st, 0x7fffffff, true);
 }
 
@@ -2030,7 +2031,8 @@ int64_t molla_sample_workspace_bytes(int32_t B, int32_t V, int32_t top_n) {
     return (int64_t)batch_workspace_bytes(B, V, sms);
 }
 
-int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B, int32_t V,
+int32_t molla_sample_batch_masked(const uint32_t *d_mask, int64_t mask_stride_words,
+                                  const float *d_logits, int64_t row_stride, int32_t B, int32_t V,
                            const float *d_temperature, const int32_t *d_top_k, const float *d_top_p,
                            const float *d_min_p, const float *d_typical_p, const float *d_repeat_penalty,
                            const float *d_frequency_penalty, const float *d_presence_penalty,
@@ -2048,6 +2050,7 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
     if ((d_hist == nullptr) != (d_hist_off == nullptr)) return fail(MOLLA_ERR_ARGUMENT, "history ids and offsets go together%s");
     if ((d_bias_ids == nullptr) != (d_bias_off == nullptr) || (d_bias_ids && !d_bias_vals))
         return fail(MOLLA_ERR_ARGUMENT, "bias ids, values and offsets go together%s");
+    if (d_mask && mask_stride_words < (V + 31) / 32) return fail(MOLLA_ERR_ARGUMENT, "a row of the mask has fewer bits than the vocabulary%s");
     if (!d_workspace || workspace_bytes < molla_sample_workspace_bytes(B, V, top_n))
         return fail(MOLLA_ERR_WORKSPACE, "workspace missing or too small%s");
     if (B == 0) return MOLLA_OK;
@@ -2055,6 +2058,7 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
     BatchArgs a;
     memset(&a, 0, sizeof(a));
     a.logits = d_logits; a.row_stride = row_stride; a.B = B; a.V = V;
+    a.mask = d_mask; a.mask_stride = mask_stride_words;
     a.temperature = d_temperature; a.top_k = d_top_k; a.top_p = d_top_p; a.min_p = d_min_p;
     a.typical_p = d_typical_p; a.repeat_penalty = d_repeat_penalty;
     a.frequency_penalty = d_frequency_penalty; a.presence_penalty = d_presence_penalty;
@@ -2078,6 +2082,23 @@ int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B,
         if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "logprob launch failed: %s", cudaGetErrorString(e));
     }
     return MOLLA_OK;
+}
+
+int32_t molla_sample_batch(const float *d_logits, int64_t row_stride, int32_t B, int32_t V,
+                           const float *d_temperature, const int32_t *d_top_k, const float *d_top_p,
+                           const float *d_min_p, const float *d_typical_p, const float *d_repeat_penalty,
+                           const float *d_frequency_penalty, const float *d_presence_penalty,
+                           const uint8_t *d_window_on, const uint64_t *d_seed, const uint64_t *d_drawn,
+                           const int64_t *d_hist, const int32_t *d_hist_off, const int64_t *d_bias_ids,
+                           const float *d_bias_vals, const int32_t *d_bias_off, int32_t top_n,
+                           void *d_workspace, int64_t workspace_bytes, void *stream, int32_t *d_tokens,
+                           float *d_chosen_logprob, int32_t *d_top_ids, float *d_top_logprobs,
+                           uint32_t *d_row_status, float *d_diag) {
+    return molla_sample_batch_masked(nullptr, 0, d_logits, row_stride, B, V, d_temperature, d_top_k, d_top_p, d_min_p,
+                                     d_typical_p, d_repeat_penalty, d_frequency_penalty, d_presence_penalty, d_window_on,
+                                     d_seed, d_drawn, d_hist, d_hist_off, d_bias_ids, d_bias_vals, d_bias_off, top_n,
+                                     d_workspace, workspace_bytes, stream, d_tokens, d_chosen_logprob, d_top_ids,
+                                     d_top_logprobs, d_row_status, d_diag);
 }
 
 int32_t molla_sample_decode_step(const float *d_logits, int64_t row_stride, int32_t n_logit_rows, int32_t V,
@@ -2427,7 +2448,7 @@ int32_t molla_sample_batch_host(const float *h_logits, int64_t row_stride, int32
     for (int r = 0; r < B; r++) {
         if (h_row_status[r] & MOLLA_ROW_UNSUPPORTED)
             return fail(MOLLA_ERR_DEVICE, "a row asked for a filter combination the library does not do yet (MOLLA_ROW_UNSUPPORTED)%s");
-        if (h_row_status[r] & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG | MOLLA_ROW_SHARD_OVERFLOW))
+        if (h_row_status[r] & (MOLLA_ROW_LOAD_TIMEOUT | MOLLA_ROW_DEGENERATE | MOLLA_ROW_INVALID_CONFIG | MOLLA_ROW_SHARD_OVERFLOW | MOLLA_ROW_EMPTY))
             return fail(MOLLA_ERR_DEVICE, "a row reported an error in its status word%s");
     }
     return MOLLA_OK;

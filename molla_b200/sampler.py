@@ -135,8 +135,11 @@ def sample_batch(logits: torch.Tensor, p: dict, top_n: int = 0, want_logprob: bo
     if diag is None and want_diag:
         diag = torch.empty((B, 4), dtype=torch.float32, device=dev)
     g = p.get
-    rc = capi.lib().molla_sample_batch(
-        _ptr(logits), logits.stride(0), B, V,
+    mask = g("mask")   # optional grammar mask: [B, ceil(V / 32)] int32 words, bit t of a row = token t allowed
+    if mask is not None and (mask.dim() != 2 or mask.shape[0] != B or mask.stride(1) != 1 or mask.element_size() != 4):
+        raise ValueError("the grammar mask is a [B, ceil(V/32)] tensor of 32-bit words")
+    rc = capi.lib().molla_sample_batch_masked(
+        _ptr(mask), mask.stride(0) if mask is not None else 0, _ptr(logits), logits.stride(0), B, V,
         _ptr(g("temperature")), _ptr(g("top_k")), _ptr(g("top_p")), _ptr(g("min_p")),
         _ptr(g("typical_p")), _ptr(g("repeat_penalty")), _ptr(g("frequency_penalty")),
         _ptr(g("presence_penalty")), _ptr(g("window_on")), _ptr(g("seed")), _ptr(g("drawn")),

@@ -222,6 +222,7 @@ typedef struct {
     int exp_mode;
     int faithful_cost;
     int sorted; /* diagnostic: has a sort run */
+    const uint32_t *mask; /* grammar mask of the row: bit t set = token t allowed (NULL = all) */
 } sampler_t;
 
 static int cfg_greedy(const sampler_t *s) { return s->temperature <= 0; }
@@ -454,12 +455,22 @@ static int64_t pick_(sampler_t *s, const float *row, float *penalised_out, diag_
                      int32_t *kept_ids_out, int64_t kept_ids_cap) {
     memset(d, 0, sizeof(*d));
     s->sorted = 0;
-    if (cfg_greedy(s) && !cfg_penalizing(s) && s->nbias <= 0) {
+    if (cfg_greedy(s) && !cfg_penalizing(s) && s->nbias <= 0 && !s->mask) {
         if (penalised_out) memcpy(penalised_out, row, sizeof(float) * (size_t)s->vocab);
         return molla_oracle_argmax(row, 0, s->vocab);
     }
     for (int64_t i = 0; i < s->vocab; i++) { s->ids[i] = i; s->vals[i] = row[i]; }
     s->kept = s->vocab;
+    if (s->mask) {
+        /* `_mask` (sample.mojo:371-379) is where a grammar drops the tokens it forbids, first of
+         * all filters; the reference ships it empty. Dropping = the candidate is gone: what is
+         * left keeps its order. Nothing left: "every candidate was filtered out" (:578-579). */
+        int64_t w = 0;
+        for (int64_t i = 0; i < s->vocab; i++)
+            if ((s->mask[i >> 5] >> (i & 31)) & 1u) { s->ids[w] = i; s->vals[w] = row[i]; w++; }
+        s->kept = w;
+        if (w == 0) return -1;
+    }
     bias_(s);
     penalise_(s);
     if (penalised_out) memcpy(penalised_out, s->vals, sizeof(float) * (size_t)s->vocab);
@@ -496,7 +507,8 @@ static int64_t pick_(sampler_t *s, const float *row, float *penalised_out, diag_
  * Outputs other than `tokens` are optional (NULL to skip).
  * Returns 0, or -1 on a bad argument.
  */
-int molla_oracle_pick_batch(
+int molla_oracle_pick_batch_masked(
+    const uint32_t *mask, int64_t mask_stride_words,
     const float *logits, int64_t row_stride, int32_t B, int32_t V,
     const float *temperature, const int32_t *top_k, const float *top_p, const float *min_p,
     const float *typical_p, const float *repeat_penalty, const float *frequency_penalty,
@@ -544,6 +556,8 @@ int molla_oracle_pick_batch(
             } else { s.bias_ids = NULL; s.bias_vals = NULL; s.nbias = 0; }
             s.exp_mode = exp_mode;
             s.faithful_cost = faithful_cost;
+            s.mask = mask ? mask + (int64_t)r * mask_stride_words : NULL;
+            if (s.mask) s.faithful_cost = 1; /* the shortcuts index candidates by token id */
             diag_t d;
             int64_t tok = pick_(&s, logits + (int64_t)r * row_stride,
                                 penalised ? penalised + (int64_t)r * V : NULL, &d,
@@ -565,6 +579,24 @@ int molla_oracle_pick_batch(
 }
 
 /* Batched logprob outputs: chosen-token logprob and the top-N, from the raw row. */
+int molla_oracle_pick_batch(
+    const float *logits, int64_t row_stride, int32_t B, int32_t V,
+    const float *temperature, const int32_t *top_k, const float *top_p, const float *min_p,
+    const float *typical_p, const float *repeat_penalty, const float *frequency_penalty,
+    const float *presence_penalty, const uint8_t *window_on, const uint64_t *seed,
+    const uint64_t *drawn, const int64_t *hist, const int32_t *hist_off, const int64_t *bias_ids,
+    const float *bias_vals, const int32_t *bias_off, int32_t exp_mode, int32_t faithful_cost,
+    int32_t nthreads,
+    int32_t *tokens, float *penalised, float *z_sum, float *keep_sum, float *target,
+    float *chosen_p, int32_t *kept_topk, int32_t *kept_final, uint32_t *flags,
+    int32_t *kept_ids, int32_t kept_ids_cap) {
+    return molla_oracle_pick_batch_masked(NULL, 0, logits, row_stride, B, V, temperature, top_k, top_p, min_p,
+                                          typical_p, repeat_penalty, frequency_penalty, presence_penalty, window_on,
+                                          seed, drawn, hist, hist_off, bias_ids, bias_vals, bias_off, exp_mode,
+                                          faithful_cost, nthreads, tokens, penalised, z_sum, keep_sum, target, chosen_p,
+                                          kept_topk, kept_final, flags, kept_ids, kept_ids_cap);
+}
+
 int molla_oracle_logprobs_batch(const float *logits, int64_t row_stride, int32_t B, int32_t V,
                                 const int32_t *tokens, int32_t top_n, int32_t exp_mode,
                                 int32_t nthreads, float *chosen_lp, int32_t *top_ids,

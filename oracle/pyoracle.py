@@ -147,6 +147,7 @@ def pick_batch(
     nthreads: int = 0,
     want_penalised: bool = False,
     kept_ids_cap: int = 0,
+    mask=None,
 ):
     """Sample every row of `logits` ([B, V] fp32) and return a dict of results."""
     logits = np.ascontiguousarray(logits, dtype=np.float32)
@@ -186,7 +187,12 @@ def pick_batch(
     kept_final = np.zeros(B, dtype=np.int32)
     flags = np.zeros(B, dtype=np.uint32)
     kept_ids = np.full((B, kept_ids_cap), -1, dtype=np.int32) if kept_ids_cap > 0 else None
-    rc = lib().molla_oracle_pick_batch(
+    if mask is not None:
+        mask = np.ascontiguousarray(mask, dtype=np.uint32)
+        assert mask.shape == (B, (V + 31) // 32)
+        want_penalised, penalised = False, None
+    rc = lib().molla_oracle_pick_batch_masked(
+        _p(mask), C.c_int64(0 if mask is None else mask.shape[1]),
         _p(logits), C.c_int64(V), C.c_int32(B), C.c_int32(V),
         _p(temperature), _p(top_k), _p(top_p), _p(min_p), _p(typical_p),
         _p(repeat_penalty), _p(frequency_penalty), _p(presence_penalty), _p(window_on),

@@ -501,6 +501,51 @@ def test_host_buffer_entry_matches_device_entry(dev, lib):
     assert np.array_equal(hb.top_ids.numpy(), got["top_ids"])
 
 
+def test_grammar_mask_against_the_oracle(dev, lib, oracle):
+    """`_mask` (sample.mojo:371-379): tokens a grammar forbids are dropped ahead of every other
+    filter. Dense and sparse masks, masks that hide the maximum, bias and penalties on hidden
+    tokens, a top-k larger than what is left, greedy rows, nothing sorted, and a mask that
+    allows nothing (the reference raises "every candidate was filtered out")."""
+    B, V = 40, 20011
+    w = W.config3(seed=61, B=B, V=V, H=24)
+    rng = np.random.default_rng(8)
+    allowed = rng.random((B, V)) < np.linspace(0.02, 0.98, B)[:, None]
+    allowed[5] = False; allowed[5, [7, 9000, V - 1]] = True         # three tokens left, top-k above that
+    w["top_k"][5] = 50
+    allowed[6] = False                                              # nothing left
+    allowed[7, int(np.argmax(w["logits"][7]))] = False              # the maximum is hidden
+    w["top_k"][8] = 0; w["top_p"][8] = 1.0; w["temperature"][8] = 1.1   # nothing sorted: vocabulary order of what is left
+    w["bias_ids"] = np.array([3, 4], np.int64); w["bias_vals"] = np.array([50.0, 50.0], np.float32)
+    off = np.zeros(B + 1, np.int32); off[10:] = 2; w["bias_off"] = off  # row 9 carries two large biases
+    allowed[9, 3] = False; allowed[9, 4] = True                     # one of them on a hidden token
+    words = (V + 31) // 32
+    bits = np.zeros((B, words * 32), bool); bits[:, :V] = allowed
+    mask = np.packbits(bits.reshape(B, words, 32), axis=2, bitorder="little").view(np.uint32).reshape(B, words)
+    ref = oracle.pick_batch(w["logits"], **{k: w[k] for k in W.SAMPLER_KEYS}, mask=mask)
+    lg = torch.from_numpy(w["logits"]).to(dev)
+    p = S.upload_params(w, dev)
+    p["mask"] = torch.from_numpy(mask.view(np.int32)).to(dev)
+    got = S.sample_batch(lg, p, want_diag=True)
+    torch.cuda.synchronize()
+    tok = got["tokens"].cpu().numpy()
+    st = got["row_status"].cpu().numpy().astype(np.uint32)
+    diag = got["diag"].cpu().numpy()
+    assert st[6] & capi.ROW_EMPTY and tok[6] == -1 and ref["tokens"][6] == -1
+    live = np.arange(B) != 6
+    assert not np.any(st[live] & np.uint32(capi.ROW_ERROR_BITS)), st
+    assert all(allowed[r, tok[r]] for r in np.nonzero(live)[0])     # never a forbidden token
+    assert tok[9] == 4
+    sampled = live & (w["temperature"] > 0) & (w["top_k"] != 1)
+    assert np.array_equal(diag[sampled, 0].view(np.uint32), ref["z_sum"][sampled].view(np.uint32))
+    tie = ((st & np.uint32(capi.ROW_TIE_BITS)) != 0) | ((ref["flags"] & 7) != 0)
+    edge = (ref["flags"] & oracle.FLAG_CDF_EDGE) != 0
+    bad = live & (tok != ref["tokens"]) & ~tie & ~edge
+    assert not bad.any(), (np.nonzero(bad)[0], tok[bad], ref["tokens"][bad])
+    ok = sampled & ~tie & (tok == ref["tokens"])
+    assert np.array_equal(diag[ok, 1].view(np.uint32), ref["keep_sum"][ok].view(np.uint32))
+    assert np.array_equal(diag[ok, 2].view(np.uint32), ref["target"][ok].view(np.uint32))
+
+
 def test_host_entry_fails_on_rows_it_cannot_answer(dev, lib):
     """A row the library leaves unanswered (typical-p with nothing sorted before it) must fail the
     host call, as `pick` would have raised: MOLLA_OK with a token of -1 would pass unnoticed."""
