@@ -245,38 +245,42 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         const bool ties_listed = tie_mode && lvl == 1 && binade_ok;
         // every thread's elements four at a time (independent loads and arithmetic)
         const int ntie_slot = phase & 1;
-        for (int i4 = c.tid; i4 < g.nloc; i4 += 4 * NT) {
-            unsigned int ebs[4];
+        const unsigned int wtau = w.tau;
+        const int nloc = g.nloc;
+        for (int i4 = c.tid; i4 < nloc; i4 += 4 * NT) {
+            // the arithmetic of the four elements first, without a branch between them
+            unsigned int ebs[4], qus[4];
+            int bins[4];
+            bool live[4], care[4], ties[4];
 #pragma unroll
-            for (int u = 0; u < 4; u++) ebs[u] = (i4 + u * NT < g.nloc) ? bits[i4 + u * NT] : 0u;
+            for (int u = 0; u < 4; u++) ebs[u] = (i4 + u * NT < nloc) ? bits[i4 + u * NT] : 0u;
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 const unsigned int eb = ebs[u];
-                if (eb == 0u || eb >= w.tau || eb < lo) continue;
-                const int i = i4 + u * NT;
-                const int bin = (int)((eb - lo) >> shift);
-                if (!binade_ok) { sred_add(&A->u.h.hc[bin], 1u); continue; }
+                live[u] = eb != 0u && eb < wtau && eb >= lo;
+                bins[u] = (int)((eb - lo) >> shift);
                 const float p = __uint_as_float(eb);
                 const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
                 const float rr = __fsub_rn(p, q);
-                const bool tie = fabsf(rr) == halfu, big = p >= bigthr;
-                if (big || (tie && !ties_listed)) {
-                    sred_max(&A->specbin, bin);
-                    if (counting) sred_add(&A->u.h.hc[bin], 1u);
-                    continue;
-                }
-                if (tie) {
-                    const int pos = atomicAdd(&lead->ntie[ntie_slot], 1);
-                    if (pos < TIE_CAP) { lead->tkey[pos] = make_key(eb, g.c0 + i); lead->tbin[pos] = bin; }
-                    if (counting) sred_add(&A->u.h.hc[bin], 1u);
-                    continue;
-                }
-                const unsigned int qu = __float2uint_rn(__fmul_rn(q, inv_u));
-                if (qu) {
-                    sred_add(&A->u.h.hq[bin], qu & MASS_LO_MASK);
-                    if (qu >> MASS_SPLIT) sred_add(&A->u.h.hqh[bin], qu >> MASS_SPLIT);
-                }
+                ties[u] = fabsf(rr) == halfu;
+                care[u] = (p >= bigthr) || (ties[u] && !ties_listed);
+                qus[u] = __float2uint_rn(__fmul_rn(q, inv_u));
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (!live[u]) continue;
+                const int bin = bins[u];
+                if (!binade_ok) { sred_add(&A->u.h.hc[bin], 1u); continue; }
                 if (counting) sred_add(&A->u.h.hc[bin], 1u);
+                if (care[u]) { sred_max(&A->specbin, bin); continue; }
+                if (ties[u]) {
+                    const int pos = atomicAdd(&lead->ntie[ntie_slot], 1);
+                    if (pos < TIE_CAP) { lead->tkey[pos] = make_key(ebs[u], g.c0 + i4 + u * NT); lead->tbin[pos] = bin; }
+                    continue;
+                }
+                const unsigned int qu = qus[u];
+                if (qu & MASS_LO_MASK) sred_add(&A->u.h.hq[bin], qu & MASS_LO_MASK);
+                if (qu >> MASS_SPLIT) sred_add(&A->u.h.hqh[bin], qu >> MASS_SPLIT);
             }
         }
         cl.sync();
