@@ -39,9 +39,6 @@ constexpr int CL_PIECE = 4096;               // floats per bulk copy
 constexpr int TIE_CAP = 64;                   // rounding ties a walk resolves by parity; more send it the slow way
 constexpr int TBINS = NT;                    // bins of the threads' maxima by distance below the row's maximum
 constexpr float TRES = (float)(NT / 32);     // bins per unit of logit: the bins cover 32 units
-// positions listed for the balanced evaluation of the second pass: they use the space of the bin
-// tables, the candidates and their values (all idle then)
-constexpr int PLIST_CAP = (3 * NBINS * 4 + NC * 8 + NC * 4) / 2;
 
 // Profiling stamps exist in the testing build only (per row 32 slots of clock readings and counts).
 #ifdef MOLLA_SAMPLE_TESTING
@@ -242,6 +239,7 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         const bool binade_ok = have_s && j >= -100 && j <= 100;
         const float Cm = __fmul_rn(1.5f, fpow2(j)), halfu = fpow2(j - 24), bigthr = fpow2(j - 1);
         const float inv_u = fpow2(23 - j);
+        const unsigned int cm_bits = __float_as_uint(Cm);
         const bool ties_listed = tie_mode && lvl == 1 && binade_ok;
         // every thread's elements four at a time (independent loads and arithmetic)
         const int ntie_slot = phase & 1;
@@ -260,11 +258,15 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
                 live[u] = eb != 0u && eb < wtau && eb >= lo;
                 bins[u] = (int)((eb - lo) >> shift);
                 const float p = __uint_as_float(eb);
-                const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
+                const float tq = __fadd_rn(p, Cm);
+                const float q = __fsub_rn(tq, Cm);
                 const float rr = __fsub_rn(p, q);
                 ties[u] = fabsf(rr) == halfu;
                 care[u] = (p >= bigthr) || (ties[u] && !ties_listed);
-                qus[u] = __float2uint_rn(__fmul_rn(q, inv_u));
+                // q in units: below bigthr, p + Cm stays in Cm's binade, whose unit is the sum's, so
+                // the difference of the two bit patterns is the count (a conversion would issue at
+                // a quarter of the rate)
+                qus[u] = __float_as_uint(tq) - cm_bits;
             }
 #pragma unroll
             for (int u = 0; u < 4; u++) {
@@ -308,10 +310,11 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
                     const int bin = (int)((eb - lo) >> shift);
                     if (!((A->tbits[bin >> 5] >> (bin & 31)) & 1u)) continue;
                     const float p = __uint_as_float(eb);
-                    const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
+                    const float tq = __fadd_rn(p, Cm);
+                    const float q = __fsub_rn(tq, Cm);
                     const float rr = __fsub_rn(p, q);
                     if (fabsf(rr) == halfu || p >= bigthr) continue;
-                    const unsigned int qu = __float2uint_rn(__fmul_rn(q, inv_u));
+                    const unsigned int qu = __float_as_uint(tq) - cm_bits;
                     const unsigned long long key = make_key(eb, g.c0 + i4 + u * NT);
                     for (int t = 0; t < ntie; t++)
                         if (A->tbin[t] == bin && key > A->tkey[t] && qu) {  // two halves, as in the bin tables
@@ -862,14 +865,15 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     CSTAMP(4);
     // ---- 4. the second pass, in place: the exponential (temperature and softmax numerator,
     // sample.mojo:419-434) of what can matter, zero for the rest. Where a row's sum is still small
-    // (its first columns) nearly everything matters, later almost nothing: the threads list the
-    // positions they keep and the whole block evaluates the list, so that no warp is left alone
-    // with the dense stretch. What does not fit the list is evaluated by its owner.
+    // (its first columns) nearly everything matters, later almost nothing: the warps go through
+    // the range in interleaved tiles, so that no warp is left alone with the dense stretch, and
+    // evaluate what they keep in full warps.
     {
+        static_assert(offsetof(AuxC, hidx) == offsetof(AuxC, pre) + sizeof(A->pre), "the head's candidates rely on this layout");
         static_assert(offsetof(AuxC, cand) == sizeof(A->u) && offsetof(AuxC, pc) == offsetof(AuxC, cand) + sizeof(A->cand) &&
-                      offsetof(AuxC, pre) == offsetof(AuxC, pc) + sizeof(A->pc) && offsetof(AuxC, hidx) == offsetof(AuxC, pre) + sizeof(A->pre),
-                      "the list and the head's candidates rely on this layout");
-        unsigned short *plist = reinterpret_cast<unsigned short *>(&A->u);
+                      sizeof(A->u) + sizeof(A->cand) >= (size_t)(NT + 4) * (CL_LMAX + 1),
+                      "the threads' lists use the idle space of the tables and the candidates");
+        static_assert(sizeof(A->pc) >= NWARP * CL_LMAX * sizeof(float) && sizeof(A->pre) >= NT * sizeof(float), "bounds per thread and per tile");
         unsigned long long *hcand = reinterpret_cast<unsigned long long *>(A->pre);  // HEADC keys over pre + hidx
         auto value = [&](float xx) -> float {
             const float v = (T == 1.0f) ? xx : __fdiv_rn(xx, T);
@@ -881,66 +885,72 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
                 if (pos < HEADC) hcand[pos] = make_key(ebits, g.c0 + i_block);
             }
         };
-        // which of this thread's elements are kept (bit j = element j; the rest becomes zero at once)
-        unsigned long long m0 = 0ull;
-        unsigned int m1 = 0u;
+        // Warp w takes the 32-wide tiles w, w + 16, w + 32, ... of the range, so the dense stretch
+        // is spread evenly over all threads. A tile tests its elements against the lowest bound of
+        // the threads it overlaps (keeping more than necessary is always right). Every thread notes
+        // the tiles in which it keeps its element in a list of its own and evaluates the list
+        // afterwards, four at a time: the lists of a warp's lanes are about equally long, and no
+        // conversion, population count, bit search or atomic (all of which issue at a fraction of
+        // the rate of the rest) is needed to build them.
+        unsigned char *klist = reinterpret_cast<unsigned char *>(&A->u);  // [entry][thread], over u + cand
+        float *thr_t = A->pc;  // a bound per tile
         {
-            const int n0 = min(g.L, 64);
-            int j = 0;
-            for (; j + 4 <= n0; j += 4) {
-                float x[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) x[u] = rowbuf[i0 + j + u];
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    if (x[u] >= mythr) m0 |= 1ull << (j + u); else rowbuf[i0 + j + u] = 0.0f;
-                }
+            float *thr_s = A->pre;  // every thread's bound
+            thr_s[c.tid] = mythr;
+            __syncthreads();
+            for (int t = c.tid; t < NWARP * g.L; t += NT) {
+                const int o0 = (32 * t) / g.L, o1 = min(NT - 1, (32 * t + 31) / g.L);
+                float m = thr_s[o0];
+                for (int o = o0 + 1; o <= o1; o++) m = fminf(m, thr_s[o]);
+                thr_t[t] = m;
             }
-            for (; j < n0; j++) {
-                if (rowbuf[i0 + j] >= mythr) m0 |= 1ull << j; else rowbuf[i0 + j] = 0.0f;
-            }
-            for (j = 64; j < g.L; j++) {
-                if (rowbuf[i0 + j] >= mythr) m1 |= 1u << (j - 64); else rowbuf[i0 + j] = 0.0f;
-            }
+            __syncthreads();
         }
-        const int cnt = __popcll(m0) + __popc(m1);
-        int tot;
-        const int base = block_excl_scan<int>(cnt, A->wsi, &tot);
         CSTAMP(16);
-#ifdef MOLLA_SAMPLE_TESTING
-        if (a.prof && leader && c.tid == 0) a.prof[(long long)r * 32 + 19] = tot;
-#endif
-        int o = base;  // the list offset of this thread's next kept element
-        for (int lo_ = 0; lo_ < tot; lo_ += PLIST_CAP) {
-            // this thread's kept positions that fall into [lo_, lo_ + PLIST_CAP) of the block's list
-            while (m0 && o < lo_ + PLIST_CAP) {
-                const int b = __ffsll((long long)m0) - 1;
-                m0 &= m0 - 1ull;
-                plist[o - lo_] = (unsigned short)(i0 + b);
-                o++;
-            }
-            while (!m0 && m1 && o < lo_ + PLIST_CAP) {
-                const int b = __ffs((int)m1) - 1;
-                m1 &= m1 - 1u;
-                plist[o - lo_] = (unsigned short)(i0 + 64 + b);
-                o++;
-            }
-            __syncthreads();
-            const int nl = min(tot - lo_, PLIST_CAP);
-            for (int i = c.tid; i < nl; i += 4 * NT) {
-                int pos[4];
-                float y[4];
+        constexpr int KSTRIDE = NT + 4;  // bytes per list entry row: rows start one bank apart
+        int cnt = 0;
+        for (int k = 0; k < g.L; k += 4) {
+            float x[4], th[4];
+            int p[4];
 #pragma unroll
-                for (int u = 0; u < 4; u++) pos[u] = (i + u * NT < nl) ? (int)plist[i + u * NT] : -1;
-#pragma unroll
-                for (int u = 0; u < 4; u++) y[u] = (pos[u] >= 0) ? value(rowbuf[pos[u]]) : 0.0f;
-#pragma unroll
-                for (int u = 0; u < 4; u++)
-                    if (pos[u] >= 0) { rowbuf[pos[u]] = y[u]; take(__float_as_uint(y[u]), pos[u]); }
+            for (int u = 0; u < 4; u++) {
+                const int t = min(k + u, g.L - 1) * NWARP + c.warp;
+                p[u] = (t << 5) + c.lane;
+                x[u] = rowbuf[p[u]];
+                th[u] = thr_t[t];
             }
-            __syncthreads();
-            if (lo_ == 0) CSTAMP(17);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (k + u >= g.L) continue;
+                // no branch: the entry is written in any case and counts only if the element is kept
+                const bool keep = x[u] >= th[u];
+                klist[cnt * KSTRIDE + c.tid] = (unsigned char)(k + u);
+                cnt += keep ? 1 : 0;
+                rowbuf[p[u]] = keep ? x[u] : 0.0f;
+            }
         }
+        CSTAMP(18);
+        const int base = (c.warp << 5) + c.lane;
+        auto entry = [&](int i) { return (((int)klist[i * KSTRIDE + c.tid] * NWARP) << 5) + base; };
+        int i = 0;
+        for (; i + 4 <= cnt; i += 4) {  // (no predicates in here: they would turn into branches around every evaluation)
+            int pos[4];
+            float y[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) pos[u] = entry(i + u);
+#pragma unroll
+            for (int u = 0; u < 4; u++) y[u] = value(rowbuf[pos[u]]);
+#pragma unroll
+            for (int u = 0; u < 4; u++) { rowbuf[pos[u]] = y[u]; take(__float_as_uint(y[u]), pos[u]); }
+        }
+        for (; i < cnt; i++) {
+            const int pos = entry(i);
+            const float y = value(rowbuf[pos]);
+            rowbuf[pos] = y;
+            take(__float_as_uint(y), pos);
+        }
+        __syncthreads();
+        CSTAMP(17);
         // the head's candidates to where the head looks for them
         const int nh = min(A->ncand, HEADC);
         unsigned long long mine[(HEADC + NT - 1) / NT];
@@ -1158,16 +1168,35 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         rowbits[i] = pb;
     }
     __syncthreads();
-    ClWalk cutw;
-    cutw.s = head_s; cutw.pos = head_pos; cutw.tau = tau_head;
-    cutw.event = EV_NONE; cutw.idx = -1; cutw.p = 0; cutw.tie = 0;
+    // One call site for both walks (the walk is most of this kernel's code, and what a row runs
+    // through has to stay in the instruction cache): round 0 is the cut walk, round 1 the draw walk.
     const bool limited = n_use < (long long)a.V;
-    descend_cluster(cl, c, g, rowbits, cutw, topp_on ? P : 3.4e38f, 3.4e38f, limited ? n_use : -1, CPROF_SLOTS(leader, 20));
-    if (cutw.event != EV_DEGENERATE) {
-        if (cutw.event == EV_CUT && cutw.tie) c.status |= MOLLA_ROW_TOPP_TIE;
-        if (cutw.event == EV_LIMIT && cutw.tie) c.status |= MOLLA_ROW_TOPK_TIE;
-        const float sum = cutw.s;
-        const float target = __fmul_rn(u01, sum);
+    ClWalk w;
+    int cut_event = EV_NONE, cut_idx = -1;
+    float cut_p = 0.0f, sum = 0.0f, target = 0.0f;
+    bool settled = false;    // the token is known, or the row is degenerate
+    bool resolved = false;
+    for (int round = 0; round < 2; round++) {
+        w.s = head_s; w.pos = head_pos; w.tau = tau_head;
+        w.event = EV_NONE; w.idx = -1; w.p = 0; w.tie = 0;
+        const bool cut_round = round == 0;
+        descend_cluster(cl, c, g, rowbits, w, (cut_round && topp_on) ? P : 3.4e38f, cut_round ? 3.4e38f : target,
+                        (cut_round && limited) ? n_use : -1, cut_round ? CPROF_SLOTS(leader, 20) : nullptr);
+        if (!cut_round) {
+            if (w.event == EV_DRAW) {
+                token = w.idx; dp = w.p; resolved = true;
+                if (w.tie) c.status |= MOLLA_ROW_CHOSEN_TIE;
+            } else if (w.event == EV_DEGENERATE) {
+                resolved = true;
+            }
+            break;
+        }
+        cut_event = w.event; cut_idx = w.idx; cut_p = w.p;
+        if (cut_event == EV_DEGENERATE) { settled = true; break; }
+        if (cut_event == EV_CUT && w.tie) c.status |= MOLLA_ROW_TOPP_TIE;
+        if (cut_event == EV_LIMIT && w.tie) c.status |= MOLLA_ROW_TOPK_TIE;
+        sum = w.s;
+        target = __fmul_rn(u01, sum);
         dsum = sum; dtarget = target;
         cl.sync();
         if (leader && c.tid == 0) {  // is the drawn element in the head?
@@ -1189,24 +1218,17 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         cl.sync();
         if (A->r_kind == EV_DRAW) {
             token = A->r_idx; dp = A->r_s; c.status |= A->r_status;
-        } else {
-            bool resolved = false;
-            if (target < sum) {
-                ClWalk dw;
-                dw.s = head_s; dw.pos = head_pos; dw.tau = tau_head;
-                dw.event = EV_NONE; dw.idx = -1; dw.p = 0; dw.tie = 0;
-                descend_cluster(cl, c, g, rowbits, dw, 3.4e38f, target, -1, nullptr);
-                if (dw.event == EV_DRAW) {
-                    token = dw.idx; dp = dw.p; resolved = true;
-                    if (dw.tie) c.status |= MOLLA_ROW_CHOSEN_TIE;
-                } else if (dw.event == EV_DEGENERATE) {
-                    resolved = true;
-                }
-            }
+            settled = true;
+            break;
+        }
+        if (!(target < sum)) break;
+    }
+    if (!settled) {
+        {
             if (!resolved) {
                 // the walk falls off the end: the last kept candidate (sample.mojo:591-594)
-                if (cutw.event == EV_CUT || cutw.event == EV_LIMIT) {
-                    token = cutw.idx; dp = cutw.p;
+                if (cut_event == EV_CUT || cut_event == EV_LIMIT) {
+                    token = cut_idx; dp = cut_p;
                 } else {
                     // everything listed was kept: its smallest value, highest id last
                     unsigned long long best = ~0ull;
@@ -1226,7 +1248,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
                     __syncthreads();
                     if (c.tid < g.G) {
                         unsigned long long m = A->wsu[0];
-                        for (int w = 1; w < NWARP; w++) m = A->wsu[w] < m ? A->wsu[w] : m;
+                        for (int v = 1; v < NWARP; v++) m = A->wsu[v] < m ? A->wsu[v] : m;
                         cl.map_shared_rank(A, c.tid)->x5_key[g.rank] = m;
                     }
                     cl.sync();
