@@ -57,7 +57,7 @@ struct __align__(16) AuxC {
             float csum[NT];
             short ja[NT];
             unsigned char dual[NT];
-            unsigned short seg[NT];
+            unsigned long long segd[NT + 1];  // the walk's segments: first chunk, binade guess, flags
         } p1;
         struct {
             unsigned int hq[NBINS];
@@ -86,6 +86,7 @@ struct __align__(16) AuxC {
     double x3_tot[CL_MAX_G]; int x3_n[CL_MAX_G];
     int x4_n[CL_MAX_G]; unsigned long long x5_key[CL_MAX_G];
     float ch_s; int ch_found, ch_at, ch_slow;   // the exact sum on its way from range to range
+    int ch_flag;                                 // which hand-over of the row has arrived (the writer releases, thread 0 acquires)
     // elements of a walk that would round on a tie: their keys, bins, the mass before them
     long long rx[8];          // words fetched from the leader for the whole block
     int ngath, ngath_over;   // a bin's entries collected by this block; blocks whose own buffer overflowed (leader's)
@@ -113,14 +114,28 @@ struct ClGeo {          // where this thread block stands
 // order: every block builds the tables of its range from an estimate of the sum before it, then
 // the exact running sum travels from range to range. With `locate`, stops at the first entry
 // whose running sum exceeds `target`; its token id is returned in `at`.
-struct ClSum { float s; int found; int at; int slow; };
+struct ClSum { float s; int found; int at; int slow; bool timeout; };
 
+// cluster-scope release / acquire of one word of (possibly another block's) shared memory
+__device__ __forceinline__ void st_release_cluster(int *p, int v) {
+    asm volatile("st.release.cluster.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_cluster(const int *p) {
+    int v;
+    asm volatile("ld.acquire.cluster.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// `epoch` counts the sums of a row (the same in every block): the hand-over from range to range
+// is a word released into the next block's shared memory, on which only that block's thread 0
+// waits (with a bound); everybody else waits once, at the cluster barrier after the last range.
 __device__ ClSum cluster_exact_sum(cg::cluster_group &cl, CtxC &c, const ClGeo &g, const unsigned int *bits,
-                                   bool locate, float target, long long *stamps = nullptr, long long *stamps2 = nullptr) {
+                                   bool locate, float target, int &epoch, long long *stamps = nullptr, long long *stamps2 = nullptr) {
     AuxC *A = c.A;
     IN_SHARED(A);
     IN_SHARED(bits);
     ValBits vals{bits};
+    epoch++;
     __syncthreads();
     const float csum = p1_csum(vals, g.nloc, g.L, c.tid);
     double tot;
@@ -132,31 +147,38 @@ __device__ ClSum cluster_exact_sum(cg::cluster_group &cl, CtxC &c, const ClGeo &
     if (stamps && c.tid == 0) stamps[0] = clock64();
     p1_tables(c, vals, g.nloc, g.L, csum, sbase + ex);
     if (stamps && c.tid == 0) stamps[1] = clock64();
-    for (int q = 0; q < g.G; q++) {
-        if (g.rank == q && c.tid == 0) {
-            Walker w;
-            if (q == 0) { w.s = 0.0f; w.found = 0; w.at = -1; w.slow = 0; }
-            else { w.s = A->ch_s; w.found = A->ch_found; w.at = A->ch_at; w.slow = A->ch_slow; }
-            if (!(locate && w.found)) {
-                const long long tw0 = clock64();
-                p1_walk(c, vals, g.nloc, g.L, locate, target, w);
-                if (w.found) w.at += g.c0;
-                if (stamps2) { stamps2[q] = clock64() - tw0; stamps2[4 + q] = w.nsim * 100000ll + w.nel; stamps2[8 + q] = A->nseg; }
-            }
-            if (q + 1 < g.G) {
-                AuxC *nx = cl.map_shared_rank(A, q + 1);
-                nx->ch_s = w.s; nx->ch_found = w.found; nx->ch_at = w.at; nx->ch_slow = w.slow;
-            } else {
-                for (int o = 0; o < g.G; o++) {
-                    AuxC *ox = cl.map_shared_rank(A, o);
-                    ox->ch_s = w.s; ox->ch_found = w.found; ox->ch_at = w.at; ox->ch_slow = w.slow;
-                }
+    if (c.tid == 0) {
+        Walker w;
+        int timed_out = 0;
+        if (g.rank == 0) { w.s = 0.0f; w.found = 0; w.at = -1; w.slow = 0; }
+        else {
+            bool here = false;
+            for (int spin = 0; spin < (1 << 22); spin++)
+                if (ld_acquire_cluster(&A->ch_flag) == epoch) { here = true; break; }
+            if (!here) timed_out = 4;
+            w.s = A->ch_s; w.found = A->ch_found; w.at = A->ch_at; w.slow = A->ch_slow;
+        }
+        if (!(locate && w.found)) {
+            const long long tw0 = clock64();
+            p1_walk(c, vals, g.nloc, g.L, locate, target, w);
+            if (w.found) w.at += g.c0;
+            if (stamps2) { stamps2[g.rank] = clock64() - tw0; stamps2[4 + g.rank] = w.nsim * 100000ll + w.nel; stamps2[8 + g.rank] = A->nseg; }
+        }
+        w.slow |= timed_out;
+        if (g.rank + 1 < g.G) {
+            AuxC *nx = cl.map_shared_rank(A, g.rank + 1);
+            nx->ch_s = w.s; nx->ch_found = w.found; nx->ch_at = w.at; nx->ch_slow = w.slow;
+            st_release_cluster(&nx->ch_flag, epoch);
+        } else {
+            for (int o = 0; o < g.G; o++) {
+                AuxC *ox = cl.map_shared_rank(A, o);
+                ox->ch_s = w.s; ox->ch_found = w.found; ox->ch_at = w.at; ox->ch_slow = w.slow;
             }
         }
-        cl.sync();
     }
+    cl.sync();
     ClSum out;
-    out.s = A->ch_s; out.found = A->ch_found; out.at = A->ch_at; out.slow = A->ch_slow;
+    out.s = A->ch_s; out.found = A->ch_found; out.at = A->ch_at; out.slow = A->ch_slow & 1; out.timeout = (A->ch_slow & 4) != 0;
     return out;
 }
 
@@ -788,7 +810,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         ox->x1_max[g.rank] = cmax; ox->x1_idx[g.rank] = cidx; ox->x1_eq[g.rank] = ceq; ox->x1_status[g.rank] = c.status;
         ox->x2_total[g.rank] = etot;
     }
-    if (c.tid == 0) { A->ncand = 0; A->evt_thread = 0x7fffffff; }
+    if (c.tid == 0) { A->ncand = 0; A->evt_thread = 0x7fffffff; A->ch_flag = 0; }
     CSTAMP(13);
     cl.sync();
     float xmax = -INFINITY;
@@ -967,9 +989,11 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     if (c.tid < g.G) cl.map_shared_rank(A, c.tid)->x3_n[g.rank] = A->ncand;
 
     // ---- 5. the softmax denominator, exactly as the sequential loop rounds it
-    const ClSum zs = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f, CPROF_SLOTS(leader, 14), CPROF_SLOTS(!p3row, 20));
+    int epoch = 0;
+    const ClSum zs = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f, epoch, CPROF_SLOTS(leader, 14), CPROF_SLOTS(!p3row, 20));
     const float Z = zs.s;
     if (zs.slow) c.status |= MOLLA_ROW_SLOW_PATH;
+    if (zs.timeout) { c.status |= MOLLA_ROW_LOAD_TIMEOUT; finish(); return; }  // (the same word in every block)
     dZ = Z;
 
     CSTAMP(6);
@@ -1018,11 +1042,12 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
             if (pb < minp_pbits) pb = 0u;
             rowbits[i] = pb;
         }
-        const ClSum s1 = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f);
+        const ClSum s1 = cluster_exact_sum(cl, c, g, rowbits, false, 0.0f, epoch);
         const float sum = s1.s;
         const float target = __fmul_rn(u01, sum);
-        const ClSum s2 = cluster_exact_sum(cl, c, g, rowbits, true, target);
+        const ClSum s2 = cluster_exact_sum(cl, c, g, rowbits, true, target, epoch);
         if (s1.slow || s2.slow) c.status |= MOLLA_ROW_SLOW_PATH;
+        if (s1.timeout || s2.timeout) { c.status |= MOLLA_ROW_LOAD_TIMEOUT; finish(); return; }
         dsum = sum; dtarget = target;
         if (s2.found) token = s2.at;
         else {
@@ -1290,14 +1315,21 @@ __global__ void __launch_bounds__(1024, 1) order_rows_rank_kernel(const float *t
 // (odd: conflict-free shared-memory strides).
 struct ClusterShape { int G, Vc, L; };
 
-ClusterShape cluster_shape(int V) {
+// The smallest cluster that holds the row; for a batch so small that larger clusters of all
+// its rows are still resident together (a lone decode stream, a few rows per GPU), the largest
+// such cluster: the passes over the row shorten with the range, and nobody waits for an SM.
+ClusterShape cluster_shape(int V, int B, int sms) {
+    ClusterShape best{0, 0, 0};
     for (int G = 1; G <= CL_MAX_G; G *= 2) {
         const int Vc = ((((V + G - 1) / G) + 3) / 4) * 4;
         int L = (Vc + NT - 1) / NT;
         if ((L & 1) == 0) L += 1;
-        if (L <= CL_LMAX) return ClusterShape{G, Vc, L};
+        if (L > CL_LMAX) continue;
+        if (best.G == 0) { best = ClusterShape{G, Vc, L}; continue; }
+        // (clusters do not fill every SM: leave the same margin the resident-cluster count shows)
+        if ((long long)B * G * 9 <= (long long)sms * 8 && L >= 9) best = ClusterShape{G, Vc, L};
     }
-    return ClusterShape{0, 0, 0};
+    return best;
 }
 
 constexpr size_t CL_SMEM = (size_t)CL_CAPF * 4 + ((sizeof(AuxC) + 15) / 16) * 16;
@@ -1333,10 +1365,12 @@ bool cluster_fits(int dev, int G) {
 }  // namespace
 
 int molla_cluster_launch(const BatchArgs &args_in, void *d_workspace, cudaStream_t st, char *err, size_t errlen) {
-    const ClusterShape cs = cluster_shape(args_in.V);
     int dev = 0, sms = 0;
-    if (cs.G == 0 || cudaGetDevice(&dev) != cudaSuccess || !cluster_fits(dev, cs.G)) return MOLLA_CLUSTER_DECLINED;
+    if (cudaGetDevice(&dev) != cudaSuccess) return MOLLA_CLUSTER_DECLINED;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    ClusterShape cs = cluster_shape(args_in.V, args_in.B, sms);
+    if (cs.G != 0 && !cluster_fits(dev, cs.G)) cs = cluster_shape(args_in.V, 1 << 30, sms);  // the smallest cluster then
+    if (cs.G == 0 || !cluster_fits(dev, cs.G)) return MOLLA_CLUSTER_DECLINED;
     BatchArgs a = args_in;
     a.G = cs.G; a.Vc = cs.Vc; a.L = cs.L;
     a.Vg = a.V; a.col0 = 0; a.mode = 0;

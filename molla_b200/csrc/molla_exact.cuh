@@ -126,11 +126,11 @@ __device__ void bitonic_desc(unsigned long long *k, int n2, int tid) {
     // most 16, the same 64 for every such stride: those stages only need the warp to agree.
     bool local = false;  // the previous stage was such a stage
     for (int size = 2; size <= n2; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int stride = size >> 1, ls = 31 - __clz(size >> 1); stride > 0; stride >>= 1, ls--) {
             if (local && stride <= 16) __syncwarp(); else __syncthreads();
             local = stride <= 16 && !(size == 2);
             for (int i = tid; i < (n2 >> 1); i += NT) {
-                int pos = ((i / stride) * stride * 2) + (i % stride);
+                int pos = ((i >> ls) << (ls + 1)) + (i & (stride - 1));  // strides are powers of two: no division
                 int par = pos + stride;
                 bool desc = ((pos & size) == 0);
                 unsigned long long x = k[pos], y = k[par];
@@ -146,10 +146,10 @@ __device__ void bitonic_desc(unsigned long long *k, int n2, int tid) {
 __device__ void bitonic_desc_warp(unsigned long long *k, int n2, int lane) {
     IN_SHARED(k);
     for (int size = 2; size <= n2; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int stride = size >> 1, ls = 31 - __clz(size >> 1); stride > 0; stride >>= 1, ls--) {
             __syncwarp();
             for (int i = lane; i < (n2 >> 1); i += 32) {
-                int pos = ((i / stride) * stride * 2) + (i % stride);
+                int pos = ((i >> ls) << (ls + 1)) + (i & (stride - 1));  // strides are powers of two: no division
                 int par = pos + stride;
                 bool desc = ((pos & size) == 0);
                 unsigned long long x = k[pos], y = k[par];
@@ -250,6 +250,11 @@ __device__ __forceinline__ float p1_csum(V lst, int n, int L, int tid) {
 
 // The tables for the walk, given every thread's estimate `csum` and the estimated sum `sst` of
 // everything before its entries.
+__device__ __forceinline__ unsigned long long seg_pack(int t0, short j, unsigned char dual, bool nonempty) {
+    return (unsigned long long)(unsigned int)t0 | ((unsigned long long)(unsigned short)j << 16) |
+           ((unsigned long long)dual << 32) | ((unsigned long long)(nonempty ? 1u : 0u) << 40);
+}
+
 template <class CX, class V>
 __device__ void p1_tables(CX &c, V lst, int n, int L, float csum, double sst) {
     auto *A = c.A;
@@ -340,8 +345,10 @@ __device__ void p1_tables(CX &c, V lst, int n, int L, float csum, double sst) {
     int wtot;
     int wex = block_excl_scan<int>(c.lane == 0 ? __popc(bal) : 0, A->wsi, &wtot);
     wex = __shfl_sync(0xffffffffu, wex, 0);
-    if (start) A->u.p1.seg[wex + __popc(bal & ((1u << c.lane) - 1u))] = (unsigned short)c.tid;
-    if (c.tid == 0) A->nseg = wtot;
+    // a segment's first chunk, its binade guess and flags in one word, so that the walk needs one
+    // load per segment (and can fetch the next one ahead); the list ends with a word for chunk NT
+    if (start) A->u.p1.segd[wex + __popc(bal & ((1u << c.lane) - 1u))] = seg_pack(c.tid, ja, dual, nonempty);
+    if (c.tid == 0) { A->nseg = wtot; A->u.p1.segd[wtot] = seg_pack(NT, SUS, 0, false); }
     __syncthreads();
 }
 
@@ -366,18 +373,20 @@ __device__ void p1_walk(CX &c, V lst, int n, int L, bool locate, float target, W
     IN_SHARED(A);
     const int nseg = A->nseg;
     const double *PA = A->u.p1.pa, *PB = A->u.p1.pb;
+    unsigned long long dn = A->u.p1.segd[0];
     for (int si = 0; si < nseg && !(locate && w.found); si++) {
-        const int t0 = A->u.p1.seg[si];
-        const int t1 = (si + 1 < nseg) ? (int)A->u.p1.seg[si + 1] : NT;
-        const int j = A->u.p1.ja[t0];
+        const unsigned long long d = dn;
+        dn = A->u.p1.segd[si + 1];  // (the list has an end word)
+        const int t0 = (int)(d & 0xffffu), t1 = (int)(dn & 0xffffu);
+        const int j = (int)(short)(unsigned short)(d >> 16);
         const int e0 = min(n, t0 * L), e1 = min(n, t1 * L);
         if (e1 <= e0) break;  // chunks past the end of the list are empty
         if (j == SUS) {
             // (the chunks behind t0 in this segment hold zeros only)
-            if (A->u.p1.csum[t0] != 0.0f) p1_sim(lst, e0, min(e1, min(n, (t0 + 1) * L)), locate, target, w);
+            if ((d >> 40) & 1u) p1_sim(lst, e0, min(e1, min(n, (t0 + 1) * L)), locate, target, w);
             continue;
         }
-        const bool dual = A->u.p1.dual[t0] != 0;
+        const bool dual = ((d >> 32) & 0xffu) != 0;
         const double pa0 = PA[t0], pa1 = PA[t1], pb0 = PB[t0], pb1 = PB[t1];
         if (pa1 == pa0 && pb1 == pb0) continue;  // every term rounds to nothing in either binade
         bool ok = false;

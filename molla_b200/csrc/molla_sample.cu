@@ -69,7 +69,7 @@ struct __align__(16) Aux {
             float csum[NT];
             short ja[NT];
             unsigned char dual[NT];
-            unsigned short seg[NT];
+            unsigned long long segd[NT + 1];  // the walk's segments: first chunk, binade guess, flags
         } p1;
         struct {
             unsigned int hq[NBINS];   // per bin: sum of the low bits of the integer contributions
