@@ -235,8 +235,19 @@ __device__ __forceinline__ void fetch_from_leader(CtxC &c, int n, F word) {
 // not stop a phase: they are listed, a second pass adds up what precedes each of them inside
 // its own bin, and one thread then resolves them from the top down, each from the exact integer
 // sum before it; their contributions go into their bins' masses before the event is searched.
+// Where a walk's last phase began. The draw walk adds up the same elements in the same order as
+// the cut walk before it, so when its target is not reached before that point it starts there,
+// on the bin tables that are still standing (merged, at the leader), and skips the passes that
+// built them.
+struct ClResume {
+    int valid;
+    float s; long long pos; unsigned int tau;
+    int lvl; unsigned int lo; int shift; int tie_mode; int ntie;
+};
+
 __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, const unsigned int *bits,
-                                ClWalk &w, float x_ge, float x_gt, long long nstop, long long *dbg = nullptr) {
+                                ClWalk &w, float x_ge, float x_gt, long long nstop, ClResume &rs, bool try_resume,
+                                long long *dbg = nullptr) {
     AuxC *A = c.A;
     IN_SHARED(A);
     IN_SHARED(bits);
@@ -247,14 +258,28 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
     unsigned int lo = 0u;
     int shift = BIN_SHIFT;
     bool tie_mode = true;
+    // (every block holds the same `rs`: its fields are values all blocks computed alike)
+    const bool resumed = try_resume && rs.valid && !counting && x_ge >= 3.0e38f && !(x_gt < rs.s);
+    if (resumed) {
+        w.s = rs.s; w.pos = rs.pos; w.tau = rs.tau;
+        lvl = rs.lvl; lo = rs.lo; shift = rs.shift; tie_mode = rs.tie_mode != 0;
+    }
     if (c.tid == 0) { A->ntie[0] = 0; A->ntie[1] = 0; }
     for (int phase = 0; phase < 8192; phase++) {
+        const bool reuse = resumed && phase == 0;  // this phase's tables stand already
         cl.sync();  // nobody still reads the tables or the leader's results of the phase before
         long long tp0 = clock64();
 #define DT(k) do { if (dbg && c.tid == 0) { const long long t_ = clock64(); dbg[k] += t_ - tp0; tp0 = t_; } } while (0)
-        for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0u; A->u.h.hqh[i] = 0u; A->u.h.hc[i] = 0u; }
-        for (int i = c.tid; i < NBINS / 32; i += NT) A->tbits[i] = 0u;
-        if (c.tid == 0) { A->specbin = -1; A->ncand = 0; A->ngath = 0; A->ngath_over = 0; A->ntie[(phase + 1) & 1] = 0; }  // the other blocks add to this phase's counter already
+        if (!reuse) {
+            for (int i = c.tid; i < NBINS; i += NT) { A->u.h.hq[i] = 0u; A->u.h.hqh[i] = 0u; A->u.h.hc[i] = 0u; }
+            for (int i = c.tid; i < NBINS / 32; i += NT) A->tbits[i] = 0u;
+            rs.valid = 1; rs.s = w.s; rs.pos = w.pos; rs.tau = w.tau;
+            rs.lvl = lvl; rs.lo = lo; rs.shift = shift; rs.tie_mode = tie_mode ? 1 : 0; rs.ntie = 0;
+        }
+        if (c.tid == 0) {
+            if (!reuse) A->specbin = -1;
+            A->ncand = 0; A->ngath = 0; A->ngath_over = 0; A->ntie[(phase + 1) & 1] = 0;  // the other blocks add to this phase's counter already
+        }
         __syncthreads();
         const bool have_s = w.s > 0.0f;
         const int j = have_s ? fexpo(w.s) : 0;
@@ -263,6 +288,8 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         const float inv_u = fpow2(23 - j);
         const unsigned int cm_bits = __float_as_uint(Cm);
         const bool ties_listed = tie_mode && lvl == 1 && binade_ok;
+        int ntie = rs.ntie;
+        if (!reuse) {
         // every thread's elements four at a time (independent loads and arithmetic)
         const int ntie_slot = phase & 1;
         const unsigned int wtau = w.tau;
@@ -309,7 +336,8 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         }
         cl.sync();
         fetch_from_leader(c, 1, [&](int) { return (long long)lead->ntie[ntie_slot]; });
-        const int ntie = ties_listed ? (int)A->rx[0] : 0;
+        ntie = ties_listed ? (int)A->rx[0] : 0;
+        rs.ntie = ntie;
         if (dbg && c.tid == 0) { dbg[0] += 1; dbg[1] += ntie; }
         DT(3);
         if (ntie > TIE_CAP) { tie_mode = false; c.status |= MOLLA_ROW_SLOW_PATH; continue; }  // too many: they stop phases instead
@@ -347,6 +375,7 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
             }
             cl.sync();
         }
+        }  // (!reuse)
         DT(4);
         // The leader adds the other blocks' tables to its own (whole rows of bins at a time, so that
         // the loads from the other blocks' memory are few and wide), searches the event bin and
@@ -373,7 +402,10 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
             qy.pos0 = 0; qy.nstop = 1;  // nothing consumed yet: take the highest non-empty bin
         }
         if (leader) {
-            {
+            if (reuse) {
+                if (c.tid < ntie) A->tc[c.tid] = 0ull;
+                __syncthreads();
+            } else {
                 uint4 *mine = reinterpret_cast<uint4 *>(&A->u.h);
                 constexpr int NV = 3 * NBINS / 4;  // the three tables, four bins at a time
                 for (int v0 = c.tid; v0 < NV; v0 += NT) {
@@ -488,11 +520,11 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         __syncthreads();
         const int mine = A->ngath;
         if (c.tid == 0) {
-            A->specbin = atomicAdd(&lead->ncand, mine);
+            A->evt_thread = atomicAdd(&lead->ncand, mine);  // (a word that is idle here; the leader's `specbin` has to survive for a resumed walk)
             if (mine > MYCAP) atomicAdd(&lead->ngath_over, 1);  // more than this block could hold: the bin is split further
         }
         __syncthreads();
-        const int cbase = A->specbin;
+        const int cbase = A->evt_thread;
         if (mine <= MYCAP && cbase + mine <= NC)
             for (int i = c.tid; i < mine; i += NT) lead->cand[cbase + i] = mybuf[i];
         cl.sync();
@@ -1197,6 +1229,8 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     // through has to stay in the instruction cache): round 0 is the cut walk, round 1 the draw walk.
     const bool limited = n_use < (long long)a.V;
     ClWalk w;
+    ClResume resume;
+    resume.valid = 0;
     int cut_event = EV_NONE, cut_idx = -1;
     float cut_p = 0.0f, sum = 0.0f, target = 0.0f;
     bool settled = false;    // the token is known, or the row is degenerate
@@ -1206,7 +1240,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         w.event = EV_NONE; w.idx = -1; w.p = 0; w.tie = 0;
         const bool cut_round = round == 0;
         descend_cluster(cl, c, g, rowbits, w, (cut_round && topp_on) ? P : 3.4e38f, cut_round ? 3.4e38f : target,
-                        (cut_round && limited) ? n_use : -1, cut_round ? CPROF_SLOTS(leader, 20) : nullptr);
+                        (cut_round && limited) ? n_use : -1, resume, !cut_round, cut_round ? CPROF_SLOTS(leader, 20) : nullptr);
         if (!cut_round) {
             if (w.event == EV_DRAW) {
                 token = w.idx; dp = w.p; resolved = true;
