@@ -1150,19 +1150,32 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
 #endif
         if (c.tid == 0) {
             float s = 0.0f;
-            long long pos = 0;
             int cut = -1, tie = 0;
-            for (int i = 0; i < nc; i++) {
-                if (pos >= n_use) break;
-                s = __fadd_rn(s, A->pc[i]);
-                A->pre[i] = s;
-                pos++;
-                if (topp_on && s >= P) {
-                    cut = i + 1;
-                    if (i + 1 < nc && (long long)(i + 1) < n_use && A->pc[i + 1] == A->pc[i]) tie |= MOLLA_ROW_TOPP_TIE;
-                    break;
+            bool by_mass = false;
+            // the prefix sums of the sorted head (sample.mojo:497-506), eight loads ahead of the
+            // additions; at most n_use elements are added
+            const int lim = (int)((long long)nc < n_use ? (long long)nc : n_use);
+            int i = 0;
+            while (i < lim && cut < 0) {
+                float v[8];
+                const int m = min(8, lim - i);
+#pragma unroll
+                for (int q = 0; q < 8; q++) v[q] = (q < m) ? A->pc[i + q] : 0.0f;
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    if (q < m && cut < 0) {
+                        s = __fadd_rn(s, v[q]);
+                        A->pre[i + q] = s;
+                        if (topp_on && s >= P) { cut = i + q + 1; by_mass = true; }
+                    }
                 }
-                if (pos >= n_use) { cut = i + 1; break; }
+                i += m;
+            }
+            const long long pos = (cut >= 0) ? (long long)cut : (long long)lim;
+            if (by_mass) {
+                if (cut < nc && (long long)cut < n_use && A->pc[cut] == A->pc[cut - 1]) tie |= MOLLA_ROW_TOPP_TIE;
+            } else if (lim > 0 && (long long)lim >= n_use) {
+                cut = lim;  // the count limit
             }
             if (cut < 0 && !p3row && !head_overflow) cut = nc;  // everything that can matter is in the head
             if (n_use < (long long)a.V && (long long)nc > n_use && A->pc[n_use] == A->pc[n_use - 1])
@@ -1174,8 +1187,14 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
                 const float sum = A->pre[cut - 1];
                 const float target = __fmul_rn(u01, sum);
                 int at = cut - 1;
-                for (int i = 0; i < cut; i++)
-                    if (target < A->pre[i]) { at = i; break; }
+                for (int i0 = 0; i0 < cut && at == cut - 1; i0 += 8) {
+                    float v[8];
+#pragma unroll
+                    for (int q = 0; q < 8; q++) v[q] = (i0 + q < cut) ? A->pre[i0 + q] : 0.0f;
+#pragma unroll
+                    for (int q = 7; q >= 0; q--)
+                        if (i0 + q < cut && target < v[q]) at = i0 + q;  // the first one wins
+                }
                 A->b_event = EV_DRAW; A->b_idx = (int)(A->hidx[at] & 0x7fffffffu); A->b_p = A->pc[at];
                 if ((at > 0 && A->pc[at - 1] == A->pc[at]) || (at + 1 < cut && A->pc[at + 1] == A->pc[at]))
                     tie |= MOLLA_ROW_CHOSEN_TIE;
@@ -1258,10 +1277,15 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         target = __fmul_rn(u01, sum);
         dsum = sum; dtarget = target;
         cl.sync();
-        if (leader && c.tid == 0) {  // is the drawn element in the head?
-            int at = -1;
-            for (int i = 0; i < nc; i++)
-                if (target < A->pre[i]) { at = i; break; }
+        if (leader) {  // is the drawn element in the head? (the first prefix sum above the target)
+            if (c.tid == 0) A->evt_thread = 0x7fffffff;
+            __syncthreads();
+            for (int i = c.tid; i < nc; i += NT)
+                if (target < A->pre[i]) { atomicMin(&A->evt_thread, i); break; }
+            __syncthreads();
+        }
+        if (leader && c.tid == 0) {
+            const int at = (A->evt_thread == 0x7fffffff) ? -1 : A->evt_thread;
             int ev = EV_NONE, idx = -1, aux = 0;
             float pv = 0.0f;
             if (at >= 0) {
