@@ -36,6 +36,8 @@ constexpr int CL_MAX_G = 8;                  // thread blocks per cluster at mos
 constexpr int CL_LMAX = 75;                  // logits per thread at most (odd: conflict-free strides)
 constexpr int CL_CAPF = NT * CL_LMAX;        // logits per thread block at most: 38400 (150 KB)
 constexpr int CL_PIECE = 4096;               // floats per bulk copy
+constexpr int CL_HEADC = 2048;                // candidates of the sorted head at most (the buffers of a gathered bin hold as many)
+constexpr int CL_HEAD_NEED = 1026;            // the sorted head covers top-k + 1 up to this many: a top-k up to 1025 never walks
 constexpr int TIE_CAP = 64;                   // rounding ties a walk resolves by parity; more send it the slow way
 constexpr int TBINS = NT;                    // bins of the threads' maxima by distance below the row's maximum
 constexpr float TRES = (float)(NT / 32);     // bins per unit of logit: the bins cover 32 units
@@ -67,8 +69,8 @@ struct __align__(16) AuxC {
     } u;
     unsigned long long cand[NC];   // first the hash of the patched tokens, then the head / a bin's candidates
     float pc[NC];
-    float pre[HEADC];
-    unsigned int hidx[HEADC];
+    float pre[CL_HEADC];
+    unsigned int hidx[CL_HEADC];
     double wsd[2 * (NWARP + 1)];
     unsigned long long wsu[NWARP + 1];
     float wsf[NWARP + 1];
@@ -868,10 +870,13 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     const float top = (T == 1.0f) ? xmax : __fdiv_rn(xmax, T);
     const float u01 = draw01(a.seed ? a.seed[q] : 0ull, a.drawn ? a.drawn[q] : 0ull);
     const bool filter_ok = fabsf(top) < 1.0e5f;
-    long long need = n_lim + 1;
-    if (need > HEAD_NEED) need = HEAD_NEED;
+    // how many the sorted head has to cover: top-k + 1 where a top-k is set (up to CL_HEAD_NEED: such
+    // rows finish in the head), a fixed number where the nucleus alone ends the row
+    const bool open_row = n_lim == (long long)a.V;
+    long long need = open_row ? (long long)HEAD_NEED : n_lim + 1;
+    if (need > CL_HEAD_NEED) need = CL_HEAD_NEED;
     if (need > a.V) need = a.V;
-    const bool p3row = !pure && (n_lim + 1 > HEAD_NEED);
+    const bool p3row = !pure && (open_row ? (n_lim + 1 > HEAD_NEED) : (n_lim + 1 > CL_HEAD_NEED));
 
     // ---- 3. the bound relative to the row's maximum, and the head's threshold: a value that at
     // least `need` of the threads' maxima reach bounds the need-th largest element from below.
@@ -928,7 +933,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
                       sizeof(A->u) + sizeof(A->cand) >= (size_t)(NT + 4) * (CL_LMAX + 1),
                       "the threads' lists use the idle space of the tables and the candidates");
         static_assert(sizeof(A->pc) >= NWARP * CL_LMAX * sizeof(float) && sizeof(A->pre) >= NT * sizeof(float), "bounds per thread and per tile");
-        unsigned long long *hcand = reinterpret_cast<unsigned long long *>(A->pre);  // HEADC keys over pre + hidx
+        unsigned long long *hcand = reinterpret_cast<unsigned long long *>(A->pre);  // CL_HEADC keys over pre + hidx
         auto value = [&](float xx) -> float {
             const float v = (T == 1.0f) ? xx : __fdiv_rn(xx, T);
             return expf_pinned_nonpos(__fsub_rn(v, top));  // no logit of the row exceeds its maximum
@@ -936,7 +941,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         auto take = [&](unsigned int ebits, int i_block) {  // the head's candidates are picked up on the way
             if (!pure && ebits >= tau_bits) {
                 const int pos = satom_add(&A->ncand, 1);
-                if (pos < HEADC) hcand[pos] = make_key(ebits, g.c0 + i_block);
+                if (pos < CL_HEADC) hcand[pos] = make_key(ebits, g.c0 + i_block);
             }
         };
         // Warp w takes the 32-wide tiles w, w + 16, w + 32, ... of the range, so the dense stretch
@@ -1006,13 +1011,13 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         __syncthreads();
         CSTAMP(17);
         // the head's candidates to where the head looks for them
-        const int nh = min(A->ncand, HEADC);
-        unsigned long long mine[(HEADC + NT - 1) / NT];
+        const int nh = min(A->ncand, CL_HEADC);
+        unsigned long long mine[(CL_HEADC + NT - 1) / NT];
 #pragma unroll
-        for (int u = 0; u < (HEADC + NT - 1) / NT; u++) mine[u] = (c.tid + u * NT < nh) ? hcand[c.tid + u * NT] : 0ull;
+        for (int u = 0; u < (CL_HEADC + NT - 1) / NT; u++) mine[u] = (c.tid + u * NT < nh) ? hcand[c.tid + u * NT] : 0ull;
         __syncthreads();
 #pragma unroll
-        for (int u = 0; u < (HEADC + NT - 1) / NT; u++)
+        for (int u = 0; u < (CL_HEADC + NT - 1) / NT; u++)
             if (c.tid + u * NT < nh) A->cand[c.tid + u * NT] = mine[u];
     }
     __syncthreads();
@@ -1118,9 +1123,9 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         const int n = A->x3_n[o];
         if (o < g.rank) cbase += n;
         nc_tot += n;
-        if (n > HEADC) head_overflow = true;
+        if (n > CL_HEADC) head_overflow = true;
     }
-    if (nc_tot > HEADC) head_overflow = true;
+    if (nc_tot > CL_HEADC) head_overflow = true;
     if (!head_overflow) {
         const int mine = A->x3_n[g.rank];
         for (int i = c.tid; i < mine; i += NT) {
@@ -1209,8 +1214,8 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         int kind = 1;  // 0: the row is finished; 1: past the head
         if (typ_on) {
             const int m = A->ncand;
-            if (m <= 0) {
-                c.status |= MOLLA_ROW_UNSUPPORTED;  // what the earlier filters left reaches past the head
+            if (m <= 0 || m > HEADC) {
+                c.status |= MOLLA_ROW_UNSUPPORTED;  // what the earlier filters left reaches past the head, or is wider than the filter's scratch
             } else {
                 typical_head(c, m, typ, u01);
                 token = A->b_idx; dp = A->b_p; dsum = A->b_sum; dtarget = A->b_target;
@@ -1354,7 +1359,7 @@ __global__ void __launch_bounds__(1024, 1) order_rows_rank_kernel(const float *t
         const int q = slot ? slot[i] : i;
         const float T = temperature ? temperature[q] : 0.0f;
         const int k = top_k ? top_k[q] : 0;
-        cost[i] = (T > 0.0f && k != 1) ? T + ((k == 0 || k >= HEAD_NEED) ? 0.25f : 0.0f) : 0.0f;
+        cost[i] = (T > 0.0f && k != 1) ? T + ((k == 0 || k >= CL_HEAD_NEED) ? 0.25f : 0.0f) : 0.0f;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < B; i += blockDim.x) {
