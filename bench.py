@@ -263,9 +263,9 @@ class Timed:
 
     def launches_per_step(self):
         sms = self.torch.cuda.get_device_properties(self.dev).multi_processor_count
-        groups = 4 if self.V > 38400 else 1   # thread blocks per row; the order kernel runs when not all rows start at once
-        if self.V > 153600:
-            groups = 8
+        # thread blocks per row (the smallest cluster whose blocks hold 38400 logits each); the kernel
+        # that ranks the rows runs when not all rows can start at once
+        groups = next(g for g in (1, 2, 4, 8, 8) if self.V <= 38400 * g or g == 8)
         return 1 + (1 if self.B * groups > sms else 0) + (1 if (self.logprob or self.top_n) else 0)
 
 

@@ -1250,7 +1250,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     }
     __syncthreads();
     // One call site for both walks (the walk is most of this kernel's code, and what a row runs
-    // through has to stay in the instruction cache): round 0 is the cut walk, round 1 the draw walk.
+    // through has to stay in the instruction cache): leg 0 is the cut walk, leg 1 the draw walk.
     const bool limited = n_use < (long long)a.V;
     ClWalk w;
     ClResume resume;
@@ -1259,10 +1259,10 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
     float cut_p = 0.0f, sum = 0.0f, target = 0.0f;
     bool settled = false;    // the token is known, or the row is degenerate
     bool resolved = false;
-    for (int round = 0; round < 2; round++) {
+    for (int leg = 0; leg < 2; leg++) {
         w.s = head_s; w.pos = head_pos; w.tau = tau_head;
         w.event = EV_NONE; w.idx = -1; w.p = 0; w.tie = 0;
-        const bool cut_round = round == 0;
+        const bool cut_round = leg == 0;
         descend_cluster(cl, c, g, rowbits, w, (cut_round && topp_on) ? P : 3.4e38f, cut_round ? 3.4e38f : target,
                         (cut_round && limited) ? n_use : -1, resume, !cut_round, cut_round ? CPROF_SLOTS(leader, 20) : nullptr);
         if (!cut_round) {
