@@ -292,48 +292,54 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         const bool ties_listed = tie_mode && lvl == 1 && binade_ok;
         int ntie = rs.ntie;
         if (!reuse) {
-        // every thread's elements four at a time (independent loads and arithmetic)
+        // Every thread's elements four at a time. The common case (an element that simply adds its
+        // mass to its bin) runs without a branch; elements that need care and rounding ties are rare
+        // and a warp turns to them only when one of its lanes has met one.
         const int ntie_slot = phase & 1;
         const unsigned int wtau = w.tau;
         const int nloc = g.nloc;
-        for (int i4 = c.tid; i4 < nloc; i4 += 4 * NT) {
-            // the arithmetic of the four elements first, without a branch between them
-            unsigned int ebs[4], qus[4];
-            int bins[4];
-            bool live[4], care[4], ties[4];
+        const bool count_all = counting || !binade_ok;
+        for (int i0 = c.tid - c.lane; i0 < nloc; i0 += 4 * NT) {  // (the same trips for all lanes of a warp)
+            const int i4 = i0 + c.lane;
+            unsigned int ebs[4];
+            bool rare = false;
 #pragma unroll
             for (int u = 0; u < 4; u++) ebs[u] = (i4 + u * NT < nloc) ? bits[i4 + u * NT] : 0u;
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 const unsigned int eb = ebs[u];
-                live[u] = eb != 0u && eb < wtau && eb >= lo;
-                bins[u] = (int)((eb - lo) >> shift);
+                const bool live = eb != 0u && eb < wtau && eb >= lo;
+                const int bin = (int)((eb - lo) >> shift);
                 const float p = __uint_as_float(eb);
                 const float tq = __fadd_rn(p, Cm);
                 const float q = __fsub_rn(tq, Cm);
                 const float rr = __fsub_rn(p, q);
-                ties[u] = fabsf(rr) == halfu;
-                care[u] = (p >= bigthr) || (ties[u] && !ties_listed);
+                const bool special = (fabsf(rr) == halfu) || (p >= bigthr);
                 // q in units: below bigthr, p + Cm stays in Cm's binade, whose unit is the sum's, so
                 // the difference of the two bit patterns is the count (a conversion would issue at
                 // a quarter of the rate)
-                qus[u] = __float_as_uint(tq) - cm_bits;
+                const unsigned int qu = __float_as_uint(tq) - cm_bits;
+                if (live && count_all) sred_add(&A->u.h.hc[bin], 1u);
+                const bool plain = live && binade_ok && !special;
+                if (plain) sred_add(&A->u.h.hq[bin], qu & MASS_LO_MASK);
+                if (plain && (qu >> MASS_SPLIT)) sred_add(&A->u.h.hqh[bin], qu >> MASS_SPLIT);
+                rare |= live && binade_ok && special;
             }
+            if (__any_sync(0xffffffffu, rare)) {
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                if (!live[u]) continue;
-                const int bin = bins[u];
-                if (!binade_ok) { sred_add(&A->u.h.hc[bin], 1u); continue; }
-                if (counting) sred_add(&A->u.h.hc[bin], 1u);
-                if (care[u]) { sred_max(&A->specbin, bin); continue; }
-                if (ties[u]) {
-                    const int pos = atomicAdd(&lead->ntie[ntie_slot], 1);
-                    if (pos < TIE_CAP) { lead->tkey[pos] = make_key(ebs[u], g.c0 + i4 + u * NT); lead->tbin[pos] = bin; }
-                    continue;
+                for (int u = 0; u < 4; u++) {
+                    const unsigned int eb = ebs[u];
+                    if (!(eb != 0u && eb < wtau && eb >= lo)) continue;
+                    const int bin = (int)((eb - lo) >> shift);
+                    const float p = __uint_as_float(eb);
+                    const float q = __fsub_rn(__fadd_rn(p, Cm), Cm);
+                    const bool tie = fabsf(__fsub_rn(p, q)) == halfu;
+                    if ((p >= bigthr) || (tie && !ties_listed)) { sred_max(&A->specbin, bin); continue; }
+                    if (tie) {
+                        const int pos = atomicAdd(&lead->ntie[ntie_slot], 1);
+                        if (pos < TIE_CAP) { lead->tkey[pos] = make_key(eb, g.c0 + i4 + u * NT); lead->tbin[pos] = bin; }
+                    }
                 }
-                const unsigned int qu = qus[u];
-                if (qu & MASS_LO_MASK) sred_add(&A->u.h.hq[bin], qu & MASS_LO_MASK);
-                if (qu >> MASS_SPLIT) sred_add(&A->u.h.hqh[bin], qu >> MASS_SPLIT);
             }
         }
         cl.sync();
@@ -351,14 +357,30 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
                 sred_or(&A->tbits[b >> 5], 1u << (b & 31));
             }
             __syncthreads();
-            for (int i4 = c.tid; i4 < g.nloc; i4 += 4 * NT) {
+            // the bins that hold a listed element span a short range: a compare against it keeps
+            // nearly every element out of the slower path
+            int tb_lo = NBINS, tb_hi = -1;
+            for (int t = 0; t < ntie; t++) { tb_lo = min(tb_lo, A->tbin[t]); tb_hi = max(tb_hi, A->tbin[t]); }
+            const unsigned int tb_span = (unsigned int)(tb_hi - tb_lo);
+
+            const unsigned int wtau2 = w.tau;
+            for (int i0 = c.tid - c.lane; i0 < g.nloc; i0 += 4 * NT) {
+                const int i4 = i0 + c.lane;
                 unsigned int ebs[4];
+                bool near = false;
 #pragma unroll
                 for (int u = 0; u < 4; u++) ebs[u] = (i4 + u * NT < g.nloc) ? bits[i4 + u * NT] : 0u;
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const unsigned int eb = ebs[u];
-                    if (eb == 0u || eb >= w.tau || eb < lo) continue;
+                    const int bin = (int)((eb - lo) >> shift);
+                    near |= eb != 0u && eb < wtau2 && eb >= lo && (unsigned int)(bin - tb_lo) <= tb_span;
+                }
+                if (!__any_sync(0xffffffffu, near)) continue;
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const unsigned int eb = ebs[u];
+                    if (eb == 0u || eb >= wtau2 || eb < lo) continue;
                     const int bin = (int)((eb - lo) >> shift);
                     if (!((A->tbits[bin >> 5] >> (bin & 31)) & 1u)) continue;
                     const float p = __uint_as_float(eb);
@@ -403,21 +425,31 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         } else {
             qy.pos0 = 0; qy.nstop = 1;  // nothing consumed yet: take the highest non-empty bin
         }
+        if (!reuse && g.G > 1) {
+            // every block adds up its share of the bins over all blocks (few, wide loads from the
+            // other blocks' memory, spread over all of them) and puts the sums into the leader's tables
+            uint4 *mine = reinterpret_cast<uint4 *>(&A->u.h);
+            uint4 *dst = reinterpret_cast<uint4 *>(&lead->u.h);
+            constexpr int NV = 3 * NBINS / 4;  // the three tables, four bins at a time
+            const int per = (NV + g.G - 1) / g.G;
+            const int v_hi = min(NV, (g.rank + 1) * per);
+            for (int v0 = g.rank * per + c.tid; v0 < v_hi; v0 += NT) {
+                uint4 acc = mine[v0];
+                for (int o = 0; o < g.G; o++) {
+                    if (o == g.rank) continue;
+                    const uint4 x = reinterpret_cast<const uint4 *>(&cl.map_shared_rank(A, o)->u.h)[v0];
+                    acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+                }
+                dst[v0] = acc;
+            }
+            if (!leader && c.tid == 0 && A->specbin >= 0) atomicMax(&lead->specbin, A->specbin);
+            cl.sync();
+        }
         if (leader) {
             if (reuse) {
                 if (c.tid < ntie) A->tc[c.tid] = 0ull;
                 __syncthreads();
             } else {
-                uint4 *mine = reinterpret_cast<uint4 *>(&A->u.h);
-                constexpr int NV = 3 * NBINS / 4;  // the three tables, four bins at a time
-                for (int v0 = c.tid; v0 < NV; v0 += NT) {
-                    uint4 acc = mine[v0];
-                    for (int o = 1; o < g.G; o++) {
-                        const uint4 x = reinterpret_cast<const uint4 *>(&cl.map_shared_rank(A, o)->u.h)[v0];
-                        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
-                    }
-                    mine[v0] = acc;
-                }
                 if (c.tid < ntie) {
                     unsigned long long s_ = 0ull;
                     for (int o = 0; o < g.G; o++) {
@@ -425,11 +457,6 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
                         s_ += (unsigned long long)ox->tpq_lo[c.tid] + ((unsigned long long)ox->tpq_hi[c.tid] << MASS_SPLIT);
                     }
                     A->tpqm[c.tid] = s_; A->tc[c.tid] = 0ull;
-                }
-                if (c.tid == 0) {
-                    int sb = A->specbin;
-                    for (int o = 1; o < g.G; o++) sb = max(sb, cl.map_shared_rank(A, o)->specbin);
-                    A->specbin = sb;
                 }
                 __syncthreads();
             }
@@ -506,14 +533,20 @@ __device__ void descend_cluster(cg::cluster_group &cl, CtxC &c, const ClGeo &g, 
         // reserves room at the leader with one addition to the leader's counter and copies them over.
         unsigned long long *mybuf = reinterpret_cast<unsigned long long *>(A->pc);
         constexpr int MYCAP = NC / 2;
-        for (int i4 = c.tid; i4 < g.nloc; i4 += 4 * NT) {
+        const unsigned int gtau = w.tau < bhi ? w.tau : bhi;  // the bin's entries: blo <= value < gtau, and not zero (an absent element)
+        for (int i0 = c.tid - c.lane; i0 < g.nloc; i0 += 4 * NT) {  // (the same trips for all lanes of a warp)
+            const int i4 = i0 + c.lane;
             unsigned int ebs[4];
+            bool any = false;
 #pragma unroll
             for (int u = 0; u < 4; u++) ebs[u] = (i4 + u * NT < g.nloc) ? bits[i4 + u * NT] : 0u;
 #pragma unroll
+            for (int u = 0; u < 4; u++) any |= ebs[u] != 0u && ebs[u] >= blo && ebs[u] < gtau;
+            if (!__any_sync(0xffffffffu, any)) continue;  // one bin of 2048: most warps pass most elements by
+#pragma unroll
             for (int u = 0; u < 4; u++) {
                 const unsigned int eb = ebs[u];
-                if (eb != 0u && eb < w.tau && eb >= blo && eb < bhi) {
+                if (eb != 0u && eb >= blo && eb < gtau) {
                     const int pos = satom_add(&A->ngath, 1);
                     if (pos < MYCAP) mybuf[pos] = make_key(eb, g.c0 + i4 + u * NT);
                 }
