@@ -266,6 +266,10 @@ __device__ void p1_tables(CX &c, V lst, int n, int L, float csum, double sst) {
     float da = 0.0f, db = 0.0f;
     const float lo = (float)(sst * (1.0 - (double)EPS));
     const float hi = (float)((sst + (double)csum) * (1.0 + (double)EPS));
+    // (a warp whose lanes disagree would run both loops below one after the other: it runs the
+    // two-binade loop for all of them instead; a lane that needs one binade ignores the second sum)
+    const bool usable = lo > 0.0f && i1 > i0 && fexpo(hi) <= fexpo(lo) + 1 && fexpo(lo) >= -100 && fexpo(hi) <= 100;
+    const bool any_two = __any_sync(0xffffffffu, usable && fexpo(hi) == fexpo(lo) + 1);
     if (lo > 0.0f && i1 > i0) {
         const int jl = fexpo(lo), j2 = fexpo(hi);
         if (j2 <= jl + 1 && jl >= -100 && j2 <= 100) {
@@ -295,7 +299,7 @@ __device__ void p1_tables(CX &c, V lst, int n, int L, float csum, double sst) {
                 xa = __fadd_rn(xa, q);
             };
             int i = i0;
-            if (two) {
+            if (any_two) {
                 for (; i + 2 <= i1; i += 2) { term(i, da, db); term(i + 1, da1, db1); }
                 if (i < i1) term(i, da, db);
                 da = __fadd_rn(da, da1); db = __fadd_rn(db, db1);
