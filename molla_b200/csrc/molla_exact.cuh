@@ -543,7 +543,7 @@ __device__ void sort_cands(CX &c, int n) {
     while (n2 < n) n2 <<= 1;
     __syncthreads();
     for (int i = n + c.tid; i < n2; i += NT) A->cand[i] = 0ull;
-    if (n2 <= 256) {
+    if (n2 <= 64) {  // one warp and no block barrier; from 128 keys on the whole block is faster
         __syncthreads();
         if (c.warp == 0) bitonic_desc_warp(A->cand, n2, c.lane);
         __syncthreads();
