@@ -1168,11 +1168,13 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         }
     }
     cl.sync();
+    CSTAMP(28);
     int nc = head_overflow ? 0 : nc_tot;
     unsigned int tau_head = 0xFFFFFFFFu;
     if (head_overflow) c.status |= MOLLA_ROW_SLOW_PATH;  // no head: the descending walk takes everything from the top
     if (leader) {
         sort_cands(c, nc);
+        CSTAMP(29);
         for (int i = c.tid; i < nc; i += NT) {
             const float p = A->pc[i];
             const bool eq = (i > 0 && A->pc[i - 1] == p) || (i + 1 < nc && A->pc[i + 1] == p);
@@ -1239,6 +1241,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
                 A->b_sum = sum; A->b_target = target;
             }
             A->b_aux = tie;
+            CSTAMP(30);
         }
         __syncthreads();
         c.status |= (unsigned int)A->b_aux;
@@ -1266,6 +1269,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         }
     }
     cl.sync();
+    CSTAMP(31);
     if (A->r_kind == 0) { finish(); return; }
     c.status |= A->r_status;
     const float head_s = A->r_s;

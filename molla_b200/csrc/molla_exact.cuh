@@ -141,25 +141,6 @@ __device__ void bitonic_desc(unsigned long long *k, int n2, int tid) {
     __syncthreads();
 }
 
-// The same sort by one warp (the others wait at the caller's barrier): a short list costs far
-// less in warp barriers than in block barriers.
-__device__ void bitonic_desc_warp(unsigned long long *k, int n2, int lane) {
-    IN_SHARED(k);
-    for (int size = 2; size <= n2; size <<= 1) {
-        for (int stride = size >> 1, ls = 31 - __clz(size >> 1); stride > 0; stride >>= 1, ls--) {
-            __syncwarp();
-            for (int i = lane; i < (n2 >> 1); i += 32) {
-                int pos = ((i >> ls) << (ls + 1)) + (i & (stride - 1));  // strides are powers of two: no division
-                int par = pos + stride;
-                bool desc = ((pos & size) == 0);
-                unsigned long long x = k[pos], y = k[par];
-                if ((x < y) == desc) { k[pos] = y; k[par] = x; }
-            }
-        }
-    }
-    __syncwarp();
-}
-
 __device__ __forceinline__ unsigned int fkey(float f) {  // order-preserving key of a float
     unsigned int b = __float_as_uint(f);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
@@ -539,15 +520,27 @@ template <class CX>
 __device__ void sort_cands(CX &c, int n) {
     auto *A = c.A;
     IN_SHARED(A);
-    int n2 = 2;
-    while (n2 < n) n2 <<= 1;
     __syncthreads();
-    for (int i = n + c.tid; i < n2; i += NT) A->cand[i] = 0ull;
-    if (n2 <= 64) {  // one warp and no block barrier; from 128 keys on the whole block is faster
+    if (n <= NT) {
+        // few keys: every key counts the keys above it (they are all different: the token id is part
+        // of the key) and goes to that place; no sorting network, two barriers
+        const unsigned long long mine = (c.tid < n) ? A->cand[c.tid] : 0ull;
+        int rank = 0;
+        if (c.tid < n) {
+            int j = 0;
+            for (; j + 4 <= n; j += 4) {
+                const unsigned long long k0 = A->cand[j], k1 = A->cand[j + 1], k2 = A->cand[j + 2], k3 = A->cand[j + 3];
+                rank += (k0 > mine ? 1 : 0) + (k1 > mine ? 1 : 0) + (k2 > mine ? 1 : 0) + (k3 > mine ? 1 : 0);
+            }
+            for (; j < n; j++) rank += A->cand[j] > mine ? 1 : 0;
+        }
         __syncthreads();
-        if (c.warp == 0) bitonic_desc_warp(A->cand, n2, c.lane);
+        if (c.tid < n) A->cand[rank] = mine;
         __syncthreads();
     } else {
+        int n2 = 2;
+        while (n2 < n) n2 <<= 1;
+        for (int i = n + c.tid; i < n2; i += NT) A->cand[i] = 0ull;
         bitonic_desc(A->cand, n2, c.tid);
     }
     for (int i = c.tid; i < n; i += NT) A->pc[i] = key_val(A->cand[i]);
