@@ -990,8 +990,10 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
             float *thr_s = A->pre;  // every thread's bound
             thr_s[c.tid] = mythr;
             __syncthreads();
+            // (x / L without a division: exact for x < 2^32 / L, and x stays below NT * L)
+            const unsigned int l_magic = (unsigned int)((0x100000000ull + (unsigned long long)g.L - 1ull) / (unsigned long long)g.L);
             for (int t = c.tid; t < NWARP * g.L; t += NT) {
-                const int o0 = (32 * t) / g.L, o1 = min(NT - 1, (32 * t + 31) / g.L);
+                const int o0 = (int)__umulhi((unsigned int)(32 * t), l_magic), o1 = min(NT - 1, (int)__umulhi((unsigned int)(32 * t + 31), l_magic));
                 float m = thr_s[o0];
                 for (int o = o0 + 1; o <= o1; o++) m = fminf(m, thr_s[o]);
                 thr_t[t] = m;
@@ -1001,24 +1003,34 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         CSTAMP(16);
         constexpr int KSTRIDE = NT + 4;  // bytes per list entry row: rows start one bank apart
         int cnt = 0;
-        for (int k = 0; k < g.L; k += 4) {
-            float x[4], th[4];
-            int p[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int t = min(k + u, g.L - 1) * NWARP + c.warp;
-                p[u] = (t << 5) + c.lane;
-                x[u] = rowbuf[p[u]];
-                th[u] = thr_t[t];
-            }
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                if (k + u >= g.L) continue;
-                // no branch: the entry is written in any case and counts only if the element is kept
-                const bool keep = x[u] >= th[u];
-                klist[cnt * KSTRIDE + c.tid] = (unsigned char)(k + u);
+        {
+            unsigned char *kp = klist + c.tid;  // where this thread's next entry goes
+            auto take_tile = [&](int k, int p, float x, float th) {
+                // no branch: the entry is written in any case and stays only if the element is kept
+                const bool keep = x >= th;
+                *kp = (unsigned char)k;
+                kp += keep ? KSTRIDE : 0;
                 cnt += keep ? 1 : 0;
-                rowbuf[p[u]] = keep ? x[u] : 0.0f;
+                rowbuf[p] = keep ? x : 0.0f;
+            };
+            int k = 0;
+            for (; k + 4 <= g.L; k += 4) {  // four tiles' loads ahead of their stores
+                int p[4];
+                float x[4], th[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int t = (k + u) * NWARP + c.warp;
+                    p[u] = (t << 5) + c.lane;
+                    x[u] = rowbuf[p[u]];
+                    th[u] = thr_t[t];
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) take_tile(k + u, p[u], x[u], th[u]);
+            }
+            for (; k < g.L; k++) {
+                const int t = k * NWARP + c.warp;
+                const int p = (t << 5) + c.lane;
+                take_tile(k, p, rowbuf[p], thr_t[t]);
             }
         }
         CSTAMP(18);
@@ -1168,14 +1180,12 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         }
     }
     cl.sync();
-    CSTAMP(28);
     int nc = head_overflow ? 0 : nc_tot;
     unsigned int tau_head = 0xFFFFFFFFu;
     if (head_overflow) c.status |= MOLLA_ROW_SLOW_PATH;  // no head: the descending walk takes everything from the top
     if (leader) {
         sort_cands(c, nc);
-        CSTAMP(29);
-        for (int i = c.tid; i < nc; i += NT) {
+            for (int i = c.tid; i < nc; i += NT) {
             const float p = A->pc[i];
             const bool eq = (i > 0 && A->pc[i - 1] == p) || (i + 1 < nc && A->pc[i + 1] == p);
             A->hidx[i] = (unsigned int)key_idx(A->cand[i]) | (eq ? 0x80000000u : 0u);
@@ -1241,8 +1251,7 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
                 A->b_sum = sum; A->b_target = target;
             }
             A->b_aux = tie;
-            CSTAMP(30);
-        }
+                }
         __syncthreads();
         c.status |= (unsigned int)A->b_aux;
         const float head_s = A->b_s;
@@ -1269,7 +1278,6 @@ __global__ void __launch_bounds__(NT, 1) sample_rows_cluster_kernel(const __grid
         }
     }
     cl.sync();
-    CSTAMP(31);
     if (A->r_kind == 0) { finish(); return; }
     c.status |= A->r_status;
     const float head_s = A->r_s;
