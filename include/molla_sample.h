@@ -265,7 +265,10 @@ int32_t molla_sample_batch_noalloc(
  * before returning. Settings are validated on the host first with the rules and
  * messages of `SamplerConfig.check` (sample.mojo:140-154) and `Sampler.bias`
  * (:225-232): MOLLA_ERR_CONFIG, nothing launched. `temperature` is required;
- * the other per-row arrays may be NULL as above.
+ * the other per-row arrays may be NULL as above. A block of 32 MB and more goes up in
+ * eight pieces on a copy stream the library makes for itself (one per device and
+ * calling thread, on first use) while the pieces that have arrived are sampled on
+ * `stream`; a row the library did not answer fails the call (MOLLA_ERR_DEVICE).
  */
 int64_t molla_sample_host_workspace_bytes(int32_t B, int32_t V, int64_t n_hist, int64_t n_bias,
                                           int32_t top_n);

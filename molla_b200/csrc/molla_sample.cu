@@ -2332,6 +2332,31 @@ int32_t molla_sample_shard_stage_c(int32_t B, int32_t V_global, const float *d_t
 
 // ---- host-buffer form ---------------------------------------------------------
 namespace {
+constexpr int CL_MAX_DEVICES_HOST = 64;
+// The library's own copy stream and events for the host-buffer form, one set per device and per
+// calling thread (calls from different threads never share them).
+struct CopyLane {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ready = nullptr;
+    cudaEvent_t arrived[8] = {};
+    bool ok = false;
+};
+CopyLane *copy_lane() {
+    static thread_local CopyLane lanes[CL_MAX_DEVICES_HOST];
+    static thread_local bool tried[CL_MAX_DEVICES_HOST] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= CL_MAX_DEVICES_HOST) return nullptr;
+    CopyLane &l = lanes[dev];
+    if (!tried[dev]) {
+        tried[dev] = true;
+        bool ok = cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking) == cudaSuccess;
+        ok = ok && cudaEventCreateWithFlags(&l.ready, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; i < 8 && ok; i++) ok = cudaEventCreateWithFlags(&l.arrived[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) (void)cudaGetLastError();
+        l.ok = ok;
+    }
+    return l.ok ? &l : nullptr;
+}
 inline size_t al256(size_t n) { return (n + 255) & ~(size_t)255; }
 struct HostLayout {
     size_t logits, f[8], win, seed, drawn, k, hist, hist_off, bias_ids, bias_vals, bias_off;
@@ -2413,7 +2438,16 @@ int32_t molla_sample_batch_host(const float *h_logits, int64_t row_stride, int32
     if (!d_workspace || workspace_bytes < (int64_t)L.total) return fail(MOLLA_ERR_WORKSPACE, "workspace missing or too small%s");
     char *w = (char *)d_workspace;
     cudaStream_t st = (cudaStream_t)stream;
-    cudaError_t e = cudaMemcpy2DAsync(w + L.logits, (size_t)V * 4, h_logits, (size_t)row_stride * 4, (size_t)V * 4, (size_t)B, cudaMemcpyHostToDevice, st);
+    // A large block goes up in pieces on a stream of the library's own (one per device, made on first
+    // use) while the pieces that have arrived are sampled on the caller's stream; a small one in one go.
+    constexpr int MAXPIECE = 8;
+    int npiece = 1;
+    if ((size_t)B * V * 4 >= ((size_t)32 << 20) && B >= 2 * MAXPIECE) npiece = MAXPIECE;
+    CopyLane *lane = npiece > 1 ? copy_lane() : nullptr;
+    if (!lane) npiece = 1;
+    cudaError_t e = cudaSuccess;
+    if (npiece == 1)
+        e = cudaMemcpy2DAsync(w + L.logits, (size_t)V * 4, h_logits, (size_t)row_stride * 4, (size_t)V * 4, (size_t)B, cudaMemcpyHostToDevice, st);
     const float *fsrc[8] = {temperature, top_p, min_p, typical_p, repeat_penalty, frequency_penalty, presence_penalty, nullptr};
     for (int i = 0; i < 7 && e == cudaSuccess; i++)
         if (fsrc[i]) e = cudaMemcpyAsync(w + L.f[i], fsrc[i], (size_t)B * 4, cudaMemcpyHostToDevice, st);
@@ -2422,18 +2456,45 @@ int32_t molla_sample_batch_host(const float *h_logits, int64_t row_stride, int32
     up(L.hist, hist, (size_t)n_hist * 8); up(L.hist_off, hist_off, (size_t)(B + 1) * 4);
     up(L.bias_ids, bias_ids, (size_t)n_bias * 8); up(L.bias_vals, bias_vals, (size_t)n_bias * 4); up(L.bias_off, bias_off, (size_t)(B + 1) * 4);
     if (e != cudaSuccess) return fail(MOLLA_ERR_CUDA, "host to device copy failed: %s", cudaGetErrorString(e));
-    auto dp = [&](size_t off, const void *src) -> void * { return src ? (void *)(w + off) : nullptr; };
-    int rc = molla_sample_batch(
-        (const float *)(w + L.logits), V, B, V, (const float *)dp(L.f[0], temperature), (const int32_t *)dp(L.k, top_k),
-        (const float *)dp(L.f[1], top_p), (const float *)dp(L.f[2], min_p), (const float *)dp(L.f[3], typical_p),
-        (const float *)dp(L.f[4], repeat_penalty), (const float *)dp(L.f[5], frequency_penalty),
-        (const float *)dp(L.f[6], presence_penalty), (const uint8_t *)dp(L.win, window_on),
-        (const uint64_t *)dp(L.seed, seed), (const uint64_t *)dp(L.drawn, drawn), (const int64_t *)dp(L.hist, hist),
-        (const int32_t *)dp(L.hist_off, hist_off), (const int64_t *)dp(L.bias_ids, bias_ids),
-        (const float *)dp(L.bias_vals, bias_vals), (const int32_t *)dp(L.bias_off, bias_off), top_n, w, (int64_t)L.inner, stream,
-        (int32_t *)(w + L.tokens), h_chosen_logprob ? (float *)(w + L.chosen) : nullptr,
-        top_n > 0 ? (int32_t *)(w + L.top_ids) : nullptr, top_n > 0 ? (float *)(w + L.top_lps) : nullptr,
-        (uint32_t *)(w + L.status), nullptr);
+    // rows [r0, r1) of the block on the device: per-row arrays advance by r0 elements (the window and
+    // bias offsets are absolute, so their arrays only shift)
+    auto dp = [&](size_t off, const void *src, size_t elem, int r0) -> void * { return src ? (void *)(w + off + elem * (size_t)r0) : nullptr; };
+    auto sample_rows = [&](int r0, int r1) -> int {
+        return molla_sample_batch(
+            (const float *)(w + L.logits) + (size_t)r0 * V, V, r1 - r0, V, (const float *)dp(L.f[0], temperature, 4, r0),
+            (const int32_t *)dp(L.k, top_k, 4, r0), (const float *)dp(L.f[1], top_p, 4, r0), (const float *)dp(L.f[2], min_p, 4, r0),
+            (const float *)dp(L.f[3], typical_p, 4, r0), (const float *)dp(L.f[4], repeat_penalty, 4, r0),
+            (const float *)dp(L.f[5], frequency_penalty, 4, r0), (const float *)dp(L.f[6], presence_penalty, 4, r0),
+            (const uint8_t *)dp(L.win, window_on, 1, r0), (const uint64_t *)dp(L.seed, seed, 8, r0),
+            (const uint64_t *)dp(L.drawn, drawn, 8, r0), (const int64_t *)dp(L.hist, hist, 8, 0),
+            (const int32_t *)dp(L.hist_off, hist_off, 4, r0), (const int64_t *)dp(L.bias_ids, bias_ids, 8, 0),
+            (const float *)dp(L.bias_vals, bias_vals, 4, 0), (const int32_t *)dp(L.bias_off, bias_off, 4, r0), top_n, w,
+            (int64_t)L.inner, stream, (int32_t *)(w + L.tokens) + r0, h_chosen_logprob ? (float *)(w + L.chosen) + r0 : nullptr,
+            top_n > 0 ? (int32_t *)(w + L.top_ids) + (size_t)r0 * top_n : nullptr,
+            top_n > 0 ? (float *)(w + L.top_lps) + (size_t)r0 * top_n : nullptr, (uint32_t *)(w + L.status) + r0, nullptr);
+    };
+    int rc = MOLLA_OK;
+    if (npiece == 1) {
+        rc = sample_rows(0, B);
+    } else {
+        // the copies start once everything queued on the caller's stream so far is done (the workspace may still be in use)
+        e = cudaEventRecord(lane->ready, st);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(lane->stream, lane->ready, 0);
+        for (int c = 0; c < npiece && e == cudaSuccess; c++) {
+            const int r0 = (int)((long long)B * c / npiece), r1 = (int)((long long)B * (c + 1) / npiece);
+            e = cudaMemcpy2DAsync(w + L.logits + (size_t)r0 * V * 4, (size_t)V * 4, h_logits + (size_t)r0 * row_stride,
+                                  (size_t)row_stride * 4, (size_t)V * 4, (size_t)(r1 - r0), cudaMemcpyHostToDevice, lane->stream);
+            if (e == cudaSuccess) e = cudaEventRecord(lane->arrived[c], lane->stream);
+        }
+        if (e != cudaSuccess) { cudaStreamSynchronize(lane->stream); return fail(MOLLA_ERR_CUDA, "host to device copy failed: %s", cudaGetErrorString(e)); }
+        for (int c = 0; c < npiece && rc == MOLLA_OK; c++) {
+            const int r0 = (int)((long long)B * c / npiece), r1 = (int)((long long)B * (c + 1) / npiece);
+            e = cudaStreamWaitEvent(st, lane->arrived[c], 0);
+            if (e != cudaSuccess) { rc = fail(MOLLA_ERR_CUDA, "waiting for a piece of the block failed: %s", cudaGetErrorString(e)); break; }
+            rc = sample_rows(r0, r1);
+        }
+        if (rc != MOLLA_OK) cudaStreamSynchronize(lane->stream);  // no copy of this call outlives it
+    }
     if (rc != MOLLA_OK) return rc;
     e = cudaMemcpyAsync(h_tokens, w + L.tokens, (size_t)B * 4, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaMemcpyAsync(h_row_status, w + L.status, (size_t)B * 4, cudaMemcpyDeviceToHost, st);
