@@ -515,6 +515,18 @@ def test_host_buffer_entry_matches_device_entry(dev, lib):
     assert np.array_equal(hb.status.numpy().astype(np.uint32), got["row_status"])
     assert np.array_equal(hb.chosen.numpy(), got["chosen_logprob"])
     assert np.array_equal(hb.top_ids.numpy(), got["top_ids"])
+    # a block large enough to go up in pieces (32 MB and more) while earlier pieces are sampled: the
+    # ragged windows and every per-row array have to line up piece by piece
+    w = W.config3(seed=22, B=75, V=151936, H=48)
+    w["top_n"] = 2
+    got = run_gpu(w, dev, top_n=2, want_logprob=True)
+    hb = S.HostBlock(w, dev, top_n=2, want_logprob=True)
+    for _ in range(2):   # twice: the copy stream and its events are reused
+        S.sample_batch_host(hb)
+        assert np.array_equal(hb.tokens.numpy(), got["tokens"])
+        assert np.array_equal(hb.status.numpy().astype(np.uint32), got["row_status"])
+        assert np.array_equal(hb.chosen.numpy(), got["chosen_logprob"])
+        assert np.array_equal(hb.top_ids.numpy(), got["top_ids"])
 
 
 def test_grammar_mask_against_the_oracle(dev, lib, oracle):
