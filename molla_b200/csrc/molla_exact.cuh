@@ -358,10 +358,20 @@ __device__ void p1_walk(CX &c, V lst, int n, int L, bool locate, float target, W
     IN_SHARED(A);
     const int nseg = A->nseg;
     const double *PA = A->u.p1.pa, *PB = A->u.p1.pb;
-    unsigned long long dn = A->u.p1.segd[0];
+    // One thread runs this and waits for every load it needs: the words and table entries of the
+    // next segment are fetched while this one is worked on.
+    unsigned long long nd = A->u.p1.segd[0], ndn = A->u.p1.segd[nseg > 0 ? 1 : 0];
+    double npa0 = PA[(int)(nd & 0xffffu)], npb0 = PB[(int)(nd & 0xffffu)];
+    double npa1 = PA[(int)(ndn & 0xffffu)], npb1 = PB[(int)(ndn & 0xffffu)];
     for (int si = 0; si < nseg && !(locate && w.found); si++) {
-        const unsigned long long d = dn;
-        dn = A->u.p1.segd[si + 1];  // (the list has an end word)
+        const unsigned long long d = nd, dn = ndn;
+        const double pa0 = npa0, pa1 = npa1, pb0 = npb0, pb1 = npb1;
+        {
+            const unsigned long long dnn = A->u.p1.segd[min(si + 2, nseg)];  // (the list has an end word)
+            nd = ndn; ndn = dnn;
+            npa0 = npa1; npb0 = npb1;
+            npa1 = PA[(int)(dnn & 0xffffu)]; npb1 = PB[(int)(dnn & 0xffffu)];
+        }
         const int t0 = (int)(d & 0xffffu), t1 = (int)(dn & 0xffffu);
         const int j = (int)(short)(unsigned short)(d >> 16);
         const int e0 = min(n, t0 * L), e1 = min(n, t1 * L);
@@ -372,15 +382,14 @@ __device__ void p1_walk(CX &c, V lst, int n, int L, bool locate, float target, W
             continue;
         }
         const bool dual = ((d >> 32) & 0xffu) != 0;
-        const double pa0 = PA[t0], pa1 = PA[t1], pb0 = PB[t0], pb1 = PB[t1];
         if (pa1 == pa0 && pb1 == pb0) continue;  // every term rounds to nothing in either binade
         bool ok = false;
         if (w.s > 0.0f) {
             const int js = fexpo(w.s);
             const double sd = (double)w.s;
             // step over chunks [ta, tb) with table P, valid while the sum stays below lim
-            auto bulk = [&](const double *P, int ta, int tb, double lim) -> bool {
-                double sn = (double)w.s + (P[tb] - P[ta]);
+            auto bulk = [&](const double *P, int ta, int tb, double lim, bool whole = false, double diff = 0.0) -> bool {
+                double sn = (double)w.s + (whole ? diff : (P[tb] - P[ta]));
                 if (!(sn < lim)) return false;
                 if (locate && target < (float)sn) {
                     int lo_ = ta, hi_ = tb - 1;  // first chunk whose end value exceeds the target
@@ -397,13 +406,13 @@ __device__ void p1_walk(CX &c, V lst, int n, int L, bool locate, float target, W
                 return true;
             };
             if (!dual) {
-                if (js == j) ok = bulk(PA, t0, t1, dpow2(j + 1));
+                if (js == j) ok = bulk(PA, t0, t1, dpow2(j + 1), true, pa1 - pa0);
             } else if (js == j + 1) {
-                ok = bulk(PB, t0, t1, dpow2(j + 2));
+                ok = bulk(PB, t0, t1, dpow2(j + 2), true, pb1 - pb0);
             } else if (js == j) {
                 const double lim = dpow2(j + 1);
                 if (sd + (pa1 - pa0) < lim) {
-                    ok = bulk(PA, t0, t1, lim);
+                    ok = bulk(PA, t0, t1, lim, true, pa1 - pa0);
                 } else {
                     // the running sum leaves binade j inside this segment: find the chunk
                     int lo_ = t0, hi_ = t1 - 1;
