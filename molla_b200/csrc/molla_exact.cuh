@@ -201,9 +201,20 @@ __device__ __forceinline__ void p1_sim_t(V lst, int i0, int i1, float target, Wa
         }
         if (LOCATE && w.found) { w.s = s; return; }
     }
-    for (; i < i1; i++) {
-        s = __fadd_rn(s, lst(i));
-        if (LOCATE && target < s) { w.found = 1; w.at = i; break; }
+    if (i < i1) {
+        // the last few in one batch as well (their loads would otherwise wait for one another);
+        // what lies past the end is read from inside the range and not added
+        const int rem = i1 - i;
+        float v[8];
+#pragma unroll
+        for (int q = 0; q < 7; q++) v[q] = lst(q < rem ? i + q : i);
+#pragma unroll
+        for (int q = 0; q < 7; q++) {
+            if (q < rem) {
+                s = __fadd_rn(s, v[q]);
+                if (LOCATE && !w.found && target < s) { w.found = 1; w.at = i + q; }
+            }
+        }
     }
     w.s = s;
 }
